@@ -1,0 +1,138 @@
+/*
+ * minit_b200 -- C ABI of the B200 (sm_100a) quantized-linear path.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the stream it
+ * is given (NULL = legacy default stream), never allocates, never synchronises and
+ * returns an int status (MT_OK or a negative MT_ERR_*).  Nothing here throws, traps
+ * or prints; mt_strerror() turns a status into text.
+ *
+ * Reference interfaces are cited by their path inside the MiniT project
+ * (GetUpEarlier/minit).
+ */
+#ifndef MINIT_B200_H_
+#define MINIT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define MT_OK                 0
+#define MT_ERR_NULL          -1  /* a required pointer is NULL */
+#define MT_ERR_ALIGN         -2  /* a pointer is not 16-byte aligned */
+#define MT_ERR_SHAPE         -3  /* m/n/k/nr_groups violate the layout rules */
+#define MT_ERR_DTYPE         -4  /* dtype is not MT_F16 / MT_BF16 */
+#define MT_ERR_BITS          -5  /* bits is not 4 or 8 */
+#define MT_ERR_WORKSPACE     -6  /* workspace missing or smaller than mt_workspace_bytes() */
+#define MT_ERR_CUDA          -7  /* the CUDA runtime reported an error at launch */
+#define MT_ERR_UNSUPPORTED   -8  /* valid request that this build has no kernel for */
+#define MT_ERR_DEVICE        -9  /* the current device is not compute capability 10.x */
+#define MT_ERR_TOO_LARGE    -10  /* request exceeds a fixed built-in capacity */
+#define MT_ERR_NCCL         -11  /* the NCCL library reported an error or could not be loaded */
+
+/* dtype of x / scales / bias / out */
+#define MT_F16   0
+#define MT_BF16  1
+
+/* flags */
+#define MT_FLAG_NONE         0
+#define MT_FLAG_FORCE_SMALL  1   /* always use the CUDA-core/mma.sync streaming kernel (tiles M by 64) */
+#define MT_FLAG_FORCE_TC     2   /* always use the tcgen05 kernel */
+#define MT_FLAG_PDL          4   /* launch with programmatic stream serialization: the kernel starts
+                                    fetching weights before the previous kernel in the stream ends and
+                                    waits for it only before touching x / out / workspace */
+
+/* Library version: major*10000 + minor*100 + patch. */
+int mt_version(void);
+
+/* Text for a status code (static storage). */
+const char* mt_strerror(int status);
+
+/*
+ * Bytes of workspace mt_qgemm / mt_w8_perchannel_gemm need for a problem size.  The
+ * caller owns the buffer, must zero it once after allocation (the kernels leave it
+ * zeroed) and must not share it between streams that run concurrently.
+ */
+size_t mt_workspace_bytes(int m, int n, int k, int bits);
+
+/*
+ * W[k,n] = (T(q[k,n]) - (T(z[g(k),n]) + 1)) * s[g(k),n], written as [K,N] row-major in T.
+ * Replaces the reference's unpack() (examples/qwen1_5_int8.py:40-50) followed by
+ * Dequantize / dispatch_dequantize (minit/quantize/operator.py:5-7,
+ * minit/quantize/dispatch.py:14-20), bit-exactly.
+ *   qweight  uint32 [K/(32/bits), N]  element k at bits ((k % pack)*bits) of word k/pack
+ *   g_idx    int32  [K] or NULL (NULL: g(k) = k / (K/nr_groups))
+ *   qzeros   uint32 [nr_groups, N/(32/bits)] or NULL (NULL: stored zero = 2^(bits-1) - 1)
+ *   scales   T      [nr_groups, N]
+ * Rules: n % 8 == 0, k % 32 == 0, all pointers 16-byte aligned.
+ */
+int mt_dequant(void* stream, const uint32_t* qweight, const int32_t* g_idx, const uint32_t* qzeros,
+               const void* scales, void* w_out, int n, int k, int nr_groups, int bits, int dtype);
+
+/*
+ * Same formula on UNPACKED operands, the form the reference's QuantizedTensor holds
+ * (minit/quantize/tensor.py:9-30: data [K,N] uint8, group [K] int32, zero [G,N] uint8,
+ * scale [G,N] T) and dequantize(x, group, zero, scale, axis=0) consumes
+ * (minit/quantize/functional.py:6-8).  g_idx NULL: g(k) = k / (K/nr_groups).  n % 4 == 0.
+ */
+int mt_dequant_unpacked(void* stream, const uint8_t* q, const int32_t* g_idx, const uint8_t* z,
+                        const void* scales, void* w_out, int n, int k, int nr_groups, int dtype);
+
+/*
+ * int32-packed -> one element per byte: the reference's unpack(x, axis)
+ * (examples/qwen1_5_int8.py:40-50), extended to 4-bit with the accessor formula of
+ * ColPackedMatrix / RowPackedMatrix (examples/qwen1_5_int8.py:97-138).  rows/cols are the
+ * UNPACKED sizes; axis 0: packed is [rows/pack, cols]; axis 1: packed is [rows, cols/pack].
+ */
+int mt_unpack(void* stream, const uint32_t* packed, uint8_t* out, int rows, int cols, int bits, int axis);
+
+/*
+ * out[M,N] = x[M,K] @ W[K,N] (+ bias[N]), W as defined by mt_dequant, fp32 accumulation,
+ * result rounded once to T.  Replaces the reference's fused kernel launcher
+ *   extern "C" void qmm_<name>(cudaStream_t, T* x, unsigned* qweight, int* g_idx, unsigned* zeros,
+ *                              T* scales, TOut* outputs, int m, int n, int k, int nr_groups)
+ * (examples/qwen1_5_int8.py:202-216, kernel :156-200) with the same argument order, extended
+ * by bias, bits, dtype, workspace and flags.  Differences a caller must know: out is
+ * OVERWRITTEN (the reference accumulates into a pre-zeroed buffer), and the int return
+ * replaces exceptions / traps.
+ * Rules: as mt_dequant; without g_idx the group size K/nr_groups must be a multiple of 32;
+ * workspace >= mt_workspace_bytes(m, n, k, bits).
+ */
+int mt_qgemm(void* stream, const void* x, const uint32_t* qweight, const int32_t* g_idx,
+             const uint32_t* qzeros, const void* scales, const void* bias, void* out,
+             int m, int n, int k, int nr_groups, int bits, int dtype,
+             void* workspace, size_t workspace_bytes, int flags);
+
+/*
+ * out[M,N] = (x[M,K] @ float(w[K,N])) * scales[N] (+ bias[N]): int8 weight-only, one scale
+ * per output channel.  This is the G = 1, g_idx = 0, stored-zero = 127, q = w + 128 special
+ * case of the formula above (minit/quantize/dispatch.py:14-20) with w kept as plain int8
+ * [K,N] row-major instead of packed words.
+ * Rules: n % 16 == 0, k % 16 == 0, pointers 16-byte aligned.
+ */
+int mt_w8_perchannel_gemm(void* stream, const void* x, const int8_t* w, const void* scales,
+                          const void* bias, void* out, int m, int n, int k, int dtype,
+                          void* workspace, size_t workspace_bytes, int flags);
+
+/*
+ * NCCL plumbing with the reference's entry-point names (minit/nccl/library.py:41-58,
+ * minit/nccl/kernel.py:47-57), returning a status instead of throwing.  libnccl is
+ * opened with dlopen() on first use: mt_nccl_load(path) selects the file (NULL:
+ * "libnccl.so.2").  dtype: MT_F16 / MT_BF16, or 2 = float32, 3 = int32.
+ */
+int    mt_nccl_load(const char* path);
+size_t nccl_unique_id_size(void);
+int    nccl_create_unique_id(char* bytes);
+int    nccl_init_rank(int nr_ranks, int rank, const char* bytes, int device, void** comm_out);
+int    nccl_destroy(void* comm);
+int    nccl_all_gather(void* stream, void* comm, const void* sendbuff, void* recvbuff, size_t count, int dtype);
+int    nccl_all_reduce(void* stream, void* comm, const void* sendbuff, void* recvbuff, size_t count, int dtype);
+int    nccl_broadcast(void* stream, void* comm, const void* sendbuff, void* recvbuff, size_t count, int dtype, int root);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MINIT_B200_H_ */

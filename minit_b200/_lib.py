@@ -1,0 +1,116 @@
+"""ctypes binding of libminit_b200.so -- the only route from Python to the kernels.
+
+There is no fallback: if the library has not been built the import of this module raises,
+and every call checks the returned status and raises on failure.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Dict, Optional, Tuple
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libminit_b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python -m minit_b200.build` (needs nvcc). "
+        "minit_b200 has no CPU or PyTorch fallback for its kernels.")
+
+lib = ctypes.CDLL(LIB_PATH)
+
+MT_F16, MT_BF16 = 0, 1
+FLAG_FORCE_SMALL, FLAG_FORCE_TC, FLAG_PDL = 1, 2, 4
+COUNTER_BYTES = 16384
+
+_vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+#: every symbol include/minit_b200.h declares: name -> (restype, argtypes)
+SYMBOLS = {
+    "mt_version": (_i, []),
+    "mt_strerror": (ctypes.c_char_p, [_i]),
+    "mt_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "mt_dequant": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i]),
+    "mt_dequant_unpacked": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i]),
+    "mt_unpack": (_i, [_vp, _vp, _vp, _i, _i, _i, _i]),
+    "mt_qgemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _i]),
+    "mt_w8_perchannel_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _i]),
+    "mt_nccl_load": (_i, [ctypes.c_char_p]),
+    "nccl_unique_id_size": (_sz, []),
+    "nccl_create_unique_id": (_i, [_vp]),
+    "nccl_init_rank": (_i, [_i, _i, _vp, _i, ctypes.POINTER(_vp)]),
+    "nccl_destroy": (_i, [_vp]),
+    "nccl_all_gather": (_i, [_vp, _vp, _vp, _vp, _sz, _i]),
+    "nccl_all_reduce": (_i, [_vp, _vp, _vp, _vp, _sz, _i]),
+    "nccl_broadcast": (_i, [_vp, _vp, _vp, _vp, _sz, _i, _i]),
+}
+for _name, (_res, _args) in SYMBOLS.items():
+    _fn = getattr(lib, _name)
+    _fn.restype, _fn.argtypes = _res, _args
+
+
+class MinitError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        super().__init__(f"{where}: status {status}: {lib.mt_strerror(status).decode()}")
+
+
+def check(status: int, where: str) -> None:
+    if status != 0:
+        # argument errors map to ValueError like the reference's asserts, the rest to RuntimeError
+        if status in (-1, -2, -3, -4, -5):
+            raise ValueError(f"{where}: {lib.mt_strerror(status).decode()} (status {status})")
+        raise MinitError(status, where)
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float16:
+        return MT_F16
+    if dtype == torch.bfloat16:
+        return MT_BF16
+    raise ValueError(f"unsupported dtype {dtype}: the quantized-linear kernels compute in float16 or bfloat16")
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def current_stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def require_cuda(*tensors: Optional[torch.Tensor]) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("minit_b200 kernels take CUDA tensors only (there is no CPU path)")
+        if not t.is_contiguous():
+            raise ValueError("minit_b200 kernels take contiguous tensors")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ValueError("all tensors of one call must live on the same device")
+    assert dev is not None
+    return dev
+
+
+# one zero-initialised workspace per (device, stream): the kernels keep the counter area zeroed
+_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        size = max(nbytes, 32 << 20)
+        ws = torch.zeros(size, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def workspace_error_word(ws: torch.Tensor) -> int:
+    """Error word the tcgen05 kernel sets when one of its bounded waits expires (test aid)."""
+    return int(ws[COUNTER_BYTES - 4:COUNTER_BYTES].view(torch.int32).item())

@@ -1,0 +1,273 @@
+// C ABI of the quantized-linear path: argument validation, kernel selection, launch
+// configuration.  No allocation, no synchronisation, no exceptions.
+#include "common.cuh"
+#include "qgemm_small.cuh"
+#include "qgemm_w8.cuh"
+
+namespace mt {
+
+int launch_small_i4_f16(cudaStream_t, const SmallParams&, int, int, int, bool, dim3, size_t);
+int launch_small_i4_bf16(cudaStream_t, const SmallParams&, int, int, int, bool, dim3, size_t);
+int launch_small_i8_f16(cudaStream_t, const SmallParams&, int, int, int, bool, dim3, size_t);
+int launch_small_i8_bf16(cudaStream_t, const SmallParams&, int, int, int, bool, dim3, size_t);
+int launch_w8_inst(cudaStream_t, const W8Params&, int dtype, int mt, int wn, int cpt, dim3, size_t);
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Compute capability of the current device, cached per device ordinal.
+static int check_device() {
+    static int cached[64] = {0};   // 0 unknown, 1 ok, -1 not sm_100
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
+    if (dev < 0 || dev >= 64) return MT_ERR_DEVICE;
+    if (cached[dev] == 0) {
+        int major = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
+            cudaGetLastError();
+            return MT_ERR_CUDA;
+        }
+        cached[dev] = (major == 10) ? 1 : -1;
+    }
+    return cached[dev] == 1 ? MT_OK : MT_ERR_DEVICE;
+}
+
+static inline int batch_tiles(int m) { return m <= 8 ? 1 : m <= 16 ? 2 : m <= 32 ? 4 : 8; }
+
+struct SplitPlan { int wn, tiles, splits, chunks_per_split; };
+
+// Pick the CTA width and the split-K factor: enough CTAs to cover 148 SMs twice, as wide a
+// column tile as that allows (longer contiguous row segments), and split-K partial traffic
+// held to about a quarter of the weight bytes.
+static SplitPlan plan_splits(int m, int n, int k, int bits, int nchunks, int cols_per_warp,
+                             const int* wn_options, int n_options, size_t partial_capacity_bytes) {
+    const int target = 148 * 2;
+    long long smax = ((long long)k * bits) / (256LL * m);
+    if (smax < 1) smax = 1;
+    if (smax > nchunks) smax = nchunks;
+    const long long cap = (long long)(partial_capacity_bytes / ((size_t)m * n * 4));
+    if (smax > cap) smax = cap < 1 ? 1 : cap;
+    SplitPlan best = {0, 0, 0, 0};
+    for (int i = 0; i < n_options; ++i) {
+        const int wn = wn_options[i];
+        const int tile_cols = wn * cols_per_warp;
+        const int tiles = (n + tile_cols - 1) / tile_cols;
+        if (tiles > kMaxTiles) continue;
+        long long s = (target + tiles - 1) / tiles;
+        if (s > smax) s = smax;
+        if (s < 1) s = 1;
+        const int cps = (nchunks + (int)s - 1) / (int)s;
+        const int splits = (nchunks + cps - 1) / cps;
+        SplitPlan cand = {wn, tiles, splits, cps};
+        if (best.wn == 0) best = cand;
+        if ((long long)tiles * splits >= (target * 3) / 4) return cand;   // widest tile that fills the GPU
+        if ((long long)tiles * splits > (long long)best.tiles * best.splits) best = cand;
+    }
+    return best;
+}
+
+int launch_small(cudaStream_t st, const QGemmArgs& a) {
+    const int bits = a.bits, pack = 32 / bits;
+    const int kc = bits == 4 ? 256 : 128, kstep = 4 * pack;
+    const int nchunks = (a.k + kc - 1) / kc;
+    const int gs = a.k / a.groups;
+    const bool act = a.g_idx != nullptr;
+    int gpc = 1;
+    if (!act) {
+        if (gs % kc == 0) gpc = 1;
+        else if (gs % (kc / 2) == 0) gpc = 2;
+        else if (gs % kstep == 0) gpc = 8;
+        else return MT_ERR_SHAPE;
+    }
+    if (a.workspace == nullptr || a.workspace_bytes < kCounterBytes) return MT_ERR_WORKSPACE;
+    const size_t partial_cap = a.workspace_bytes - kCounterBytes;
+    auto fn = bits == 4 ? (a.dtype == MT_F16 ? launch_small_i4_f16 : launch_small_i4_bf16)
+                        : (a.dtype == MT_F16 ? launch_small_i8_f16 : launch_small_i8_bf16);
+    const size_t esz = 2;
+    for (int r0 = 0; r0 < a.m; r0 += 64) {
+        const int m = a.m - r0 < 64 ? a.m - r0 : 64;
+        const int mt = batch_tiles(m);
+        const int pitch = kc * 2 + (bits == 4 ? 64 : 32);
+        int opts[3]; int nopts = 0;
+        const int all[3] = {8, 4, 2};
+        for (int i = 0; i < 3; ++i) {
+            const int wn = all[i];
+            if (mt == 8 && wn != 8) continue;
+            if (mt == 4 && wn == 2) continue;
+            const size_t smem = (size_t)2 * mt * 8 * pitch + (act ? (size_t)a.groups * wn * 32 * 4 + 2 * kc * 4 : 0);
+            if (smem > 200 * 1024) continue;
+            opts[nopts++] = wn;
+        }
+        if (nopts == 0) return MT_ERR_TOO_LARGE;
+        const SplitPlan pl = plan_splits(m, a.n, a.k, bits, nchunks, 32, opts, nopts, partial_cap);
+        if (pl.wn == 0) return MT_ERR_TOO_LARGE;
+        if (pl.splits > 1 && (size_t)pl.splits * m * a.n * 4 > partial_cap) return MT_ERR_WORKSPACE;
+        SmallParams p;
+        p.x = static_cast<const char*>(a.x) + (size_t)r0 * a.k * esz;
+        p.qw = a.qweight; p.g_idx = a.g_idx; p.qz = a.qzeros; p.scales = a.scales; p.bias = a.bias;
+        p.out = static_cast<char*>(a.out) + (size_t)r0 * a.n * esz;
+        p.counters = static_cast<unsigned*>(a.workspace);
+        p.partial = reinterpret_cast<float*>(static_cast<char*>(a.workspace) + kCounterBytes);
+        p.m = m; p.n = a.n; p.k = a.k; p.groups = a.groups; p.gs = gs;
+        p.nchunks = nchunks; p.chunks_per_split = pl.chunks_per_split; p.splits = pl.splits;
+        p.zp1_const = 1 << (bits - 1);
+        p.pdl = (a.flags & MT_FLAG_PDL) ? 1 : 0;
+        const size_t smem = (size_t)2 * mt * 8 * pitch + (act ? (size_t)a.groups * pl.wn * 32 * 4 + 2 * kc * 4 : 0);
+        const int rc = fn(st, p, mt, pl.wn, gpc, act, dim3(pl.tiles, pl.splits), smem);
+        if (rc != MT_OK) return rc;
+    }
+    return MT_OK;
+}
+
+int launch_small_w8(cudaStream_t st, const QGemmArgs& a) {
+    const int kc = 128;
+    const int nchunks = (a.k + kc - 1) / kc;
+    if (a.workspace == nullptr || a.workspace_bytes < kCounterBytes) return MT_ERR_WORKSPACE;
+    const size_t partial_cap = a.workspace_bytes - kCounterBytes;
+    for (int r0 = 0; r0 < a.m; r0 += 64) {
+        const int m = a.m - r0 < 64 ? a.m - r0 : 64;
+        const int mt = batch_tiles(m);
+        const int cpt = mt <= 2 ? 16 : 8;
+        int opts[2]; int nopts = 0;
+        if (mt <= 2) { opts[nopts++] = 4; opts[nopts++] = 2; } else { opts[nopts++] = 4; }
+        const SplitPlan pl = plan_splits(m, a.n, a.k, 8, nchunks, 8 * cpt, opts, nopts, partial_cap);
+        if (pl.wn == 0) return MT_ERR_TOO_LARGE;
+        if (pl.splits > 1 && (size_t)pl.splits * m * a.n * 4 > partial_cap) return MT_ERR_WORKSPACE;
+        W8Params p;
+        p.x = static_cast<const char*>(a.x) + (size_t)r0 * a.k * 2;
+        p.w = a.w8; p.scales = a.scales; p.bias = a.bias;
+        p.out = static_cast<char*>(a.out) + (size_t)r0 * a.n * 2;
+        p.counters = static_cast<unsigned*>(a.workspace);
+        p.partial = reinterpret_cast<float*>(static_cast<char*>(a.workspace) + kCounterBytes);
+        p.m = m; p.n = a.n; p.k = a.k;
+        p.nchunks = nchunks; p.chunks_per_split = pl.chunks_per_split; p.splits = pl.splits;
+        p.pdl = (a.flags & MT_FLAG_PDL) ? 1 : 0;
+        const size_t smem = (size_t)2 * mt * 8 * (kc * 2 + 32);
+        const int rc = launch_w8_inst(st, p, a.dtype, mt, pl.wn, cpt, dim3(pl.tiles, pl.splits), smem);
+        if (rc != MT_OK) return rc;
+    }
+    return MT_OK;
+}
+
+}  // namespace mt
+
+using namespace mt;
+
+extern "C" {
+
+int mt_version(void) { return 100; }
+
+const char* mt_strerror(int status) {
+    switch (status) {
+        case MT_OK: return "ok";
+        case MT_ERR_NULL: return "a required pointer is NULL";
+        case MT_ERR_ALIGN: return "a pointer is not 16-byte aligned";
+        case MT_ERR_SHAPE: return "m/n/k/nr_groups violate the layout rules";
+        case MT_ERR_DTYPE: return "dtype must be MT_F16 (0) or MT_BF16 (1)";
+        case MT_ERR_BITS: return "bits must be 4 or 8";
+        case MT_ERR_WORKSPACE: return "workspace is missing or smaller than mt_workspace_bytes()";
+        case MT_ERR_CUDA: return "the CUDA runtime reported an error";
+        case MT_ERR_UNSUPPORTED: return "no kernel in this build for the request";
+        case MT_ERR_DEVICE: return "the current device is not compute capability 10.x (B200)";
+        case MT_ERR_TOO_LARGE: return "the request exceeds a fixed built-in capacity";
+        case MT_ERR_NCCL: return "NCCL reported an error or could not be loaded";
+    }
+    return "unknown status";
+}
+
+size_t mt_workspace_bytes(int m, int n, int k, int bits) {
+    if (m <= 0 || n <= 0 || k <= 0 || (bits != 4 && bits != 8)) return kCounterBytes;
+    // split-K keeps splits * min(m,64) <= k*bits/256 + 64 rows of fp32 partials
+    const size_t rows = (size_t)k * bits / 256 + 64;
+    return kCounterBytes + rows * (size_t)n * 4;
+}
+
+static int validate_gptq(const uint32_t* qweight, const uint32_t* qzeros, const void* scales,
+                         int n, int k, int nr_groups, int bits, int dtype) {
+    if (bits != 4 && bits != 8) return MT_ERR_BITS;
+    if (dtype != MT_F16 && dtype != MT_BF16) return MT_ERR_DTYPE;
+    if (n < 0 || k < 0 || nr_groups < 1) return MT_ERR_SHAPE;
+    if (n % 8 != 0 || k % 32 != 0 || k % nr_groups != 0) return MT_ERR_SHAPE;
+    if (n == 0 || k == 0) return MT_OK;
+    if (!qweight || !scales) return MT_ERR_NULL;
+    if (!aligned16(qweight) || !aligned16(scales) || (qzeros && !aligned16(qzeros))) return MT_ERR_ALIGN;
+    return MT_OK;
+}
+
+int mt_dequant(void* stream, const uint32_t* qweight, const int32_t* g_idx, const uint32_t* qzeros,
+               const void* scales, void* w_out, int n, int k, int nr_groups, int bits, int dtype) {
+    int rc = validate_gptq(qweight, qzeros, scales, n, k, nr_groups, bits, dtype);
+    if (rc != MT_OK) return rc;
+    if (n == 0 || k == 0) return MT_OK;
+    if (!w_out) return MT_ERR_NULL;
+    if (!aligned16(w_out)) return MT_ERR_ALIGN;
+    if ((rc = check_device()) != MT_OK) return rc;
+    return launch_dequant(static_cast<cudaStream_t>(stream), qweight, g_idx, qzeros, scales, w_out, n, k, nr_groups, bits, dtype);
+}
+
+int mt_dequant_unpacked(void* stream, const uint8_t* q, const int32_t* g_idx, const uint8_t* z, const void* scales,
+                        void* w_out, int n, int k, int nr_groups, int dtype) {
+    if (dtype != MT_F16 && dtype != MT_BF16) return MT_ERR_DTYPE;
+    if (n < 0 || k < 0 || nr_groups < 1 || n % 4 != 0 || (!g_idx && k % nr_groups != 0)) return MT_ERR_SHAPE;
+    if (n == 0 || k == 0) return MT_OK;
+    if (!q || !z || !scales || !w_out) return MT_ERR_NULL;
+    if (!aligned16(q) || !aligned16(z) || !aligned16(scales) || !aligned16(w_out)) return MT_ERR_ALIGN;
+    int rc = check_device();
+    if (rc != MT_OK) return rc;
+    return launch_dequant_unpacked(static_cast<cudaStream_t>(stream), q, g_idx, z, scales, w_out, n, k, nr_groups, dtype);
+}
+
+int mt_unpack(void* stream, const uint32_t* packed, uint8_t* out, int rows, int cols, int bits, int axis) {
+    if (bits != 4 && bits != 8) return MT_ERR_BITS;
+    if (axis != 0 && axis != 1) return MT_ERR_SHAPE;
+    const int pack = 32 / bits;
+    if (rows < 0 || cols < 0 || (axis == 0 ? rows % pack : cols % pack) != 0) return MT_ERR_SHAPE;
+    if (rows == 0 || cols == 0) return MT_OK;
+    if (!packed || !out) return MT_ERR_NULL;
+    int rc = check_device();
+    if (rc != MT_OK) return rc;
+    return launch_unpack(static_cast<cudaStream_t>(stream), packed, out, rows, cols, bits, axis);
+}
+
+int mt_qgemm(void* stream, const void* x, const uint32_t* qweight, const int32_t* g_idx,
+             const uint32_t* qzeros, const void* scales, const void* bias, void* out,
+             int m, int n, int k, int nr_groups, int bits, int dtype,
+             void* workspace, size_t workspace_bytes, int flags) {
+    int rc = validate_gptq(qweight, qzeros, scales, n, k, nr_groups, bits, dtype);
+    if (rc != MT_OK) return rc;
+    if (m < 0) return MT_ERR_SHAPE;
+    if (m == 0 || n == 0) return MT_OK;
+    if (k == 0) return MT_ERR_SHAPE;
+    if (!x || !out) return MT_ERR_NULL;
+    if (!aligned16(x) || !aligned16(out) || (bias && !aligned16(bias))) return MT_ERR_ALIGN;
+    if (!g_idx && (k / nr_groups) % (4 * (32 / bits)) != 0) return MT_ERR_SHAPE;
+    if (workspace && !aligned16(workspace)) return MT_ERR_ALIGN;
+    if ((rc = check_device()) != MT_OK) return rc;
+    QGemmArgs a = {};
+    a.x = x; a.qweight = qweight; a.g_idx = g_idx; a.qzeros = qzeros; a.scales = scales; a.bias = bias; a.out = out;
+    a.m = m; a.n = n; a.k = k; a.groups = nr_groups; a.bits = bits; a.dtype = dtype;
+    a.workspace = workspace; a.workspace_bytes = workspace_bytes; a.flags = flags;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (flags & MT_FLAG_FORCE_TC) return tc_supported(a) ? launch_tc(st, a) : MT_ERR_UNSUPPORTED;
+    if (!(flags & MT_FLAG_FORCE_SMALL) && m > 64 && tc_supported(a)) return launch_tc(st, a);
+    return launch_small(st, a);
+}
+
+int mt_w8_perchannel_gemm(void* stream, const void* x, const int8_t* w, const void* scales,
+                          const void* bias, void* out, int m, int n, int k, int dtype,
+                          void* workspace, size_t workspace_bytes, int flags) {
+    if (dtype != MT_F16 && dtype != MT_BF16) return MT_ERR_DTYPE;
+    if (m < 0 || n < 0 || k <= 0 || n % 16 != 0 || k % 16 != 0) return MT_ERR_SHAPE;
+    if (m == 0 || n == 0) return MT_OK;
+    if (!x || !w || !scales || !out) return MT_ERR_NULL;
+    if (!aligned16(x) || !aligned16(w) || !aligned16(scales) || !aligned16(out) || (bias && !aligned16(bias)) ||
+        (workspace && !aligned16(workspace))) return MT_ERR_ALIGN;
+    int rc = check_device();
+    if (rc != MT_OK) return rc;
+    QGemmArgs a = {};
+    a.x = x; a.w8 = w; a.scales = scales; a.bias = bias; a.out = out;
+    a.m = m; a.n = n; a.k = k; a.groups = 1; a.bits = 8; a.dtype = dtype;
+    a.workspace = workspace; a.workspace_bytes = workspace_bytes; a.flags = flags;
+    return launch_small_w8(static_cast<cudaStream_t>(stream), a);
+}
+
+}  // extern "C"

@@ -1,0 +1,118 @@
+// Shared device helpers for the quantized-linear kernels (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include "../../include/minit_b200.h"
+
+namespace mt {
+
+// ----------------------------------------------------------------------------------
+// 16-bit float traits: register-level (uint32 = two packed elements) arithmetic
+// ----------------------------------------------------------------------------------
+template <typename T> struct F16x2;
+
+template <> struct F16x2<__half> {
+    static constexpr bool kIsBf16 = false;
+    static __device__ __forceinline__ uint32_t sub(uint32_t a, uint32_t b) {
+        uint32_t d; asm("sub.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+    static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {
+        uint32_t d; asm("mul.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+    static __device__ __forceinline__ uint32_t fma(uint32_t a, uint32_t b, uint32_t c) {
+        uint32_t d; asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d; }
+    static __device__ __forceinline__ float to_float(uint16_t v) { return __half2float(__ushort_as_half(v)); }
+    static __device__ __forceinline__ uint16_t from_float(float f) { return __half_as_ushort(__float2half_rn(f)); }
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+        __half2 h = __floats2half2_rn(lo, hi); return *reinterpret_cast<uint32_t*>(&h); }
+};
+
+template <> struct F16x2<__nv_bfloat16> {
+    static constexpr bool kIsBf16 = true;
+    static __device__ __forceinline__ uint32_t sub(uint32_t a, uint32_t b) {
+        uint32_t d; asm("sub.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+    static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {
+        uint32_t d; asm("mul.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+    static __device__ __forceinline__ uint32_t fma(uint32_t a, uint32_t b, uint32_t c) {
+        uint32_t d; asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d; }
+    static __device__ __forceinline__ float to_float(uint16_t v) { return __uint_as_float(uint32_t(v) << 16); }
+    static __device__ __forceinline__ uint16_t from_float(float f) { return __bfloat16_as_ushort(__float2bfloat16_rn(f)); }
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi); return *reinterpret_cast<uint32_t*>(&h); }
+};
+
+// (a & b) | c in one LOP3
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d; asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d; asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel)); return d;
+}
+
+// streaming 128-bit global load: weights are read exactly once, keep them out of L1
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_stream8(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+// L2-coherent loads for data another CTA of the same grid has just written
+__device__ __forceinline__ float4 ldcg_f4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
+
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// m16n8k16, A row-major (16x16), B col-major (16x8), fp32 accumulate
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    if constexpr (F16x2<T>::kIsBf16) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    } else {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+}
+
+// ----------------------------------------------------------------------------------
+// host-side launch plumbing shared by the .cu files
+// ----------------------------------------------------------------------------------
+struct QGemmArgs {
+    const void* x;            // [M,K] T
+    const uint32_t* qweight;  // [K/pack, N]
+    const int32_t* g_idx;     // [K] or null
+    const uint32_t* qzeros;   // [G, N/pack] or null
+    const void* scales;       // [G,N] T (per-channel: [N])
+    const void* bias;         // [N] T or null
+    void* out;                // [M,N] T
+    const int8_t* w8;         // per-channel path: [K,N] int8
+    int m, n, k, groups, bits, dtype;
+    void* workspace;
+    size_t workspace_bytes;
+    int flags;
+};
+
+// workspace layout: [0, kCounterBytes) tile counters (kept zero between launches),
+// then fp32 split-K partials.
+constexpr size_t kCounterBytes = 16384;           // 4096 tile counters
+constexpr int kMaxTiles = int(kCounterBytes / 4);
+
+int launch_dequant(cudaStream_t st, const uint32_t* qweight, const int32_t* g_idx, const uint32_t* qzeros,
+                   const void* scales, void* w_out, int n, int k, int groups, int bits, int dtype);
+int launch_dequant_unpacked(cudaStream_t st, const uint8_t* q, const int32_t* g_idx, const uint8_t* z, const void* scales,
+                            void* w_out, int n, int k, int groups, int dtype);
+int launch_unpack(cudaStream_t st, const uint32_t* packed, uint8_t* out, int rows, int cols, int bits, int axis);
+int launch_small(cudaStream_t st, const QGemmArgs& a);          // GPTQ layout, M <= 64 per launch
+int launch_small_w8(cudaStream_t st, const QGemmArgs& a);       // int8 [K,N] per-channel, M <= 64 per launch
+int launch_tc(cudaStream_t st, const QGemmArgs& a);             // tcgen05 path (any M), GPTQ layout without g_idx
+bool tc_supported(const QGemmArgs& a);
+
+}  // namespace mt

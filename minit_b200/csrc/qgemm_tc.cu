@@ -1,0 +1,389 @@
+// Prefill-sized fused dequant + GEMM on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// Roofline: dense fp16/bf16 tensor throughput.
+//
+// out^T tile = W^T tile x x^T tile:  the 128 output columns of a tile are the MMA "M" rows
+// (TMEM lanes), BM batch rows are the MMA "N" columns, so one dequantised 128 x 64 weight tile
+// feeds BM = 256 batch rows per k-block and the CUDA-core dequant cost is amortised 256 ways.
+//
+// Per CTA (persistent, one per SM, 320 threads):
+//   warp 0      TMA producer: per k-block (64 k) one 2-D bulk tensor load of the packed qweight
+//               rows [64/pack, 128 columns] (plain layout) and one of the x tile [BM, 64]
+//               (128-byte swizzle, K-major = the canonical UMMA operand layout).
+//   warps 2-5   dequant: thread i owns output column i of the tile; it reads its packed words
+//               from shared memory, rebuilds exactly the reference's W[k,n] (T arithmetic, see
+//               qgemm_small.cuh) and writes 16-byte k-chunks into the A operand buffer in the
+//               K-major 128-byte-swizzled layout (chunk index XOR row%8), then
+//               fence.proxy.async + mbarrier arrive.
+//   warp 1      MMA issuer: one elected thread issues 4 x tcgen05.mma (128 x BM x 16, fp32
+//               accumulate in TMEM) per k-block and tcgen05.commit's the stage back to the
+//               producer; two TMEM accumulators (2 x BM columns) alternate between tiles.
+//   warps 6-9   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, + bias, round to T,
+//               store out[m, n]; overlaps the next tile's main loop.
+// Every mbarrier wait is bounded; on expiry the kernel records a code in the error word
+// (last counter slot of the workspace) and every role leaves its loop.
+#include <cuda.h>
+#include "common.cuh"
+#include "qgemm_small.cuh"   // GroupConst / dequant_word
+
+namespace mt {
+
+struct TcParams {
+    const uint32_t* qz;
+    const void* scales;
+    const void* bias;
+    void* out;
+    unsigned* err;          // error word (may be null)
+    int m, n, k, groups, gs;
+    int n_tiles, m_tiles;
+    int zp1_const;
+};
+
+constexpr int TC_BN = 128;     // output columns per tile (MMA M)
+constexpr int TC_BK = 64;      // k per stage
+constexpr int TC_STAGES = 4;
+constexpr int TC_THREADS = 320;
+
+template <int BITS, int BM> struct TcSmem {
+    static constexpr int PACK = 32 / BITS;
+    static constexpr int QROWS = TC_BK / PACK;
+    static constexpr int A_BYTES = TC_BN * 128;
+    static constexpr int B_BYTES = BM * 128;
+    static constexpr int Q_BYTES = QROWS * TC_BN * 4;
+    static constexpr int OFF_A = 0;
+    static constexpr int OFF_B = OFF_A + TC_STAGES * A_BYTES;
+    static constexpr int OFF_Q = OFF_B + TC_STAGES * B_BYTES;
+    static constexpr int OFF_BAR = OFF_Q + TC_STAGES * Q_BYTES;
+    static constexpr int TOTAL = OFF_BAR + 256 + 1024;   // barriers + slack for manual 1024-byte alignment
+};
+
+// ---- PTX wrappers ----------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: spins, then backs off with nanosleep; gives up after roughly a second.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (int i = 0; i < 4096; ++i) if (mbar_try_wait(bar, parity)) return true;
+    for (int i = 0; i < (1 << 22); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        __nanosleep(128);
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128-byte swizzle: rows of 128 bytes, 8-row atoms 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
+    d |= (uint64_t)1 << 16;                 // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset: next 8-row atom
+    d |= (uint64_t)1 << 46;                 // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+    return d;
+}
+
+template <int BITS, typename T, int BM>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_q, const TcParams p) {
+    using S = TcSmem<BITS, BM>;
+    using H = F16x2<T>;
+    constexpr int PACK = S::PACK, QROWS = S::QROWS;
+    constexpr uint32_t TMEM_COLS = 2 * BM < 32 ? 32 : 2 * BM;
+    static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns must be a power of two <= 512");
+
+    extern __shared__ unsigned char smem_raw[];
+    // operand tiles need 1024-byte alignment in the shared address space (swizzle atoms)
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar0 = sbase + S::OFF_BAR;
+    auto bar_full = [&](int s) { return bar0 + 8u * s; };
+    auto bar_aready = [&](int s) { return bar0 + 8u * (TC_STAGES + s); };
+    auto bar_empty = [&](int s) { return bar0 + 8u * (2 * TC_STAGES + s); };
+    auto bar_tfull = [&](int a) { return bar0 + 8u * (3 * TC_STAGES + a); };
+    auto bar_tempty = [&](int a) { return bar0 + 8u * (3 * TC_STAGES + 2 + a); };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + S::OFF_BAR + 8 * (3 * TC_STAGES + 4));
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kblocks = (p.k + TC_BK - 1) / TC_BK;
+    const int total_tiles = p.n_tiles * p.m_tiles;
+
+    if (tid == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_aready(s), 128); mbar_init(bar_empty(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(bar_tfull(a), 1); mbar_init(bar_tempty(a), 128); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int n0 = (tile / p.m_tiles) * TC_BN, m0 = (tile % p.m_tiles) * BM;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % TC_STAGES; const uint32_t ph = (it / TC_STAGES) & 1;
+                    if (!mbar_wait(bar_empty(s), ph ^ 1, &abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(bar_full(s), S::Q_BYTES + S::B_BYTES);
+                    tma_load_2d(sbase + S::OFF_Q + s * S::Q_BYTES, &tmap_q, n0, kb * QROWS, bar_full(s));
+                    tma_load_2d(sbase + S::OFF_B + s * S::B_BYTES, &tmap_x, kb * TC_BK, m0, bar_full(s));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            // instruction descriptor: D=f32, A/B = f16|bf16, both K-major, N = BM, M = 128
+            const uint32_t fmt = H::kIsBf16 ? 1u : 0u;
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BM >> 3) << 17) | ((uint32_t)(TC_BN >> 4) << 24);
+            int it = 0, lt = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
+                const int acc = lt & 1; const uint32_t aph = (lt >> 1) & 1;
+                if (!mbar_wait(bar_tempty(acc), aph ^ 1, &abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BM);
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % TC_STAGES; const uint32_t ph = (it / TC_STAGES) & 1;
+                    if (!mbar_wait(bar_full(s), ph, &abort_flag) || !mbar_wait(bar_aready(s), ph, &abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t adesc = umma_desc_sw128(sbase + S::OFF_A + s * S::A_BYTES);
+                    const uint64_t bdesc = umma_desc_sw128(sbase + S::OFF_B + s * S::B_BYTES);
+#pragma unroll
+                    for (int k4 = 0; k4 < TC_BK / 16; ++k4)
+                        tc_mma_f16(d_tmem, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, (kb | k4) != 0 ? 1u : 0u);
+                    tc_commit(bar_empty(s));
+                }
+                if (ok) tc_commit(bar_tfull(acc));
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------- dequant warps: thread i <-> output column i of the tile ----------------
+        const int i = tid - 64;
+        const T* __restrict__ sg = reinterpret_cast<const T*>(p.scales);
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int n0 = (tile / p.m_tiles) * TC_BN;
+            const int n = n0 + i;
+            const bool n_ok = n < p.n;
+            int g_cur = -1;
+            GroupConst<BITS, T> gc;
+            for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                const int s = it % TC_STAGES; const uint32_t ph = (it / TC_STAGES) & 1;
+                const int g = min((kb * TC_BK) / p.gs, p.groups - 1);
+                if (g != g_cur) {
+                    g_cur = g;
+                    uint32_t sv = 0, zb = 0;
+                    if (n_ok) {
+                        sv = (uint32_t)reinterpret_cast<const uint16_t*>(sg)[(size_t)g * p.n + n];
+                        if (p.qz) zb = __ldg(p.qz + (size_t)g * (p.n / PACK) + n / PACK) >> ((n % PACK) * BITS);
+                    }
+                    make_group_const<BITS, T>(gc, make_uint2(sv, 0u), zb, p.qz != nullptr, p.zp1_const);
+                }
+                if (!mbar_wait(bar_full(s), ph, &abort_flag)) { ok = false; break; }
+                const uint32_t* q = reinterpret_cast<const uint32_t*>(smem + S::OFF_Q + s * S::Q_BYTES) + i;
+                unsigned char* arow = smem + S::OFF_A + s * S::A_BYTES + (i >> 3) * 1024 + (i & 7) * 128;
+                if constexpr (BITS == 4) {
+#pragma unroll
+                    for (int r = 0; r < QROWS; ++r) {
+                        uint32_t f[4];
+                        dequant_word<4, T>(q[r * TC_BN], gc, 0, f);   // (k0,k4) (k1,k5) (k2,k6) (k3,k7)
+                        uint4 v;
+                        v.x = prmt(f[0], f[1], 0x5410u); v.y = prmt(f[2], f[3], 0x5410u);   // (k0,k1) (k2,k3)
+                        v.z = prmt(f[0], f[1], 0x7632u); v.w = prmt(f[2], f[3], 0x7632u);   // (k4,k5) (k6,k7)
+                        *reinterpret_cast<uint4*>(arow + ((r ^ (i & 7)) << 4)) = v;
+                    }
+                } else {
+#pragma unroll
+                    for (int r = 0; r < QROWS; r += 2) {
+                        uint32_t f0[2], f1[2];
+                        dequant_word<8, T>(q[r * TC_BN], gc, 0, f0);
+                        dequant_word<8, T>(q[(r + 1) * TC_BN], gc, 0, f1);
+                        *reinterpret_cast<uint4*>(arow + (((r >> 1) ^ (i & 7)) << 4)) = make_uint4(f0[0], f0[1], f1[0], f1[1]);
+                    }
+                }
+                fence_proxy_async();
+                mbar_arrive(bar_aready(s));
+            }
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        const int q4 = warp & 3;                  // TMEM lane quarter this warp may access
+        const int nl = q4 * 32 + lane;            // output column inside the tile
+        const T* __restrict__ bias = reinterpret_cast<const T*>(p.bias);
+        T* __restrict__ out = reinterpret_cast<T*>(p.out);
+        int lt = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
+            const int n0 = (tile / p.m_tiles) * TC_BN, m0 = (tile % p.m_tiles) * BM;
+            const int acc = lt & 1; const uint32_t aph = (lt >> 1) & 1;
+            const int n = n0 + nl;
+            const float bv = (bias && n < p.n) ? H::to_float(reinterpret_cast<const uint16_t*>(bias)[n]) : 0.f;
+            if (!mbar_wait(bar_tfull(acc), aph, &abort_flag)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll 1
+            for (int c0 = 0; c0 < BM; c0 += 32) {
+                uint32_t r[32];
+                tc_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(acc * BM + c0), r);
+                tc_wait_ld();
+                if (n < p.n) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int mrow = m0 + c0 + j;
+                        if (mrow < p.m)
+                            reinterpret_cast<uint16_t*>(out)[(size_t)mrow * p.n + n] = H::from_float(__uint_as_float(r[j]) + bv);
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar_tempty(acc));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+    if (tid == 0 && abort_flag && p.err) atomicExch(p.err, 1u);
+}
+
+// ---- host side -------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+        else
+            cudaGetLastError();
+    }
+    return fn;
+}
+
+bool tc_supported(const QGemmArgs& a) {
+    if (a.g_idx != nullptr) return false;
+    const int gs = a.k / a.groups;
+    if (gs % TC_BK != 0) return false;
+    if (a.n % 8 != 0 || a.k % 32 != 0) return false;
+    return true;
+}
+
+template <int BITS, typename T, int BM>
+static int launch_tc_inst(cudaStream_t st, const QGemmArgs& a, const CUtensorMap& mx, const CUtensorMap& mq, const TcParams& p) {
+    using S = TcSmem<BITS, BM>;
+    auto kern = qgemm_tc_kernel<BITS, T, BM>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) != cudaSuccess) {
+        cudaGetLastError();
+        return MT_ERR_TOO_LARGE;
+    }
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int tiles = p.n_tiles * p.m_tiles;
+    const int grid = tiles < sms ? tiles : sms;
+    kern<<<grid, TC_THREADS, S::TOTAL, st>>>(mx, mq, p);
+    return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_CUDA;
+}
+
+int launch_tc(cudaStream_t st, const QGemmArgs& a) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return MT_ERR_UNSUPPORTED;
+    const int pack = 32 / a.bits;
+    const int bm = a.m > 128 ? 256 : (a.m > 64 ? 128 : 64);
+    CUtensorMap mx, mq;
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)a.m};
+        cuuint64_t strides[1] = {(cuuint64_t)a.k * 2};
+        cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)bm};
+        cuuint32_t es[2] = {1, 1};
+        const CUtensorMapDataType dt = a.dtype == MT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+        if (enc(&mx, dt, 2, const_cast<void*>(a.x), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return MT_ERR_CUDA;
+    }
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)a.n, (cuuint64_t)(a.k / pack)};
+        cuuint64_t strides[1] = {(cuuint64_t)a.n * 4};
+        cuuint32_t box[2] = {(cuuint32_t)TC_BN, (cuuint32_t)(TC_BK / pack)};
+        cuuint32_t es[2] = {1, 1};
+        if (enc(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(a.qweight), dims, strides, box, es,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return MT_ERR_CUDA;
+    }
+    TcParams p;
+    p.qz = a.qzeros; p.scales = a.scales; p.bias = a.bias; p.out = a.out;
+    p.err = (a.workspace && a.workspace_bytes >= kCounterBytes) ? static_cast<unsigned*>(a.workspace) + (kMaxTiles - 1) : nullptr;
+    p.m = a.m; p.n = a.n; p.k = a.k; p.groups = a.groups; p.gs = a.k / a.groups;
+    p.n_tiles = (a.n + TC_BN - 1) / TC_BN; p.m_tiles = (a.m + bm - 1) / bm;
+    p.zp1_const = 1 << (a.bits - 1);
+#define MT_TC(B_, T_) \
+    (bm == 256 ? launch_tc_inst<B_, T_, 256>(st, a, mx, mq, p) : bm == 128 ? launch_tc_inst<B_, T_, 128>(st, a, mx, mq, p) \
+                                                                          : launch_tc_inst<B_, T_, 64>(st, a, mx, mq, p))
+    if (a.bits == 4) return a.dtype == MT_F16 ? MT_TC(4, __half) : MT_TC(4, __nv_bfloat16);
+    return a.dtype == MT_F16 ? MT_TC(8, __half) : MT_TC(8, __nv_bfloat16);
+#undef MT_TC
+}
+
+}  // namespace mt

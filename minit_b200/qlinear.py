@@ -1,0 +1,180 @@
+"""The quantized-linear operators with the reference's Python call signatures.
+
+Reference (examples/qwen1_5_int8.py): ``unpack`` :40-50, ``quantized_matrix_multiply`` :244-267,
+``QLinear`` :270-289, ``QLinearWithBias`` :292-317.  Tensors are torch CUDA tensors; every
+function is one call into the C ABI on the current stream (no per-call allocation besides
+the output, no synchronisation).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .module import Module
+from .quantize.tensor import QuantizedTensor
+
+default_dtype = "float16"
+
+
+def unpack(x: torch.Tensor, axis: int, bits: int = 8) -> torch.Tensor:
+    """int32-packed [.., ..] -> one element per uint8 along ``axis`` (little-endian inside the word)."""
+    if x.dtype != torch.int32 or x.dim() != 2:
+        raise ValueError("unpack takes a 2-D int32 tensor")
+    if axis not in (0, 1):
+        raise ValueError("axis must be 0 or 1")
+    dev = _lib.require_cuda(x)
+    pack = 32 // bits
+    rows = x.shape[0] * pack if axis == 0 else x.shape[0]
+    cols = x.shape[1] if axis == 0 else x.shape[1] * pack
+    out = torch.empty((rows, cols), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib.mt_unpack(_lib.current_stream(dev), x.data_ptr(), out.data_ptr(), rows, cols, bits, axis)
+    _lib.check(rc, "mt_unpack")
+    return out
+
+
+def quantized_matrix_multiply(x: torch.Tensor, qweight: torch.Tensor, zeros: Optional[torch.Tensor],
+                              scales: torch.Tensor, groups: Optional[torch.Tensor], *, bits: int = 8,
+                              bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                              flags: int = 0) -> torch.Tensor:
+    """out[*ms, N] = x[*ms, K] @ W[K, N] (+ bias) with W = (q - (z + 1)) * s per group.
+
+    Same positional arguments as the reference (x, qweight, zeros, scales, groups); ``bits``
+    defaults to 8 because that is the only width the reference instantiates.  ``groups`` is
+    the per-k group index (g_idx) or None for contiguous groups; ``zeros`` None means the
+    symmetric midpoint.  The shape contract is the reference's (examples/qwen1_5_int8.py:247-254).
+    """
+    if bits not in (4, 8):
+        raise ValueError("bits must be 4 or 8")
+    pack = 32 // bits
+    *ms, k0 = x.shape
+    pk1, n0 = qweight.shape
+    g1, n2 = scales.shape
+    if not (k0 == pk1 * pack and n0 == n2):
+        raise ValueError(f"shape mismatch: x[..,{k0}] qweight[{pk1}*{pack},{n0}] scales[{g1},{n2}]")
+    if zeros is not None and tuple(zeros.shape) != (g1, n0 // pack):
+        raise ValueError(f"zeros must be [{g1},{n0 // pack}], got {tuple(zeros.shape)}")
+    if groups is not None and tuple(groups.shape) != (k0,):
+        raise ValueError(f"groups must be [{k0}], got {tuple(groups.shape)}")
+    if scales.dtype != x.dtype:
+        raise ValueError("scales.dtype must equal x.dtype")
+    if bias is not None and (bias.dtype != x.dtype or tuple(bias.shape) != (n0,)):
+        raise ValueError("bias must be [N] in x.dtype")
+    dev = _lib.require_cuda(x, qweight, zeros, scales, groups, bias)
+    m = 1
+    for d in ms:
+        m *= d
+    if out is None:
+        out = torch.empty((*ms, n0), dtype=x.dtype, device=dev)
+    else:
+        _lib.require_cuda(out)
+        if tuple(out.shape) != (*ms, n0) or out.dtype != x.dtype:
+            raise ValueError("out has the wrong shape or dtype")
+    stream = _lib.current_stream(dev)
+    need = _lib.lib.mt_workspace_bytes(m, n0, k0, bits)
+    ws = _lib.workspace(dev, stream, need)
+    with torch.cuda.device(dev):
+        rc = _lib.lib.mt_qgemm(stream, x.data_ptr(), qweight.data_ptr(), _lib.ptr(groups), _lib.ptr(zeros),
+                               scales.data_ptr(), _lib.ptr(bias), out.data_ptr(), m, n0, k0, g1, bits,
+                               _lib.dtype_code(x.dtype), ws.data_ptr(), ws.numel(), flags)
+    _lib.check(rc, "mt_qgemm")
+    return out
+
+
+def w8_perchannel_matrix_multiply(x: torch.Tensor, weight: torch.Tensor, scales: torch.Tensor, *,
+                                  bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                                  flags: int = 0) -> torch.Tensor:
+    """out = (x @ float(weight)) * scales (+ bias); weight int8 [K,N], scales [N] in x.dtype."""
+    *ms, k0 = x.shape
+    if weight.dtype != torch.int8 or weight.dim() != 2 or weight.shape[0] != k0:
+        raise ValueError("weight must be int8 [K,N]")
+    n0 = weight.shape[1]
+    if tuple(scales.shape) != (n0,) or scales.dtype != x.dtype:
+        raise ValueError("scales must be [N] in x.dtype")
+    if bias is not None and (bias.dtype != x.dtype or tuple(bias.shape) != (n0,)):
+        raise ValueError("bias must be [N] in x.dtype")
+    dev = _lib.require_cuda(x, weight, scales, bias)
+    m = 1
+    for d in ms:
+        m *= d
+    if out is None:
+        out = torch.empty((*ms, n0), dtype=x.dtype, device=dev)
+    stream = _lib.current_stream(dev)
+    ws = _lib.workspace(dev, stream, _lib.lib.mt_workspace_bytes(m, n0, k0, 8))
+    with torch.cuda.device(dev):
+        rc = _lib.lib.mt_w8_perchannel_gemm(stream, x.data_ptr(), weight.data_ptr(), scales.data_ptr(), _lib.ptr(bias),
+                                            out.data_ptr(), m, n0, k0, _lib.dtype_code(x.dtype), ws.data_ptr(), ws.numel(), flags)
+    _lib.check(rc, "mt_w8_perchannel_gemm")
+    return out
+
+
+def _trivial_groups(g_idx: torch.Tensor, nr_groups: int) -> bool:
+    k = g_idx.numel()
+    if k % nr_groups:
+        return False
+    ref = torch.arange(k, device=g_idx.device, dtype=torch.int32) // (k // nr_groups)
+    return bool(torch.equal(g_idx, ref))
+
+
+class QLinear(Module):
+    """GPTQ linear: buffers qweight (in/pack, out) int32, qzeros (nr_groups, out/pack) int32,
+    scales (nr_groups, out), g_idx (in,) int32.  ``bits`` = 8 reproduces the reference module;
+    4 is the int4 layout."""
+
+    def __init__(self, in_features: int, out_features: int, nr_groups: int, bits: int = 8,
+                 dtype: str = default_dtype) -> None:
+        super().__init__()
+        pack = 32 // bits
+        self.bits = bits
+        self.qweight = self.register_buffer("qweight", (in_features // pack, out_features), "int32")
+        self.qzeros = self.register_buffer("qzeros", (nr_groups, out_features // pack), "int32")
+        self.scales = self.register_buffer("scales", (nr_groups, out_features), dtype)
+        self.g_idx = self.register_buffer("g_idx", (in_features,), "int32")
+        self._groups_arg = "unchecked"
+
+    def update_buffer(self, name: str, value: torch.Tensor) -> None:
+        super().update_buffer(name, value)
+        if name == "g_idx":
+            self._groups_arg = "unchecked"
+
+    def _groups(self):
+        # a g_idx that is just k // group_size selects the faster contiguous-group kernel;
+        # decided once per load (one device->host read), not per call
+        if self._groups_arg == "unchecked":
+            self._groups_arg = None if _trivial_groups(self.g_idx, self.scales.shape[0]) else self.g_idx
+        return self._groups_arg
+
+    @property
+    def weight(self) -> QuantizedTensor:
+        return QuantizedTensor(unpack(self.qweight, 0, self.bits), self.g_idx, unpack(self.qzeros, 1, self.bits),
+                               self.scales, packed=(self.qweight, self.qzeros, self.bits))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return quantized_matrix_multiply(x, self.qweight, self.qzeros, self.scales, self._groups(), bits=self.bits)
+
+
+class QLinearWithBias(QLinear):
+    def __init__(self, in_features: int, out_features: int, nr_groups: int, bits: int = 8,
+                 dtype: str = default_dtype) -> None:
+        super().__init__(in_features, out_features, nr_groups, bits, dtype)
+        self.bias = self.register_buffer("bias", (out_features,), dtype)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        # the reference adds the bias with two extra kernels (examples/qwen1_5_int8.py:313-316); here it is the GEMM epilogue
+        return quantized_matrix_multiply(x, self.qweight, self.qzeros, self.scales, self._groups(), bits=self.bits,
+                                         bias=self.bias)
+
+
+class W8Linear(Module):
+    """int8 weight-only linear with one scale per output channel: weight (in, out) int8, scales (out,)."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, dtype: str = default_dtype) -> None:
+        super().__init__()
+        self.weight = self.register_buffer("weight", (in_features, out_features), "int8")
+        self.scales = self.register_buffer("scales", (out_features,), dtype)
+        self.bias = self.register_buffer("bias", (out_features,), dtype) if bias else None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return w8_perchannel_matrix_multiply(x, self.weight, self.scales, bias=self.bias)

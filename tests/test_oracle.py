@@ -1,0 +1,115 @@
+"""The CPU oracle against the committed golden vectors (outputs of the reference's own
+dispatch_dequantize, see tests/golden/make_golden.py) and against hand-computed known answers."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import qlinear_oracle as O
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "dequant_golden.npz")
+CASES = ["int4_f16", "int4_f16_act", "int4_bf16", "int4_f16_g32", "int8_f16", "int8_f16_act", "int8_bf16_act"]
+
+
+def load_case(g, name):
+    dt = torch.bfloat16 if int(g[f"{name}.is_bf16"]) else torch.float16
+    scales = torch.from_numpy(g[f"{name}.scales_bits"]).view(dt)
+    return dict(bits=int(g[f"{name}.bits"]), qweight=g[f"{name}.qweight"], qzeros=g[f"{name}.qzeros"],
+                g_idx=g[f"{name}.g_idx"], scales=scales, w_bits=g[f"{name}.w_bits"])
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_oracle_matches_reference_dequantize_bit_exactly(name):
+    c = load_case(np.load(GOLDEN), name)
+    w = O.dequantize_packed(c["qweight"], c["g_idx"], c["qzeros"], c["scales"], c["bits"])
+    assert np.array_equal(w.view(torch.int16).numpy(), c["w_bits"])
+
+
+def test_oracle_w8_perchannel_is_the_one_group_special_case():
+    g = np.load(GOLDEN)
+    w_i8 = g["w8pc.w_i8"]
+    scales = torch.from_numpy(g["w8pc.scales_bits"]).view(torch.float16)
+    qweight, g_idx, qzeros, s = O.w8_perchannel_as_gptq(w_i8, scales)
+    w = O.dequantize_packed(qweight, g_idx, qzeros, s, 8)
+    assert np.array_equal(w.view(torch.int16).numpy(), g["w8pc.w_bits"])
+    # and it equals w * scale rounded once
+    direct = (torch.from_numpy(w_i8).float() * scales.float()).half()
+    assert torch.equal(w, direct)
+
+
+def test_known_answers():
+    s = torch.tensor([[0.5, 0.25, 2.0, 1.0]], dtype=torch.float16)
+    # 4-bit: q=0,z=15 -> (0-16)*s ; q=15,z=0 -> 14*s ; no wrap-around of z+1
+    q = np.array([[0, 15, 0, 7]], dtype=np.uint8)
+    z = np.array([[15, 0, 0, 7]], dtype=np.uint8)
+    w = O.dequantize(q, np.zeros(1, np.int32), z, s)
+    assert w.tolist() == [[-8.0, 3.5, -2.0, -1.0]]
+    # 8-bit: q=255,z=255 -> -1*s ; per-channel midpoint z=127
+    q = np.array([[255, 0, 128, 255]], dtype=np.uint8)
+    z = np.array([[255, 255, 127, 0]], dtype=np.uint8)
+    w = O.dequantize(q, np.zeros(1, np.int32), z, s)
+    assert w.tolist() == [[-0.5, -64.0, 0.0, 254.0]]
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_pack_unpack_roundtrip_and_bit_positions(bits):
+    rng = np.random.default_rng(bits)
+    ps = 32 // bits
+    q = rng.integers(0, 1 << bits, size=(4 * ps, 16), dtype=np.uint8)
+    assert np.array_equal(O.unpack_rows(O.pack_rows(q, bits), bits), q)
+    z = rng.integers(0, 1 << bits, size=(3, 2 * ps), dtype=np.uint8)
+    assert np.array_equal(O.unpack_cols(O.pack_cols(z, bits), bits), z)
+    # element k of a column sits at bits (k % pack) * bits of word k // pack (little-endian in the word)
+    one = np.zeros((ps, 1), dtype=np.uint8)
+    one[3, 0] = (1 << bits) - 1
+    assert int(O.pack_rows(one, bits).view(np.uint32)[0, 0]) == ((1 << bits) - 1) << (3 * bits)
+    onec = np.zeros((1, ps), dtype=np.uint8)
+    onec[0, 2] = 1
+    assert int(O.pack_cols(onec, bits).view(np.uint32)[0, 0]) == 1 << (2 * bits)
+
+
+def test_int8_unpack_is_the_byte_view_the_reference_uses():
+    # the reference's unpack reinterprets int32 as uint8 (examples/qwen1_5_int8.py:44): byte j of a word = element j
+    rng = np.random.default_rng(0)
+    qweight = rng.integers(-2**31, 2**31 - 1, size=(5, 7), dtype=np.int64).astype(np.int32)
+    bytes_view = qweight.view(np.uint8).reshape(5, 7, 4).transpose(0, 2, 1).reshape(20, 7)
+    assert np.array_equal(O.unpack_rows(qweight, 8), bytes_view)
+    qzeros = rng.integers(-2**31, 2**31 - 1, size=(3, 6), dtype=np.int64).astype(np.int32)
+    assert np.array_equal(O.unpack_cols(qzeros, 8), qzeros.view(np.uint8).reshape(3, 24))
+
+
+def test_qlinear_fp32_accumulate_and_bias():
+    c = O.make_gptq_case(256, 32, 3, bits=4, seed=5, bias=True)
+    w = O.dequantize_packed(c["qweight"], c["g_idx"], c["qzeros"], c["scales"], 4)
+    out = O.qlinear(c["x"], w, c["bias"])
+    ref = (c["x"].double() @ w.double() + c["bias"].double())
+    assert out.dtype == torch.float16
+    assert (out.double() - ref).abs().max() <= 2e-3 * ref.abs().max()
+
+
+def test_null_zeros_and_null_gidx_defaults():
+    c = O.make_gptq_case(128, 16, 1, bits=4, group_size=64, seed=9)
+    z = np.full((2, 16), 7, dtype=np.uint8)
+    a = O.dequantize_packed(c["qweight"], None, None, c["scales"], 4)
+    b = O.dequantize(O.unpack_rows(c["qweight"].numpy(), 4), np.arange(128) // 64, z, c["scales"])
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("size", [2, 4])
+def test_tensor_parallel_sharding_identities(size):
+    c = O.make_gptq_case(512, 64, 4, bits=4, seed=11)
+    w = O.dequantize_packed(c["qweight"], None, c["qzeros"], c["scales"], 4)
+    full = c["x"].float() @ w.float()
+    cols = []
+    for r in range(size):
+        qw, qz, s = O.shard_column(c["qweight"], c["qzeros"], c["scales"], 4, r, size)
+        cols.append(c["x"].float() @ O.dequantize_packed(qw.contiguous(), None, qz.contiguous(), s.contiguous(), 4).float())
+    assert torch.allclose(torch.cat(cols, dim=1), full, atol=1e-4)
+    part = torch.zeros_like(full)
+    ks = 512 // size
+    for r in range(size):
+        qw, qz, s = O.shard_row(c["qweight"], c["qzeros"], c["scales"], 4, r, size)
+        wr = O.dequantize_packed(qw.contiguous(), None, qz.contiguous(), s.contiguous(), 4)
+        part += c["x"][:, ks * r:ks * (r + 1)].float() @ wr.float()
+    assert torch.allclose(part, full, atol=1e-3)
