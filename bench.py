@@ -1,0 +1,348 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--m M]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (config.workload): the GPTQ int4 (group 128) linears of Llama-3-70B at decode batch
+M (default 1), tensor-parallel over N GPUs: per layer qkv (8192 -> 10240/N, column-parallel),
+o (8192/N -> 8192, row-parallel + all-reduce), fused gate/up (8192 -> 57344/N, column-parallel),
+down (28672/N -> 8192, row-parallel + all-reduce); 80 layers, distinct random weights per layer
+(35.6 GB at N=1, far larger than L2).  One step = one pass over all 80 layers.  Strong
+scaling: the total work is fixed, each rank holds 1/N of every weight.
+
+Metric: aggregate weight GB/s = packed weight bytes (qweight + qzeros + scales) of all ranks
+read per step / step time (device time, CUDA events, max over ranks).
+
+The reference arm (--impl reference) times the reference's dequantize-then-matmul restated on
+the host CPU (oracle/, torch with all host threads) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HIDDEN, INTER, Q_HEADS, KV_HEADS, HEAD_DIM, LAYERS, GROUP = 8192, 28672, 64, 8, 128, 80, 128
+BITS = 4
+
+
+def layer_shapes(tp: int):
+    """(name, K, N, kind) of one rank's four linears."""
+    qkv_n = (Q_HEADS + 2 * KV_HEADS) * HEAD_DIM
+    return [("qkv", HIDDEN, qkv_n // tp, "column"), ("o", HIDDEN // tp, HIDDEN, "row"),
+            ("gate_up", HIDDEN, 2 * INTER // tp, "column"), ("down", INTER // tp, HIDDEN, "row")]
+
+
+def weight_bytes(k: int, n: int, bits: int = BITS, gs: int = GROUP) -> int:
+    g = k // gs
+    return k * n * bits // 8 + g * n * 2 + g * n * bits // 8
+
+
+def algorithmic_bytes(m: int, k: int, n: int) -> int:
+    return weight_bytes(k, n) + 2 * m * k + 2 * m * n
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ---------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.path = f"/tmp/minit_b200_clocks_{os.getpid()}.csv"
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(index)], stdout=open(self.path, "w"),
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 6:
+                    continue
+                try:
+                    sm.append(float(parts[0])); mx.append(float(parts[1]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[2:6]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.remove(self.path)
+        except OSError:
+            pass
+        if sm:
+            busy = [s for s in sm if s > 0.5 * max(sm)]
+            out["sm_mhz"] = statistics.median(busy or sm)
+            out["sm_max_mhz"] = max(mx)
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# ---------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch.distributed as dist
+    import minit_b200 as M
+    from minit_b200 import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    comm = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        from minit_b200.distributed import DistributedCommunicator, initialize_world
+        from minit_b200.nccl import NCCLTensor
+        from minit_b200.nccl.library import exchange_unique_id
+        from minit_b200.nccl.dispatch import all_reduce_
+        initialize_world(rank, world)
+        uid = exchange_unique_id(rank)
+        version = NCCLTensor.connect(uid, rank, world, device=local_rank)
+        comm = DistributedCommunicator(version)
+
+    m = args.m
+    shapes = layer_shapes(world)
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    layers = []
+    for _ in range(args.layers):
+        lin = []
+        for name, k, n, kind in shapes:
+            qw = torch.randint(-2**31, 2**31 - 1, (k // 8, n), device=dev, dtype=torch.int64, generator=gen).to(torch.int32)
+            qz = torch.randint(-2**31, 2**31 - 1, (k // GROUP, n // 8), device=dev, dtype=torch.int64, generator=gen).to(torch.int32)
+            sc = (0.002 + 0.018 * torch.rand((k // GROUP, n), device=dev, generator=gen)).half()
+            lin.append((qw, qz, sc))
+        layers.append(lin)
+    # synthetic activations, one per distinct input width (N(0,1)); pinned host copies feed the e2e run
+    xs_host = [torch.randn((m, k), generator=torch.Generator().manual_seed(7 + i)).half().pin_memory()
+               for i, (_, k, _, _) in enumerate(shapes)]
+    xs = [x.to(dev) for x in xs_host]
+    outs = [torch.empty((m, n), dtype=torch.float16, device=dev) for _, _, n, _ in shapes]
+    out_host = torch.empty((m, HIDDEN), dtype=torch.float16).pin_memory()
+    flags = _lib.FLAG_PDL if args.pdl else 0
+
+    def one_pass():
+        for lin in layers:
+            for i, (qw, qz, sc) in enumerate(lin):
+                M.quantized_matrix_multiply(xs[i], qw, qz, sc, None, bits=BITS, out=outs[i], flags=flags)
+                if comm is not None and shapes[i][3] == "row":
+                    all_reduce_(comm.version, outs[i])
+
+    def one_pass_e2e():
+        for x, xh in zip(xs, xs_host):
+            x.copy_(xh, non_blocking=True)
+        one_pass()
+        out_host.copy_(outs[3], non_blocking=True)
+
+    def make_runner(fn):
+        if args.no_graph:
+            return fn, "eager"
+        try:
+            fn(); torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            return g.replay, "cuda_graph"
+        except Exception as e:  # noqa: BLE001  graph capture is an optimisation, eager is the same work
+            torch.cuda.synchronize()
+            if rank == 0:
+                print(f"[bench] graph capture unavailable ({type(e).__name__}); running eager", file=sys.stderr)
+            return fn, "eager"
+
+    def timed(fn, steps, warmup, sample_clocks=False):
+        for _ in range(warmup):
+            fn()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(local_rank) if sample_clocks else None
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        clocks = sampler.stop() if sampler else None
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps, clocks
+
+    runner, mode = make_runner(one_pass)
+    ms_step, clocks = timed(runner, args.steps, args.warmup, sample_clocks=True)
+    e2e_runner, e2e_mode = make_runner(one_pass_e2e)
+    ms_e2e, _ = timed(e2e_runner, args.steps, args.warmup)
+
+    per_rank_wbytes = args.layers * sum(weight_bytes(k, n) for _, k, n, _ in shapes)
+    per_rank_abytes = args.layers * sum(algorithmic_bytes(m, k, n) for _, k, n, _ in shapes)
+    total_wbytes = per_rank_wbytes * world
+    launches_per_step = args.layers * len(shapes)
+    hbm_peak, peak_kind = peaks()
+    achieved = per_rank_abytes / (ms_step * 1e-3) / 1e9     # per GPU: bytes of its launches / time of its launches
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if os.path.exists(tpath):
+        ratio = json.load(open(tpath)).get("qgemm_small_dram_bytes_per_algorithmic_byte")
+        if ratio:
+            traffic = ratio * per_rank_abytes / launches_per_step
+    line = {
+        "metric": "int4 dequant-GEMM weight GB/s at M=%d" % m, "value": total_wbytes / (ms_step * 1e-3) / 1e9, "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 (int4 weights, f32 accumulate)",
+        "data": "synthetic",
+        "config": {"workload": f"llama3-70b-gptq-int4-g128-decode-linears-tp{world}", "m": m, "layers": args.layers,
+                   "linears_per_layer": [[n_, k_, nn_] for n_, k_, nn_, _ in shapes], "launch": mode, "pdl": bool(args.pdl),
+                   "l2": "inputs larger than L2 (%.1f GB of weights per rank per step)" % (per_rank_wbytes / 1e9),
+                   "tokens_per_s": m / (ms_step * 1e-3)},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                     "traffic": traffic, "peak_source": peak_kind,
+                     "note": "per GPU, averaged over the %d launches of a step (algorithmic bytes / device time)" % launches_per_step},
+        "e2e": {"value": total_wbytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e, "launch": e2e_mode,
+                "h2d_bytes_per_step": sum(x.numel() * 2 for x in xs_host), "d2h_bytes_per_step": out_host.numel() * 2,
+                "note": "weights stay resident (loaded once, like model parameters); activations cross PCIe every step"},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(budget_s=20.0)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------
+# CPU arm: the oracle port (reference dequantize-then-matmul restated with torch on host cores)
+# ---------------------------------------------------------------------------------------
+def _cpu_sample(n_cols: int, m: int = 1, seed: int = 0):
+    from oracle import qlinear_oracle as O
+    gen = torch.Generator().manual_seed(seed)
+    k = HIDDEN
+    qw = torch.randint(-2**31, 2**31 - 1, (k // 8, n_cols), generator=gen, dtype=torch.int64).to(torch.int32)
+    qz = torch.randint(-2**31, 2**31 - 1, (k // GROUP, n_cols // 8), generator=gen, dtype=torch.int64).to(torch.int32)
+    sc = (0.002 + 0.018 * torch.rand((k // GROUP, n_cols), generator=gen)).half()
+    x = torch.randn((m, k), generator=gen).half()
+
+    def run():
+        w = O.dequantize_packed(qw, None, qz, sc, BITS)
+        return O.qlinear(x, w)
+    return run, weight_bytes(k, n_cols)
+
+
+def cpu_baseline(budget_s: float):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    run, nbytes = _cpu_sample(1024)
+    run()
+    t0 = time.perf_counter(); run(); dt = time.perf_counter() - t0
+    cols = int(max(1024, min(57344, (budget_s / 3 / max(dt, 1e-4)) * 1024)) // 1024 * 1024)
+    run, nbytes = _cpu_sample(cols)
+    run()
+    ts = []
+    for _ in range(2):
+        t0 = time.perf_counter(); run(); ts.append(time.perf_counter() - t0)
+    dt = statistics.median(ts)
+    return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+            "sample": f"dequantize-then-matmul (torch, fp32 accumulate) of one int4 g128 linear K=8192 N={cols} at M=1, "
+                      f"median of 2 runs of {dt:.2f} s"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    total = args.steps + args.warmup
+    run, _ = _cpu_sample(1024, args.m)
+    run()
+    t0 = time.perf_counter(); run(); dt = time.perf_counter() - t0
+    per_step = min(10.0, 150.0 / max(total, 1))
+    cols = int(max(1024, min(57344, (per_step / max(dt, 1e-4)) * 1024)) // 1024 * 1024)
+    run, nbytes = _cpu_sample(cols, args.m)
+    for _ in range(args.warmup):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        run()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = nbytes / dt / 1e9
+    sample = (f"each step = dequantize-then-matmul (oracle port of minit/quantize/dispatch.py:14-20 + fp32-accumulate matmul, "
+              f"torch on host cores) of one int4 g128 linear K=8192 N={cols} at M={args.m}")
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    print(json.dumps({
+        "impl": "reference", "metric": "int4 dequant-GEMM weight GB/s at M=%d" % args.m, "value": value, "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16 (int4 weights, f32 accumulate)", "data": "synthetic",
+        "config": {"workload": f"llama3-70b-gptq-int4-g128-decode-linears-tp{world}", "m": args.m},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--pdl", type=int, default=1)
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

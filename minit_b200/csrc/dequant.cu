@@ -36,7 +36,7 @@ dequant_kernel(const uint32_t* __restrict__ qweight, const int32_t* __restrict__
 #pragma unroll
         for (int j = 0; j < PACK; ++j) {
             const int kk = pr * PACK + j;
-            const int g = g_idx ? __ldg(g_idx + kk) : kk / gs;
+            const int g = g_idx ? min(max(__ldg(g_idx + kk), 0), groups - 1) : kk / gs;
             if (g != g_prev) {
                 g_prev = g;
                 const uint2 sv = __ldg(reinterpret_cast<const uint2*>(scales + (size_t)g * n + c));
@@ -76,7 +76,7 @@ dequant_unpacked_kernel(const uint8_t* __restrict__ q, const int32_t* __restrict
          idx += (long long)gridDim.x * blockDim.x) {
         const int kk = int(idx / (n >> 2));
         const int c = int(idx - (long long)kk * (n >> 2)) << 2;
-        const int g = g_idx ? __ldg(g_idx + kk) : kk / gs;
+        const int g = g_idx ? min(max(__ldg(g_idx + kk), 0), groups - 1) : kk / gs;
         const uint32_t qv = __ldg(reinterpret_cast<const uint32_t*>(q + (size_t)kk * n + c));
         const uint32_t zv = __ldg(reinterpret_cast<const uint32_t*>(z + (size_t)g * n + c));
         const uint2 sv = __ldg(reinterpret_cast<const uint2*>(scales + (size_t)g * n + c));

@@ -144,6 +144,7 @@ qgemm_small_kernel(const SmallParams p) {
     constexpr int XUNITS = ROWS * KC / 8;                 // 16-byte units in one staged x chunk
     constexpr int XPT = (XUNITS + THREADS - 1) / THREADS; // units per thread
     constexpr int SPG = ACT ? 1 : U / GPC;                // steps per group inside a chunk
+    constexpr int GPT = (KC + THREADS - 1) / THREADS;     // act-order: group ids each thread stages per chunk
 
     extern __shared__ __align__(16) unsigned char smem[];
     unsigned char* xs = smem;                              // [2][ROWS][PITCH]
@@ -179,7 +180,7 @@ qgemm_small_kernel(const SmallParams p) {
     uint2 sraw[GPC];
     uint32_t zraw[GPC];
     uint4 xreg[XPT];
-    int greg = 0;
+    int greg[GPT];
 
     auto load_weight = [&](int chunk, int u) {
         const int pr = chunk * (KC / PACK) + 4 * u + t;
@@ -205,7 +206,11 @@ qgemm_small_kernel(const SmallParams p) {
             else xreg[i] = make_uint4(0, 0, 0, 0);
         }
         if constexpr (ACT) {
-            if (tid < KC) { const int kk = chunk * KC + tid; greg = kk < p.k ? __ldg(p.g_idx + kk) : 0; }
+#pragma unroll
+            for (int i = 0; i < GPT; ++i) {   // out-of-range group ids are clamped, never dereferenced
+                const int kk = chunk * KC + tid + i * THREADS;
+                greg[i] = (tid + i * THREADS < KC && kk < p.k) ? min(max(__ldg(p.g_idx + kk), 0), p.groups - 1) : 0;
+            }
         }
     };
     auto store_x = [&](int buf) {
@@ -225,7 +230,11 @@ qgemm_small_kernel(const SmallParams p) {
                 *reinterpret_cast<uint4*>(dst + r * PITCH + u8 * 16) = v;
             }
         }
-        if constexpr (ACT) { if (tid < KC) gsm[buf * KC + tid] = greg; }
+        if constexpr (ACT) {
+#pragma unroll
+            for (int i = 0; i < GPT; ++i)
+                if (tid + i * THREADS < KC) gsm[buf * KC + tid + i * THREADS] = greg[i];
+        }
     };
 
     // ---- prologue: everything that does not depend on the previous kernel in the stream ----

@@ -1,0 +1,60 @@
+"""The tcgen05 prefill kernel (forced with MT_FLAG_FORCE_TC) through the C ABI against the oracle."""
+import pytest
+import torch
+
+from oracle import qlinear_oracle as O
+from tests.gpu_util import assert_close, oracle_out, to_dev
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def M(lib_built):
+    import minit_b200
+    return minit_b200
+
+
+def run(M, c, bits, bias=None, flags=2):
+    from minit_b200 import _lib
+    d = to_dev(c, DEV)
+    out = M.quantized_matrix_multiply(d["x"], d["qweight"], d["qzeros"], d["scales"], None, bits=bits,
+                                      bias=None if bias is None else bias.to(DEV), flags=flags)
+    torch.cuda.synchronize()
+    for ws in _lib._workspaces.values():
+        assert _lib.workspace_error_word(ws) == 0, "a bounded wait inside the tcgen05 kernel expired"
+    return out
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m", [64, 128, 256, 300, 1000])
+def test_tc_matches_oracle(M, bits, dtype, m):
+    c = O.make_gptq_case(1024, 512, m, bits=bits, dtype=dtype, seed=m)
+    assert_close(run(M, c, bits), oracle_out(c, False), f"tc bits={bits} {dtype} M={m}")
+
+
+@pytest.mark.parametrize("k,n", [(64, 128), (192, 136), (4096, 6144), (2048, 1000)])
+def test_tc_shapes_edges_bias(M, k, n):
+    c = O.make_gptq_case(k, n, 260, bits=4, group_size=64, seed=k + n, bias=True)
+    assert_close(run(M, c, 4, bias=c["bias"]), oracle_out(c, False, c["bias"]), f"tc {k}x{n}")
+
+
+def test_tc_many_tiles_per_cta_and_both_accumulators(M):
+    """More tiles than SMs so every persistent CTA loops and alternates its two TMEM accumulators."""
+    c = O.make_gptq_case(512, 128 * 40, 2048, bits=4, seed=9)
+    assert_close(run(M, c, 4), oracle_out(c, False), "tc 320 tiles")
+
+
+def test_tc_is_the_default_above_64_rows(M):
+    c = O.make_gptq_case(1024, 256, 200, bits=4, seed=2)
+    assert_close(run(M, c, 4, flags=0), oracle_out(c, False), "default dispatch M=200")
+
+
+def test_tc_prefill_shape_4096(M):
+    """Prefill config: (K,N) = (4096, 6144), M = 4096, bf16; oracle on 3 row blocks to bound CPU time."""
+    c = O.make_gptq_case(4096, 6144, 4096, bits=4, dtype=torch.bfloat16, seed=1)
+    out = run(M, c, 4).cpu()
+    w = O.dequantize_packed(c["qweight"], None, c["qzeros"], c["scales"], 4)
+    for r0 in (0, 2000, 3968):
+        assert_close(out[r0:r0 + 128], O.qlinear(c["x"][r0:r0 + 128], w), f"prefill rows {r0}")
