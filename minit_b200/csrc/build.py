@@ -1,6 +1,9 @@
 """Ahead-of-time build of libminit_b200.so (sm_100a only) with nvcc.
 
-    python -m minit_b200.build [--force] [--verbose]
+    python minit_b200/csrc/build.py [--force]
+
+(run as a script, or loaded by path: it must work while the library is missing or stale, so it
+does not import the minit_b200 package, whose import binds the library's symbols)
 
 Objects go to minit_b200/csrc/_obj/, the library to minit_b200/libminit_b200.so (in-tree, so
 it travels with the source tree; both are git-ignored).  A source is recompiled when it or any
@@ -14,8 +17,8 @@ import subprocess
 import sys
 from concurrent.futures import ThreadPoolExecutor
 
-HERE = os.path.dirname(os.path.abspath(__file__))
-CSRC = os.path.join(HERE, "csrc")
+CSRC = os.path.dirname(os.path.abspath(__file__))
+HERE = os.path.dirname(CSRC)
 OBJ = os.path.join(CSRC, "_obj")
 LIB = os.path.join(HERE, "libminit_b200.so")
 

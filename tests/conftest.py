@@ -15,6 +15,9 @@ def pytest_configure(config):
 @pytest.fixture(scope="session")
 def lib_built():
     """Builds libminit_b200.so if nvcc is present and it is stale; the package import fails loudly otherwise."""
-    from minit_b200 import build
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("minit_b200_build", os.path.join(ROOT, "minit_b200", "csrc", "build.py"))
+    build = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(build)
     build.build()
     return build.LIB
