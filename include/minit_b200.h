@@ -107,6 +107,30 @@ int mt_qgemm(void* stream, const void* x, const uint32_t* qweight, const int32_t
              void* workspace, size_t workspace_bytes, int flags);
 
 /*
+ * mt_qgemm for callers that cannot allocate.  No counterpart in the reference (its launcher
+ * needs no scratch because it accumulates with atomics into a pre-zeroed output).
+ *
+ * Same computation and argument meaning as mt_qgemm, always on the streaming kernel, but the
+ * split-K scratch is a fixed MT_STATIC_SCRATCH_BYTES array inside the library instead of a
+ * caller-supplied workspace; this call and everything under it allocates nothing.  It is meant
+ * for hosts that have given all device memory to their own pool (a later cudaMalloc by a
+ * library would fail) or that cannot tolerate the synchronisation an allocation implies inside
+ * a decode loop.  Every GPU that loads the library holds the array until the process exits.
+ *   - Limit: refused with MT_ERR_TOO_LARGE when mt_workspace_bytes(m, n, k, bits) exceeds
+ *     MT_STATIC_SCRATCH_BYTES (e.g. int4 K = N = 8192 fits, K = 8192 x N = 57344 does not).
+ *   - The first call on a device looks up the array's device address; make that first call
+ *     before starting any stream capture on that device.
+ *   - All calls on a device share the one array (it keeps the previous call's contents; the
+ *     part that must start at zero is cleared on `stream` by each call).  Two calls that can
+ *     overlap on the GPU -- different streams, no dependency -- race on it: serialise them.
+ *   - MT_FLAG_PDL and MT_FLAG_FORCE_TC are ignored.
+ */
+#define MT_STATIC_SCRATCH_BYTES (8u << 20)
+int mt_qgemm_static(void* stream, const void* x, const uint32_t* qweight, const int32_t* g_idx,
+                    const uint32_t* qzeros, const void* scales, const void* bias, void* out,
+                    int m, int n, int k, int nr_groups, int bits, int dtype, int flags);
+
+/*
  * out[M,N] = (x[M,K] @ float(w[K,N])) * scales[N] (+ bias[N]): int8 weight-only, one scale
  * per output channel.  This is the G = 1, g_idx = 0, stored-zero = 127, q = w + 128 special
  * case of the formula above (minit/quantize/dispatch.py:14-20) with w kept as plain int8

@@ -6,15 +6,15 @@ examples/qwen1_5_int8.py, minit.distributed / minit.nccl / minit.collective) on 
 tensors, with every kernel reached through the C ABI of libminit_b200.so.
 """
 from . import _lib  # noqa: F401  (fails loudly when the CUDA library is not built)
-from .qlinear import (QLinear, QLinearWithBias, W8Linear, quantized_matrix_multiply, unpack,
-                      w8_perchannel_matrix_multiply)
+from .qlinear import (QLinear, QLinearWithBias, W8Linear, quantized_matrix_multiply,
+                      quantized_matrix_multiply_noalloc, unpack, w8_perchannel_matrix_multiply)
 from .quantize import Dequantize, QuantizedTensor, dequantize
 from .operator.linalg import MatrixMultiply
 from .functional.linalg import matrix_multiply
 from .core.dispatch import dispatch, register_dispatch
 
 __all__ = [
-    "QLinear", "QLinearWithBias", "W8Linear", "quantized_matrix_multiply", "w8_perchannel_matrix_multiply",
+    "QLinear", "QLinearWithBias", "W8Linear", "quantized_matrix_multiply", "quantized_matrix_multiply_noalloc", "w8_perchannel_matrix_multiply",
     "unpack", "Dequantize", "QuantizedTensor", "dequantize", "MatrixMultiply", "matrix_multiply",
     "dispatch", "register_dispatch",
 ]

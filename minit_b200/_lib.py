@@ -16,7 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libminit_b200.so")
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
-        f"{LIB_PATH} is missing: build it with `python -m minit_b200.build` (needs nvcc). "
+        f"{LIB_PATH} is missing: build it with `python minit_b200/csrc/build.py` (needs nvcc). "
         "minit_b200 has no CPU or PyTorch fallback for its kernels.")
 
 lib = ctypes.CDLL(LIB_PATH)
@@ -24,6 +24,7 @@ lib = ctypes.CDLL(LIB_PATH)
 MT_F16, MT_BF16 = 0, 1
 FLAG_FORCE_SMALL, FLAG_FORCE_TC, FLAG_PDL = 1, 2, 4
 COUNTER_BYTES = 16384
+STATIC_SCRATCH_BYTES = 8 << 20
 
 _vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
 #: every symbol include/minit_b200.h declares: name -> (restype, argtypes)
@@ -35,6 +36,7 @@ SYMBOLS = {
     "mt_dequant_unpacked": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i]),
     "mt_unpack": (_i, [_vp, _vp, _vp, _i, _i, _i, _i]),
     "mt_qgemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _i]),
+    "mt_qgemm_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i]),
     "mt_w8_perchannel_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _i]),
     "mt_nccl_load": (_i, [ctypes.c_char_p]),
     "nccl_unique_id_size": (_sz, []),

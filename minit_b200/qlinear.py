@@ -83,6 +83,35 @@ def quantized_matrix_multiply(x: torch.Tensor, qweight: torch.Tensor, zeros: Opt
     return out
 
 
+def quantized_matrix_multiply_noalloc(x: torch.Tensor, qweight: torch.Tensor, zeros: Optional[torch.Tensor],
+                                      scales: torch.Tensor, groups: Optional[torch.Tensor], out: torch.Tensor, *,
+                                      bits: int = 8, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``quantized_matrix_multiply`` for programs that must not allocate device memory while
+    they run -- a server that handed the whole GPU to its own pool, or a decode loop that cannot
+    absorb an allocator's synchronisation.  The caller supplies ``out``; the scratch the kernel
+    needs lives in a fixed 8 MiB array inside the library, so neither this function nor the C
+    call under it allocates.  Shapes whose scratch would not fit raise (status -10); calls share
+    the array, so do not let two of them overlap on the GPU.  Call it once before any stream
+    capture on a device: the first call looks up the array's address."""
+    pack = 32 // bits
+    *ms, k0 = x.shape
+    n0 = qweight.shape[1]
+    if k0 != qweight.shape[0] * pack or tuple(scales.shape) != (scales.shape[0], n0) or scales.dtype != x.dtype:
+        raise ValueError("shape or dtype mismatch between x, qweight and scales")
+    if tuple(out.shape) != (*ms, n0) or out.dtype != x.dtype:
+        raise ValueError("out has the wrong shape or dtype")
+    dev = _lib.require_cuda(x, qweight, zeros, scales, groups, bias, out)
+    m = 1
+    for d in ms:
+        m *= d
+    with torch.cuda.device(dev):
+        rc = _lib.lib.mt_qgemm_static(_lib.current_stream(dev), x.data_ptr(), qweight.data_ptr(), _lib.ptr(groups),
+                                      _lib.ptr(zeros), scales.data_ptr(), _lib.ptr(bias), out.data_ptr(), m, n0, k0,
+                                      scales.shape[0], bits, _lib.dtype_code(x.dtype), 0)
+    _lib.check(rc, "mt_qgemm_static")
+    return out
+
+
 def w8_perchannel_matrix_multiply(x: torch.Tensor, weight: torch.Tensor, scales: torch.Tensor, *,
                                   bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                                   flags: int = 0) -> torch.Tensor:
