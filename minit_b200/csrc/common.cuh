@@ -112,6 +112,8 @@ int launch_dequant_unpacked(cudaStream_t st, const uint8_t* q, const int32_t* g_
 int launch_unpack(cudaStream_t st, const uint32_t* packed, uint8_t* out, int rows, int cols, int bits, int axis);
 int launch_small(cudaStream_t st, const QGemmArgs& a);          // GPTQ layout, M <= 64 per launch
 int launch_small_w8(cudaStream_t st, const QGemmArgs& a);       // int8 [K,N] per-channel, M <= 64 per launch
+int launch_dtc(cudaStream_t st, const QGemmArgs& a);            // tcgen05 decode kernel, M <= 32, contiguous groups
+bool dtc_supported(const QGemmArgs& a);
 int launch_tc(cudaStream_t st, const QGemmArgs& a);             // tcgen05 path (any M), GPTQ layout without g_idx
 bool tc_supported(const QGemmArgs& a);
 

@@ -177,8 +177,9 @@ qgemm_small_kernel(const SmallParams p) {
             for (int e = 0; e < 4; ++e) acc[j][s][e] = 0.f;
 
     uint4 w[U];              // register ring: w[u] is refilled with the next chunk's step u right after use
-    uint2 sraw[GPC];
-    uint32_t zraw[GPC];
+    // scales / zeros stream from HBM: fetched two chunks ahead (set A = this chunk, set B = the next)
+    uint2 sraw[GPC], sraw_b[GPC];
+    uint32_t zraw[GPC], zraw_b[GPC];
     uint4 xreg[XPT];
     int greg[GPT];
 
@@ -187,12 +188,13 @@ qgemm_small_kernel(const SmallParams p) {
         if (col_ok && pr < kp_total) w[u] = ldg_stream(p.qw + (size_t)pr * p.n + col);
         else w[u] = make_uint4(0, 0, 0, 0);
     };
-    auto load_scale = [&](int chunk, int q) {
+    auto load_scale = [&](int chunk, int q, uint2 (&sraw)[GPC], uint32_t (&zraw)[GPC]) {
         const int kk = chunk * KC + q * (KC / GPC);
         const int gi = min(kk / p.gs, p.groups - 1);
-        if (col_ok) {
+        if (col_ok && chunk < c_end) {
             sraw[q] = __ldg(reinterpret_cast<const uint2*>(sg + (size_t)gi * p.n + col));
-            zraw[q] = p.qz ? (__ldg(p.qz + (size_t)gi * (p.n / PACK) + col / PACK) >> ((col % PACK) * BITS)) : 0u;
+            // raw word: the shift happens when the value is consumed, so nothing waits on this load here
+            zraw[q] = p.qz ? __ldg(p.qz + (size_t)gi * (p.n / PACK) + col / PACK) : 0u;
         } else { sraw[q] = make_uint2(0, 0); zraw[q] = 0; }
     };
     auto load_x = [&](int chunk) {
@@ -243,7 +245,7 @@ qgemm_small_kernel(const SmallParams p) {
         for (int u = 0; u < U; ++u) load_weight(c_begin, u);
         if constexpr (!ACT) {
 #pragma unroll
-            for (int q = 0; q < GPC; ++q) load_scale(c_begin, q);
+            for (int q = 0; q < GPC; ++q) { load_scale(c_begin, q, sraw, zraw); load_scale(c_begin + 1, q, sraw_b, zraw_b); }
         }
     }
     if constexpr (ACT) {
@@ -288,8 +290,8 @@ qgemm_small_kernel(const SmallParams p) {
             uint32_t f[4][NF];
             if constexpr (!ACT) {
                 if (u % SPG == 0) {
-                    make_group_const<BITS, T>(gc, sraw[u / SPG], zraw[u / SPG], p.qz != nullptr, p.zp1_const);
-                    if (more) load_scale(c + 1, u / SPG);
+                    make_group_const<BITS, T>(gc, sraw[u / SPG], zraw[u / SPG] >> ((col % PACK) * BITS), p.qz != nullptr, p.zp1_const);
+                    load_scale(c + 2, u / SPG, sraw, zraw);   // the slot just consumed takes the chunk after next
                 }
 #pragma unroll
                 for (int i = 0; i < 4; ++i) dequant_word<BITS, T>(w4[i], gc, i, f[i]);
@@ -337,6 +339,13 @@ qgemm_small_kernel(const SmallParams p) {
                     mma16816<T>(acc[j][0], f[0][0], f[1][0], f[0][1], f[1][1], b.x, b.y);
                     mma16816<T>(acc[j][1], f[2][0], f[3][0], f[2][1], f[3][1], b.x, b.y);
                 }
+            }
+        }
+        if constexpr (!ACT) {   // rotate: set B (next chunk) becomes current, the refilled set A waits one more chunk
+#pragma unroll
+            for (int q = 0; q < GPC; ++q) {
+                const uint2 ts = sraw[q]; sraw[q] = sraw_b[q]; sraw_b[q] = ts;
+                const uint32_t tz = zraw[q]; zraw[q] = zraw_b[q]; zraw_b[q] = tz;
             }
         }
     }

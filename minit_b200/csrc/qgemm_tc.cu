@@ -22,8 +22,7 @@
 //               store out[m, n]; overlaps the next tile's main loop.
 // Every mbarrier wait is bounded; on expiry the kernel records a code in the error word
 // (last counter slot of the workspace) and every role leaves its loop.
-#include <cuda.h>
-#include "common.cuh"
+#include "tma.cuh"
 #include "qgemm_small.cuh"   // GroupConst / dequant_word
 
 namespace mt {
@@ -57,39 +56,6 @@ template <int BITS, int BM> struct TcSmem {
     static constexpr int TOTAL = OFF_BAR + 256 + 1024;   // barriers + slack for manual 1024-byte alignment
 };
 
-// ---- PTX wrappers ----------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: spins, then backs off with nanosleep; gives up after roughly a second.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (int i = 0; i < 4096; ++i) if (mbar_try_wait(bar, parity)) return true;
-    for (int i = 0; i < (1 << 22); ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        __nanosleep(128);
-    }
-    *abort_flag = 1;
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -218,17 +184,26 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
             const bool n_ok = n < p.n;
             int g_cur = -1;
             GroupConst<BITS, T> gc;
+            // scale / zero of the next two groups are already in flight when a group starts: a load
+            // that is waited for right away costs a DRAM round trip per group in every dequant thread
+            uint32_t sraw0 = 0, zraw0 = 0, sraw1 = 0, zraw1 = 0;
+            auto fetch = [&](int g, uint32_t& sr, uint32_t& zr) {
+                sr = 0; zr = 0;
+                if (n_ok && g < p.groups) {
+                    sr = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(sg) + (size_t)g * p.n + n);
+                    if (p.qz) zr = __ldg(p.qz + (size_t)g * (p.n / PACK) + n / PACK);
+                }
+            };
+            fetch(0, sraw0, zraw0);
+            fetch(1, sraw1, zraw1);
             for (int kb = 0; kb < kblocks; ++kb, ++it) {
                 const int s = it % TC_STAGES; const uint32_t ph = (it / TC_STAGES) & 1;
                 const int g = min((kb * TC_BK) / p.gs, p.groups - 1);
                 if (g != g_cur) {
                     g_cur = g;
-                    uint32_t sv = 0, zb = 0;
-                    if (n_ok) {
-                        sv = (uint32_t)reinterpret_cast<const uint16_t*>(sg)[(size_t)g * p.n + n];
-                        if (p.qz) zb = __ldg(p.qz + (size_t)g * (p.n / PACK) + n / PACK) >> ((n % PACK) * BITS);
-                    }
-                    make_group_const<BITS, T>(gc, make_uint2(sv, 0u), zb, p.qz != nullptr, p.zp1_const);
+                    make_group_const<BITS, T>(gc, make_uint2(sraw0, 0u), zraw0 >> ((n % PACK) * BITS), p.qz != nullptr, p.zp1_const);
+                    sraw0 = sraw1; zraw0 = zraw1;
+                    fetch(g + 2, sraw1, zraw1);
                 }
                 if (!mbar_wait(bar_full(s), ph, &abort_flag)) { ok = false; break; }
                 const uint32_t* q = reinterpret_cast<const uint32_t*>(smem + S::OFF_Q + s * S::Q_BYTES) + i;
@@ -301,11 +276,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
 }
 
 // ---- host side -------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode() {
+EncodeTiledFn get_tensor_map_encoder() {
     static EncodeTiledFn fn = nullptr;
     static bool tried = false;
     if (!tried) {
@@ -347,7 +318,7 @@ static int launch_tc_inst(cudaStream_t st, const QGemmArgs& a, const CUtensorMap
 }
 
 int launch_tc(cudaStream_t st, const QGemmArgs& a) {
-    EncodeTiledFn enc = get_encode();
+    EncodeTiledFn enc = get_tensor_map_encoder();
     if (!enc) return MT_ERR_UNSUPPORTED;
     const int pack = 32 / a.bits;
     const int bm = a.m > 128 ? 256 : (a.m > 64 ? 128 : 64);

@@ -1,4 +1,6 @@
-"""mt_qgemm (streaming small-M kernel) through the C ABI against the oracle.
+"""mt_qgemm decode kernels through the C ABI against the oracle: flags=1 forces the register-ring
+kernel (mma.sync), flags=8 the tcgen05 decode kernel (M <= 16, contiguous groups), flags=0 lets
+the library choose.
 Tolerance from the north star: max|out - ref| <= 1e-2 * rms(ref), ref = T(float(x) @ float(W_oracle))."""
 import numpy as np
 import pytest
@@ -23,18 +25,25 @@ def run(M, c, act, bits, bias=None, flags=1):
                                        bits=bits, bias=None if bias is None else bias.to(DEV), flags=flags)
 
 
+KERNELS = [0, 1, 8]
+
+
+@pytest.mark.parametrize("flags", KERNELS)
 @pytest.mark.parametrize("m", [1, 16])
-def test_config1_single_int4_linear(M, m):
+def test_config1_single_int4_linear(M, m, flags):
     c = O.make_gptq_case(4096, 4096, m, bits=4, seed=0)
-    assert_close(run(M, c, False, 4), oracle_out(c, False), f"cfg1 M={m}")
+    assert_close(run(M, c, False, 4, flags=flags), oracle_out(c, False), f"cfg1 M={m}")
 
 
 @pytest.mark.parametrize("bits", [4, 8])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 32, 33, 64])
-def test_batch_sizes_and_dtypes(M, bits, dtype, m):
+@pytest.mark.parametrize("flags", KERNELS)
+def test_batch_sizes_and_dtypes(M, bits, dtype, m, flags):
+    if flags == 8 and (m > 16 or (bits == 8 and dtype == torch.bfloat16)):
+        pytest.skip("outside the tcgen05 decode kernel's range")
     c = O.make_gptq_case(1024, 768, m, bits=bits, dtype=dtype, seed=m)
-    assert_close(run(M, c, False, bits), oracle_out(c, False), f"bits={bits} {dtype} M={m}")
+    assert_close(run(M, c, False, bits, flags=flags), oracle_out(c, False), f"bits={bits} {dtype} M={m}")
 
 
 @pytest.mark.parametrize("bits", [4, 8])
@@ -54,29 +63,36 @@ def test_config3_mistral_shapes_act_order(M, k, n, m):
 
 @pytest.mark.parametrize("gs", [32, 64, 128, 256, 1024])
 @pytest.mark.parametrize("bits", [4, 8])
-def test_group_sizes(M, gs, bits):
+@pytest.mark.parametrize("flags", KERNELS)
+def test_group_sizes(M, gs, bits, flags):
+    if flags == 8 and gs < 64:
+        pytest.skip("the tcgen05 decode kernel folds in units of 64 k")
     c = O.make_gptq_case(1024, 256, 5, bits=bits, group_size=gs, seed=gs)
-    assert_close(run(M, c, False, bits), oracle_out(c, False), f"group {gs} bits {bits}")
+    assert_close(run(M, c, False, bits, flags=flags), oracle_out(c, False), f"group {gs} bits {bits}")
 
 
 @pytest.mark.parametrize("k,n", [(32, 8), (96, 40), (1056, 8), (2080, 1000), (11008, 264)])
-def test_ragged_shapes(M, k, n):
+@pytest.mark.parametrize("flags", KERNELS)
+def test_ragged_shapes(M, k, n, flags):
     """K not a multiple of the 256-wide chunk, N not a multiple of the column tile."""
     gs = 32 if k % 128 else 128
+    if flags == 8 and gs < 64:
+        pytest.skip("the tcgen05 decode kernel folds in units of 64 k")
     c = O.make_gptq_case(k, n, 7, bits=4, group_size=gs, seed=k)
-    assert_close(run(M, c, False, 4), oracle_out(c, False), f"ragged {k}x{n}")
+    assert_close(run(M, c, False, 4, flags=flags), oracle_out(c, False), f"ragged {k}x{n}")
     c8 = O.make_gptq_case(k, n, 2, bits=8, group_size=gs, seed=k + 1)
-    assert_close(run(M, c8, False, 8), oracle_out(c8, False), f"ragged int8 {k}x{n}")
+    assert_close(run(M, c8, False, 8, flags=flags), oracle_out(c8, False), f"ragged int8 {k}x{n}")
 
 
-def test_bias_null_zeros_and_output_is_overwritten(M):
+@pytest.mark.parametrize("flags", KERNELS)
+def test_bias_null_zeros_and_output_is_overwritten(M, flags):
     c = O.make_gptq_case(512, 256, 4, bits=4, seed=77, bias=True)
-    out = run(M, c, False, 4, bias=c["bias"])
+    out = run(M, c, False, 4, bias=c["bias"], flags=flags)
     assert_close(out, oracle_out(c, False, c["bias"]), "bias")
     d = to_dev(c, DEV)
     ref0 = O.qlinear(c["x"], O.dequantize_packed(c["qweight"], None, None, c["scales"], 4))
     buf = torch.full((4, 256), 1000.0, dtype=torch.float16, device=DEV)   # garbage that must not be accumulated into
-    M.quantized_matrix_multiply(d["x"], d["qweight"], None, d["scales"], None, bits=4, out=buf, flags=1)
+    M.quantized_matrix_multiply(d["x"], d["qweight"], None, d["scales"], None, bits=4, out=buf, flags=flags)
     assert_close(buf, ref0, "null zeros / overwrite")
 
 
@@ -96,23 +112,35 @@ def test_m_above_64_tiles_through_the_small_kernel(M):
     assert_close(run(M, c, False, 4, flags=1), oracle_out(c, False), "M=150 forced small")
 
 
-def test_deterministic_and_workspace_left_clean(M):
+@pytest.mark.parametrize("flags", KERNELS)
+def test_deterministic_and_workspace_left_clean(M, flags):
     from minit_b200 import _lib
     c = O.make_gptq_case(8192, 512, 2, bits=4, seed=4)    # deep K -> split-K is active
-    a = run(M, c, False, 4)
-    b = run(M, c, False, 4)
+    a = run(M, c, False, 4, flags=flags)
+    b = run(M, c, False, 4, flags=flags)
     assert torch.equal(a, b)
     torch.cuda.synchronize()
     for ws in _lib._workspaces.values():
         assert int(ws[:_lib.COUNTER_BYTES].view(torch.int32).abs().sum().item()) == 0
 
 
-def test_pdl_launch_flag(M):
+@pytest.mark.parametrize("flags", KERNELS)
+def test_pdl_launch_flag(M, flags):
     c = O.make_gptq_case(2048, 512, 1, bits=4, seed=12)
     ref = oracle_out(c, False)
     for _ in range(3):
-        out = run(M, c, False, 4, flags=1 | 4)
+        out = run(M, c, False, 4, flags=flags | 4)
     assert_close(out, ref, "PDL launches back to back")
+
+
+def test_large_scales_and_small_x_stay_inside_tolerance(M):
+    """The tcgen05 decode kernel cancels a per-group offset in fp32; scales up to 1 and x values that
+    underflow when divided by 16 must not break the bound."""
+    c = O.make_gptq_case(4096, 256, 3, bits=4, seed=31, scale_lo=0.5, scale_hi=1.0)
+    assert_close(run(M, c, False, 4, flags=8), oracle_out(c, False), "large scales")
+    c = O.make_gptq_case(4096, 256, 3, bits=4, seed=32)
+    c["x"] = (c["x"].float() * 1e-4).half()
+    assert_close(run(M, c, False, 4, flags=8), oracle_out(c, False), "tiny x")
 
 
 def test_full_size_linearity_property(M):
