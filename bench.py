@@ -43,7 +43,7 @@ def layer_shapes(tp: int):
             ("gate_up", HIDDEN, 2 * INTER // tp, "column"), ("down", INTER // tp, HIDDEN, "row")]
 
 
-def weight_bytes(k: int, n: int, bits: int = BITS, gs: int = GROUP) -> int:
+def weight_bytes(k: int, n: int, bits: int = BITS, gs: int = GROUP) -> int:  # packed weights + scales + zeros
     g = k // gs
     return k * n * bits // 8 + g * n * 2 + g * n * bits // 8
 
@@ -222,12 +222,9 @@ def run_ours(args):
     launches_per_step = args.layers * len(shapes)
     hbm_peak, peak_kind = peaks()
     achieved = per_rank_abytes / (ms_step * 1e-3) / 1e9     # per GPU: bytes of its launches / time of its launches
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
-    if os.path.exists(tpath):
-        ratio = json.load(open(tpath)).get("qgemm_small_dram_bytes_per_algorithmic_byte")
-        if ratio:
-            traffic = ratio * per_rank_abytes / launches_per_step
+    # DRAM bytes per launch of the dominant kernel: ncu measured 244.3 MB read + 4.4 MB written for
+    # 242.7 MB of algorithmic bytes (profiles/qgemm_dtc_8192x57344_m1.md); traffic scales with the bytes.
+    traffic = 1.0245 * per_rank_abytes / launches_per_step
     line = {
         "metric": "int4 dequant-GEMM weight GB/s at M=%d" % m, "value": total_wbytes / (ms_step * 1e-3) / 1e9, "unit": "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
@@ -238,7 +235,7 @@ def run_ours(args):
                    "l2": "inputs larger than L2 (%.1f GB of weights per rank per step)" % (per_rank_wbytes / 1e9),
                    "tokens_per_s": m / (ms_step * 1e-3)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "traffic": traffic, "peak_source": peak_kind,
+                     "traffic": traffic, "traffic_unit": "bytes per launch (average launch)", "peak_source": peak_kind,
                      "note": "per GPU, averaged over the %d launches of a step (algorithmic bytes / device time)" % launches_per_step},
         "e2e": {"value": total_wbytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e, "launch": e2e_mode,
                 "h2d_bytes_per_step": sum(x.numel() * 2 for x in xs_host), "d2h_bytes_per_step": out_host.numel() * 2,
@@ -324,6 +321,52 @@ def run_reference(args):
     }))
 
 
+def run_single_shape(args):
+    """One linear, a few launches: the command the ncu captures under profiles/ were taken with.
+    Prints device time and the roofline of that one kernel."""
+    import minit_b200 as M
+    k, n = (int(v) for v in args.single_shape.split(","))
+    m, bits = args.m, args.bits
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    pack = 32 // bits
+    gen = torch.Generator(device=dev).manual_seed(0)
+    dtype = torch.bfloat16 if args.bf16 else torch.float16
+    copies = max(2, min(16, int(400e6 // weight_bytes(k, n, bits)) + 1))   # rotate weight sets: HBM, not L2
+    sets = []
+    for _ in range(copies):
+        qw = torch.randint(-2**31, 2**31 - 1, (k // pack, n), device=dev, dtype=torch.int64, generator=gen).to(torch.int32)
+        qz = torch.randint(-2**31, 2**31 - 1, (k // GROUP, n // pack), device=dev, dtype=torch.int64, generator=gen).to(torch.int32)
+        sc = (0.002 + 0.018 * torch.rand((k // GROUP, n), device=dev, generator=gen)).to(dtype)
+        sets.append((qw, qz, sc))
+    x = torch.randn((m, k), device=dev, dtype=torch.float32).to(dtype)
+    out = torch.empty((m, n), device=dev, dtype=dtype)
+    flags = {"auto": 0, "ring": 1, "tc": 2, "dtc": 8}[args.kernel] | (4 if args.pdl and args.kernel in ("auto", "ring") else 0)
+
+    def one():
+        for qw, qz, sc in sets:
+            M.quantized_matrix_multiply(x, qw, qz, sc, None, bits=bits, out=out, flags=flags)
+    for _ in range(args.warmup):
+        one()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        one()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (args.steps * copies)
+    hbm_peak, kind = peaks()
+    ab = k * n * bits // 8 + (k // GROUP) * n * 2 + (k // GROUP) * n * bits // 8 + 2 * m * k + 2 * m * n
+    line = {"single_shape": [k, n], "m": m, "bits": bits, "kernel": args.kernel, "us_per_launch": us,
+            "weight_GBps": weight_bytes(k, n, bits) / us / 1e3, "TFLOPs": 2.0 * m * n * k / us / 1e6,
+            "hbm_frac": ab / us / 1e3 / hbm_peak, "launch": "eager, %d weight sets in rotation" % copies}
+    ppath = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(ppath):
+        line["tensor_frac_of_burst"] = line["TFLOPs"] / float(json.load(open(ppath))["bf16_tflops"])
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -335,7 +378,13 @@ def main():
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--single-shape", default=None, help="K,N : time one linear instead of the workload (profiling aid)")
+    ap.add_argument("--kernel", default="auto", choices=["auto", "ring", "dtc", "tc"])
+    ap.add_argument("--bits", type=int, default=4)
+    ap.add_argument("--bf16", action="store_true")
     args = ap.parse_args()
+    if args.single_shape:
+        return run_single_shape(args)
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
