@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-linear hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--m M]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch M]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
 Workload (config.workload): the GPTQ int4 (group 128) linears of Llama-3-70B at decode batch
@@ -72,7 +72,7 @@ class ClockSampler:
         self.proc = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(index)], stdout=open(self.path, "w"),
+                                          "-lms", "20", "-i", str(index)], stdout=open(self.path, "w"),
                                          stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -129,6 +129,7 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     comm = None
+    far = None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         from minit_b200.distributed import DistributedCommunicator, initialize_world
@@ -139,6 +140,9 @@ def run_ours(args):
         uid = exchange_unique_id(rank)
         version = NCCLTensor.connect(uid, rank, world, device=local_rank)
         comm = DistributedCommunicator(version)
+        if args.allreduce == "fused":
+            from minit_b200.collective import FusedAllReduce
+            far = FusedAllReduce(m_max=max(16, args.m), n_max=HIDDEN)
 
     m = args.m
     shapes = layer_shapes(world)
@@ -163,6 +167,9 @@ def run_ours(args):
     def one_pass():
         for lin in layers:
             for i, (qw, qz, sc) in enumerate(lin):
+                if comm is not None and shapes[i][3] == "row" and far is not None:
+                    far.matmul(xs[i], qw, qz, sc, None, bits=BITS, out=outs[i], flags=flags)   # GEMM + all-reduce, one kernel
+                    continue
                 M.quantized_matrix_multiply(xs[i], qw, qz, sc, None, bits=BITS, out=outs[i], flags=flags)
                 if comm is not None and shapes[i][3] == "row":
                     all_reduce_(comm.version, outs[i])
@@ -231,7 +238,7 @@ def run_ours(args):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 (int4 weights, f32 accumulate)",
         "data": "synthetic",
         "config": {"workload": f"llama3-70b-gptq-int4-g128-decode-linears-tp{world}", "m": m, "layers": args.layers,
-                   "linears_per_layer": [[n_, k_, nn_] for n_, k_, nn_, _ in shapes], "launch": mode, "pdl": bool(args.pdl),
+                   "linears_per_layer": [[n_, k_, nn_] for n_, k_, nn_, _ in shapes], "launch": mode, "pdl": bool(args.pdl), "allreduce": (args.allreduce if world > 1 else "none"),
                    "l2": "inputs larger than L2 (%.1f GB of weights per rank per step)" % (per_rank_wbytes / 1e9),
                    "tokens_per_s": m / (ms_step * 1e-3)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
@@ -373,10 +380,12 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--batch", "--m", dest="m", type=int, default=1, help="decode batch M (use --batch under torchrun)")
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
+                    help="row-parallel exchange: fused into the GEMM epilogue over peer memory, or an NCCL all-reduce after it")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--single-shape", default=None, help="K,N : time one linear instead of the workload (profiling aid)")
     ap.add_argument("--kernel", default="auto", choices=["auto", "ring", "dtc", "tc"])

@@ -108,6 +108,29 @@ int mt_qgemm(void* stream, const void* x, const uint32_t* qweight, const int32_t
              void* workspace, size_t workspace_bytes, int flags);
 
 /*
+ * Row-parallel linear with the all-reduce fused into the GEMM epilogue: out[M,N] on EVERY rank =
+ * sum over ranks of (x_r[M,K_r] @ W_r[K_r,N]) (+ bias, pass it on one rank only).  Replaces the pair
+ * "local matmul, then Partial -> all_reduce" of the reference (minit/collective/dispatch.py:33-37,
+ * minit/collective/tensor.py:72-73, ncclAllReduce at minit/nccl/kernel.py:51-53) with one kernel:
+ * the thread that finishes four fp32 partials of a row pushes them, each paired with the call's
+ * sequence number, into its mailbox in every peer's symmetric buffer with plain peer stores, then
+ * polls (bounded; on expiry the workspace error word is set to 4) the peers' mailboxes in its own
+ * memory and sums over all ranks in rank order.  One NVLink crossing per value, no fence, no
+ * NCCL call, no multicast; results are bit-identical on all ranks.
+ *   peer_buffers  DEVICE array [world] of pointers: entry r is rank r's symmetric buffer as mapped
+ *                 into this process (entry `rank` is the local one).  Every buffer has buffer_bytes
+ *                 >= mt_allreduce_buffer_bytes(m_max, n_max, world) and must be zero before first use.
+ *   All ranks must issue the same sequence of calls on the same buffers; m <= 64 per call.
+ * world == 1 degenerates to mt_qgemm on the streaming kernel.
+ */
+int mt_qgemm_allreduce(void* stream, const void* x, const uint32_t* qweight, const int32_t* g_idx,
+                       const uint32_t* qzeros, const void* scales, const void* bias, void* out,
+                       int m, int n, int k, int nr_groups, int bits, int dtype,
+                       void* workspace, size_t workspace_bytes, int flags,
+                       void* const* peer_buffers, int rank, int world, size_t buffer_bytes);
+size_t mt_allreduce_buffer_bytes(int m_max, int n_max, int world);
+
+/*
  * mt_qgemm for callers that cannot allocate.  No counterpart in the reference (its launcher
  * needs no scratch because it accumulates with atomics into a pre-zeroed output).
  *

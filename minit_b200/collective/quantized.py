@@ -88,17 +88,21 @@ class RowParallelQLinear(Module):
     current stream.  The bias is added by rank 0 only, so the sum counts it once."""
 
     def __init__(self, communicator: Optional[DistributedCommunicator], qweight, qzeros, scales, g_idx, bits: int,
-                 bias=None, *, rank=None, size=None) -> None:
+                 bias=None, *, rank=None, size=None, fused=None) -> None:
         super().__init__()
         world = get_world()
         rank = world.rank if rank is None else rank
         size = world.size if size is None else size
         self.communicator = communicator
         self.size = size
+        self.fused = fused   # a collective.fused.FusedAllReduce: GEMM and all-reduce become one kernel
         qw, qz, s, gi = shard_gptq_row(qweight, qzeros, scales, bits, rank, size, g_idx)
         self.shard = ShardedQuantized("row", qw, qz, s, gi, bits, bias if rank == 0 else None)
 
     def forward(self, x, out=None, flags: int = 0, reduce: bool = True):
+        if reduce and self.size > 1 and self.fused is not None:
+            sh = self.shard
+            return self.fused.matmul(x, sh.qweight, sh.qzeros, sh.scales, sh.g_idx, bits=sh.bits, bias=sh.bias, out=out, flags=flags)
         partial = self.shard.local_matmul(x, out=out, flags=flags)
         if reduce and self.size > 1:
             return self.all_reduce(partial)

@@ -111,6 +111,10 @@ int launch_small(cudaStream_t st, const QGemmArgs& a) {
         p.nchunks = nchunks; p.chunks_per_split = pl.chunks_per_split; p.splits = pl.splits;
         p.zp1_const = 1 << (bits - 1);
         p.pdl = (a.flags & MT_FLAG_PDL) ? 1 : 0;
+        p.peers = a.ar_peers; p.rank = a.ar_rank; p.world = a.ar_peers ? a.ar_world : 1;
+        p.err = p.counters + (kMaxTiles - 1);
+        p.slot_bytes = a.ar_peers ? ((a.ar_bytes - kArDataOffset) / (2 * (size_t)p.world)) & ~(size_t)255 : 0;
+        if (p.world > 1 && (size_t)m * a.n * 8 > p.slot_bytes) return MT_ERR_TOO_LARGE;
         const size_t smem = (size_t)2 * mt * 8 * pitch + (act ? (size_t)a.groups * pl.wn * 32 * 4 + 2 * kc * 4 : 0);
         const int rc = fn(st, p, mt, pl.wn, gpc, act, dim3(pl.tiles, pl.splits), smem);
         if (rc != MT_OK) return rc;
@@ -255,6 +259,38 @@ int mt_qgemm(void* stream, const void* x, const uint32_t* qweight, const int32_t
     // (measured cross-over ~64 MB of packed weights at M <= 2); below that the register-ring kernel.
     if (m <= 2 && (size_t)k * n * bits / 8 >= ((size_t)64 << 20) && dtc_supported(a)) return launch_dtc(st, a);
     return launch_small(st, a);
+}
+
+int mt_qgemm_allreduce(void* stream, const void* x, const uint32_t* qweight, const int32_t* g_idx,
+                       const uint32_t* qzeros, const void* scales, const void* bias, void* out,
+                       int m, int n, int k, int nr_groups, int bits, int dtype,
+                       void* workspace, size_t workspace_bytes, int flags,
+                       void* const* peer_buffers, int rank, int world, size_t buffer_bytes) {
+    int rc = validate_gptq(qweight, qzeros, scales, n, k, nr_groups, bits, dtype);
+    if (rc != MT_OK) return rc;
+    if (m < 0 || m > 64 || k == 0) return MT_ERR_SHAPE;          // one launch: the exchange is per launch
+    if (world < 1 || world > kArMaxWorld || rank < 0 || rank >= world) return MT_ERR_SHAPE;
+    if (m == 0 || n == 0) return MT_OK;
+    if (!x || !out || (world > 1 && !peer_buffers)) return MT_ERR_NULL;
+    if (!aligned16(x) || !aligned16(out) || (bias && !aligned16(bias)) || (workspace && !aligned16(workspace))) return MT_ERR_ALIGN;
+    if (!g_idx && (k / nr_groups) % (4 * (32 / bits)) != 0) return MT_ERR_SHAPE;
+    if (world > 1 && buffer_bytes < kArDataOffset + 2 * (size_t)world * 256) return MT_ERR_WORKSPACE;
+    if ((rc = check_device()) != MT_OK) return rc;
+    QGemmArgs a = {};
+    a.x = x; a.qweight = qweight; a.g_idx = g_idx; a.qzeros = qzeros; a.scales = scales; a.bias = bias; a.out = out;
+    a.m = m; a.n = n; a.k = k; a.groups = nr_groups; a.bits = bits; a.dtype = dtype;
+    a.workspace = workspace; a.workspace_bytes = workspace_bytes; a.flags = flags;
+    if (world > 1) {
+        a.ar_peers = reinterpret_cast<unsigned char* const*>(peer_buffers);
+        a.ar_rank = rank; a.ar_world = world; a.ar_bytes = buffer_bytes;
+    }
+    return launch_small(static_cast<cudaStream_t>(stream), a);
+}
+
+size_t mt_allreduce_buffer_bytes(int m_max, int n_max, int world) {
+    if (m_max < 1 || n_max < 1 || world < 1 || world > kArMaxWorld) return 0;
+    const size_t slot = (((size_t)m_max * n_max * 8) + 255) & ~(size_t)255;   // 8-byte cells {value, epoch}
+    return kArDataOffset + 2 * (size_t)world * slot;
 }
 
 int mt_w8_perchannel_gemm(void* stream, const void* x, const int8_t* w, const void* scales,

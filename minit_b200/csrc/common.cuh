@@ -98,6 +98,10 @@ struct QGemmArgs {
     void* workspace;
     size_t workspace_bytes;
     int flags;
+    // fused all-reduce (row-parallel): device array of the ranks' symmetric buffers, or null
+    unsigned char* const* ar_peers;
+    int ar_rank, ar_world;
+    size_t ar_bytes;          // size of one symmetric buffer
 };
 
 // workspace layout: [0, kCounterBytes) tile counters (kept zero between launches),

@@ -43,6 +43,30 @@ def _worker(rank, size, port, results):
         ref = O.qlinear(h, w2, c2["bias"])
         ok, err, bound = O.tolerance_ok(y, ref, 2e-2)   # two chained linears + fp16 all-reduce: 2e-2 * rms
         assert ok, f"rank {rank}: err {err} > {bound}"
+        # the same row-parallel linear with the all-reduce fused into the GEMM epilogue (peer memory, no NCCL):
+        # several calls in a row (alternating slots), two shapes, bit-identical on all ranks
+        from minit_b200.collective import FusedAllReduce
+        far = FusedAllReduce(m_max=16, n_max=4096)
+        rowf = RowParallelQLinear(comm, g(c2, "qweight"), g(c2, "qzeros"), g(c2, "scales"), None, 4, bias=g(c2, "bias"), fused=far)
+        c3 = O.make_gptq_case(8192, 512, 1, bits=4, seed=3)
+        rowf3 = RowParallelQLinear(comm, g(c3, "qweight"), g(c3, "qzeros"), g(c3, "scales"), None, 4, fused=far)
+        ks3 = 8192 // size
+        x3 = g(c3, "x")[:, ks3 * rank:ks3 * (rank + 1)].contiguous()
+        ref3 = O.qlinear(c3["x"], O.dequantize_packed(c3["qweight"], None, c3["qzeros"], c3["scales"], 4))
+        for it in range(5):
+            yf = rowf(h_local * 0.05)
+            ok, err, bound = O.tolerance_ok(yf, ref, 2e-2)
+            assert ok, f"rank {rank} fused call {it}: err {err} > {bound}"
+            y3 = rowf3(x3)
+            ok, err, bound = O.tolerance_ok(y3, ref3, 1e-2)
+            assert ok, f"rank {rank} fused (split-K) call {it}: err {err} > {bound}"
+        gathered = [torch.empty_like(y3) for _ in range(size)]
+        dist.all_gather(gathered, y3)
+        assert all(torch.equal(gathered[0], t) for t in gathered), "fused all-reduce results differ between ranks"
+        from minit_b200 import _lib
+        torch.cuda.synchronize()
+        for ws in _lib._workspaces.values():
+            assert _lib.workspace_error_word(ws) == 0, "a bounded wait of the fused all-reduce expired"
         # the three collectives of the communicator
         t = torch.full((4, 8), float(rank + 1), device=dev, dtype=torch.float16)
         assert torch.equal(comm.all_reduce(t), torch.full_like(t, float(sum(range(1, size + 1)))))
