@@ -254,10 +254,11 @@ int mt_qgemm(void* stream, const void* x, const uint32_t* qweight, const int32_t
     if (flags & MT_FLAG_FORCE_TC) return tc_supported(a) ? launch_tc(st, a) : MT_ERR_UNSUPPORTED;
     if (flags & MT_FLAG_FORCE_SMALL) return launch_small(st, a);
     if (flags & MT_FLAG_FORCE_DTC) return dtc_supported(a) ? launch_dtc(st, a) : MT_ERR_UNSUPPORTED;
+    if (flags & MT_FLAG_FORCE_VEC) return vec_supported(a) ? launch_vec(st, a) : MT_ERR_UNSUPPORTED;
     if (m > 64 && tc_supported(a)) return launch_tc(st, a);
-    // Decode: the tcgen05 kernel wins once a launch streams enough bytes to amortise its set-up
-    // (measured cross-over ~64 MB of packed weights at M <= 2); below that the register-ring kernel.
-    if (m <= 2 && (size_t)k * n * bits / 8 >= ((size_t)64 << 20) && dtc_supported(a)) return launch_dtc(st, a);
+    // Decode at M <= 2: the CUDA-core GEMV (packed integers multiplied as fp16 subnormals) streams
+    // 1.5-2x faster than either tensor-core decode kernel on every shape measured.
+    if (m <= 2 && vec_supported(a)) return launch_vec(st, a);
     return launch_small(st, a);
 }
 

@@ -118,6 +118,8 @@ int launch_small(cudaStream_t st, const QGemmArgs& a);          // GPTQ layout, 
 int launch_small_w8(cudaStream_t st, const QGemmArgs& a);       // int8 [K,N] per-channel, M <= 64 per launch
 int launch_dtc(cudaStream_t st, const QGemmArgs& a);            // tcgen05 decode kernel, M <= 32, contiguous groups
 bool dtc_supported(const QGemmArgs& a);
+int launch_vec(cudaStream_t st, const QGemmArgs& a);            // CUDA-core decode GEMV, M <= 2, contiguous groups
+bool vec_supported(const QGemmArgs& a);
 int launch_tc(cudaStream_t st, const QGemmArgs& a);             // tcgen05 path (any M), GPTQ layout without g_idx
 bool tc_supported(const QGemmArgs& a);
 

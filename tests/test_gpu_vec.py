@@ -1,0 +1,117 @@
+"""Parity of the CUDA-core decode GEMV (M <= 2, MT_FLAG_FORCE_VEC) with the oracle, through the C ABI.
+
+The kernel multiplies the packed integers as fp16 subnormals against block-scaled activations and
+folds scale and zero point per chunk in fp32, so besides the usual shapes the cases cover what that
+scheme is sensitive to: activations with outliers, tiny and huge magnitudes, every fold chunk size,
+ragged warp runs (forced split-K factors) and bf16 activations.
+"""
+import pytest
+import torch
+
+from oracle import qlinear_oracle as O
+from tests.gpu_util import assert_close, to_dev
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def M(lib_built):
+    import minit_b200
+    return minit_b200
+
+VEC = 16
+
+
+def splits_flag(s):
+    return (s & 0xff) << 16
+
+
+def run(M, c, bits, bias=None, flags=VEC, zeros=True):
+    d = to_dev(c, DEV)
+    return M.quantized_matrix_multiply(d["x"], d["qweight"], d["qzeros"] if zeros else None, d["scales"], None,
+                                       bits=bits, bias=None if bias is None else bias.to(DEV), flags=flags)
+
+
+def ref(c, bits, bias=None, zeros=True):
+    w = O.dequantize_packed(c["qweight"], None, c["qzeros"] if zeros else None, c["scales"], bits)
+    return O.qlinear(c["x"], w, bias)
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m", [1, 2])
+@pytest.mark.parametrize("k,n", [(1024, 768), (4096, 4096), (8192, 512), (256, 128)])
+def test_shapes_dtypes(M, bits, dtype, m, k, n):
+    c = O.make_gptq_case(k, n, m, bits=bits, dtype=dtype, seed=k + n + m)
+    assert_close(run(M, c, bits), ref(c, bits), f"vec bits={bits} {dtype} M={m} {k}x{n}")
+
+
+@pytest.mark.parametrize("gs", [32, 64, 96, 128, 256, 1024])
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("m", [1, 2])
+def test_group_sizes(M, gs, bits, m):
+    k = 3072 if gs == 96 else 2048
+    c = O.make_gptq_case(k, 256, m, bits=bits, group_size=gs, seed=gs + m)
+    assert_close(run(M, c, bits), ref(c, bits), f"vec group {gs} bits {bits}")
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 5, 7])
+@pytest.mark.parametrize("k,gs", [(2080, 32), (4160, 64), (8192, 128)])
+def test_ragged_warp_runs(M, splits, k, gs):
+    """Chunk counts that do not divide by splits * 8: warp runs of unequal length, odd chunk counts."""
+    c = O.make_gptq_case(k, 384, 2, bits=4, group_size=gs, seed=k + splits)
+    assert_close(run(M, c, 4, flags=VEC | splits_flag(splits)), ref(c, 4), f"vec splits={splits} K={k}")
+
+
+def test_bias_null_zeros_overwrite(M):
+    c = O.make_gptq_case(2048, 256, 2, bits=4, seed=77, bias=True)
+    assert_close(run(M, c, 4, bias=c["bias"]), ref(c, 4, c["bias"]), "vec bias")
+    d = to_dev(c, DEV)
+    buf = torch.full((2, 256), 1000.0, dtype=torch.float16, device=DEV)
+    M.quantized_matrix_multiply(d["x"], d["qweight"], None, d["scales"], None, bits=4, out=buf, flags=VEC)
+    assert_close(buf, ref(c, 4, zeros=False), "vec null zeros / overwrite")
+    c8 = O.make_gptq_case(2048, 256, 1, bits=8, seed=78, bias=True)
+    assert_close(run(M, c8, 8, bias=c8["bias"], zeros=False), ref(c8, 8, c8["bias"], zeros=False), "vec int8 null zeros")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("kind", ["outliers", "tiny", "huge", "zeros", "one_hot"])
+def test_activation_ranges(M, dtype, kind):
+    """Block scaling of the activations: per-chunk maxima far apart, subnormal fp16 inputs, values near the
+    top of the fp16 range, all-zero chunks."""
+    c = O.make_gptq_case(4096, 256, 2, bits=4, dtype=dtype, seed=91)
+    x = c["x"].float()
+    if kind == "outliers":
+        x[:, ::257] *= 300.0
+    elif kind == "tiny":
+        x *= 2.0 ** -18
+    elif kind == "huge":
+        x *= 2000.0
+    elif kind == "zeros":
+        x[:, 512:2048] = 0.0
+    else:
+        x.zero_(); x[0, 1234] = 1.0; x[1, 7] = -3.0
+    c["x"] = x.to(dtype)
+    assert_close(run(M, c, 4), ref(c, 4), f"vec activations {kind} {dtype}")
+
+
+def test_deterministic_pdl_and_workspace_left_clean(M):
+    from minit_b200 import _lib
+    c = O.make_gptq_case(8192, 512, 2, bits=4, seed=4)
+    a = run(M, c, 4)
+    for _ in range(3):
+        b = run(M, c, 4, flags=VEC | 4)
+    assert torch.equal(a, b)
+    torch.cuda.synchronize()
+    for ws in _lib._workspaces.values():
+        assert int(ws[:_lib.COUNTER_BYTES].view(torch.int32).abs().sum().item()) == 0
+
+
+def test_unsupported_shapes_are_refused(M):
+    c = O.make_gptq_case(1024, 136, 1, bits=4, seed=2)       # N not a multiple of 128
+    with pytest.raises(RuntimeError):
+        run(M, c, 4)
+    c = O.make_gptq_case(1024, 128, 3, bits=4, seed=2)       # M > 2
+    with pytest.raises(RuntimeError):
+        run(M, c, 4)
