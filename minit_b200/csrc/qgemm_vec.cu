@@ -21,6 +21,7 @@
 //     last-arriver reduction as the streaming kernel.  The weight, scale and zero loads of the
 //     prologue do not depend on the previous kernel and are issued before griddepcontrol.wait.
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace mt {
 namespace {
@@ -29,6 +30,15 @@ constexpr int VEC_THREADS = 256;
 constexpr int VEC_WARPS = 8;
 constexpr int VEC_COLS = 128;   // columns per CTA
 constexpr int VEC_D = 8;        // packed rows in flight per thread
+
+// Optional phase timeline for tuning (compile with -DMT_VEC_TIMING): lane 0 of every warp stores
+// the global timer at eight points into the tail of the workspace.
+#ifdef MT_VEC_TIMING
+#define MT_TL(buf, idx, i) do { if ((threadIdx.x & 31) == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
+    reinterpret_cast<unsigned long long*>(buf)[(1 << 17) + (size_t)(idx) * 8 + (i)] = t_; } } while (0)
+#else
+#define MT_TL(buf, idx, i) do { } while (0)
+#endif
 
 struct VecParams {
     const void* x; const uint32_t* qw; const uint32_t* qz; const void* scales; const void* bias; void* out;
@@ -78,6 +88,8 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
 
     // this warp's run of chunks
     const int u = split * VEC_WARPS + warp;
+    const int tl_id = (blockIdx.y * gridDim.x + blockIdx.x) * VEC_WARPS + warp; (void)tl_id;
+    MT_TL(p.partial, tl_id, 0);
     const int c_lo = int((long long)u * p.nchunks / p.units);
     const int c_hi = int((long long)(u + 1) * p.nchunks / p.units);
     const int nks = (c_hi - c_lo) * CKS;
@@ -108,7 +120,9 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
     uint2 s0 = load_s(g), s1 = load_s(g + 1), s2 = load_s(g + 2);
     uint32_t z0 = load_z(g), z1 = load_z(g + 1), z2 = load_z(g + 2);
 
+    MT_TL(p.partial, tl_id, 1);
     if (p.pdl) { griddep_launch_dependents(); griddep_wait(); }
+    MT_TL(p.partial, tl_id, 2);
 
     // ---- stage the activations of this warp's run: block-scale, permute, fp16 ----
     unsigned char* xs_base = smem + (size_t)warp * MB * p.slice_ks * 16;
@@ -157,6 +171,7 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
         }
     }
     __syncwarp();
+    MT_TL(p.partial, tl_id, 3);
 
     // ---- main loop ----
     float sf[4], zf[4];
@@ -250,10 +265,12 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
     }
 
     // ---- reduce the 8 warps of the CTA, then the splits ----
+    MT_TL(p.partial, tl_id, 4);
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb)
         *reinterpret_cast<float4*>(red + ((size_t)warp * MB + mb) * VEC_COLS + lane * 4) = make_float4(acc[mb][0], acc[mb][1], acc[mb][2], acc[mb][3]);
     __syncthreads();
+    MT_TL(p.partial, tl_id, 5);
     const int mb_r = tid / VEC_COLS, cc = tid % VEC_COLS;
     const bool active = mb_r < MB && mb_r < p.m;
     float v = 0.f;
@@ -276,6 +293,7 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
     __syncthreads();
     if (tid == 0) s_last = (atomicAdd(p.counters + tile, 1u) == unsigned(p.splits - 1));
     __syncthreads();
+    MT_TL(p.partial, tl_id, 6);
     if (!s_last) return;
     __threadfence();
     if (active) {
@@ -285,6 +303,423 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
         out[(size_t)mb_r * p.n + gc] = H::from_float(sum);
     }
     if (tid == 0) p.counters[tile] = 0;
+    MT_TL(p.partial, tl_id, 7);
+}
+
+
+// ----------------------------------------------------------------------------------------------
+// Stream-K variant: the same arithmetic, a different schedule.
+//
+// The (column block, chunk) units of the whole problem are laid out in one line, column block
+// major, and cut into equal runs, one per WARP; the grid is one CTA per SM whatever the shape, so
+// there is no wave quantisation and no split-K factor to pick.  Warps never synchronise with one
+// another: a lane copies its own 16 bytes of every packed row with cp.async into a shared-memory
+// ring (D rows deep, so the bytes in flight do not cost registers) and reads them back itself.  A
+// run that ends inside a column block leaves an fp32 partial row; the last warp to arrive at a
+// column block adds the partials in warp order (deterministic) and writes the output.
+// The activations are staged just in time: 32 k-steps (256 values of k) per warp, double
+// buffered, the global load issued two blocks ahead.
+// A CTA uses half of an SM (registers, shared memory), and the kernel releases its dependents
+// at once: under programmatic dependent launch the next kernel's CTAs become resident beside this
+// one's, fill their rings with weights and wait, so the stream does not stop between kernels.
+// ----------------------------------------------------------------------------------------------
+struct StreamParams {
+    const void* x; const uint32_t* qw; const uint32_t* qz; const void* scales; const void* bias; void* out;
+    unsigned* counters; float* partial;
+    int m, n, k, groups;
+    int cpg, nchunks, tiles;
+    int units;         // tiles * nchunks
+    int warps;         // warps that get a run (<= units)
+    int per, rem;      // units / warps, units % warps: the first `rem` warps get per + 1 units
+    int zp1_const;
+    int pdl;
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int sz = valid ? 16 : 0;   // 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr)); return v;
+}
+
+template <int BITS, typename T, int MB, int CK, int NW, int D, int MINB>
+__global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const StreamParams p) {
+    using H = F16x2<T>;
+    constexpr int PACK = 32 / BITS;
+    constexpr int RPK = 8 / PACK;            // packed rows per k-step (8 values of k)
+    constexpr int CKS = CK / 8;              // k-steps per chunk
+    constexpr int CRW = CKS * RPK;           // packed rows per chunk
+    constexpr int BODY = D > 16 ? D : 16;    // packed rows per unrolled body
+    constexpr int RG = 4;                    // packed rows per cp.async group
+    constexpr int NG = D / RG;               // groups in flight
+    constexpr int XB = 32;                   // k-steps per activation block
+    constexpr uint32_t MASK_LO = BITS == 4 ? 0x000f000fu : 0x00ff00ffu;
+    constexpr uint32_t MASK_HI = 0x00f000f0u;
+    static_assert(D % RG == 0 && BODY % D == 0, "ring depth");
+
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // partial rows of column blocks that this warp shares with others: at most two per warp (the
+    // block its run starts in and the block it ends in), combined across the CTA before they leave it
+    __shared__ __align__(16) float seg[NW * 2 * MB * VEC_COLS];
+    __shared__ int seg_tile[NW * 2];
+    if (p.pdl) griddep_launch_dependents();
+    const int j = blockIdx.x * NW + warp;
+    const bool idle = j >= p.warps;
+    MT_TL(p.partial, j, 0);
+
+    const int u0 = idle ? 0 : j * p.per + (j < p.rem ? j : p.rem);
+    const int nun = idle ? 0 : p.per + (j < p.rem ? 1 : 0);   // chunks of this warp's run (0: no run, the warp only joins the CTA's combine step)
+    int tile = u0 / p.nchunks;
+    const int c_first = u0 - tile * p.nchunks;
+    const int total_rows = nun * CRW;
+    const int total_ks = nun * CKS;
+
+    // ---- shared memory: weight ring | per-warp activation blocks | per-warp block meta ----
+    const uint32_t ring_s = smem_u32(smem) + uint32_t(tid) * 16;                       // + slot * NW*32*16
+    constexpr uint32_t SLOT_BYTES = NW * 32 * 16;
+    unsigned char* xw = smem + (size_t)D * SLOT_BYTES + (size_t)warp * (2 * MB * XB * 16);
+    float2* metaw = reinterpret_cast<float2*>(smem + (size_t)D * SLOT_BYTES + (size_t)NW * (2 * MB * XB * 16)) + (size_t)warp * (2 * MB * (XB / CKS));
+    const uint32_t xw_s = smem_u32(xw);
+
+    // ---- activations: block b covers k-steps [32b, 32b+32) of the run, lane = k-step ----
+    const T* xg = reinterpret_cast<const T*>(p.x);
+    auto load_x = [&](int b, uint4 (&xr)[MB]) {
+        const int ks = b * XB + lane;
+        const bool ok = ks < total_ks;
+        const int cl = (c_first + ks / CKS) % p.nchunks;               // chunk inside K
+        const size_t k = (size_t)cl * CK + (size_t)(ks % CKS) * 8;
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb)
+            xr[mb] = (ok && mb < p.m) ? __ldg(reinterpret_cast<const uint4*>(xg + (size_t)mb * p.k + k)) : make_uint4(0, 0, 0, 0);
+    };
+    auto stage_x = [&](int b, const uint4 (&xr)[MB]) {
+        const int buf = b & 1;
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+            float f[8];
+            const uint32_t rw[4] = {xr[mb].x, xr[mb].y, xr[mb].z, xr[mb].w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                f[2 * q] = H::to_float(uint16_t(rw[q] & 0xffff));
+                f[2 * q + 1] = H::to_float(uint16_t(rw[q] >> 16));
+            }
+            float amax = 0.f, sum = 0.f;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) { amax = fmaxf(amax, fabsf(f[q])); sum += f[q]; }
+#pragma unroll
+            for (int o = 1; o < CKS; o <<= 1) {
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            }
+            int e = 0;
+            if (amax > 0.f && amax < 3.0e38f) e = 14 - (int((__float_as_uint(amax) >> 23) & 0xff) - 127);
+            e = e < -100 ? -100 : (e > 100 ? 100 : e);
+            const float up = __uint_as_float(uint32_t(127 + e) << 23);
+            const float post = __uint_as_float(uint32_t(127 + 24 - e) << 23);
+            uint4 o4;
+            if constexpr (BITS == 4) {
+                const float dn = up * 0.0625f;
+                o4.x = pack_h2(f[0] * up, f[4] * up); o4.y = pack_h2(f[1] * dn, f[5] * dn);
+                o4.z = pack_h2(f[2] * up, f[6] * up); o4.w = pack_h2(f[3] * dn, f[7] * dn);
+            } else {
+                o4.x = pack_h2(f[0] * up, f[2] * up); o4.y = pack_h2(f[1] * up, f[3] * up);
+                o4.z = pack_h2(f[4] * up, f[6] * up); o4.w = pack_h2(f[5] * up, f[7] * up);
+            }
+            *reinterpret_cast<uint4*>(xw + ((size_t)(buf * MB + mb) * XB + lane) * 16) = o4;
+            if ((lane % CKS) == 0) metaw[(buf * MB + mb) * (XB / CKS) + lane / CKS] = make_float2(post, sum);
+        }
+    };
+    // The weight prefetch comes before the wait for the previous kernel: the activation loads then
+    // queue behind 64 KB of weight requests per CTA, but a CTA that becomes resident early fills its
+    // ring during the previous kernel's tail (measured: waiting first costs 1-2 us per launch).
+    uint4 xr[MB], xr0[MB];
+
+    // ---- weight copies: issue iterator runs D rows ahead of the consumer ----
+    const size_t rstride = size_t(p.n) / 4;
+    const uint4* qbase = reinterpret_cast<const uint4*>(p.qw) + lane;
+    const uint4* it_ptr = qbase + (size_t)tile * (VEC_COLS / 4) + (size_t)c_first * CRW * rstride;
+    int it_rows = (p.nchunks - c_first) * CRW;
+    int it_tile = tile;
+    int issued = 0;
+    auto issue = [&](int slot) {
+        const bool valid = issued < total_rows;
+        cp_async16(ring_s + uint32_t(slot) * SLOT_BYTES, valid ? it_ptr : qbase, valid);
+        ++issued;
+        it_ptr += rstride;
+        if (--it_rows == 0) { ++it_tile; it_ptr = qbase + (size_t)it_tile * (VEC_COLS / 4); it_rows = p.nchunks * CRW; }
+    };
+#pragma unroll
+    for (int gq = 0; gq < NG; ++gq) {
+#pragma unroll
+        for (int r = 0; r < RG; ++r) issue(gq * RG + r);
+        cp_async_commit();
+    }
+
+    // ---- scales / zero points: current group converted, next two raw ----
+    const T* sc = reinterpret_cast<const T*>(p.scales);
+    int g = c_first / p.cpg;
+    int left = p.cpg - (c_first - g * p.cpg);
+    const int zshift = (lane & (PACK / 4 - 1)) * (4 * BITS);
+    int pf_tile = tile, pf_g = g;
+    auto pf_advance = [&]() { if (++pf_g == p.groups) { pf_g = 0; ++pf_tile; } };
+    auto load_s = [&]() -> uint2 {
+        const int tt = pf_tile < p.tiles ? pf_tile : p.tiles - 1;
+        return __ldg(reinterpret_cast<const uint2*>(sc + (size_t)pf_g * p.n + tt * VEC_COLS + lane * 4));
+    };
+    auto load_z = [&]() -> uint32_t {
+        if (!p.qz) return 0u;
+        const int tt = pf_tile < p.tiles ? pf_tile : p.tiles - 1;
+        return __ldg(p.qz + (size_t)pf_g * (p.n / PACK) + (tt * VEC_COLS + lane * 4) / PACK);
+    };
+    uint2 s0 = load_s(); uint32_t z0 = load_z(); pf_advance();
+    uint2 s1 = load_s(); uint32_t z1 = load_z(); pf_advance();
+    uint2 s2 = load_s(); uint32_t z2 = load_z();
+
+    MT_TL(p.partial, j, 1);
+    if (p.pdl) griddep_wait();
+    load_x(0, xr0);
+    load_x(1, xr);
+    MT_TL(p.partial, j, 2);
+
+    stage_x(0, xr0);
+    MT_TL(p.partial, j, 3);
+
+    float sf[4], zf[4];
+    auto convert = [&](uint2 s, uint32_t z) {
+        sf[0] = H::to_float(uint16_t(s.x & 0xffff)); sf[1] = H::to_float(uint16_t(s.x >> 16));
+        sf[2] = H::to_float(uint16_t(s.y & 0xffff)); sf[3] = H::to_float(uint16_t(s.y >> 16));
+        if (p.qz) {
+            const uint32_t zz = z >> zshift;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) zf[c] = float(int((zz >> (BITS * c)) & ((1u << BITS) - 1u)) + 1);
+        } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) zf[c] = float(p.zp1_const);
+        }
+    };
+    convert(s0, z0);
+
+    float acc[MB][4];
+#pragma unroll
+    for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[mb][c] = 0.f;
+    uint32_t a[MB][4][4];
+
+    const T* bias = reinterpret_cast<const T*>(p.bias);
+    uint16_t* out = reinterpret_cast<uint16_t*>(p.out);
+    auto write_out = [&](int t, const float4 (&r)[MB]) {
+        const int colb = t * VEC_COLS + lane * 4;
+        float b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
+        if (bias) {
+            const uint2 bv = __ldg(reinterpret_cast<const uint2*>(bias + colb));
+            b0 = H::to_float(uint16_t(bv.x & 0xffff)); b1 = H::to_float(uint16_t(bv.x >> 16));
+            b2 = H::to_float(uint16_t(bv.y & 0xffff)); b3 = H::to_float(uint16_t(bv.y >> 16));
+        }
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb)
+            if (mb < p.m) {
+                uint2 o; o.x = H::pack(r[mb].x + b0, r[mb].y + b1); o.y = H::pack(r[mb].z + b2, r[mb].w + b3);
+                *reinterpret_cast<uint2*>(out + (size_t)mb * p.n + colb) = o;
+            }
+    };
+    // first and last warp with a run in column block t
+    auto owner = [&](int u) -> int {
+        const int big = p.rem * (p.per + 1);              // units held by the warps with per + 1
+        return u < big ? u / (p.per + 1) : p.rem + (u - big) / p.per;
+    };
+    auto owners = [&](int t, int& jf, int& jl) {
+        jf = owner(t * p.nchunks);
+        jl = owner(t * p.nchunks + p.nchunks - 1);
+    };
+    int nseg = 0;
+    // the finished part of column block `tile`: written out if no other warp has a share in the
+    // block, else parked in shared memory for the CTA's combine step
+    auto flush = [&]() {
+        int jf, jl;
+        owners(tile, jf, jl);
+        float4 r[MB];
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) r[mb] = make_float4(acc[mb][0], acc[mb][1], acc[mb][2], acc[mb][3]);
+        if (jf == jl) {
+            write_out(tile, r);
+        } else {
+            const int slot = warp * 2 + (nseg < 1 ? nseg : 1);
+#pragma unroll
+            for (int mb = 0; mb < MB; ++mb)
+                *reinterpret_cast<float4*>(seg + ((size_t)slot * MB + mb) * VEC_COLS + lane * 4) = r[mb];
+            if (lane == 0) seg_tile[slot] = tile;
+            ++nseg;
+        }
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[mb][c] = 0.f;
+    };
+
+    // ---- main loop: BODY packed rows per trip ----
+    int chunks_todo = nun;
+    bool dirty = false, done = idle;
+    for (int body = 0; !done; ++body) {
+        const int ks_body = body * (BODY / RPK);          // first k-step of this body
+        if ((ks_body % XB) == 0) {
+            // entering activation block b: stage block b+1 (loaded one block ago), start the load of b+2
+            const int b = ks_body / XB;
+            __syncwarp();                                 // every lane is done reading block b-1, whose buffer is rewritten
+            stage_x(b + 1, xr);
+            load_x(b + 2, xr);
+            __syncwarp();
+        }
+        const int buf = (ks_body / XB) & 1;
+        const uint32_t xs_s = xw_s + uint32_t(buf * MB * XB + (ks_body % XB)) * 16;
+        const float2* meta = metaw + buf * MB * (XB / CKS) + (ks_body % XB) / CKS;
+#pragma unroll
+        for (int rb = 0; rb < BODY; ++rb) {
+            if (rb % RG == 0) cp_async_wait<NG - 1>();
+            const int slot = rb % D;
+            const int kj = rb / RPK, rr = rb % RPK;          // k-step inside the body, row inside the k-step
+            const uint4 wv = lds128(ring_s + uint32_t(slot) * SLOT_BYTES);
+            uint4 xv[MB];
+#pragma unroll
+            for (int mb = 0; mb < MB; ++mb) xv[mb] = lds128(xs_s + uint32_t(mb * XB + kj) * 16);
+            const bool first = (kj % CKS) == 0;
+            const uint32_t q4[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t q = q4[c], q8 = q >> 8;
+#pragma unroll
+                for (int mb = 0; mb < MB; ++mb) {
+                    if constexpr (BITS == 4) {
+                        const uint32_t w0 = q & MASK_LO, w1 = q & MASK_HI, w2 = q8 & MASK_LO, w3 = q8 & MASK_HI;
+                        if (first) {
+                            a[mb][c][0] = hmul2(w0, xv[mb].x); a[mb][c][1] = hmul2(w1, xv[mb].y);
+                            a[mb][c][2] = hmul2(w2, xv[mb].z); a[mb][c][3] = hmul2(w3, xv[mb].w);
+                        } else {
+                            a[mb][c][0] = hfma2(w0, xv[mb].x, a[mb][c][0]); a[mb][c][1] = hfma2(w1, xv[mb].y, a[mb][c][1]);
+                            a[mb][c][2] = hfma2(w2, xv[mb].z, a[mb][c][2]); a[mb][c][3] = hfma2(w3, xv[mb].w, a[mb][c][3]);
+                        }
+                    } else {
+                        const uint32_t w0 = q & MASK_LO, w1 = q8 & MASK_LO;
+                        const uint32_t x0 = rr == 0 ? xv[mb].x : xv[mb].z, x1 = rr == 0 ? xv[mb].y : xv[mb].w;
+                        if (first) {
+                            a[mb][c][2 * rr] = hmul2(w0, x0); a[mb][c][2 * rr + 1] = hmul2(w1, x1);
+                        } else {
+                            a[mb][c][2 * rr] = hfma2(w0, x0, a[mb][c][2 * rr]); a[mb][c][2 * rr + 1] = hfma2(w1, x1, a[mb][c][2 * rr + 1]);
+                        }
+                    }
+                }
+            }
+            if (rb % RG == RG - 1) {
+                // the four rows of this group are in registers: refill their slots
+#pragma unroll
+                for (int r = 0; r < RG; ++r) issue((rb - (RG - 1) + r) % D);
+                cp_async_commit();
+            }
+            if (rr == RPK - 1 && (kj + 1) % CKS == 0) {
+                if (!done) {
+                    // ---- fold the chunk that ends here ----
+                    const int ci = kj / CKS;
+#pragma unroll
+                    for (int mb = 0; mb < MB; ++mb) {
+                        const float2 mt2 = meta[mb * (XB / CKS) + ci];   // (2^(24-e), sum of x)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const float f = h2sum(hadd2(hadd2(a[mb][c][0], a[mb][c][1]), hadd2(a[mb][c][2], a[mb][c][3])));
+                            const float t = fmaf(f, mt2.x, -zf[c] * mt2.y);
+                            acc[mb][c] = fmaf(sf[c], t, acc[mb][c]);
+                        }
+                    }
+                    dirty = true;
+                    if (--left == 0) {
+                        left = p.cpg;
+                        if (++g == p.groups) { flush(); dirty = false; g = 0; ++tile; }
+                        convert(s1, z1);
+                        s1 = s2; z1 = z2;
+                        pf_advance();
+                        s2 = load_s(); z2 = load_z();
+                    }
+                    if (--chunks_todo == 0) {
+                        if (dirty) flush();
+                        done = true;
+                    }
+                }
+            }
+        }
+    }
+    MT_TL(p.partial, j, 4);
+    cp_async_wait<0>();
+
+    // ---- combine the shared partial rows: CTA first, then across CTAs ----
+    if (lane == 0) {
+        if (nseg < 1) seg_tile[warp * 2] = -1;
+        if (nseg < 2) seg_tile[warp * 2 + 1] = -1;
+    }
+#ifdef MT_VEC_TIMING
+    if (lane == 0) { unsigned smid_; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid_)); reinterpret_cast<unsigned long long*>(p.partial)[(1 << 17) + (size_t)j * 8 + 5] = smid_ + 1; }
+#endif
+    __syncthreads();
+    MT_TL(p.partial, j, 6);
+    const int cta = blockIdx.x;
+    for (int q = 0; q < 2; ++q) {
+        const int slot = warp * 2 + q;
+        const int t = seg_tile[slot];
+        if (t < 0) continue;
+        bool lead = true;                                   // the first slot of the CTA that holds this column block does the sum
+        for (int s2i = 0; s2i < slot; ++s2i) lead = lead && seg_tile[s2i] != t;
+        if (!lead) continue;
+        float4 r[MB];
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) r[mb] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s2i = slot; s2i < NW * 2; ++s2i) {
+            if (seg_tile[s2i] != t) continue;
+#pragma unroll
+            for (int mb = 0; mb < MB; ++mb) {
+                const float4 v = *reinterpret_cast<const float4*>(seg + ((size_t)s2i * MB + mb) * VEC_COLS + lane * 4);
+                r[mb].x += v.x; r[mb].y += v.y; r[mb].z += v.z; r[mb].w += v.w;
+            }
+        }
+        int jf, jl;
+        owners(t, jf, jl);
+        const int cf = jf / NW, cl = jl / NW;               // first and last CTA with a share in the block
+        bool write = true;
+        if (cf != cl) {
+#pragma unroll
+            for (int mb = 0; mb < MB; ++mb)
+                if (mb < p.m) __stcg(reinterpret_cast<float4*>(p.partial + ((size_t)(cta + t) * MB + mb) * VEC_COLS + lane * 4), r[mb]);
+            __threadfence();
+            __syncwarp();
+            unsigned old = 0;
+            if (lane == 0) old = atomicAdd(p.counters + t, 1u);
+            old = __shfl_sync(0xffffffffu, old, 0);
+            write = old == unsigned(cl - cf);
+            if (write) {
+                __threadfence();
+#pragma unroll
+                for (int mb = 0; mb < MB; ++mb) r[mb] = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int cc = cf; cc <= cl; cc += 8) {      // eight independent loads in flight, summed in CTA order
+                    float4 v[8][MB];
+#pragma unroll
+                    for (int qq = 0; qq < 8; ++qq)
+#pragma unroll
+                        for (int mb = 0; mb < MB; ++mb)
+                            v[qq][mb] = (cc + qq <= cl && mb < p.m)
+                                ? __ldcg(reinterpret_cast<const float4*>(p.partial + ((size_t)(cc + qq + t) * MB + mb) * VEC_COLS + lane * 4))
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int qq = 0; qq < 8; ++qq)
+#pragma unroll
+                        for (int mb = 0; mb < MB; ++mb) { r[mb].x += v[qq][mb].x; r[mb].y += v[qq][mb].y; r[mb].z += v[qq][mb].z; r[mb].w += v[qq][mb].w; }
+                }
+                if (lane == 0) p.counters[t] = 0;
+            }
+        }
+        if (write) write_out(t, r);
+    }
+    MT_TL(p.partial, j, 7);
 }
 
 template <int BITS, typename T, int MB, int CK>
@@ -309,6 +744,61 @@ int launch_mb(cudaStream_t st, const VecParams& p, int ck, dim3 grid, size_t sme
     return ck == 64 ? launch_one<BITS, T, 2, 64>(st, p, grid, smem) : launch_one<BITS, T, 2, 32>(st, p, grid, smem);
 }
 
+template <int BITS, typename T, int MB, int CK, int NW, int D, int MINB>
+int launch_stream_one(cudaStream_t st, const StreamParams& p, int grid) {
+    auto kern = qgemm_vstream_kernel<BITS, T, MB, CK, NW, D, MINB>;
+    constexpr int CKS = CK / 8;
+    const size_t smem = (size_t)D * NW * 32 * 16 + (size_t)NW * 2 * MB * 32 * 16 + (size_t)NW * 2 * MB * (32 / CKS) * 8;
+    static bool configured[64] = {};                       // per device ordinal: the attribute is set once
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return MT_ERR_CUDA; }
+    if (!configured[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
+        configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(NW * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = p.pdl ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
+    return MT_OK;
+}
+
+template <int BITS, typename T, int NW, int D, int MINB>
+int launch_stream_mb(cudaStream_t st, const StreamParams& p, int ck, int grid) {
+    if (p.m == 1) return ck == 64 ? launch_stream_one<BITS, T, 1, 64, NW, D, MINB>(st, p, grid) : launch_stream_one<BITS, T, 1, 32, NW, D, MINB>(st, p, grid);
+    return ck == 64 ? launch_stream_one<BITS, T, 2, 64, NW, D, MINB>(st, p, grid) : launch_stream_one<BITS, T, 2, 32, NW, D, MINB>(st, p, grid);
+}
+
+template <int NW, int D, int MINB>
+int launch_stream_cfg(cudaStream_t st, const QGemmArgs& a, int ctas) {
+    const int gs = a.k / a.groups;
+    const int ck = gs % 64 == 0 ? 64 : 32;
+    StreamParams p;
+    p.x = a.x; p.qw = a.qweight; p.qz = a.qzeros; p.scales = a.scales; p.bias = a.bias; p.out = a.out;
+    p.counters = static_cast<unsigned*>(a.workspace);
+    p.partial = reinterpret_cast<float*>(static_cast<char*>(a.workspace) + kCounterBytes);
+    p.m = a.m; p.n = a.n; p.k = a.k; p.groups = a.groups;
+    p.cpg = gs / ck; p.nchunks = a.k / ck; p.tiles = a.n / VEC_COLS;
+    if ((long long)p.tiles * p.nchunks > (1LL << 30)) return MT_ERR_TOO_LARGE;
+    p.units = p.tiles * p.nchunks;
+    const int mb = a.m == 1 ? 1 : 2;
+    long long warps = (long long)ctas * NW;
+    if (warps > p.units) warps = p.units;
+    const long long cap = (long long)((a.workspace_bytes - kCounterBytes) / ((size_t)mb * VEC_COLS * 4)) - p.tiles;
+    if (warps > cap) warps = cap;
+    if (warps < 1) return MT_ERR_WORKSPACE;
+    p.warps = (int)warps;
+    p.per = p.units / p.warps; p.rem = p.units % p.warps;
+    p.zp1_const = 1 << (a.bits - 1);
+    p.pdl = (a.flags & MT_FLAG_PDL) ? 1 : 0;
+    const int grid = (p.warps + NW - 1) / NW;
+    if (a.bits == 4) return a.dtype == MT_F16 ? launch_stream_mb<4, __half, NW, D, MINB>(st, p, ck, grid) : launch_stream_mb<4, __nv_bfloat16, NW, D, MINB>(st, p, ck, grid);
+    return a.dtype == MT_F16 ? launch_stream_mb<8, __half, NW, D, MINB>(st, p, ck, grid) : launch_stream_mb<8, __nv_bfloat16, NW, D, MINB>(st, p, ck, grid);
+}
+
 }  // namespace
 
 bool vec_supported(const QGemmArgs& a) {
@@ -322,6 +812,9 @@ bool vec_supported(const QGemmArgs& a) {
 
 int launch_vec(cudaStream_t st, const QGemmArgs& a) {
     if (!vec_supported(a)) return MT_ERR_UNSUPPORTED;
+    const int variant = (a.flags >> 24) & 0xf;
+    const int ctas_arg = (a.flags >> 16) & 0xff;
+    if (variant == 2) return launch_stream_cfg<8, 16, 2>(st, a, ctas_arg ? ctas_arg * 37 : 296);
     const int gs = a.k / a.groups;
     const int ck = gs % 64 == 0 ? 64 : 32;
     const int cks = ck / 8;
@@ -331,7 +824,8 @@ int launch_vec(cudaStream_t st, const QGemmArgs& a) {
     // in shared memory) and the partial sums must fit the workspace.  Among the admissible factors
     // pick the one a small cost model likes best: 2 CTAs fit an SM; a CTA that shares its SM
     // streams ~23.6 GB/s, one that has the SM to itself ~32 GB/s (its own loads in flight are the
-    // limit); a wave costs ~4 us of launch, prologue and reduction, later waves ~1.5 us.
+    // limit); a wave costs ~4 us of launch, prologue and reduction, later waves ~3 us.  When no
+    // factor fills the waves well the stream-K schedule takes over.
     const int forced = (a.flags >> 16) & 0xff;
     int splits = forced;
     const int min_splits = (a.k + VEC_WARPS * 2048 - 1) / (VEC_WARPS * 2048);
@@ -344,7 +838,7 @@ int launch_vec(cudaStream_t st, const QGemmArgs& a) {
     if (forced) {
         splits = splits < min_splits ? min_splits : (splits > max_splits ? max_splits : splits);
     } else {
-        const double slots = 296.0, sms = 148.0;
+        const double slots = 296.0;
         const double total_kb = (double)a.k * VEC_COLS * a.bits / 8.0 / 1024.0;
         double best = 1e30;
         for (int s = min_splits; s <= max_splits; ++s) {
@@ -353,11 +847,14 @@ int launch_vec(cudaStream_t st, const QGemmArgs& a) {
             const long long full = ctas / (long long)slots;
             const double rem = double(ctas - full * (long long)slots);
             double t = 0.0;
-            if (full > 0) t += 4.0 + kb / 23.6 + double(full - 1) * (1.5 + kb / 23.6);
-            if (rem > 0) t += (full > 0 ? 1.5 : 4.0) + kb / (rem <= sms ? 32.0 : 23.6);
+            if (full > 0) t += 4.0 + kb / 23.6 + double(full - 1) * (3.0 + kb / 23.6);
+            if (rem > 0) t += (full > 0 ? 3.0 : 4.0) + kb / (rem <= 160.0 ? 32.0 : 23.6);
             t += 0.02 * s;                                        // more partial sums to write and add
             if (t < best) { best = t; splits = s; }
         }
+        // the stream-K schedule has no waves to fill: ~6.5 us of fixed cost, then ~6 TB/s
+        const double t_stream = 6.5 + total_kb * 1.024 * tiles / 6000.0;
+        if (variant == 0 && t_stream < best) return launch_stream_cfg<8, 16, 2>(st, a, 296);
     }
     VecParams p;
     p.x = a.x; p.qw = a.qweight; p.qz = a.qzeros; p.scales = a.scales; p.bias = a.bias; p.out = a.out;
