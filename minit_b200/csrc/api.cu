@@ -111,10 +111,8 @@ int launch_small(cudaStream_t st, const QGemmArgs& a) {
         p.nchunks = nchunks; p.chunks_per_split = pl.chunks_per_split; p.splits = pl.splits;
         p.zp1_const = 1 << (bits - 1);
         p.pdl = (a.flags & MT_FLAG_PDL) ? 1 : 0;
-        p.peers = a.ar_peers; p.rank = a.ar_rank; p.world = a.ar_peers ? a.ar_world : 1;
-        p.err = p.counters + (kMaxTiles - 1);
-        p.slot_bytes = a.ar_peers ? ((a.ar_bytes - kArDataOffset) / (2 * (size_t)p.world)) & ~(size_t)255 : 0;
-        if (p.world > 1 && (size_t)m * a.n * 8 > p.slot_bytes) return MT_ERR_TOO_LARGE;
+        p.ar = make_ar_params(a);
+        if (p.ar.world > 1 && (size_t)m * a.n * 8 > p.ar.slot_bytes) return MT_ERR_TOO_LARGE;
         const size_t smem = (size_t)2 * mt * 8 * pitch + (act ? (size_t)a.groups * pl.wn * 32 * 4 + 2 * kc * 4 : 0);
         const int rc = fn(st, p, mt, pl.wn, gpc, act, dim3(pl.tiles, pl.splits), smem);
         if (rc != MT_OK) return rc;
@@ -285,7 +283,9 @@ int mt_qgemm_allreduce(void* stream, const void* x, const uint32_t* qweight, con
         a.ar_peers = reinterpret_cast<unsigned char* const*>(peer_buffers);
         a.ar_rank = rank; a.ar_world = world; a.ar_bytes = buffer_bytes;
     }
-    return launch_small(static_cast<cudaStream_t>(stream), a);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!(flags & MT_FLAG_FORCE_SMALL) && m <= 2 && vec_supported(a)) return launch_vec(st, a);
+    return launch_small(st, a);
 }
 
 size_t mt_allreduce_buffer_bytes(int m_max, int n_max, int world) {

@@ -1,0 +1,83 @@
+// One-shot all-reduce over peer memory, fused into the epilogue of a row-parallel GEMM.
+//
+// Replaces "local matmul, then Partial -> all_reduce" of the reference
+// (minit/collective/dispatch.py:33-37, minit/collective/tensor.py:72-73, ncclAllReduce at
+// minit/nccl/kernel.py:51-53) for outputs of at most 64 rows.
+//
+// Layout of a rank's symmetric buffer:
+//   [0, kArHeaderBytes)   control: word 0 = epoch of the last finished call, word 1 = CTAs done
+//   then mailboxes [2 call parities][world senders] of slot_bytes each: 8-byte cells {fp32 partial,
+//   epoch} indexed row * N + col, written by the sender with 16-byte stores of two cells.  A cell
+//   is valid for a call when its epoch word equals the call's epoch, so data and "ready" travel in
+//   one store and the receiver needs no fence and no separate flag.
+//
+// The thread that holds four finished fp32 partials of a row pushes them into its mailbox in every
+// peer's buffer (plain peer stores), then polls -- bounded -- the same cells of the peers'
+// mailboxes in its OWN memory and sums over all ranks in rank order: one NVLink crossing per value,
+// and every rank adds the same numbers in the same order, so the outputs are bit-identical across
+// ranks.  Calls are numbered by a device-side epoch (so a captured graph can be replayed); even and
+// odd calls use different mailboxes, and a peer can be at most one call ahead because it needs this
+// rank's cells of call e+1 to finish call e+1.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mt {
+
+constexpr int kArMaxWorld = 8;
+constexpr size_t kArHeaderBytes = 256;
+constexpr size_t kArDataOffset = kArHeaderBytes;
+
+struct ArParams {
+    unsigned char* const* peers;   // device array [world]: base of every rank's symmetric buffer (null: no all-reduce)
+    unsigned* err;                 // error word: set to 4 when a peer's cells never arrive
+    int rank, world;
+    size_t slot_bytes;             // bytes of one (parity, sender) mailbox
+};
+
+__device__ __forceinline__ bool ar_active(const ArParams& a) { return a.world > 1; }
+
+// epoch of the running call: the previous call on this stream has completed, so word 0 is stable
+__device__ __forceinline__ unsigned ar_epoch(const ArParams& a) {
+    return *reinterpret_cast<volatile unsigned*>(a.peers[a.rank]) + 1u;
+}
+
+// Sum v over all ranks.  `cell` = row * N + col of v.x; the four values are adjacent columns.
+__device__ __forceinline__ float4 ar_exchange(const ArParams& a, unsigned epoch, size_t cell, float4 v) {
+    const int slot = int(epoch & 1u);
+    const size_t off = cell * 8;
+    const unsigned u0 = __float_as_uint(v.x), u1 = __float_as_uint(v.y), u2 = __float_as_uint(v.z), u3 = __float_as_uint(v.w);
+    for (int r = 0; r < a.world; ++r) {
+        if (r == a.rank) continue;
+        unsigned char* dst = a.peers[r] + kArDataOffset + ((size_t)slot * a.world + a.rank) * a.slot_bytes + off;
+        asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(u0), "r"(epoch), "r"(u1), "r"(epoch) : "memory");
+        asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 16), "r"(u2), "r"(epoch), "r"(u3), "r"(epoch) : "memory");
+    }
+    const unsigned char* mine = a.peers[a.rank];
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < a.world; ++r) {
+        if (r == a.rank) { sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w; continue; }
+        const unsigned char* src = mine + kArDataOffset + ((size_t)slot * a.world + r) * a.slot_bytes + off;
+        uint4 c0, c1;
+        int spins = 0;
+        for (;;) {
+            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(c0.x), "=r"(c0.y), "=r"(c0.z), "=r"(c0.w) : "l"(src) : "memory");
+            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(c1.x), "=r"(c1.y), "=r"(c1.z), "=r"(c1.w) : "l"(src + 16) : "memory");
+            if (c0.y == epoch && c0.w == epoch && c1.y == epoch && c1.w == epoch) break;
+            if (++spins > (1 << 22)) { if (a.err) atomicExch(a.err, 4u); break; }   // a peer never arrived: give up, flag the error
+            if (spins > 32) __nanosleep(32);
+        }
+        sum.x += __uint_as_float(c0.x); sum.y += __uint_as_float(c0.z); sum.z += __uint_as_float(c1.x); sum.w += __uint_as_float(c1.z);
+    }
+    return sum;
+}
+
+// Called by ONE thread of every CTA of the grid, after the CTA's last exchange: the last CTA to
+// leave publishes the epoch for the next call.
+__device__ __forceinline__ void ar_leave(const ArParams& a, unsigned epoch, unsigned total_ctas) {
+    unsigned* ctl = reinterpret_cast<unsigned*>(a.peers[a.rank]);
+    __threadfence();
+    if (atomicAdd(ctl + 1, 1u) == total_ctas - 1) { ctl[1] = 0; __threadfence(); *reinterpret_cast<volatile unsigned*>(ctl) = epoch; }
+}
+
+}  // namespace mt

@@ -5,6 +5,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include "../../include/minit_b200.h"
+#include "ar_mailbox.cuh"
 
 namespace mt {
 
@@ -104,10 +105,19 @@ struct QGemmArgs {
     size_t ar_bytes;          // size of one symmetric buffer
 };
 
-// workspace layout: [0, kCounterBytes) tile counters (kept zero between launches),
+// workspace layout: [0, kCounterBytes) tile counters (the last word is the error word) (kept zero between launches),
 // then fp32 split-K partials.
 constexpr size_t kCounterBytes = 16384;           // 4096 tile counters
 constexpr int kMaxTiles = int(kCounterBytes / 4);
+
+// all-reduce parameters of a launch (world 1 when the call has no peers)
+inline ArParams make_ar_params(const QGemmArgs& a) {
+    ArParams r;
+    r.peers = a.ar_peers; r.rank = a.ar_rank; r.world = a.ar_peers ? a.ar_world : 1;
+    r.err = a.workspace ? static_cast<unsigned*>(a.workspace) + (kMaxTiles - 1) : nullptr;
+    r.slot_bytes = (a.ar_peers && a.ar_world > 0) ? ((a.ar_bytes - kArDataOffset) / (2 * (size_t)a.ar_world)) & ~(size_t)255 : 0;
+    return r;
+}
 
 int launch_dequant(cudaStream_t st, const uint32_t* qweight, const int32_t* g_idx, const uint32_t* qzeros,
                    const void* scales, void* w_out, int n, int k, int groups, int bits, int dtype);

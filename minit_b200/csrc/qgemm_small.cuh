@@ -24,6 +24,7 @@
 //           adds the bias, rounds once to T and resets the counter.  No spin-waits.
 #pragma once
 #include "common.cuh"
+#include "ar_mailbox.cuh"
 
 namespace mt {
 
@@ -41,22 +42,8 @@ struct SmallParams {
     int nchunks, chunks_per_split, splits;
     int zp1_const;         // zero+1 used when qz == nullptr
     int pdl;
-    // fused one-shot all-reduce over peer memory (world > 1): see the epilogue
-    unsigned char* const* peers;   // device array [world]: base of every rank's symmetric buffer
-    unsigned* err;                 // error word
-    int rank, world;
-    size_t slot_bytes;             // bytes of one (parity, sender) mailbox inside the symmetric buffer
+    ArParams ar;           // fused one-shot all-reduce over peer memory (ar.world > 1): see ar_mailbox.cuh
 };
-
-// Layout of a rank's symmetric buffer for the fused all-reduce:
-//   [0, kArHeaderBytes)   control: word 0 = epoch of the last finished call, word 1 = CTAs done
-//   then mailboxes [2 call parities][world senders] of slot_bytes each: 8-byte cells {fp32 partial,
-//   epoch} indexed row * N + col, written by the sender with 16-byte stores of two cells.  A cell
-//   is valid for a call when its epoch word equals the call's epoch, so data and "ready" travel in
-//   one store and the receiver needs no fence and no separate flag.
-constexpr int kArMaxWorld = 8;
-constexpr size_t kArHeaderBytes = 256;
-constexpr size_t kArDataOffset = kArHeaderBytes;
 
 // ---------------------------------------------------------------------------
 // per-(group, 4 columns) constants
@@ -369,23 +356,13 @@ qgemm_small_kernel(const SmallParams p) {
     // ---- epilogue ----
     // acc[j][s][e]: batch row 8j + 2t + (e&1), column col + 2s + (e>>1)
     //
-    // Row-parallel use (p.world > 1): the thread that holds four finished fp32 partials of a row
-    // pushes them, each paired with the call's epoch, into its mailbox in every peer's symmetric
-    // buffer (plain 16-byte peer stores), then polls -- bounded -- the same cells of the peers'
-    // mailboxes in its OWN memory and sums over all ranks in rank order.  One NVLink crossing per
-    // value, no fence, no flag; every rank adds the same numbers in the same order, so the outputs
-    // are bit-identical across ranks, and the exchange of one tile overlaps the other tiles' main
-    // loops.  Calls are numbered by a device-side epoch; even and odd calls use different mailboxes.
+    // Row-parallel use (p.ar.world > 1): the finished fp32 partials go through the mailbox
+    // all-reduce of ar_mailbox.cuh before they are rounded and stored; the exchange of one tile
+    // overlaps the other tiles' main loops.
     const T* __restrict__ bias = reinterpret_cast<const T*>(p.bias);
     T* __restrict__ out = reinterpret_cast<T*>(p.out);
-    const bool fused_ar = p.world > 1;
-    unsigned epoch = 0;
-    unsigned char* mine = nullptr;
-    if (fused_ar) {
-        mine = p.peers[p.rank];
-        epoch = *reinterpret_cast<volatile unsigned*>(mine) + 1u;   // safe: the previous call on this stream has completed
-    }
-    const int slot = int(epoch & 1u);
+    const bool fused_ar = ar_active(p.ar);
+    const unsigned epoch = fused_ar ? ar_epoch(p.ar) : 0u;
     auto finish = [&](int row, float v0, float v1, float v2, float v3) {
         if (bias) {
             const uint2 bv = __ldg(reinterpret_cast<const uint2*>(bias + col));
@@ -393,45 +370,17 @@ qgemm_small_kernel(const SmallParams p) {
             v2 += H::to_float(uint16_t(bv.y & 0xffff)); v3 += H::to_float(uint16_t(bv.y >> 16));
         }
         if (fused_ar) {
-            const size_t cell = ((size_t)row * p.n + col) * 8;
-            const unsigned u0 = __float_as_uint(v0), u1 = __float_as_uint(v1), u2 = __float_as_uint(v2), u3 = __float_as_uint(v3);
-            for (int r = 0; r < p.world; ++r) {
-                if (r == p.rank) continue;
-                unsigned char* dst = p.peers[r] + kArDataOffset + ((size_t)slot * p.world + p.rank) * p.slot_bytes + cell;
-                asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(u0), "r"(epoch), "r"(u1), "r"(epoch) : "memory");
-                asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 16), "r"(u2), "r"(epoch), "r"(u3), "r"(epoch) : "memory");
-            }
-            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int r = 0; r < p.world; ++r) {
-                if (r == p.rank) { sum.x += v0; sum.y += v1; sum.z += v2; sum.w += v3; continue; }
-                const unsigned char* src = mine + kArDataOffset + ((size_t)slot * p.world + r) * p.slot_bytes + cell;
-                uint4 a, b;
-                int spins = 0;
-                for (;;) {
-                    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(src) : "memory");
-                    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(src + 16) : "memory");
-                    if (a.y == epoch && a.w == epoch && b.y == epoch && b.w == epoch) break;
-                    if (++spins > (1 << 22)) { if (p.err) atomicExch(p.err, 4u); break; }   // a peer never arrived: give up, flag the error
-                    if (spins > 32) __nanosleep(32);
-                }
-                sum.x += __uint_as_float(a.x); sum.y += __uint_as_float(a.z); sum.z += __uint_as_float(b.x); sum.w += __uint_as_float(b.z);
-            }
-            uint2 o; o.x = H::pack(sum.x, sum.y); o.y = H::pack(sum.z, sum.w);
-            *reinterpret_cast<uint2*>(out + (size_t)row * p.n + col) = o;
-        } else {
-            uint2 o; o.x = H::pack(v0, v1); o.y = H::pack(v2, v3);
-            *reinterpret_cast<uint2*>(out + (size_t)row * p.n + col) = o;
+            const float4 sum = ar_exchange(p.ar, epoch, (size_t)row * p.n + col, make_float4(v0, v1, v2, v3));
+            v0 = sum.x; v1 = sum.y; v2 = sum.z; v3 = sum.w;
         }
+        uint2 o; o.x = H::pack(v0, v1); o.y = H::pack(v2, v3);
+        *reinterpret_cast<uint2*>(out + (size_t)row * p.n + col) = o;
     };
     // Grid-wide bookkeeping of the fused path: the last CTA to leave publishes the epoch for the next call.
     auto leave = [&]() {
         if (!fused_ar) return;
         __syncthreads();
-        if (tid == 0) {
-            unsigned* ctl = reinterpret_cast<unsigned*>(mine);
-            __threadfence();
-            if (atomicAdd(ctl + 1, 1u) == gridDim.x * gridDim.y - 1) { ctl[1] = 0; __threadfence(); *reinterpret_cast<volatile unsigned*>(ctl) = epoch; }
-        }
+        if (tid == 0) ar_leave(p.ar, epoch, gridDim.x * gridDim.y);
     };
     if (p.splits == 1) {
         if (col_ok) {

@@ -51,6 +51,7 @@ struct VecParams {
     int slice_ks;     // k-steps (8 values of k) of shared memory per warp and batch row
     int zp1_const;
     int pdl;
+    ArParams ar;      // row-parallel use: all-reduce of the finished sums over peer memory (ar_mailbox.cuh)
 };
 
 __device__ __forceinline__ uint32_t hfma2(uint32_t a, uint32_t b, uint32_t c) {
@@ -281,28 +282,44 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
     const int gc = tile * VEC_COLS + cc;
     const T* bias = reinterpret_cast<const T*>(p.bias);
     uint16_t* out = reinterpret_cast<uint16_t*>(p.out);
-    if (p.splits == 1) {
-        if (active) {
-            if (bias) v += H::to_float(reinterpret_cast<const uint16_t*>(bias)[gc]);
-            out[(size_t)mb_r * p.n + gc] = H::from_float(v);
+    const bool fused_ar = ar_active(p.ar);
+    const unsigned epoch = fused_ar ? ar_epoch(p.ar) : 0u;      // after griddepcontrol.wait: the previous call has published its epoch
+    if (p.splits > 1) {
+        if (active) __stcg(p.partial + ((size_t)split * p.m + mb_r) * p.n + gc, v);
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) s_last = (atomicAdd(p.counters + tile, 1u) == unsigned(p.splits - 1));
+        __syncthreads();
+        MT_TL(p.partial, tl_id, 6);
+        if (!s_last) {
+            if (fused_ar && tid == 0) ar_leave(p.ar, epoch, gridDim.x * gridDim.y);
+            return;
         }
-        return;
+        __threadfence();
+        if (active) {
+            v = 0.f;
+            for (int s = 0; s < p.splits; ++s) v += __ldcg(p.partial + ((size_t)s * p.m + mb_r) * p.n + gc);
+        }
+        if (tid == 0) p.counters[tile] = 0;
     }
-    if (active) __stcg(p.partial + ((size_t)split * p.m + mb_r) * p.n + gc, v);
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) s_last = (atomicAdd(p.counters + tile, 1u) == unsigned(p.splits - 1));
-    __syncthreads();
-    MT_TL(p.partial, tl_id, 6);
-    if (!s_last) return;
-    __threadfence();
-    if (active) {
-        float sum = 0.f;
-        for (int s = 0; s < p.splits; ++s) sum += __ldcg(p.partial + ((size_t)s * p.m + mb_r) * p.n + gc);
-        if (bias) sum += H::to_float(reinterpret_cast<const uint16_t*>(bias)[gc]);
-        out[(size_t)mb_r * p.n + gc] = H::from_float(sum);
+    if (active && bias) v += H::to_float(reinterpret_cast<const uint16_t*>(bias)[gc]);
+    if (!fused_ar) {
+        if (active) out[(size_t)mb_r * p.n + gc] = H::from_float(v);
+    } else {
+        // four adjacent columns per thread for the exchange: regroup through shared memory
+        __syncthreads();                                     // every warp is done reading `red`
+        if (active) red[mb_r * VEC_COLS + cc] = v;
+        __syncthreads();
+        if (tid < 32 * MB && tid / 32 < p.m) {
+            const int mb = tid / 32, c4 = (tid % 32) * 4;
+            const float4 mine4 = *reinterpret_cast<const float4*>(red + mb * VEC_COLS + c4);
+            const float4 sum = ar_exchange(p.ar, epoch, (size_t)mb * p.n + tile * VEC_COLS + c4, mine4);
+            uint2 o; o.x = H::pack(sum.x, sum.y); o.y = H::pack(sum.z, sum.w);
+            *reinterpret_cast<uint2*>(out + (size_t)mb * p.n + tile * VEC_COLS + c4) = o;
+        }
+        __syncthreads();
+        if (tid == 0) ar_leave(p.ar, epoch, gridDim.x * gridDim.y);
     }
-    if (tid == 0) p.counters[tile] = 0;
     MT_TL(p.partial, tl_id, 7);
 }
 
@@ -333,6 +350,7 @@ struct StreamParams {
     int per, rem;      // units / warps, units % warps: the first `rem` warps get per + 1 units
     int zp1_const;
     int pdl;
+    ArParams ar;       // row-parallel use: all-reduce of the finished sums over peer memory (ar_mailbox.cuh)
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
@@ -512,6 +530,8 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
 
     const T* bias = reinterpret_cast<const T*>(p.bias);
     uint16_t* out = reinterpret_cast<uint16_t*>(p.out);
+    const bool fused_ar = ar_active(p.ar);
+    const unsigned epoch = fused_ar ? ar_epoch(p.ar) : 0u;      // after griddepcontrol.wait: the previous call has published its epoch
     auto write_out = [&](int t, const float4 (&r)[MB]) {
         const int colb = t * VEC_COLS + lane * 4;
         float b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
@@ -523,7 +543,9 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb)
             if (mb < p.m) {
-                uint2 o; o.x = H::pack(r[mb].x + b0, r[mb].y + b1); o.y = H::pack(r[mb].z + b2, r[mb].w + b3);
+                float4 v = make_float4(r[mb].x + b0, r[mb].y + b1, r[mb].z + b2, r[mb].w + b3);
+                if (fused_ar) v = ar_exchange(p.ar, epoch, (size_t)mb * p.n + colb, v);
+                uint2 o; o.x = H::pack(v.x, v.y); o.y = H::pack(v.z, v.w);
                 *reinterpret_cast<uint2*>(out + (size_t)mb * p.n + colb) = o;
             }
     };
@@ -719,6 +741,10 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
         }
         if (write) write_out(t, r);
     }
+    if (fused_ar) {
+        __syncthreads();
+        if (tid == 0) ar_leave(p.ar, epoch, gridDim.x);
+    }
     MT_TL(p.partial, j, 7);
 }
 
@@ -792,6 +818,8 @@ int launch_stream_cfg(cudaStream_t st, const QGemmArgs& a, int ctas) {
     if (warps < 1) return MT_ERR_WORKSPACE;
     p.warps = (int)warps;
     p.per = p.units / p.warps; p.rem = p.units % p.warps;
+    p.ar = make_ar_params(a);
+    if (p.ar.world > 1 && (size_t)a.m * a.n * 8 > p.ar.slot_bytes) return MT_ERR_TOO_LARGE;
     p.zp1_const = 1 << (a.bits - 1);
     p.pdl = (a.flags & MT_FLAG_PDL) ? 1 : 0;
     const int grid = (p.warps + NW - 1) / NW;
@@ -868,6 +896,8 @@ int launch_vec(cudaStream_t st, const QGemmArgs& a) {
     p.slice_ks = slice_ks;
     p.zp1_const = 1 << (a.bits - 1);
     p.pdl = (a.flags & MT_FLAG_PDL) ? 1 : 0;
+    p.ar = make_ar_params(a);
+    if (p.ar.world > 1 && (size_t)a.m * a.n * 8 > p.ar.slot_bytes) return MT_ERR_TOO_LARGE;
     const int mb = a.m == 1 ? 1 : 2;
     const size_t smem = (size_t)VEC_WARPS * mb * slice_ks * 16 + (size_t)VEC_WARPS * mb * (slice_ks / cks) * 8;
     if (smem > 160 * 1024) return MT_ERR_TOO_LARGE;

@@ -47,6 +47,7 @@ def _worker(rank, size, port, results):
         # several calls in a row (alternating slots), two shapes, bit-identical on all ranks
         from minit_b200.collective import FusedAllReduce
         far = FusedAllReduce(m_max=16, n_max=4096)
+        far8k = FusedAllReduce(m_max=2, n_max=8192)
         rowf = RowParallelQLinear(comm, g(c2, "qweight"), g(c2, "qzeros"), g(c2, "scales"), None, 4, bias=g(c2, "bias"), fused=far)
         c3 = O.make_gptq_case(8192, 512, 1, bits=4, seed=3)
         rowf3 = RowParallelQLinear(comm, g(c3, "qweight"), g(c3, "qzeros"), g(c3, "scales"), None, 4, fused=far)
@@ -60,6 +61,38 @@ def _worker(rank, size, port, results):
             y3 = rowf3(x3)
             ok, err, bound = O.tolerance_ok(y3, ref3, 1e-2)
             assert ok, f"rank {rank} fused (split-K) call {it}: err {err} > {bound}"
+        # decode shapes (M = 1, 2) take the CUDA-core GEMV, both schedules; N = 8192 crosses many column blocks
+        for m4, seed4, tune in [(1, 41, 0), (2, 42, 1 << 24), (2, 43, 2 << 24), (1, 44, 2 << 24)]:
+            c4 = O.make_gptq_case(4096, 8192, m4, bits=4, seed=seed4, bias=True)
+            rowf4 = RowParallelQLinear(comm, g(c4, "qweight"), g(c4, "qzeros"), g(c4, "scales"), None, 4, bias=g(c4, "bias"), fused=far8k)
+            ks4 = 4096 // size
+            x4 = g(c4, "x")[:, ks4 * rank:ks4 * (rank + 1)].contiguous()
+            ref4 = O.qlinear(c4["x"], O.dequantize_packed(c4["qweight"], None, c4["qzeros"], c4["scales"], 4), c4["bias"])
+            for it in range(3):
+                y4 = rowf4(x4, flags=tune)
+                ok, err, bound = O.tolerance_ok(y4, ref4, 1e-2)
+                assert ok, f"rank {rank} fused GEMV M={m4} tune={tune:#x} call {it}: err {err} > {bound}"
+            g4 = [torch.empty_like(y4) for _ in range(size)]
+            dist.all_gather(g4, y4)
+            assert all(torch.equal(g4[0], t) for t in g4), "fused GEMV all-reduce results differ between ranks"
+        # a captured graph of fused calls replays correctly: the call counter lives on the device
+        xg = x4.clone(); yg = torch.empty_like(y4)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            rowf4(xg, out=yg); rowf3(x3)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                rowf4(xg, out=yg)
+                rowf4(xg, out=yg)
+                rowf4(xg, out=yg)
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+        ok, err, bound = O.tolerance_ok(yg, ref4, 1e-2)
+        assert ok, f"rank {rank} graph replay of the fused GEMV: err {err} > {bound}"
+        torch.cuda.current_stream().wait_stream(side)
         gathered = [torch.empty_like(y3) for _ in range(size)]
         dist.all_gather(gathered, y3)
         assert all(torch.equal(gathered[0], t) for t in gathered), "fused all-reduce results differ between ranks"
