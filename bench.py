@@ -229,9 +229,11 @@ def run_ours(args):
     launches_per_step = args.layers * len(shapes)
     hbm_peak, peak_kind = peaks()
     achieved = per_rank_abytes / (ms_step * 1e-3) / 1e9     # per GPU: bytes of its launches / time of its launches
-    # DRAM bytes per launch of the dominant kernel: ncu measured 244.3 MB read + 4.4 MB written for
-    # 242.7 MB of algorithmic bytes (profiles/qgemm_dtc_8192x57344_m1.md); traffic scales with the bytes.
-    traffic = 1.0245 * per_rank_abytes / launches_per_step
+    # DRAM bytes per launch of the decode GEMV: ncu measured 245.85 MB read + 3.77 MB written for
+    # 244.2 MB of algorithmic bytes on gate/up, 122.12 + 3.41 MB for 122.1 MB on down
+    # (profiles/qgemm_vstream_8192x57344_m1.md, profiles/qgemm_vec_split_28672x8192_m1.md); traffic
+    # scales with the bytes.
+    traffic = 1.025 * per_rank_abytes / launches_per_step
     line = {
         "metric": "int4 dequant-GEMM weight GB/s at M=%d" % m, "value": total_wbytes / (ms_step * 1e-3) / 1e9, "unit": "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
