@@ -133,6 +133,14 @@ int mt_qgemm_allreduce(void* stream, const void* x, const uint32_t* qweight, con
 size_t mt_allreduce_buffer_bytes(int m_max, int n_max, int world);
 
 /*
+ * Which schedule mt_qgemm would run a decode call (M <= 2, no g_idx) with: > 0 = split-K factor of the
+ * CUDA-core GEMV, 0 = its stream-K schedule, MT_ERR_UNSUPPORTED = the request goes to another kernel.
+ * Inspection only (no launch); no counterpart in the reference, whose launcher has one fixed grid
+ * (examples/qwen1_5_int8.py:202-216).
+ */
+int mt_decode_plan(int m, int n, int k, int nr_groups, int bits, size_t workspace_bytes, int flags);
+
+/*
  * mt_qgemm for callers that cannot allocate.  No counterpart in the reference (its launcher
  * needs no scratch because it accumulates with atomics into a pre-zeroed output).
  *

@@ -38,6 +38,7 @@ SYMBOLS = {
     "mt_qgemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _i]),
     "mt_qgemm_allreduce": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _i, _vp, _i, _i, _sz]),
     "mt_allreduce_buffer_bytes": (_sz, [_i, _i, _i]),
+    "mt_decode_plan": (_i, [_i, _i, _i, _i, _i, _sz, _i]),
     "mt_qgemm_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i]),
     "mt_w8_perchannel_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _i]),
     "mt_nccl_load": (_i, [ctypes.c_char_p]),

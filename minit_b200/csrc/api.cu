@@ -288,6 +288,16 @@ int mt_qgemm_allreduce(void* stream, const void* x, const uint32_t* qweight, con
     return launch_small(st, a);
 }
 
+int mt_decode_plan(int m, int n, int k, int nr_groups, int bits, size_t workspace_bytes, int flags) {
+    if ((bits != 4 && bits != 8) || m < 1 || n < 1 || k < 1 || nr_groups < 1 || k % nr_groups != 0) return MT_ERR_SHAPE;
+    if (check_device() != MT_OK) return MT_ERR_DEVICE;
+    QGemmArgs a = {};
+    a.m = m; a.n = n; a.k = k; a.groups = nr_groups; a.bits = bits; a.dtype = MT_F16;
+    a.workspace = reinterpret_cast<void*>(16); a.workspace_bytes = workspace_bytes; a.flags = flags;   // only tested for null
+    if (m > 2) return MT_ERR_UNSUPPORTED;
+    return vec_plan(a);
+}
+
 size_t mt_allreduce_buffer_bytes(int m_max, int n_max, int world) {
     if (m_max < 1 || n_max < 1 || world < 1 || world > kArMaxWorld) return 0;
     const size_t slot = (((size_t)m_max * n_max * 8) + 255) & ~(size_t)255;   // 8-byte cells {value, epoch}

@@ -130,6 +130,7 @@ int launch_dtc(cudaStream_t st, const QGemmArgs& a);            // tcgen05 decod
 bool dtc_supported(const QGemmArgs& a);
 int launch_vec(cudaStream_t st, const QGemmArgs& a);            // CUDA-core decode GEMV, M <= 2, contiguous groups
 bool vec_supported(const QGemmArgs& a);
+int vec_plan(const QGemmArgs& a);                               // > 0 split-K factor, 0 stream-K, < 0 MT_ERR_*
 int launch_tc(cudaStream_t st, const QGemmArgs& a);             // tcgen05 path (any M), GPTQ layout without g_idx
 bool tc_supported(const QGemmArgs& a);
 

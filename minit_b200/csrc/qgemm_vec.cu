@@ -51,8 +51,19 @@ struct VecParams {
     int slice_ks;     // k-steps (8 values of k) of shared memory per warp and batch row
     int zp1_const;
     int pdl;
+    int cluster;      // the `splits` CTAs of a column block form a thread-block cluster: split-K sums meet in CTA 0's shared memory
     ArParams ar;      // row-parallel use: all-reduce of the finished sums over peer memory (ar_mailbox.cuh)
 };
+
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ void st_cluster_f32(const float* local, unsigned cta_rank, float v) {
+    const uint32_t la = (uint32_t)__cvta_generic_to_shared(local);
+    uint32_t ra;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(la), "r"(cta_rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ra), "f"(v) : "memory");
+}
 
 __device__ __forceinline__ uint32_t hfma2(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d; asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d; }
@@ -81,10 +92,12 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
 
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ __align__(16) float red[VEC_WARPS * MB * VEC_COLS];
+    __shared__ __align__(16) float xred[8 * MB * VEC_COLS];      // cluster mode: one row of sums per split, in CTA 0 of the cluster
     __shared__ int s_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tile = blockIdx.x, split = blockIdx.y;
+    if (p.cluster) cluster_arrive_relaxed();                      // phase 0: "this CTA runs, its shared memory exists"
     const int col = tile * VEC_COLS + lane * 4;
 
     // this warp's run of chunks
@@ -284,7 +297,22 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
     uint16_t* out = reinterpret_cast<uint16_t*>(p.out);
     const bool fused_ar = ar_active(p.ar);
     const unsigned epoch = fused_ar ? ar_epoch(p.ar) : 0u;      // after griddepcontrol.wait: the previous call has published its epoch
-    if (p.splits > 1) {
+    if (p.splits > 1 && p.cluster) {
+        // split-K inside a cluster: every CTA stores its row into CTA 0's shared memory, one cluster
+        // barrier, CTA 0 adds the rows in split order.  No global-memory round trip.
+        cluster_wait_acquire();                                  // phase 0 complete: CTA 0 is resident
+        if (active) st_cluster_f32(xred + ((size_t)split * MB + mb_r) * VEC_COLS + cc, 0u, v);
+        cluster_arrive_release();
+        cluster_wait_acquire();
+        if (split != 0) {
+            if (fused_ar && tid == 0) ar_leave(p.ar, epoch, gridDim.x * gridDim.y);
+            return;
+        }
+        if (active) {
+            v = 0.f;
+            for (int s = 0; s < p.splits; ++s) v += xred[((size_t)s * MB + mb_r) * VEC_COLS + cc];
+        }
+    } else if (p.splits > 1) {
         if (active) __stcg(p.partial + ((size_t)split * p.m + mb_r) * p.n + gc, v);
         __threadfence();
         __syncthreads();
@@ -751,15 +779,28 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
 template <int BITS, typename T, int MB, int CK>
 int launch_one(cudaStream_t st, const VecParams& p, dim3 grid, size_t smem) {
     auto kern = qgemm_vec_kernel<BITS, T, MB, CK>;
-    if (smem > 48 * 1024) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
+    static bool configured[64] = {};                       // per device ordinal: opt in to large dynamic shared memory once
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return MT_ERR_CUDA; }
+    if (!configured[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
+        configured[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = dim3(VEC_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = p.pdl ? 1 : 0;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (p.pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (p.cluster) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1; attr[na].val.clusterDim.y = grid.y; attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    cfg.attrs = attr; cfg.numAttrs = na;
     if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
     return MT_OK;
 }
@@ -829,6 +870,26 @@ int launch_stream_cfg(cudaStream_t st, const QGemmArgs& a, int ctas) {
 
 }  // namespace
 
+// CTAs of the split-K kernel that can be resident at once when launched as clusters of s (cached
+// per device).  All instantiations share the launch bounds, so one of them stands for all.
+static int cluster_slots(int s) {
+    static int cache[64][9] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || s < 1 || s > 8) { cudaGetLastError(); return 256; }
+    if (cache[dev][s] == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1, s * 64); cfg.blockDim = dim3(VEC_THREADS); cfg.dynamicSmemBytes = 20 * 1024;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = s; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, qgemm_vec_kernel<4, __half, 1, 64>, &cfg) != cudaSuccess || n < 1) { cudaGetLastError(); n = 256 / s; }
+        cache[dev][s] = n * s;
+    }
+    return cache[dev][s];
+}
+
 bool vec_supported(const QGemmArgs& a) {
     if (a.g_idx || a.m < 1 || a.m > 2 || a.groups < 1) return false;
     if (a.n % VEC_COLS != 0 || a.k % a.groups != 0) return false;
@@ -838,23 +899,26 @@ bool vec_supported(const QGemmArgs& a) {
     return a.workspace != nullptr && a.workspace_bytes >= kCounterBytes;
 }
 
-int launch_vec(cudaStream_t st, const QGemmArgs& a) {
+// Schedule of the decode GEMV for a request: > 0 = split-K factor, 0 = stream-K, < 0 = MT_ERR_*.
+int vec_plan(const QGemmArgs& a) {
     if (!vec_supported(a)) return MT_ERR_UNSUPPORTED;
     const int variant = (a.flags >> 24) & 0xf;
-    const int ctas_arg = (a.flags >> 16) & 0xff;
-    if (variant == 2) return launch_stream_cfg<8, 16, 2>(st, a, ctas_arg ? ctas_arg * 37 : 296);
+    if (variant == 2) return 0;
     const int gs = a.k / a.groups;
     const int ck = gs % 64 == 0 ? 64 : 32;
-    const int cks = ck / 8;
     const int nchunks = a.k / ck;
     const int tiles = a.n / VEC_COLS;
     // split-K: every warp gets at least one chunk and at most 2048 values of k (its activations live
-    // in shared memory) and the partial sums must fit the workspace.  Among the admissible factors
-    // pick the one a small cost model likes best: 2 CTAs fit an SM; a CTA that shares its SM
-    // streams ~23.6 GB/s, one that has the SM to itself ~32 GB/s (its own loads in flight are the
-    // limit); a wave costs ~4 us of launch, prologue and reduction, later waves ~3 us.  When no
-    // factor fills the waves well the stream-K schedule takes over.
+    // in shared memory) and the partial sums must fit the workspace.  Among the admissible factors a
+    // small cost model picks: CTA slots come from the occupancy of the cluster launch, capped at 256
+    // (2 CTAs fit an SM, but clusters do not tile every GPC and the previous launch of a chain still
+    // holds slots); a CTA that shares its SM streams ~23.6 GB/s, one that has the SM to itself ~30 GB/s
+    // (its own loads in flight are the limit); a wave costs ~2.4 us of launch, prologue and reduction
+    // (+0.3 us for the cluster hand-over, +1.8 us when the splits meet in global memory), every further
+    // wave 3 us and 5 % for its ragged end.  When no factor fills the waves well the stream-K schedule
+    // (~6.5 us fixed, then ~6 TB/s) takes over.
     const int forced = (a.flags >> 16) & 0xff;
+    const bool no_cluster = ((a.flags >> 28) & 1) != 0;          // bit 28 of the flags: tuning, no clusters
     int splits = forced;
     const int min_splits = (a.k + VEC_WARPS * 2048 - 1) / (VEC_WARPS * 2048);
     int max_splits = nchunks / VEC_WARPS;
@@ -863,27 +927,43 @@ int launch_vec(cudaStream_t st, const QGemmArgs& a) {
     if ((size_t)max_splits > cap) max_splits = cap < 1 ? 1 : (int)cap;
     if (max_splits > 64) max_splits = 64;
     if (min_splits > max_splits) return min_splits > 1 && (size_t)min_splits > cap ? MT_ERR_WORKSPACE : MT_ERR_TOO_LARGE;
-    if (forced) {
-        splits = splits < min_splits ? min_splits : (splits > max_splits ? max_splits : splits);
-    } else {
-        const double slots = 296.0;
-        const double total_kb = (double)a.k * VEC_COLS * a.bits / 8.0 / 1024.0;
-        double best = 1e30;
-        for (int s = min_splits; s <= max_splits; ++s) {
-            const double kb = total_kb / s * 1.024;              // KB -> 1e3 bytes: GB/s == KB/us
-            const long long ctas = (long long)tiles * s;
-            const long long full = ctas / (long long)slots;
-            const double rem = double(ctas - full * (long long)slots);
-            double t = 0.0;
-            if (full > 0) t += 4.0 + kb / 23.6 + double(full - 1) * (3.0 + kb / 23.6);
-            if (rem > 0) t += (full > 0 ? 3.0 : 4.0) + kb / (rem <= 160.0 ? 32.0 : 23.6);
-            t += 0.02 * s;                                        // more partial sums to write and add
-            if (t < best) { best = t; splits = s; }
-        }
-        // the stream-K schedule has no waves to fill: ~6.5 us of fixed cost, then ~6 TB/s
-        const double t_stream = 6.5 + total_kb * 1.024 * tiles / 6000.0;
-        if (variant == 0 && t_stream < best) return launch_stream_cfg<8, 16, 2>(st, a, 296);
+    if (forced) return splits < min_splits ? min_splits : (splits > max_splits ? max_splits : splits);
+    const double slow = a.m == 1 ? 1.0 : 0.65;                  // two batch rows: the FMA pipe, not HBM, sets the rate
+    const double total_kb = (double)a.k * VEC_COLS * a.bits / 8.0 / 1024.0;
+    double best = 1e30;
+    for (int s = min_splits; s <= max_splits; ++s) {
+        const bool cl = s >= 2 && s <= 8 && !no_cluster;
+        int slots = 296;
+        if (cl) { slots = cluster_slots(s); if (slots > 256) slots = 256 / s * s; }
+        const double kb = total_kb / s * 1.024;                  // KB -> 1e3 bytes: GB/s == KB/us
+        const long long ctas = (long long)tiles * s;
+        const long long full = ctas / slots;
+        const long long rem = ctas - full * slots;
+        const double t0 = 2.4 + (s == 1 ? 0.0 : cl ? 0.3 : 1.8);
+        double t = 0.0;
+        if (full > 0) t += t0 + kb / (23.6 * slow) + double(full - 1) * (3.0 + kb / (23.6 * slow));
+        if (rem > 0) t += (full > 0 ? 3.0 : t0) + kb / ((rem <= 160 ? 30.0 : 23.6) * slow);
+        if (full + (rem > 0) > 1) t *= 1.05;
+        t += 0.02 * s;                                            // more partial sums to write and add
+        if (t < best) { best = t; splits = s; }
     }
+    const double t_stream = 6.5 + total_kb * 1.024 * tiles / (6000.0 * slow);
+    if (variant == 0 && t_stream < best) return 0;
+    return splits;
+}
+
+int launch_vec(cudaStream_t st, const QGemmArgs& a) {
+    const int plan = vec_plan(a);
+    if (plan < 0) return plan;
+    const int ctas_arg = (a.flags >> 16) & 0xff;
+    if (plan == 0) return launch_stream_cfg<8, 16, 2>(st, a, ((a.flags >> 24) & 0xf) == 2 && ctas_arg ? ctas_arg * 37 : 296);
+    const int splits = plan;
+    const bool no_cluster = ((a.flags >> 28) & 1) != 0;
+    const int gs = a.k / a.groups;
+    const int ck = gs % 64 == 0 ? 64 : 32;
+    const int cks = ck / 8;
+    const int nchunks = a.k / ck;
+    const int tiles = a.n / VEC_COLS;
     VecParams p;
     p.x = a.x; p.qw = a.qweight; p.qz = a.qzeros; p.scales = a.scales; p.bias = a.bias; p.out = a.out;
     p.counters = static_cast<unsigned*>(a.workspace);
@@ -896,6 +976,7 @@ int launch_vec(cudaStream_t st, const QGemmArgs& a) {
     p.slice_ks = slice_ks;
     p.zp1_const = 1 << (a.bits - 1);
     p.pdl = (a.flags & MT_FLAG_PDL) ? 1 : 0;
+    p.cluster = (splits >= 2 && splits <= 8 && !no_cluster) ? 1 : 0;
     p.ar = make_ar_params(a);
     if (p.ar.world > 1 && (size_t)a.m * a.n * 8 > p.ar.slot_bytes) return MT_ERR_TOO_LARGE;
     const int mb = a.m == 1 ? 1 : 2;
