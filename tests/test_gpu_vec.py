@@ -124,6 +124,21 @@ def test_wide_and_deep_shapes_cross_column_blocks(M, variant):
         assert_close(run(M, c, 4, flags=VEC | variant), ref(c, 4), f"vec {k}x{n} M={m}")
 
 
+def test_decode_plan_reports_the_schedule(M):
+    """mt_decode_plan: > 0 split-K factor, 0 stream-K, negative status when the GEMV does not take the call."""
+    from minit_b200 import _lib
+    L = _lib.lib
+    ws = lambda m, n, k: L.mt_workspace_bytes(m, n, k, 4)
+    assert L.mt_decode_plan(1, 8192, 8192, 64, 4, ws(1, 8192, 8192), 0) == 4            # 64 column blocks x 4 = one wave
+    assert L.mt_decode_plan(1, 10240, 8192, 64, 4, ws(1, 10240, 8192), 0) == 3
+    assert L.mt_decode_plan(1, 57344, 8192, 64, 4, ws(1, 57344, 8192), 0) in (0, 1)     # 448 blocks: stream-K ties with one split
+    assert L.mt_decode_plan(1, 57344, 28672, 224, 4, ws(1, 57344, 28672), 0) == 0        # far more blocks than slots: stream-K
+    assert L.mt_decode_plan(1, 8192, 8192, 64, 4, ws(1, 8192, 8192), 2 << 24) == 0       # forced stream-K
+    assert L.mt_decode_plan(1, 8192, 8192, 64, 4, ws(1, 8192, 8192), (1 << 24) | (5 << 16)) == 5
+    assert L.mt_decode_plan(3, 8192, 8192, 64, 4, ws(3, 8192, 8192), 0) < 0              # M > 2: another kernel
+    assert L.mt_decode_plan(1, 136, 1024, 8, 4, ws(1, 136, 1024), 0) < 0                 # N % 128 != 0
+
+
 def test_unsupported_shapes_are_refused(M):
     c = O.make_gptq_case(1024, 136, 1, bits=4, seed=2)       # N not a multiple of 128
     with pytest.raises(RuntimeError):
