@@ -176,6 +176,37 @@ int mt_w8_perchannel_gemm(void* stream, const void* x, const int8_t* w, const vo
                           void* workspace, size_t workspace_bytes, int flags);
 
 /*
+ * mt_w8_pack: plain int8 weights w[K,N] -> the 8-bit GPTQ word layout qweight[K/4, N] (byte i of word
+ * (kw, n) = w[4 kw + i][n] + 128).  A per-channel int8 linear is then mt_qgemm(bits = 8, nr_groups = 1,
+ * qzeros = NULL, scales [1,N]) and runs on the same kernels as a GPTQ linear (CUDA-core GEMV at M <= 2,
+ * tcgen05 at M > 64); mt_w8_perchannel_gemm on the plain layout remains for callers that cannot repack.
+ * Load-time; n % 4 == 0, k % 4 == 0.
+ */
+int mt_w8_pack(void* stream, const int8_t* w, uint32_t* qweight, int n, int k);
+
+/*
+ * Act-order (desc_act) checkpoints: g_idx[k] is the group of row k, in arbitrary order
+ * (examples/qwen1_5_int8.py:97-138 looks scales and zeros up through it for every element).  Sorted
+ * once by group, the weights have the contiguous-group layout of all fast kernels, and the
+ * activations are read through the same permutation: x[:, perm] @ W[perm, :] == x @ W.
+ *   mt_act_order_perm    perm[K] = stable argsort of g_idx; *status (device int, may be NULL) = 0 ok,
+ *                        1 a group does not hold exactly K / nr_groups rows, 2 a g_idx value out of range.
+ *   mt_repack_rows       qweight_out row r = qweight row perm[r] (inside the packed words; not in place).
+ *   mt_gather_columns    x_out[m, j] = x[m, perm[j]].
+ *   mt_qgemm_ordered     out = x[:, x_perm] @ dequant(qweight sorted, contiguous groups) (+ bias).  At
+ *                        M <= 2 the GEMV gathers while it stages x; otherwise x is gathered into
+ *                        x_scratch ([M,K], required then) by one extra launch.  x_perm NULL = mt_qgemm.
+ * Load-time functions may be called once per layer; none allocates or synchronises.
+ */
+int mt_act_order_perm(void* stream, const int32_t* g_idx, int32_t* perm, int* status, int k, int nr_groups);
+int mt_repack_rows(void* stream, const uint32_t* qweight, const int32_t* perm, uint32_t* qweight_out, int n, int k, int bits);
+int mt_gather_columns(void* stream, const void* x, const int32_t* perm, void* x_out, int m, int k, int dtype);
+int mt_qgemm_ordered(void* stream, const void* x, const int32_t* x_perm, void* x_scratch, const uint32_t* qweight,
+                     const uint32_t* qzeros, const void* scales, const void* bias, void* out,
+                     int m, int n, int k, int nr_groups, int bits, int dtype,
+                     void* workspace, size_t workspace_bytes, int flags);
+
+/*
  * NCCL plumbing with the reference's entry-point names (minit/nccl/library.py:41-58,
  * minit/nccl/kernel.py:47-57), returning a status instead of throwing.  libnccl is
  * opened with dlopen() on first use: mt_nccl_load(path) selects the file (NULL:

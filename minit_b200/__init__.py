@@ -6,8 +6,9 @@ examples/qwen1_5_int8.py, minit.distributed / minit.nccl / minit.collective) on 
 tensors, with every kernel reached through the C ABI of libminit_b200.so.
 """
 from . import _lib  # noqa: F401  (fails loudly when the CUDA library is not built)
-from .qlinear import (QLinear, QLinearWithBias, W8Linear, quantized_matrix_multiply,
-                      quantized_matrix_multiply_noalloc, unpack, w8_perchannel_matrix_multiply)
+from .qlinear import (QLinear, QLinearWithBias, W8Linear, pack_w8, quantized_matrix_multiply,
+                      quantized_matrix_multiply_noalloc, quantized_matrix_multiply_ordered, sort_act_order, unpack,
+                      w8_perchannel_matrix_multiply)
 from .quantize import Dequantize, QuantizedTensor, dequantize
 from .operator.linalg import MatrixMultiply
 from .functional.linalg import matrix_multiply
@@ -15,6 +16,7 @@ from .core.dispatch import dispatch, register_dispatch
 
 __all__ = [
     "QLinear", "QLinearWithBias", "W8Linear", "quantized_matrix_multiply", "quantized_matrix_multiply_noalloc", "w8_perchannel_matrix_multiply",
+    "quantized_matrix_multiply_ordered", "sort_act_order", "pack_w8",
     "unpack", "Dequantize", "QuantizedTensor", "dequantize", "MatrixMultiply", "matrix_multiply",
     "dispatch", "register_dispatch",
 ]

@@ -39,6 +39,11 @@ SYMBOLS = {
     "mt_qgemm_allreduce": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _i, _vp, _i, _i, _sz]),
     "mt_allreduce_buffer_bytes": (_sz, [_i, _i, _i]),
     "mt_decode_plan": (_i, [_i, _i, _i, _i, _i, _sz, _i]),
+    "mt_w8_pack": (_i, [_vp, _vp, _vp, _i, _i]),
+    "mt_act_order_perm": (_i, [_vp, _vp, _vp, _vp, _i, _i]),
+    "mt_repack_rows": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i]),
+    "mt_gather_columns": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i]),
+    "mt_qgemm_ordered": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _i]),
     "mt_qgemm_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i]),
     "mt_w8_perchannel_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _i]),
     "mt_nccl_load": (_i, [ctypes.c_char_p]),

@@ -304,6 +304,80 @@ size_t mt_allreduce_buffer_bytes(int m_max, int n_max, int world) {
     return kArDataOffset + 2 * (size_t)world * slot;
 }
 
+int mt_w8_pack(void* stream, const int8_t* w, uint32_t* qweight, int n, int k) {
+    if (n < 0 || k < 0 || n % 4 != 0 || k % 4 != 0) return MT_ERR_SHAPE;
+    if (n == 0 || k == 0) return MT_OK;
+    if (!w || !qweight) return MT_ERR_NULL;
+    if (!aligned16(w) || !aligned16(qweight)) return MT_ERR_ALIGN;
+    int rc = check_device();
+    if (rc != MT_OK) return rc;
+    return launch_w8_pack(static_cast<cudaStream_t>(stream), w, qweight, n, k);
+}
+
+int mt_act_order_perm(void* stream, const int32_t* g_idx, int32_t* perm, int* status, int k, int nr_groups) {
+    if (k < 0 || nr_groups < 1 || k % nr_groups != 0) return MT_ERR_SHAPE;
+    if (k == 0) return MT_OK;
+    if (!g_idx || !perm) return MT_ERR_NULL;
+    int rc = check_device();
+    if (rc != MT_OK) return rc;
+    return launch_act_order_perm(static_cast<cudaStream_t>(stream), g_idx, perm, status, k, nr_groups);
+}
+
+int mt_repack_rows(void* stream, const uint32_t* qweight, const int32_t* perm, uint32_t* qweight_out, int n, int k, int bits) {
+    if (bits != 4 && bits != 8) return MT_ERR_BITS;
+    if (n < 0 || k < 0 || k % (32 / bits) != 0) return MT_ERR_SHAPE;
+    if (n == 0 || k == 0) return MT_OK;
+    if (!qweight || !perm || !qweight_out) return MT_ERR_NULL;
+    if (qweight == qweight_out) return MT_ERR_SHAPE;             // not in place: rows are gathered
+    int rc = check_device();
+    if (rc != MT_OK) return rc;
+    return launch_repack_rows(static_cast<cudaStream_t>(stream), qweight, perm, qweight_out, n, k, bits);
+}
+
+int mt_gather_columns(void* stream, const void* x, const int32_t* perm, void* x_out, int m, int k, int dtype) {
+    if (dtype != MT_F16 && dtype != MT_BF16) return MT_ERR_DTYPE;
+    if (m < 0 || k < 0) return MT_ERR_SHAPE;
+    if (m == 0 || k == 0) return MT_OK;
+    if (!x || !perm || !x_out) return MT_ERR_NULL;
+    if (x == x_out) return MT_ERR_SHAPE;
+    int rc = check_device();
+    if (rc != MT_OK) return rc;
+    return launch_gather_columns(static_cast<cudaStream_t>(stream), x, perm, x_out, m, k);
+}
+
+int mt_qgemm_ordered(void* stream, const void* x, const int32_t* x_perm, void* x_scratch, const uint32_t* qweight,
+                     const uint32_t* qzeros, const void* scales, const void* bias, void* out,
+                     int m, int n, int k, int nr_groups, int bits, int dtype,
+                     void* workspace, size_t workspace_bytes, int flags) {
+    if (!x_perm) return mt_qgemm(stream, x, qweight, nullptr, qzeros, scales, bias, out, m, n, k, nr_groups, bits, dtype,
+                                 workspace, workspace_bytes, flags);
+    int rc = validate_gptq(qweight, qzeros, scales, n, k, nr_groups, bits, dtype);
+    if (rc != MT_OK) return rc;
+    if (m < 0) return MT_ERR_SHAPE;
+    if (m == 0 || n == 0) return MT_OK;
+    if (k == 0) return MT_ERR_SHAPE;
+    if (!x || !out) return MT_ERR_NULL;
+    if (!aligned16(x) || !aligned16(out) || !aligned16(x_perm) || (bias && !aligned16(bias))) return MT_ERR_ALIGN;
+    if ((k / nr_groups) % (4 * (32 / bits)) != 0) return MT_ERR_SHAPE;
+    if (workspace && !aligned16(workspace)) return MT_ERR_ALIGN;
+    if ((rc = check_device()) != MT_OK) return rc;
+    QGemmArgs a = {};
+    a.x = x; a.qweight = qweight; a.qzeros = qzeros; a.scales = scales; a.bias = bias; a.out = out;
+    a.m = m; a.n = n; a.k = k; a.groups = nr_groups; a.bits = bits; a.dtype = dtype;
+    a.workspace = workspace; a.workspace_bytes = workspace_bytes; a.flags = flags;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool forced_other = (flags & (MT_FLAG_FORCE_SMALL | MT_FLAG_FORCE_TC | MT_FLAG_FORCE_DTC)) != 0;
+    if (m <= 2 && !forced_other && vec_supported(a)) {          // the GEMV gathers while it stages the activations
+        a.x_perm = x_perm;
+        return launch_vec(st, a);
+    }
+    if (!x_scratch) return MT_ERR_NULL;
+    if (!aligned16(x_scratch)) return MT_ERR_ALIGN;
+    if ((rc = launch_gather_columns(st, x, x_perm, x_scratch, m, k)) != MT_OK) return rc;
+    return mt_qgemm(stream, x_scratch, qweight, nullptr, qzeros, scales, bias, out, m, n, k, nr_groups, bits, dtype,
+                    workspace, workspace_bytes, flags);
+}
+
 int mt_w8_perchannel_gemm(void* stream, const void* x, const int8_t* w, const void* scales,
                           const void* bias, void* out, int m, int n, int k, int dtype,
                           void* workspace, size_t workspace_bytes, int flags) {

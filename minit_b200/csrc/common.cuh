@@ -95,6 +95,7 @@ struct QGemmArgs {
     const void* bias;         // [N] T or null
     void* out;                // [M,N] T
     const int8_t* w8;         // per-channel path: [K,N] int8
+    const int32_t* x_perm;    // [K] or null: rows of qweight were sorted by group (act-order), read x through this permutation
     int m, n, k, groups, bits, dtype;
     void* workspace;
     size_t workspace_bytes;
@@ -123,6 +124,10 @@ int launch_dequant(cudaStream_t st, const uint32_t* qweight, const int32_t* g_id
                    const void* scales, void* w_out, int n, int k, int groups, int bits, int dtype);
 int launch_dequant_unpacked(cudaStream_t st, const uint8_t* q, const int32_t* g_idx, const uint8_t* z, const void* scales,
                             void* w_out, int n, int k, int groups, int dtype);
+int launch_w8_pack(cudaStream_t st, const int8_t* w, uint32_t* out, int n, int k);
+int launch_act_order_perm(cudaStream_t st, const int32_t* g_idx, int32_t* perm, int* status, int k, int groups);
+int launch_repack_rows(cudaStream_t st, const uint32_t* qw, const int32_t* perm, uint32_t* out, int n, int k, int bits);
+int launch_gather_columns(cudaStream_t st, const void* x, const int32_t* perm, void* out, int m, int k);
 int launch_unpack(cudaStream_t st, const uint32_t* packed, uint8_t* out, int rows, int cols, int bits, int axis);
 int launch_small(cudaStream_t st, const QGemmArgs& a);          // GPTQ layout, M <= 64 per launch
 int launch_small_w8(cudaStream_t st, const QGemmArgs& a);       // int8 [K,N] per-channel, M <= 64 per launch

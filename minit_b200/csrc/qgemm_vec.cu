@@ -42,6 +42,7 @@ constexpr int VEC_D = 8;        // packed rows in flight per thread
 
 struct VecParams {
     const void* x; const uint32_t* qw; const uint32_t* qz; const void* scales; const void* bias; void* out;
+    const int32_t* xperm;   // act-order: activations are read as x[perm[k]] (null: in order)
     unsigned* counters; float* partial;
     int m, n, k, groups;
     int cpg;          // chunks per group
@@ -77,6 +78,21 @@ __device__ __forceinline__ float h2sum(uint32_t h) {
 }
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi); return *reinterpret_cast<const uint32_t*>(&h); }
+
+// Eight consecutive activations of a row, optionally read through the act-order permutation
+// (x[perm[k0 .. k0+7]]): the weights' rows were sorted by group once, the activations follow here.
+template <typename T>
+__device__ __forceinline__ uint4 load_x8(const T* __restrict__ xrow, const int32_t* __restrict__ perm, size_t k0) {
+    if (!perm) return __ldg(reinterpret_cast<const uint4*>(xrow + k0));
+    const int4 i0 = __ldg(reinterpret_cast<const int4*>(perm + k0)), i1 = __ldg(reinterpret_cast<const int4*>(perm + k0 + 4));
+    const unsigned short* xs = reinterpret_cast<const unsigned short*>(xrow);
+    uint4 r;
+    r.x = uint32_t(__ldg(xs + i0.x)) | (uint32_t(__ldg(xs + i0.y)) << 16);
+    r.y = uint32_t(__ldg(xs + i0.z)) | (uint32_t(__ldg(xs + i0.w)) << 16);
+    r.z = uint32_t(__ldg(xs + i1.x)) | (uint32_t(__ldg(xs + i1.y)) << 16);
+    r.w = uint32_t(__ldg(xs + i1.z)) | (uint32_t(__ldg(xs + i1.w)) << 16);
+    return r;
+}
 
 // BITS 4 | 8; T the activation / scale type; MB batch rows; CK values of k per fold chunk (64 | 32)
 template <int BITS, typename T, int MB, int CK>
@@ -148,7 +164,7 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
         for (int i = 0; i < p.slice_ks; i += 32) {
             const int ks = i + lane;
             uint4 raw = make_uint4(0, 0, 0, 0);
-            if (row_ok && ks < nks) raw = __ldg(reinterpret_cast<const uint4*>(xg + (size_t)mb * p.k + ((size_t)c_lo * CKS + ks) * 8));
+            if (row_ok && ks < nks) raw = load_x8(xg + (size_t)mb * p.k, p.xperm, ((size_t)c_lo * CKS + ks) * 8);
             float f[8];
             const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
@@ -370,6 +386,7 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
 // ----------------------------------------------------------------------------------------------
 struct StreamParams {
     const void* x; const uint32_t* qw; const uint32_t* qz; const void* scales; const void* bias; void* out;
+    const int32_t* xperm;   // act-order: activations are read as x[perm[k]] (null: in order)
     unsigned* counters; float* partial;
     int m, n, k, groups;
     int cpg, nchunks, tiles;
@@ -440,7 +457,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
         const size_t k = (size_t)cl * CK + (size_t)(ks % CKS) * 8;
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb)
-            xr[mb] = (ok && mb < p.m) ? __ldg(reinterpret_cast<const uint4*>(xg + (size_t)mb * p.k + k)) : make_uint4(0, 0, 0, 0);
+            xr[mb] = (ok && mb < p.m) ? load_x8(xg + (size_t)mb * p.k, p.xperm, k) : make_uint4(0, 0, 0, 0);
     };
     auto stage_x = [&](int b, const uint4 (&xr)[MB]) {
         const int buf = b & 1;
@@ -845,6 +862,7 @@ int launch_stream_cfg(cudaStream_t st, const QGemmArgs& a, int ctas) {
     const int ck = gs % 64 == 0 ? 64 : 32;
     StreamParams p;
     p.x = a.x; p.qw = a.qweight; p.qz = a.qzeros; p.scales = a.scales; p.bias = a.bias; p.out = a.out;
+    p.xperm = a.x_perm;
     p.counters = static_cast<unsigned*>(a.workspace);
     p.partial = reinterpret_cast<float*>(static_cast<char*>(a.workspace) + kCounterBytes);
     p.m = a.m; p.n = a.n; p.k = a.k; p.groups = a.groups;
@@ -966,6 +984,7 @@ int launch_vec(cudaStream_t st, const QGemmArgs& a) {
     const int tiles = a.n / VEC_COLS;
     VecParams p;
     p.x = a.x; p.qw = a.qweight; p.qz = a.qzeros; p.scales = a.scales; p.bias = a.bias; p.out = a.out;
+    p.xperm = a.x_perm;
     p.counters = static_cast<unsigned*>(a.workspace);
     p.partial = reinterpret_cast<float*>(static_cast<char*>(a.workspace) + kCounterBytes);
     p.m = a.m; p.n = a.n; p.k = a.k; p.groups = a.groups;

@@ -83,6 +83,72 @@ def quantized_matrix_multiply(x: torch.Tensor, qweight: torch.Tensor, zeros: Opt
     return out
 
 
+def sort_act_order(qweight: torch.Tensor, g_idx: torch.Tensor, nr_groups: int, bits: int = 8):
+    """Load-time preparation of an act-order (desc_act) GPTQ layer: sort the rows of ``qweight`` by group
+    (stable), so that the contiguous-group kernels apply, and return ``(qweight_sorted, perm)``;
+    ``x[..., perm] @ W_sorted == x @ W``.  Raises when ``g_idx`` does not assign exactly K / nr_groups rows
+    to every group (such a layer stays on the g_idx kernel).  One device->host read of a status word."""
+    pack = 32 // bits
+    k0 = qweight.shape[0] * pack
+    if tuple(g_idx.shape) != (k0,) or g_idx.dtype != torch.int32 or qweight.dtype != torch.int32:
+        raise ValueError("qweight int32 [K/pack,N] and g_idx int32 [K] expected")
+    dev = _lib.require_cuda(qweight, g_idx)
+    perm = torch.empty(k0, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = torch.empty_like(qweight)
+    with torch.cuda.device(dev):
+        stream = _lib.current_stream(dev)
+        _lib.check(_lib.lib.mt_act_order_perm(stream, g_idx.data_ptr(), perm.data_ptr(), status.data_ptr(), k0, nr_groups),
+                   "mt_act_order_perm")
+        st = int(status.item())
+        if st != 0:
+            raise ValueError("g_idx is not a permutation of equal-sized groups" if st == 1 else "g_idx holds a group index out of range")
+        _lib.check(_lib.lib.mt_repack_rows(stream, qweight.data_ptr(), perm.data_ptr(), out.data_ptr(), qweight.shape[1], k0, bits),
+                   "mt_repack_rows")
+    return out, perm
+
+
+def quantized_matrix_multiply_ordered(x: torch.Tensor, qweight_sorted: torch.Tensor, zeros: Optional[torch.Tensor],
+                                      scales: torch.Tensor, perm: torch.Tensor, *, bits: int = 8,
+                                      bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                                      flags: int = 0) -> torch.Tensor:
+    """``quantized_matrix_multiply`` for a layer prepared with ``sort_act_order``: out = x[..., perm] @ W_sorted.
+    At M <= 2 the gather is part of the GEMV; for larger M one extra launch gathers x into a scratch tensor."""
+    pack = 32 // bits
+    *ms, k0 = x.shape
+    pk1, n0 = qweight_sorted.shape
+    g1 = scales.shape[0]
+    if k0 != pk1 * pack or scales.shape[1] != n0 or scales.dtype != x.dtype or tuple(perm.shape) != (k0,) or perm.dtype != torch.int32:
+        raise ValueError("shape or dtype mismatch between x, qweight, scales and perm")
+    dev = _lib.require_cuda(x, qweight_sorted, zeros, scales, perm, bias)
+    m = 1
+    for d in ms:
+        m *= d
+    if out is None:
+        out = torch.empty((*ms, n0), dtype=x.dtype, device=dev)
+    scratch = torch.empty((m, k0), dtype=x.dtype, device=dev) if m > 2 else None
+    stream = _lib.current_stream(dev)
+    ws = _lib.workspace(dev, stream, _lib.lib.mt_workspace_bytes(m, n0, k0, bits))
+    with torch.cuda.device(dev):
+        rc = _lib.lib.mt_qgemm_ordered(stream, x.data_ptr(), perm.data_ptr(), _lib.ptr(scratch), qweight_sorted.data_ptr(),
+                                       _lib.ptr(zeros), scales.data_ptr(), _lib.ptr(bias), out.data_ptr(), m, n0, k0, g1, bits,
+                                       _lib.dtype_code(x.dtype), ws.data_ptr(), ws.numel(), flags)
+    _lib.check(rc, "mt_qgemm_ordered")
+    return out
+
+
+def pack_w8(weight: torch.Tensor) -> torch.Tensor:
+    """Load-time: plain int8 weights [K,N] -> the 8-bit GPTQ word layout int32 [K/4,N] (stored value w + 128)."""
+    if weight.dtype != torch.int8 or weight.dim() != 2 or weight.shape[0] % 4 or weight.shape[1] % 4:
+        raise ValueError("weight must be int8 [K,N] with K and N multiples of 4")
+    dev = _lib.require_cuda(weight)
+    out = torch.empty((weight.shape[0] // 4, weight.shape[1]), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib.mt_w8_pack(_lib.current_stream(dev), weight.data_ptr(), out.data_ptr(), weight.shape[1], weight.shape[0]),
+                   "mt_w8_pack")
+    return out
+
+
 def quantized_matrix_multiply_noalloc(x: torch.Tensor, qweight: torch.Tensor, zeros: Optional[torch.Tensor],
                                       scales: torch.Tensor, groups: Optional[torch.Tensor], out: torch.Tensor, *,
                                       bits: int = 8, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -162,11 +228,13 @@ class QLinear(Module):
         self.scales = self.register_buffer("scales", (nr_groups, out_features), dtype)
         self.g_idx = self.register_buffer("g_idx", (in_features,), "int32")
         self._groups_arg = "unchecked"
+        self._sorted = None       # (qweight_sorted, perm) of an act-order layer, built on first use
 
     def update_buffer(self, name: str, value: torch.Tensor) -> None:
         super().update_buffer(name, value)
-        if name == "g_idx":
+        if name in ("g_idx", "qweight"):
             self._groups_arg = "unchecked"
+            self._sorted = None
 
     def _groups(self):
         # a g_idx that is just k // group_size selects the faster contiguous-group kernel;
@@ -180,8 +248,24 @@ class QLinear(Module):
         return QuantizedTensor(unpack(self.qweight, 0, self.bits), self.g_idx, unpack(self.qzeros, 1, self.bits),
                                self.scales, packed=(self.qweight, self.qzeros, self.bits))
 
+    def _matmul(self, x: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+        groups = self._groups()
+        if groups is None:
+            return quantized_matrix_multiply(x, self.qweight, self.qzeros, self.scales, None, bits=self.bits, bias=bias)
+        # act-order: sort the rows by group once (a second copy of qweight), then every call is a contiguous-group
+        # kernel reading x through the permutation; a g_idx with unequal groups keeps the per-k lookup kernel
+        if self._sorted is None:
+            try:
+                self._sorted = sort_act_order(self.qweight, self.g_idx, self.scales.shape[0], self.bits)
+            except ValueError:
+                self._sorted = False
+        if self._sorted is False:
+            return quantized_matrix_multiply(x, self.qweight, self.qzeros, self.scales, groups, bits=self.bits, bias=bias)
+        qw, perm = self._sorted
+        return quantized_matrix_multiply_ordered(x, qw, self.qzeros, self.scales, perm, bits=self.bits, bias=bias)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return quantized_matrix_multiply(x, self.qweight, self.qzeros, self.scales, self._groups(), bits=self.bits)
+        return self._matmul(x, None)
 
 
 class QLinearWithBias(QLinear):
@@ -192,8 +276,7 @@ class QLinearWithBias(QLinear):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         # the reference adds the bias with two extra kernels (examples/qwen1_5_int8.py:313-316); here it is the GEMM epilogue
-        return quantized_matrix_multiply(x, self.qweight, self.qzeros, self.scales, self._groups(), bits=self.bits,
-                                         bias=self.bias)
+        return self._matmul(x, self.bias)
 
 
 class W8Linear(Module):
@@ -204,6 +287,19 @@ class W8Linear(Module):
         self.weight = self.register_buffer("weight", (in_features, out_features), "int8")
         self.scales = self.register_buffer("scales", (out_features,), dtype)
         self.bias = self.register_buffer("bias", (out_features,), dtype) if bias else None
+        self._packed = None       # the weights in the GPTQ word layout, built on first use
+
+    def update_buffer(self, name: str, value: torch.Tensor) -> None:
+        super().update_buffer(name, value)
+        if name == "weight":
+            self._packed = None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return w8_perchannel_matrix_multiply(x, self.weight, self.scales, bias=self.bias)
+        # packed once into the 8-bit GPTQ layout (one group, stored zero 127) the layer runs on the GPTQ kernels:
+        # CUDA-core GEMV at M <= 2, tcgen05 at M > 64
+        k0, n0 = self.weight.shape
+        if k0 % 32 or n0 % 8:
+            return w8_perchannel_matrix_multiply(x, self.weight, self.scales, bias=self.bias)
+        if self._packed is None:
+            self._packed = pack_w8(self.weight)
+        return quantized_matrix_multiply(x, self._packed, None, self.scales.view(1, -1), None, bits=8, bias=self.bias)
