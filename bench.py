@@ -350,7 +350,7 @@ def run_single_shape(args):
         sets.append((qw, qz, sc))
     x = torch.randn((m, k), device=dev, dtype=torch.float32).to(dtype)
     out = torch.empty((m, n), device=dev, dtype=dtype)
-    flags = {"auto": 0, "ring": 1, "tc": 2, "dtc": 8, "vec": 16}[args.kernel] | (4 if args.pdl and args.kernel in ("auto", "ring", "vec") else 0) | args.tune
+    flags = {"auto": 0, "ring": 1, "tc": 2, "dtc": 8, "vec": 16, "umma": 32}[args.kernel] | (4 if args.pdl and args.kernel in ("auto", "ring", "vec") else 0) | args.tune
 
     def one():
         for qw, qz, sc in sets:
@@ -391,7 +391,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--single-shape", default=None, help="K,N : time one linear instead of the workload (profiling aid)")
     ap.add_argument("--tune", type=lambda v: int(v, 0), default=0, help="single-shape mode: extra tuning bits ORed into the flags")
-    ap.add_argument("--kernel", default="auto", choices=["auto", "ring", "dtc", "tc", "vec"])
+    ap.add_argument("--kernel", default="auto", choices=["auto", "ring", "dtc", "tc", "vec", "umma"])
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--bf16", action="store_true")
     args = ap.parse_args()

@@ -180,7 +180,12 @@ size_t mt_workspace_bytes(int m, int n, int k, int bits) {
     if (m <= 0 || n <= 0 || k <= 0 || (bits != 4 && bits != 8)) return kCounterBytes;
     // split-K keeps splits * min(m,64) <= k*bits/256 + 64 rows of fp32 partials
     const size_t rows = (size_t)k * bits / 256 + 64;
-    return kCounterBytes + rows * (size_t)n * 4;
+    size_t bytes = rows * (size_t)n * 4;
+    if (m > 2 && m <= 192 && k % 64 == 0) {                     // fp32 partial tiles of the mid-batch kernel
+        const size_t mid = umma_workspace_bytes(m, n, k);
+        if (mid > bytes) bytes = mid;
+    }
+    return kCounterBytes + bytes;
 }
 
 static int validate_gptq(const uint32_t* qweight, const uint32_t* qzeros, const void* scales,
@@ -253,7 +258,11 @@ int mt_qgemm(void* stream, const void* x, const uint32_t* qweight, const int32_t
     if (flags & MT_FLAG_FORCE_SMALL) return launch_small(st, a);
     if (flags & MT_FLAG_FORCE_DTC) return dtc_supported(a) ? launch_dtc(st, a) : MT_ERR_UNSUPPORTED;
     if (flags & MT_FLAG_FORCE_VEC) return vec_supported(a) ? launch_vec(st, a) : MT_ERR_UNSUPPORTED;
+    if (flags & MT_FLAG_FORCE_UMMA) return umma_supported(a) ? launch_umma(st, a) : MT_ERR_UNSUPPORTED;
     if (m > 64 && tc_supported(a)) return launch_tc(st, a);
+    // 32 < M <= 64: the register-ring kernel is bound by the legacy mma.sync rate (0.13-0.19 of HBM peak);
+    // the tcgen05 kernel with sixteen converting warps holds 0.21-0.26 whatever M
+    if (m > 32 && umma_supported(a)) return launch_umma(st, a);
     // Decode at M <= 2: the CUDA-core GEMV (packed integers multiplied as fp16 subnormals) streams
     // 1.5-2x faster than either tensor-core decode kernel on every shape measured.
     if (m <= 2 && vec_supported(a)) return launch_vec(st, a);

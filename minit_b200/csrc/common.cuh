@@ -136,6 +136,9 @@ bool dtc_supported(const QGemmArgs& a);
 int launch_vec(cudaStream_t st, const QGemmArgs& a);            // CUDA-core decode GEMV, M <= 2, contiguous groups
 bool vec_supported(const QGemmArgs& a);
 int vec_plan(const QGemmArgs& a);                               // > 0 split-K factor, 0 stream-K, < 0 MT_ERR_*
+int launch_umma(cudaStream_t st, const QGemmArgs& a);           // tcgen05 with all-warp dequant, 2 < M <= 192, contiguous groups
+bool umma_supported(const QGemmArgs& a);
+size_t umma_workspace_bytes(int m, int n, int k);
 int launch_tc(cudaStream_t st, const QGemmArgs& a);             // tcgen05 path (any M), GPTQ layout without g_idx
 bool tc_supported(const QGemmArgs& a);
 
