@@ -259,10 +259,18 @@ int mt_qgemm(void* stream, const void* x, const uint32_t* qweight, const int32_t
     if (flags & MT_FLAG_FORCE_DTC) return dtc_supported(a) ? launch_dtc(st, a) : MT_ERR_UNSUPPORTED;
     if (flags & MT_FLAG_FORCE_VEC) return vec_supported(a) ? launch_vec(st, a) : MT_ERR_UNSUPPORTED;
     if (flags & MT_FLAG_FORCE_UMMA) return umma_supported(a) ? launch_umma(st, a) : MT_ERR_UNSUPPORTED;
+    // Mid-size batches: the tcgen05 kernel with sixteen converting warps holds 0.24-0.31 of HBM peak up to
+    // M = 64 on large weights, where the register-ring kernel falls from 0.25 (M = 16) to 0.13 (M = 64) with
+    // the legacy mma.sync rate; it costs ~12 us of set-up, so small weights stay on the ring kernel until
+    // M > 32.  Between 64 and 128 rows two passes of it beat the prefill kernels when K is deep (their
+    // grid has no split along K).
+    const long long weights = (long long)k * n;
+    if (umma_supported(a)) {
+        if (m > 32 && m <= 64) return launch_umma(st, a);
+        if (m > 8 && m <= 32 && weights >= (128LL << 20)) return launch_umma(st, a);
+        if (m > 64 && m <= 128 && k >= 8192) return launch_umma(st, a);
+    }
     if (m > 64 && tc_supported(a)) return launch_tc(st, a);
-    // 32 < M <= 64: the register-ring kernel is bound by the legacy mma.sync rate (0.13-0.19 of HBM peak);
-    // the tcgen05 kernel with sixteen converting warps holds 0.21-0.26 whatever M
-    if (m > 32 && umma_supported(a)) return launch_umma(st, a);
     // Decode at M <= 2: the CUDA-core GEMV (packed integers multiplied as fp16 subnormals) streams
     // 1.5-2x faster than either tensor-core decode kernel on every shape measured.
     if (m <= 2 && vec_supported(a)) return launch_vec(st, a);

@@ -18,8 +18,8 @@
 //                       TMEM, B from shared memory, fp32 accumulators in TMEM for the CTA's whole
 //                       run of a column tile (scales are already in the weights: no per-group fold).
 //                       One such MMA costs ~46 cycles whatever N <= 91: the HBM rate at N = 16 and 64 alike.
-//   1 producer warp     1-D bulk copies of the packed rows (1 KB contiguous each) into an 8-stage ring:
-//                       64 KB in flight per SM, tracked by the copy engine.
+//   1 producer warp     one 2-D tensor copy (TMA) per k-block of the CTA tile into an 8-stage ring: 64 KB
+//                       in flight per SM, tracked by the copy engine.
 //   2 loader warps      x[m, k-block] -> the B operand tile (K-major, 128-byte swizzle), k-slots in the
 //                       order the converter produces them.
 //   epilogue            the converter warps drain the accumulators at the end of a run's part of a tile
@@ -93,6 +93,17 @@ __device__ __forceinline__ uint64_t um_desc_sw128(uint32_t saddr) {
 // Bounded wait that does not poll: mbarrier.try_wait with a suspend-time hint parks the thread until the
 // phase completes or the hint expires, so waiting warps leave the issue slots to the converters.
 __device__ __forceinline__ bool um_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#ifdef UM_SPIN
+    for (int i = 0; i < (1 << 26); ++i) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((i & 4095) == 4095 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+#endif
     for (int i = 0; i < (1 << 20); ++i) {                // ~1 us per turn: gives up after about a second
         uint32_t ok;
         asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.b32 %0, 1, 0, p;\n}"
@@ -123,7 +134,7 @@ template <int BITS, int BM> struct UmSmem {
 
 // BITS 4 | 8; T __half | __nv_bfloat16 (8-bit needs __half: 128 + b is not exact in bf16); BM batch rows per pass (16 | 32 | 64)
 template <int BITS, typename T, int BM>
-__global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const UmParams p) {
+__global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const UmParams p) {
     using S = UmSmem<BITS, BM>;
     using H = F16x2<T>;
     constexpr int PACK = 32 / BITS, PROWS = 64 / PACK;               // packed rows per k-block: 8 | 16
@@ -152,7 +163,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const UmParam
 
     if (tid == 0) {
         abort_flag = 0;
-        for (int s = 0; s < UM_ASTAGES; ++s) { mbar_init(bar_afull(s), 4); mbar_init(bar_aempty(s), 1); }
+        for (int s = 0; s < UM_ASTAGES; ++s) { mbar_init(bar_afull(s), 4 + 1); mbar_init(bar_aempty(s), 1); }   // both operands of a k-block meet at one barrier
         for (int s = 0; s < UM_BSTAGES; ++s) { mbar_init(bar_bfull(s), UM_LOADERS); mbar_init(bar_bempty(s), 1); }
         mbar_init(bar_dfull, 1); mbar_init(bar_dempty, UM_CONV); mbar_init(bar_esync, UM_CONV);
         for (int s = 0; s < S::PSTAGES; ++s) { mbar_init(bar_pfull(s), 1); mbar_init(bar_pempty(s), 4); }
@@ -196,69 +207,70 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const UmParam
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BM >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
             int seg = 0; bool ok = true;
             int kb = x0 % p.kbt;
-            for (int i = 0; i < nrun && ok; ++i, kb = (kb + 1 == p.kbt ? 0 : kb + 1)) {
-                const bool first = (i == 0) || (kb == 0);
-                const bool last = (i == nrun - 1) || (kb == p.kbt - 1);
-                UM_SLOT(0);
-                if (first) { if (!wait(bar_dempty, (seg & 1) ^ 1)) { ok = false; break; } }
-                const int as = i % UM_ASTAGES; const uint32_t aph = (i / UM_ASTAGES) & 1;
-                const int bs = i % UM_BSTAGES; const uint32_t bph = (i / UM_BSTAGES) & 1;
-                UM_SLOT(1);
-                if (!wait(bar_bfull(bs), bph)) { ok = false; break; }
-                UM_SLOT(2);
-                if (!wait(bar_afull(as), aph)) { ok = false; break; }
-                um_fence_after();
-#ifdef MT_UMMA_TIMING
-                const long long t_m0 = clock64();
-#endif
-                const uint64_t bdesc = um_desc_sw128(sbase + S::OFF_B + bs * S::B_BYTES);
+            uint32_t aph = 0;                            // parity of the ring pass
+            for (int i0 = 0; i0 < nrun && ok; i0 += UM_ASTAGES, aph ^= 1u) {
 #pragma unroll
-                for (int k4 = 0; k4 < 4; ++k4)
+                for (int as = 0; as < UM_ASTAGES; ++as) {        // slot index is static: addresses and descriptors fold to constants
+                    const int i = i0 + as;
+                    if (i >= nrun) break;
+                    const bool first = (i == 0) || (kb == 0);
+                    const bool last = (i == nrun - 1) || (kb == p.kbt - 1);
+                    kb = (kb + 1 == p.kbt) ? 0 : kb + 1;
+                    UM_SLOT(0);
+                    if (first) { if (!wait(bar_dempty, (seg & 1) ^ 1)) { ok = false; break; } }
+                    UM_SLOT(2);
+                    if (!wait(bar_afull(as), aph)) { ok = false; break; }
+                    um_fence_after();
+#ifdef MT_UMMA_TIMING
+                    const long long t_m0 = clock64();
+#endif
+                    const uint64_t bdesc = um_desc_sw128(sbase + S::OFF_B + as * S::B_BYTES);
 #pragma unroll
-                    for (int nt = 0; nt < UM_NT; ++nt)
-                        um_mma_ts(tmem_base + (uint32_t)(nt * BM), tmem_a + (uint32_t)((as * UM_NT + nt) * 32 + k4 * 8),
-                                  bdesc + (uint64_t)(k4 * 2), idesc, (first && k4 == 0) ? 0u : 1u);
+                    for (int k4 = 0; k4 < 4; ++k4)
+#pragma unroll
+                        for (int nt = 0; nt < UM_NT; ++nt)
+                            um_mma_ts(tmem_base + (uint32_t)(nt * BM), tmem_a + (uint32_t)((as * UM_NT + nt) * 32 + k4 * 8),
+                                      bdesc + (uint64_t)(k4 * 2), idesc, (first && k4 == 0) ? 0u : 1u);
 #ifdef MT_UMMA_TIMING
-                const long long t_m1 = clock64();
-                tw[3] += t_m1 - t_m0;
+                    const long long t_m1 = clock64();
+                    tw[3] += t_m1 - t_m0;
 #endif
-                um_commit(bar_aempty(as));               // frees the A slot and the B slot of this k-block
-                if (last) { um_commit(bar_dfull); ++seg; }
+                    um_commit(bar_aempty(as));           // frees the A slot and the B slot of this k-block
+                    if (last) { um_commit(bar_dfull); ++seg; }
 #ifdef MT_UMMA_TIMING
-                tw[4] += clock64() - t_m1;
+                    tw[4] += clock64() - t_m1;
 #endif
+                }
             }
         }
     } else if (warp == UM_W_PROD) {
         // ------------------------------ packed-weight producer ------------------------------
-        // One 1-D bulk copy per packed row of the CTA tile (1 KB contiguous), one lane per row: the copy
-        // engine tracks the bytes in flight, not the load/store unit (4-byte loads per thread cap the SM
-        // near 1.4 TB/s: too many requests for the bytes they carry).
+        // One 2-D tensor copy per k-block: the box is the CTA tile's 256 columns x the k-block's packed rows
+        // (8 | 16 KB; columns beyond N are zero-filled).  The copy engine tracks the bytes in flight, not the
+        // load/store unit: 4-byte loads per thread capped the SM near 1.4 TB/s, and one 1 KB bulk copy per
+        // packed row is eight times the descriptors for the same bytes.
         int tile = x0 / p.kbt, kb = x0 - tile * p.kbt;
         bool ok = true;
         for (int i = 0; i < nrun && ok; ++i) {
             const int ps = i % S::PSTAGES; const uint32_t pph = (i / S::PSTAGES) & 1;
             if (!wait(bar_pempty(ps), pph ^ 1)) { ok = false; break; }
-            const int col0 = tile * UM_COLS;
-            const uint32_t row_bytes = (uint32_t)(p.n - col0 < UM_COLS ? p.n - col0 : UM_COLS) * 4u;
-            if (lane == 0) mbar_expect_tx(bar_pfull(ps), row_bytes * PROWS);
-            __syncwarp();
-            if (lane < PROWS) {
-                const uint32_t dst = sbase + S::OFF_P + ps * S::P_BYTES + lane * (UM_COLS * 4);
-                const uint32_t* src = p.qw + ((size_t)kb * PROWS + lane) * p.n + col0;
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                             ::"r"(dst), "l"(src), "r"(row_bytes), "r"(bar_pfull(ps)) : "memory");
+            if (lane == 0) {
+                mbar_expect_tx(bar_pfull(ps), (uint32_t)S::P_BYTES);
+                tma_load_2d(sbase + S::OFF_P + ps * S::P_BYTES, &tmap_q, tile * UM_COLS, kb * PROWS, bar_pfull(ps));
             }
+            __syncwarp();
             if (++kb == p.kbt) { kb = 0; ++tile; }
         }
     } else if (warp >= UM_W_LOAD) {
         // ------------------------------ B loaders ------------------------------
-        // 16-byte units of a tile: BM rows x 8; loader lw takes units [lw * BM * 4, (lw + 1) * BM * 4).
-        // A lane copies its units raw into a staging ring with cp.async, UM_XSTAGES k-blocks ahead (an L2
-        // round trip per k-block would otherwise pace the whole kernel), and later moves the ones it copied
-        // itself into the operand tile, permuting the k-slots on the way.
+        // Loader lw builds the operand tiles of k-blocks lw, lw + 2, ... (two independent chains hide each
+        // other's latencies).  A tile is BM rows x 8 units of 16 bytes.  A lane copies its units raw into a
+        // staging ring with cp.async, three of its k-blocks ahead (an L2 round trip per k-block would
+        // otherwise pace the whole kernel), and later moves the ones it copied itself into the operand
+        // tile, permuting the k-slots on the way.
         const int lw = warp - UM_W_LOAD;
-        constexpr int UPL = BM * 4 / 32;                 // units per lane per k-block
+        constexpr int UPL = BM * 8 / 32;                 // units per lane per k-block
+        constexpr int AHEAD = UM_XSTAGES / UM_LOADERS;   // k-blocks of this loader in flight
         const T* __restrict__ xg = reinterpret_cast<const T*>(p.x);
         const uint32_t stage_s = sbase + S::OFF_XS;
         auto issue = [&](int i) {
@@ -266,7 +278,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const UmParam
                 const int kb = (x0 + i) % p.kbt;
 #pragma unroll
                 for (int t = 0; t < UPL; ++t) {
-                    const int un = lw * (BM * 4) + t * 32 + lane;
+                    const int un = t * 32 + lane;
                     const int row = un >> 3, ch = un & 7;
                     const bool live = row < p.m;
                     const T* src = xg + (live ? (size_t)row * p.k + (size_t)kb * 64 + ch * 8 : 0);
@@ -278,11 +290,11 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const UmParam
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
 #pragma unroll
-        for (int d = 0; d < UM_XSTAGES - 1; ++d) issue(d);
+        for (int d = 0; d < AHEAD - 1; ++d) issue(lw + UM_LOADERS * d);
         bool ok = true;
-        for (int i = 0; i < nrun && ok; ++i) {
-            issue(i + UM_XSTAGES - 1);
-            asm volatile("cp.async.wait_group %0;" ::"n"(UM_XSTAGES - 1) : "memory");
+        for (int i = lw; i < nrun && ok; i += UM_LOADERS) {
+            issue(i + UM_LOADERS * (AHEAD - 1));
+            asm volatile("cp.async.wait_group %0;" ::"n"(AHEAD - 1) : "memory");
             const int bs = i % UM_BSTAGES; const uint32_t bph = (i / UM_BSTAGES) & 1;
             UM_SLOT(0);
             if (!wait(bar_aempty(bs), bph ^ 1)) { ok = false; break; }
@@ -290,7 +302,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const UmParam
             const unsigned char* raw_s = smem + S::OFF_XS + (i % UM_XSTAGES) * S::B_BYTES;
 #pragma unroll
             for (int t = 0; t < UPL; ++t) {
-                const int un = lw * (BM * 4) + t * 32 + lane;
+                const int un = t * 32 + lane;
                 const int row = un >> 3, ch = un & 7;
                 uint4 v = *reinterpret_cast<const uint4*>(raw_s + un * 16);
                 if constexpr (BITS == 4) {               // (h0..h7) -> (h0,h4,h1,h5,h2,h6,h3,h7): the k-slot order of the A registers
@@ -303,7 +315,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const UmParam
             }
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_bfull(bs));
+            if (lane == 0) mbar_arrive(bar_afull(bs));
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else {
@@ -510,7 +522,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const UmParam
 }
 
 template <int BITS, typename T, int BM>
-int launch_inst(cudaStream_t st, const UmParams& p, int grid) {
+int launch_inst(cudaStream_t st, const CUtensorMap& mq, const UmParams& p, int grid) {
     using S = UmSmem<BITS, BM>;
     auto kern = qgemm_umma_kernel<BITS, T, BM>;
     static bool configured[64] = {};
@@ -520,15 +532,15 @@ int launch_inst(cudaStream_t st, const UmParams& p, int grid) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
         configured[dev] = true;
     }
-    kern<<<grid, UM_THREADS, S::TOTAL, st>>>(p);
+    kern<<<grid, UM_THREADS, S::TOTAL, st>>>(mq, p);
     return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_CUDA;
 }
 
 template <int BITS, typename T>
-int launch_bm(cudaStream_t st, const UmParams& p, int grid, int bm) {
-    if (bm == 16) return launch_inst<BITS, T, 16>(st, p, grid);
-    if (bm == 32) return launch_inst<BITS, T, 32>(st, p, grid);
-    return launch_inst<BITS, T, 64>(st, p, grid);
+int launch_bm(cudaStream_t st, const CUtensorMap& mq, const UmParams& p, int grid, int bm) {
+    if (bm == 16) return launch_inst<BITS, T, 16>(st, mq, p, grid);
+    if (bm == 32) return launch_inst<BITS, T, 32>(st, mq, p, grid);
+    return launch_inst<BITS, T, 64>(st, mq, p, grid);
 }
 
 int plan(const QGemmArgs& a, int m, int& grid, int& bm, size_t& need) {
@@ -557,6 +569,7 @@ bool umma_supported(const QGemmArgs& a) {
     if ((a.n + UM_COLS - 1) / UM_COLS >= kMaxTiles - 1) return false;
     if ((long long)((a.n + UM_COLS - 1) / UM_COLS) * (a.k / 64) > (1LL << 30)) return false;
     if (a.workspace == nullptr || a.workspace_bytes < kCounterBytes) return false;
+    if (!get_tensor_map_encoder()) return false;
     int grid, bm; size_t need;
     plan(a, a.m < 64 ? a.m : 64, grid, bm, need);
     return need <= a.workspace_bytes - kCounterBytes;
@@ -572,6 +585,18 @@ size_t umma_workspace_bytes(int m, int n, int k) {
 
 int launch_umma(cudaStream_t st, const QGemmArgs& a) {
     if (!umma_supported(a)) return MT_ERR_UNSUPPORTED;
+    CUtensorMap mq;
+    {
+        const int pack = 32 / a.bits;
+        cuuint64_t dims[2] = {(cuuint64_t)a.n, (cuuint64_t)(a.k / pack)};
+        cuuint64_t strides[1] = {(cuuint64_t)a.n * 4};
+        cuuint32_t box[2] = {(cuuint32_t)UM_COLS, (cuuint32_t)(64 / pack)};
+        cuuint32_t es[2] = {1, 1};
+        if (get_tensor_map_encoder()(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(a.qweight), dims, strides, box, es,
+                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return MT_ERR_CUDA;
+    }
     for (int r0 = 0; r0 < a.m; r0 += 64) {
         const int m = a.m - r0 < 64 ? a.m - r0 : 64;
         int grid, bm; size_t need;
@@ -588,8 +613,8 @@ int launch_umma(cudaStream_t st, const QGemmArgs& a) {
         p.per = p.units / grid; p.rem = p.units % grid;
         p.zp1_const = 1 << (a.bits - 1);
         int rc;
-        if (a.bits == 4) rc = a.dtype == MT_F16 ? launch_bm<4, __half>(st, p, grid, bm) : launch_bm<4, __nv_bfloat16>(st, p, grid, bm);
-        else rc = launch_bm<8, __half>(st, p, grid, bm);
+        if (a.bits == 4) rc = a.dtype == MT_F16 ? launch_bm<4, __half>(st, mq, p, grid, bm) : launch_bm<4, __nv_bfloat16>(st, mq, p, grid, bm);
+        else rc = launch_bm<8, __half>(st, mq, p, grid, bm);
         if (rc != MT_OK) return rc;
     }
     return MT_OK;
