@@ -339,7 +339,9 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
         int f_i = grp;
         int f_tile = (x0 + f_i) / p.kbt, f_kb = (x0 + f_i) - f_tile * p.kbt;
         int f_g = f_kb / kpg, f_kin = f_kb - f_g * kpg;
-        uint32_t sr[UM_NT], zr[UM_NT], sr_n[UM_NT], zr_n[UM_NT];
+        constexpr int SZ = 3;                            // turns of scale / zero words in flight: they stream from HBM (nothing
+                                                         // else reads them), so one turn ahead is less than their latency
+        uint32_t sr[UM_NT], zr[UM_NT], sr_n[SZ][UM_NT], zr_n[SZ][UM_NT];
         auto fetch = [&](uint32_t (&s)[UM_NT], uint32_t (&z)[UM_NT]) {
             const bool live = f_i < nrun;
 #pragma unroll
@@ -359,7 +361,8 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
                 f_g = f_kb / kpg; f_kin = f_kb - f_g * kpg;
             }
         };
-        fetch(sr_n, zr_n);
+#pragma unroll
+        for (int d = 0; d < SZ; ++d) fetch(sr_n[d], zr_n[d]);
 
         int seg = 0, nsync = 0; bool ok = true;
         // bounded meeting of the converter warps (an mbarrier, not bar.sync: a warp that gave up must not hang the others)
@@ -438,8 +441,12 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
             drain_until(i);                              // tiles that ended before this unit: this warp has converted its share of them
             if (!ok) break;
 #pragma unroll
-            for (int nt = 0; nt < UM_NT; ++nt) { sr[nt] = sr_n[nt]; zr[nt] = zr_n[nt]; }
-            fetch(sr_n, zr_n);
+            for (int nt = 0; nt < UM_NT; ++nt) { sr[nt] = sr_n[0][nt]; zr[nt] = zr_n[0][nt]; }
+#pragma unroll
+            for (int d = 0; d + 1 < SZ; ++d)
+#pragma unroll
+                for (int nt = 0; nt < UM_NT; ++nt) { sr_n[d][nt] = sr_n[d + 1][nt]; zr_n[d][nt] = zr_n[d + 1][nt]; }
+            fetch(sr_n[SZ - 1], zr_n[SZ - 1]);
             const int as = i % UM_ASTAGES; const uint32_t aph = (i / UM_ASTAGES) & 1;
             const int ps = i % S::PSTAGES; const uint32_t pph = (i / S::PSTAGES) & 1;
             UM_SLOT(3);
