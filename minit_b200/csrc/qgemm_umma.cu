@@ -43,6 +43,7 @@ constexpr int UM_LOADERS = 2;
 constexpr int UM_W_PROD = UM_W_LOAD + UM_LOADERS;   // warp 19: bulk-copy producer of the packed weights
 constexpr int UM_THREADS = (UM_CONV + 1 + UM_LOADERS + 1) * 32;   // 640
 constexpr int UM_ASTAGES = 6;               // A ring in TMEM (k-blocks): 6 x 64 columns + 128 accumulator columns = all 512
+constexpr int UM_NPAIR = UM_ASTAGES / 2;     // k-block pairs in the rings
 constexpr int UM_BSTAGES = UM_ASTAGES;      // B ring in shared memory: slot i % 4 like the A ring, so one barrier frees both
 constexpr int UM_XSTAGES = 6;               // raw activation tiles in flight per loader (k-blocks)
 
@@ -163,7 +164,9 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
 
     if (tid == 0) {
         abort_flag = 0;
-        for (int s = 0; s < UM_ASTAGES; ++s) { mbar_init(bar_afull(s), 4 + 1); mbar_init(bar_aempty(s), 1); }   // both operands of a k-block meet at one barrier
+        // one full / empty barrier per PAIR of k-blocks (slots 2p, 2p+1): both operands of both k-blocks meet there, so the
+        // MMA thread waits and commits once per 16 MMAs (its per-hand-off cost, not the MMAs, paces the kernel)
+        for (int s = 0; s < UM_NPAIR; ++s) { mbar_init(bar_afull(s), 2 * (4 + 1)); mbar_init(bar_aempty(s), 1); }
         for (int s = 0; s < UM_BSTAGES; ++s) { mbar_init(bar_bfull(s), UM_LOADERS); mbar_init(bar_bempty(s), 1); }
         mbar_init(bar_dfull, 1); mbar_init(bar_dempty, UM_CONV); mbar_init(bar_esync, UM_CONV);
         for (int s = 0; s < S::PSTAGES; ++s) { mbar_init(bar_pfull(s), 1); mbar_init(bar_pempty(s), 4); }
@@ -210,33 +213,41 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
             uint32_t aph = 0;                            // parity of the ring pass
             for (int i0 = 0; i0 < nrun && ok; i0 += UM_ASTAGES, aph ^= 1u) {
 #pragma unroll
-                for (int as = 0; as < UM_ASTAGES; ++as) {        // slot index is static: addresses and descriptors fold to constants
-                    const int i = i0 + as;
-                    if (i >= nrun) break;
-                    const bool first = (i == 0) || (kb == 0);
-                    const bool last = (i == nrun - 1) || (kb == p.kbt - 1);
-                    kb = (kb + 1 == p.kbt) ? 0 : kb + 1;
-                    UM_SLOT(0);
-                    if (first) { if (!wait(bar_dempty, (seg & 1) ^ 1)) { ok = false; break; } }
+                for (int pr = 0; pr < UM_NPAIR; ++pr) {          // slot indices are static: addresses and descriptors fold to constants
+                    if (i0 + 2 * pr >= nrun || !ok) break;
                     UM_SLOT(2);
-                    if (!wait(bar_afull(as), aph)) { ok = false; break; }
+                    if (!wait(bar_afull(pr), aph)) { ok = false; break; }
                     um_fence_after();
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int as = 2 * pr + h;
+                        const int i = i0 + as;
+                        if (i >= nrun) break;
+                        const bool first = (i == 0) || (kb == 0);
+                        const bool last = (i == nrun - 1) || (kb == p.kbt - 1);
+                        kb = (kb + 1 == p.kbt) ? 0 : kb + 1;
+                        UM_SLOT(0);
+                        if (first) { if (!wait(bar_dempty, (seg & 1) ^ 1)) { ok = false; break; } um_fence_after(); }
 #ifdef MT_UMMA_TIMING
-                    const long long t_m0 = clock64();
+                        const long long t_m0 = clock64();
 #endif
-                    const uint64_t bdesc = um_desc_sw128(sbase + S::OFF_B + as * S::B_BYTES);
+                        const uint64_t bdesc = um_desc_sw128(sbase + S::OFF_B + as * S::B_BYTES);
 #pragma unroll
-                    for (int k4 = 0; k4 < 4; ++k4)
+                        for (int k4 = 0; k4 < 4; ++k4)
 #pragma unroll
-                        for (int nt = 0; nt < UM_NT; ++nt)
-                            um_mma_ts(tmem_base + (uint32_t)(nt * BM), tmem_a + (uint32_t)((as * UM_NT + nt) * 32 + k4 * 8),
-                                      bdesc + (uint64_t)(k4 * 2), idesc, (first && k4 == 0) ? 0u : 1u);
+                            for (int nt = 0; nt < UM_NT; ++nt)
+                                um_mma_ts(tmem_base + (uint32_t)(nt * BM), tmem_a + (uint32_t)((as * UM_NT + nt) * 32 + k4 * 8),
+                                          bdesc + (uint64_t)(k4 * 2), idesc, (first && k4 == 0) ? 0u : 1u);
+#ifdef MT_UMMA_TIMING
+                        tw[3] += clock64() - t_m0;
+#endif
+                        if (last) { um_commit(bar_dfull); ++seg; }
+                    }
+                    if (!ok) break;
 #ifdef MT_UMMA_TIMING
                     const long long t_m1 = clock64();
-                    tw[3] += t_m1 - t_m0;
 #endif
-                    um_commit(bar_aempty(as));           // frees the A slot and the B slot of this k-block
-                    if (last) { um_commit(bar_dfull); ++seg; }
+                    um_commit(bar_aempty(pr));           // frees the A and B slots of both k-blocks
 #ifdef MT_UMMA_TIMING
                     tw[4] += clock64() - t_m1;
 #endif
@@ -292,12 +303,15 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
 #pragma unroll
         for (int d = 0; d < AHEAD - 1; ++d) issue(lw + UM_LOADERS * d);
         bool ok = true;
-        for (int i = lw; i < nrun && ok; i += UM_LOADERS) {
+        const int nrun_pad = (nrun + 1) & ~1;            // the second k-block of the last pair may not exist: its owners still arrive
+        for (int i = lw; i < nrun_pad && ok; i += UM_LOADERS) {
             issue(i + UM_LOADERS * (AHEAD - 1));
             asm volatile("cp.async.wait_group %0;" ::"n"(AHEAD - 1) : "memory");
             const int bs = i % UM_BSTAGES; const uint32_t bph = (i / UM_BSTAGES) & 1;
+            const int pr = bs >> 1;
             UM_SLOT(0);
-            if (!wait(bar_aempty(bs), bph ^ 1)) { ok = false; break; }
+            if (!wait(bar_aempty(pr), bph ^ 1)) { ok = false; break; }
+            if (i >= nrun) { __syncwarp(); if (lane == 0) mbar_arrive(bar_afull(pr)); continue; }
             unsigned char* tile_s = smem + S::OFF_B + bs * S::B_BYTES;
             const unsigned char* raw_s = smem + S::OFF_XS + (i % UM_XSTAGES) * S::B_BYTES;
 #pragma unroll
@@ -315,7 +329,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
             }
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_afull(bs));
+            if (lane == 0) mbar_arrive(bar_afull(pr));
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else {
@@ -437,9 +451,16 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
             }
         };
 
-        for (int i = grp; i < nrun && ok; i += UM_GROUPS) {
-            drain_until(i);                              // tiles that ended before this unit: this warp has converted its share of them
-            if (!ok) break;
+        const int nrun_pad = (nrun + 1) & ~1;            // the second k-block of the last pair may not exist: its owners still arrive
+        for (int i = grp; i < nrun_pad && ok; i += UM_GROUPS) {
+            const int as = i % UM_ASTAGES; const uint32_t aph = (i / UM_ASTAGES) & 1;
+            const int pr = as >> 1;
+            if (i >= nrun) {
+                if (!wait(bar_aempty(pr), aph ^ 1)) { ok = false; break; }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_afull(pr));
+                continue;
+            }
 #pragma unroll
             for (int nt = 0; nt < UM_NT; ++nt) { sr[nt] = sr_n[0][nt]; zr[nt] = zr_n[0][nt]; }
 #pragma unroll
@@ -447,7 +468,6 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
 #pragma unroll
                 for (int nt = 0; nt < UM_NT; ++nt) { sr_n[d][nt] = sr_n[d + 1][nt]; zr_n[d][nt] = zr_n[d + 1][nt]; }
             fetch(sr_n[SZ - 1], zr_n[SZ - 1]);
-            const int as = i % UM_ASTAGES; const uint32_t aph = (i / UM_ASTAGES) & 1;
             const int ps = i % S::PSTAGES; const uint32_t pph = (i / S::PSTAGES) & 1;
             UM_SLOT(3);
             if (!wait(bar_pfull(ps), pph)) { ok = false; break; }
@@ -496,7 +516,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
                 }
                 if (!waited) {
                     UM_SLOT(0);
-                    if (!wait(bar_aempty(as), aph ^ 1)) { ok = false; break; }
+                    if (!wait(bar_aempty(pr), aph ^ 1)) { ok = false; break; }
                     um_fence_after();
                     waited = true;
                 }
@@ -506,7 +526,12 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             um_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_afull(as));
+            if (lane == 0) mbar_arrive(bar_afull(pr));
+            // Tiles that end before this group's next k-block (i + 4): the group has converted its share of them.  The
+            // MMA thread starts a pair of k-blocks only when both are converted, and a pair may straddle two tiles: a
+            // tile that ends on the even k-block just before an odd next k-block needs that k-block converted before
+            // it can finish, so it is drained one turn later.
+            drain_until((i & 1) ? i + UM_GROUPS - 1 : i + UM_GROUPS);
         }
         drain_until(nrun);
     }

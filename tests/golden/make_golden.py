@@ -115,7 +115,9 @@ def _load_reference(root):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2 and "MINIT_REFERENCE" not in os.environ:
+        raise SystemExit("usage: make_golden.py <path to a checkout of the reference project>  (or set MINIT_REFERENCE)")
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ["MINIT_REFERENCE"]
     ref_dequantize = _load_reference(root)
     from oracle import qlinear_oracle as O
 
