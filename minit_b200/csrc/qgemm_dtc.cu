@@ -29,6 +29,7 @@
 // acceptance bound.  Every mbarrier wait is bounded and reports through the workspace error word.
 #include <stdlib.h>
 #include "tma.cuh"
+#include "tcgen05.cuh"
 
 namespace mt {
 
@@ -81,56 +82,6 @@ template <int BITS, int MP, int KPB> struct DtcSmem {
     static_assert(D_COLS + A_COLS <= TMEM_COLS, "TMEM budget");
 };
 
-__device__ __forceinline__ void tc_fence_before_d() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after_d() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit_d(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem descriptor]
-__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
-                 ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-                 : "memory");
-}
-template <int NR>
-__device__ __forceinline__ void tc_ld(uint32_t taddr, uint32_t (&r)[NR]) {
-    static_assert(NR == 1 || NR == 2 || NR == 4 || NR == 8 || NR == 16, "tcgen05.ld width");
-    if constexpr (NR == 1) {
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r[0]) : "r"(taddr) : "memory");
-    } else if constexpr (NR == 2) {
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(taddr) : "memory");
-    } else if constexpr (NR == 4) {
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
-                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr) : "memory");
-    } else if constexpr (NR == 8) {
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                     : "r"(taddr) : "memory");
-    } else {
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                       "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                     : "r"(taddr) : "memory");
-    }
-}
-__device__ __forceinline__ uint64_t umma_desc_sw128_d(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
 __device__ __forceinline__ void fold_bar_sync(int set) { asm volatile("bar.sync %0, 128;" ::"r"(1 + set) : "memory"); }
 
 // BITS: 4 | 8.  T: __half | __nv_bfloat16 (int8 needs __half).  MLD: batch rows the fold reads
@@ -185,9 +136,9 @@ qgemm_dtc_kernel(const DtcParams p) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)S::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    tc_fence_before_d();
+    tc_fence_before();
     __syncthreads();
-    tc_fence_after_d();
+    tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_a = tmem_base + S::D_COLS;
 
@@ -252,8 +203,8 @@ qgemm_dtc_kernel(const DtcParams p) {
                         const int as = ait % DT_ASTAGES; const uint32_t aph = (ait / DT_ASTAGES) & 1;
                         MT_SLOT(2); if (!wait(bar_afull(as), aph)) { ok = false; break; }
                         MT_TIC;
-                        tc_fence_after_d();
-                        const uint64_t bdesc = umma_desc_sw128_d(sbase + S::OFF_X + xs * S::XSLOT_STRIDE + kb * S::XB_BYTES);
+                        tc_fence_after();
+                        const uint64_t bdesc = tc_desc_sw128(sbase + S::OFF_X + xs * S::XSLOT_STRIDE + kb * S::XB_BYTES);
 #pragma unroll
                         for (int k4 = 0; k4 < 4; ++k4)
 #pragma unroll
@@ -261,10 +212,10 @@ qgemm_dtc_kernel(const DtcParams p) {
                                 tc_mma_ts(tmem_base + (uint32_t)((nt * DT_DBUF + buf) * MP),
                                           tmem_a + (uint32_t)((as * DT_NTILES + nt) * 32 + k4 * 8),
                                           bdesc + (uint64_t)(k4 * 2), idesc, (kb | k4) != 0 ? 1u : 0u);
-                        tc_commit_d(bar_aempty(as));
+                        tc_commit(bar_aempty(as));
                         MT_TOC(3);
                     }
-                    if (ok) { tc_commit_d(bar_dfull(buf)); tc_commit_d(bar_xempty(xs)); }
+                    if (ok) { tc_commit(bar_dfull(buf)); tc_commit(bar_xempty(xs)); }
                 }
             }
         }
@@ -382,10 +333,10 @@ qgemm_dtc_kernel(const DtcParams p) {
 #ifdef MT_DTC_TIMING
                 _tic = clock64();
 #endif
-                tc_fence_after_d();
+                tc_fence_after();
                 tc_st32(tmem_a + ((uint32_t)(q4 * 32) << 16) + (uint32_t)((as * DT_NTILES + nt) * 32), a);
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                tc_fence_before_d();
+                tc_fence_before();
                 mbar_arrive(bar_afull(as));
                 MT_TOC(3);
             }
@@ -453,7 +404,7 @@ qgemm_dtc_kernel(const DtcParams p) {
 #ifdef MT_DTC_TIMING
                 _tic = clock64();
 #endif
-                tc_fence_after_d();
+                tc_fence_after();
                 const float* X1 = reinterpret_cast<const float*>(smem + S::OFF_X + xs * S::XSLOT_STRIDE + KPB * S::XB_BYTES);
                 const float* X2 = X1 + MP;
                 uint32_t r[DT_NTILES][MLD];
@@ -470,7 +421,7 @@ qgemm_dtc_kernel(const DtcParams p) {
                         oacc[nt][m] = fmaf(sc[nt], v, oacc[nt][m]);
                     }
                 }
-                tc_fence_before_d();
+                tc_fence_before();
                 mbar_arrive(bar_dempty(buf));
                 mbar_arrive(bar_xempty(xs));
                 MT_TOC(3);
@@ -531,11 +482,11 @@ qgemm_dtc_kernel(const DtcParams p) {
         }
     }
 #endif
-    tc_fence_before_d();
+    tc_fence_before();
     __syncthreads();
     if (warp == DT_W_MMA) {
         __syncwarp();
-        tc_fence_after_d();
+        tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS) : "memory");
     }
     if (tid == 0 && abort_flag && p.err) atomicExch(p.err, 3u);

@@ -23,6 +23,7 @@
 // Every mbarrier wait is bounded; on expiry the kernel records a code in the error word
 // (last counter slot of the workspace) and every role leaves its loop.
 #include "tma.cuh"
+#include "tcgen05.cuh"
 #include "qgemm_small.cuh"   // GroupConst / dequant_word
 
 namespace mt {
@@ -55,38 +56,6 @@ template <int BITS, int BM> struct TcSmem {
     static constexpr int OFF_BAR = OFF_Q + TC_STAGES * Q_BYTES;
     static constexpr int TOTAL = OFF_BAR + 256 + 1024;   // barriers + slack for manual 1024-byte alignment
 };
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// K-major, 128-byte swizzle: rows of 128 bytes, 8-row atoms 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
-    d |= (uint64_t)1 << 16;                 // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset: next 8-row atom
-    d |= (uint64_t)1 << 46;                 // descriptor version (sm_100)
-    d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
-    return d;
-}
 
 template <int BITS, typename T, int BM>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -162,11 +131,11 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                     const int s = it % TC_STAGES; const uint32_t ph = (it / TC_STAGES) & 1;
                     if (!mbar_wait(bar_full(s), ph, &abort_flag) || !mbar_wait(bar_aready(s), ph, &abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint64_t adesc = umma_desc_sw128(sbase + S::OFF_A + s * S::A_BYTES);
-                    const uint64_t bdesc = umma_desc_sw128(sbase + S::OFF_B + s * S::B_BYTES);
+                    const uint64_t adesc = tc_desc_sw128(sbase + S::OFF_A + s * S::A_BYTES);
+                    const uint64_t bdesc = tc_desc_sw128(sbase + S::OFF_B + s * S::B_BYTES);
 #pragma unroll
                     for (int k4 = 0; k4 < TC_BK / 16; ++k4)
-                        tc_mma_f16(d_tmem, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, (kb | k4) != 0 ? 1u : 0u);
+                        tc_mma_ss(d_tmem, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, (kb | k4) != 0 ? 1u : 0u);
                     tc_commit(bar_empty(s));
                 }
                 if (ok) tc_commit(bar_tfull(acc));
@@ -363,13 +332,13 @@ qgemm_tcw_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     const int s = it % TCW_STAGES; const uint32_t ph = (it / TCW_STAGES) & 1;
                     if (!mbar_wait(bar_full(s), ph, &abort_flag) || !mbar_wait(bar_aready(s), ph, &abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint64_t bdesc = umma_desc_sw128(sbase + S::OFF_B + s * S::B_BYTES);
+                    const uint64_t bdesc = tc_desc_sw128(sbase + S::OFF_B + s * S::B_BYTES);
 #pragma unroll
                     for (int k4 = 0; k4 < TC_BK / 16; ++k4)
 #pragma unroll
                         for (int nt = 0; nt < 2; ++nt) {
-                            const uint64_t adesc = umma_desc_sw128(sbase + S::OFF_A + s * S::A_BYTES + nt * (TC_BN * 128));
-                            tc_mma_f16(tmem_base + (uint32_t)(nt * BM), adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, (kb | k4) != 0 ? 1u : 0u);
+                            const uint64_t adesc = tc_desc_sw128(sbase + S::OFF_A + s * S::A_BYTES + nt * (TC_BN * 128));
+                            tc_mma_ss(tmem_base + (uint32_t)(nt * BM), adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, (kb | k4) != 0 ? 1u : 0u);
                         }
                     tc_commit(bar_empty(s));
                 }

@@ -29,6 +29,7 @@
 // Every mbarrier wait is bounded and reports through the workspace error word.
 #include <stdlib.h>
 #include "tma.cuh"
+#include "tcgen05.cuh"
 
 namespace mt {
 namespace {
@@ -55,41 +56,6 @@ struct UmParams {
     int units, per, rem;     // tiles * kbt units; CTA c gets per (+1 if c < rem) units
     int zp1_const;
 };
-
-__device__ __forceinline__ void um_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void um_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void um_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem descriptor]
-__device__ __forceinline__ void um_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
-                 ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void um_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-                 : "memory");
-}
-__device__ __forceinline__ void um_ld8(uint32_t taddr, uint32_t (&r)[8]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ uint64_t um_desc_sw128(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
 
 // Bounded wait that does not poll: mbarrier.try_wait with a suspend-time hint parks the thread until the
 // phase completes or the hint expires, so waiting warps leave the issue slots to the converters.
@@ -176,9 +142,9 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)S::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    um_fence_before();
+    tc_fence_before();
     __syncthreads();
-    um_fence_after();
+    tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_a = tmem_base + S::D_COLS;
 #ifdef MT_UMMA_TIMING
@@ -217,7 +183,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
                     if (i0 + 2 * pr >= nrun || !ok) break;
                     UM_SLOT(2);
                     if (!wait(bar_afull(pr), aph)) { ok = false; break; }
-                    um_fence_after();
+                    tc_fence_after();
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const int as = 2 * pr + h;
@@ -227,27 +193,27 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
                         const bool last = (i == nrun - 1) || (kb == p.kbt - 1);
                         kb = (kb + 1 == p.kbt) ? 0 : kb + 1;
                         UM_SLOT(0);
-                        if (first) { if (!wait(bar_dempty, (seg & 1) ^ 1)) { ok = false; break; } um_fence_after(); }
+                        if (first) { if (!wait(bar_dempty, (seg & 1) ^ 1)) { ok = false; break; } tc_fence_after(); }
 #ifdef MT_UMMA_TIMING
                         const long long t_m0 = clock64();
 #endif
-                        const uint64_t bdesc = um_desc_sw128(sbase + S::OFF_B + as * S::B_BYTES);
+                        const uint64_t bdesc = tc_desc_sw128(sbase + S::OFF_B + as * S::B_BYTES);
 #pragma unroll
                         for (int k4 = 0; k4 < 4; ++k4)
 #pragma unroll
                             for (int nt = 0; nt < UM_NT; ++nt)
-                                um_mma_ts(tmem_base + (uint32_t)(nt * BM), tmem_a + (uint32_t)((as * UM_NT + nt) * 32 + k4 * 8),
+                                tc_mma_ts(tmem_base + (uint32_t)(nt * BM), tmem_a + (uint32_t)((as * UM_NT + nt) * 32 + k4 * 8),
                                           bdesc + (uint64_t)(k4 * 2), idesc, (first && k4 == 0) ? 0u : 1u);
 #ifdef MT_UMMA_TIMING
                         tw[3] += clock64() - t_m0;
 #endif
-                        if (last) { um_commit(bar_dfull); ++seg; }
+                        if (last) { tc_commit(bar_dfull); ++seg; }
                     }
                     if (!ok) break;
 #ifdef MT_UMMA_TIMING
                     const long long t_m1 = clock64();
 #endif
-                    um_commit(bar_aempty(pr));           // frees the A and B slots of both k-blocks
+                    tc_commit(bar_aempty(pr));           // frees the A and B slots of both k-blocks
 #ifdef MT_UMMA_TIMING
                     tw[4] += clock64() - t_m1;
 #endif
@@ -391,7 +357,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
         auto epilogue = [&](int tile) {
             UM_SLOT(1);
             if (!wait(bar_dfull, seg & 1)) { ok = false; return; }
-            um_fence_after();
+            tc_fence_after();
             const int nt = grp & 1;
             const int cc = nt * 128 + cl;
             const int col = tile * UM_COLS + cc;
@@ -405,7 +371,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
 #pragma unroll
             for (int jb = 0; jb < HALF; jb += 8) {
                 uint32_t r[8];
-                um_ld8(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(nt * BM + j0 + jb), r);
+                tc_ld<8>(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(nt * BM + j0 + jb), r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
@@ -416,7 +382,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
                     }
                 }
             }
-            um_fence_before();
+            tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_dempty);
             ++seg;
@@ -517,14 +483,14 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
                 if (!waited) {
                     UM_SLOT(0);
                     if (!wait(bar_aempty(pr), aph ^ 1)) { ok = false; break; }
-                    um_fence_after();
+                    tc_fence_after();
                     waited = true;
                 }
-                um_st32(tmem_a + ((uint32_t)(q4 * 32) << 16) + (uint32_t)((as * UM_NT + nt) * 32), a);
+                tc_st32(tmem_a + ((uint32_t)(q4 * 32) << 16) + (uint32_t)((as * UM_NT + nt) * 32), a);
             }
             if (!ok) break;
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            um_fence_before();
+            tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_afull(pr));
             // Tiles that end before this group's next k-block (i + 4): the group has converted its share of them.  The
@@ -543,11 +509,11 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
         for (int q = 0; q < 7; ++q) dst[1 + q] = tw[q];
     }
 #endif
-    um_fence_before();
+    tc_fence_before();
     __syncthreads();
     if (warp == UM_W_MMA) {
         __syncwarp();
-        um_fence_after();
+        tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS) : "memory");
     }
     if (tid == 0 && abort_flag && p.err) atomicExch(p.err, 5u);
