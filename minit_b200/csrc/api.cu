@@ -410,6 +410,7 @@ int mt_w8_perchannel_gemm(void* stream, const void* x, const int8_t* w, const vo
     a.x = x; a.w8 = w; a.scales = scales; a.bias = bias; a.out = out;
     a.m = m; a.n = n; a.k = k; a.groups = 1; a.bits = 8; a.dtype = dtype;
     a.workspace = workspace; a.workspace_bytes = workspace_bytes; a.flags = flags;
+    if (!(flags & MT_FLAG_FORCE_SMALL) && m <= 2 && w8vec_supported(a)) return launch_w8vec(static_cast<cudaStream_t>(stream), a);
     return launch_small_w8(static_cast<cudaStream_t>(stream), a);
 }
 

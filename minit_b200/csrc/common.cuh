@@ -131,6 +131,8 @@ int launch_gather_columns(cudaStream_t st, const void* x, const int32_t* perm, v
 int launch_unpack(cudaStream_t st, const uint32_t* packed, uint8_t* out, int rows, int cols, int bits, int axis);
 int launch_small(cudaStream_t st, const QGemmArgs& a);          // GPTQ layout, M <= 64 per launch
 int launch_small_w8(cudaStream_t st, const QGemmArgs& a);       // int8 [K,N] per-channel, M <= 64 per launch
+int launch_w8vec(cudaStream_t st, const QGemmArgs& a);          // int8 [K,N] per-channel, CUDA-core GEMV, M <= 2, N % 256 == 0
+bool w8vec_supported(const QGemmArgs& a);
 int launch_dtc(cudaStream_t st, const QGemmArgs& a);            // tcgen05 decode kernel, M <= 32, contiguous groups
 bool dtc_supported(const QGemmArgs& a);
 int launch_vec(cudaStream_t st, const QGemmArgs& a);            // CUDA-core decode GEMV, M <= 2, contiguous groups
