@@ -33,25 +33,9 @@ struct W8VParams {
     int pdl, cluster;
 };
 
-__device__ __forceinline__ uint32_t w8v_fma(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t d; asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d; }
-__device__ __forceinline__ uint32_t w8v_mul(uint32_t a, uint32_t b) {
-    uint32_t d; asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
-__device__ __forceinline__ uint32_t w8v_add(uint32_t a, uint32_t b) {
-    uint32_t d; asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
 // (a ^ b) & c
 __device__ __forceinline__ uint32_t xor_and(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d; asm("lop3.b32 %0, %1, %2, %3, 0x28;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d; }
-__device__ __forceinline__ void w8v_cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
-__device__ __forceinline__ void w8v_cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
-__device__ __forceinline__ void w8v_cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-__device__ __forceinline__ void w8v_st_cluster(const float* local, unsigned cta_rank, float v) {
-    const uint32_t la = (uint32_t)__cvta_generic_to_shared(local);
-    uint32_t ra;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(la), "r"(cta_rank));
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ra), "f"(v) : "memory");
-}
-
 template <typename T, int MB>
 __global__ void __launch_bounds__(W8V_THREADS, 2) qgemm_w8vec_kernel(const W8VParams p) {
     using H = F16x2<T>;
@@ -63,7 +47,7 @@ __global__ void __launch_bounds__(W8V_THREADS, 2) qgemm_w8vec_kernel(const W8VPa
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tile = blockIdx.x, split = blockIdx.y;
     const int col = tile * W8V_COLS + lane * 8;
-    if (p.cluster) w8v_cluster_arrive_relaxed();
+    if (p.cluster) cluster_arrive_relaxed();
 
     const int u = split * W8V_WARPS + warp;
     const int c_lo = int((long long)u * p.nchunks / p.units);
@@ -134,11 +118,11 @@ __global__ void __launch_bounds__(W8V_THREADS, 2) qgemm_w8vec_kernel(const W8VPa
             for (int mb = 0; mb < MB; ++mb) {
                 const uint32_t x2 = xs[((size_t)mb * p.slice_chunks + ch) * 16 + r];
                 if (r < 2) {
-                    a[mb][set][0] = w8v_mul(q0, x2); a[mb][set][1] = w8v_mul(q1, x2);
-                    a[mb][set][2] = w8v_mul(q2, x2); a[mb][set][3] = w8v_mul(q3, x2);
+                    a[mb][set][0] = hmul2(q0, x2); a[mb][set][1] = hmul2(q1, x2);
+                    a[mb][set][2] = hmul2(q2, x2); a[mb][set][3] = hmul2(q3, x2);
                 } else {
-                    a[mb][set][0] = w8v_fma(q0, x2, a[mb][set][0]); a[mb][set][1] = w8v_fma(q1, x2, a[mb][set][1]);
-                    a[mb][set][2] = w8v_fma(q2, x2, a[mb][set][2]); a[mb][set][3] = w8v_fma(q3, x2, a[mb][set][3]);
+                    a[mb][set][0] = hfma2(q0, x2, a[mb][set][0]); a[mb][set][1] = hfma2(q1, x2, a[mb][set][1]);
+                    a[mb][set][2] = hfma2(q2, x2, a[mb][set][2]); a[mb][set][3] = hfma2(q3, x2, a[mb][set][3]);
                 }
             }
         }
@@ -148,7 +132,7 @@ __global__ void __launch_bounds__(W8V_THREADS, 2) qgemm_w8vec_kernel(const W8VPa
             const float zs = 128.f * mt2.y;
 #pragma unroll
             for (int pr = 0; pr < 4; ++pr) {
-                const uint32_t hsum = w8v_add(a[mb][0][pr], a[mb][1][pr]);
+                const uint32_t hsum = hadd2(a[mb][0][pr], a[mb][1][pr]);
                 const __half2 hv = *reinterpret_cast<const __half2*>(&hsum);
                 // pair pr of word (pr >> 1): columns (4 * (pr >> 1) + (pr & 1)) and the same + 2
                 const int c0 = 4 * (pr >> 1) + (pr & 1);
@@ -179,11 +163,11 @@ __global__ void __launch_bounds__(W8V_THREADS, 2) qgemm_w8vec_kernel(const W8VPa
         for (int wi = 0; wi < W8V_WARPS; ++wi) v[mb] += red[((size_t)wi * MB + mb) * W8V_COLS + tid];
     }
     if (p.splits > 1 && p.cluster) {
-        w8v_cluster_wait();
+        cluster_wait_acquire();
 #pragma unroll
-        for (int mb = 0; mb < MB; ++mb) w8v_st_cluster(xred + ((size_t)split * MB + mb) * W8V_COLS + tid, 0u, v[mb]);
-        w8v_cluster_arrive();
-        w8v_cluster_wait();
+        for (int mb = 0; mb < MB; ++mb) st_cluster_f32(xred + ((size_t)split * MB + mb) * W8V_COLS + tid, 0u, v[mb]);
+        cluster_arrive_release();
+        cluster_wait_acquire();
         if (split != 0) return;
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb) {
