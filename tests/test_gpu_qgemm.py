@@ -160,3 +160,25 @@ def test_full_size_linearity_property(M):
     sl = slice(4096, 4096 + 512)
     w = O.dequantize_packed(qw[:, sl].contiguous(), None, qz[:, 512:576].contiguous(), s[:, sl].contiguous(), 4)
     assert_close(o1[:, sl], O.qlinear(x1, w), "column slice of the full-size linear")
+
+
+@pytest.mark.parametrize("m,k,n,bits", [(2, 8192, 57344, 4), (32, 8192, 57344, 4), (64, 28672, 8192, 4), (1, 8192, 28672, 8)])
+def test_full_size_shapes_every_dispatch_path(M, m, k, n, bits):
+    """The 70B linears at the batch sizes each decode kernel serves (GEMV stream-K, mid-batch tcgen05 kernel, 8-bit GEMV):
+    linearity in x, and the oracle on a slice of columns that starts inside a column tile."""
+    pack = 32 // bits
+    gen = torch.Generator().manual_seed(m + k)
+    qw = torch.randint(-2**31, 2**31 - 1, (k // pack, n), generator=gen, dtype=torch.int64).to(torch.int32)
+    qz = torch.randint(-2**31, 2**31 - 1, (k // 128, n // pack), generator=gen, dtype=torch.int64).to(torch.int32)
+    s = (0.002 + 0.018 * torch.rand((k // 128, n), generator=gen)).half()
+    x1 = torch.randn((m, k), generator=gen).half()
+    x2 = torch.randn((m, k), generator=gen).half()
+    dq, dz, ds = qw.to(DEV), qz.to(DEV), s.to(DEV)
+    f = lambda x: M.quantized_matrix_multiply(x.to(DEV), dq, dz, ds, None, bits=bits).float().cpu()
+    o1, o2, o12 = f(x1), f(x2), f((x1.float() + x2.float()).half())
+    rms = o12.pow(2).mean().sqrt()
+    assert (o12 - (o1 + o2)).abs().max() <= 2e-2 * rms
+    c0 = 4096 + 64                                           # not a multiple of 128 or 256
+    sl = slice(c0, c0 + 512)
+    w = O.dequantize_packed(qw[:, sl].contiguous(), None, qz[:, c0 // pack:(c0 + 512) // pack].contiguous(), s[:, sl].contiguous(), bits)
+    assert_close(o1[:, sl], O.qlinear(x1, w), f"column slice of {k}x{n} M={m} bits={bits}")
