@@ -134,6 +134,50 @@ int mt_qgemm_allreduce(void* stream, const void* x, const uint32_t* qweight, con
 size_t mt_allreduce_buffer_bytes(int m_max, int n_max, int world);
 
 /*
+ * Epilogues of a decoder layer fused into the linear (the reference runs each as separate elementwise
+ * kernels on the linear's rounded output):
+ *
+ * mt_qgemm_residual: out[M,N] = residual[M,N] + (x @ W (+ bias)), the `x + attention_output` /
+ *   `x + feed_forward_output` of a decoder block (examples/llama3_70b.py:160).  With world > 1 it is
+ *   mt_qgemm_allreduce (same buffers and rules, m <= 64) with the residual, replicated on every rank,
+ *   added to the reduced sum; with world <= 1 peer_buffers is ignored and any m is accepted.  At M <= 2
+ *   the decode GEMV adds the residual in fp32 before its one rounding; other batch sizes run the GEMM,
+ *   then one elementwise launch (two roundings, as in the reference).  residual must not overlap out
+ *   unless M <= 2; residual NULL = mt_qgemm / mt_qgemm_allreduce.
+ *
+ * mt_interleave_gate_up (load time): the gate and up projections of a gated feed-forward
+ *   (examples/llama3_70b.py:118-130, examples/qwen1_5_int8.py:371-383), each [K, n_half] in the GPTQ layout
+ *   with the same K, groups and bits, become ONE linear of N = 2 n_half columns: output column c holds
+ *   gate column 4 (c / 8) + c % 8 if c % 8 < 4, else up column 4 (c / 8) + c % 8 - 4.  qzeros and bias
+ *   are optional (all three pointers of a kind NULL or none); n_half % 8 == 0.  Not in place.
+ *
+ * mt_qgemm_swiglu: out[M, N/2] = silu(G) * U where [G | U] = x @ W (+ bias) on that interleaved
+ *   layout: out[m, j] = silu(y[m, 8 (j / 4) + j % 4]) * y[m, 8 (j / 4) + 4 + j % 4], computed in fp32
+ *   and rounded once (the reference rounds the linear outputs, sigmoid, silu and the product separately:
+ *   Sigmoid rule at minit/cuda/dispatch.py:143).  At M <= 2 it runs in the epilogue of the decode GEMV;
+ *   otherwise the GEMM writes y into scratch ([M,N], required then) and mt_swiglu follows.  N % 16 == 0,
+ *   no act-order.
+ *
+ * mt_swiglu: the activation alone, gate_up[M,N] interleaved -> out[M,N/2].
+ */
+#define MT_EPILOGUE_NONE    0
+#define MT_EPILOGUE_SWIGLU  1
+int mt_qgemm_residual(void* stream, const void* x, const uint32_t* qweight, const int32_t* g_idx,
+                      const uint32_t* qzeros, const void* scales, const void* bias, const void* residual, void* out,
+                      int m, int n, int k, int nr_groups, int bits, int dtype,
+                      void* workspace, size_t workspace_bytes, int flags,
+                      void* const* peer_buffers, int rank, int world, size_t buffer_bytes);
+int mt_interleave_gate_up(void* stream, const uint32_t* gate_qweight, const uint32_t* up_qweight,
+                          const uint32_t* gate_qzeros, const uint32_t* up_qzeros, const void* gate_scales, const void* up_scales,
+                          const void* gate_bias, const void* up_bias,
+                          uint32_t* qweight_out, uint32_t* qzeros_out, void* scales_out, void* bias_out,
+                          int n_half, int k, int nr_groups, int bits);
+int mt_qgemm_swiglu(void* stream, const void* x, const uint32_t* qweight, const uint32_t* qzeros, const void* scales,
+                    const void* bias, void* out, void* scratch, int m, int n, int k, int nr_groups, int bits, int dtype,
+                    void* workspace, size_t workspace_bytes, int flags);
+int mt_swiglu(void* stream, const void* gate_up, void* out, int m, int n, int dtype);
+
+/*
  * Which schedule mt_qgemm would run a decode call (M <= 2, no g_idx) with: > 0 = split-K factor of the
  * CUDA-core GEMV, 0 = its stream-K schedule, MT_ERR_UNSUPPORTED = the request goes to another kernel.
  * Inspection only (no launch); no counterpart in the reference, whose launcher has one fixed grid

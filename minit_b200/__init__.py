@@ -9,6 +9,8 @@ from . import _lib  # noqa: F401  (fails loudly when the CUDA library is not bui
 from .qlinear import (QLinear, QLinearWithBias, W8Linear, pack_w8, quantized_matrix_multiply,
                       quantized_matrix_multiply_noalloc, quantized_matrix_multiply_ordered, sort_act_order, unpack,
                       w8_perchannel_matrix_multiply)
+from .feedforward import (QFeedForward, interleave_gate_up, quantized_gate_up_swiglu, quantized_matrix_multiply_residual,
+                          swiglu_interleaved)
 from .quantize import Dequantize, QuantizedTensor, dequantize
 from .operator.linalg import MatrixMultiply
 from .functional.linalg import matrix_multiply
@@ -19,5 +21,6 @@ __all__ = [
     "quantized_matrix_multiply_ordered", "sort_act_order", "pack_w8",
     "unpack", "Dequantize", "QuantizedTensor", "dequantize", "MatrixMultiply", "matrix_multiply",
     "dispatch", "register_dispatch",
+    "QFeedForward", "interleave_gate_up", "quantized_gate_up_swiglu", "quantized_matrix_multiply_residual", "swiglu_interleaved",
 ]
 __version__ = "0.1.0"

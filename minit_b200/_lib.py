@@ -38,6 +38,10 @@ SYMBOLS = {
     "mt_qgemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _i]),
     "mt_qgemm_allreduce": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _i, _vp, _i, _i, _sz]),
     "mt_allreduce_buffer_bytes": (_sz, [_i, _i, _i]),
+    "mt_qgemm_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _i, _vp, _i, _i, _sz]),
+    "mt_interleave_gate_up": (_i, [_vp] * 13 + [_i, _i, _i, _i]),
+    "mt_qgemm_swiglu": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _i]),
+    "mt_swiglu": (_i, [_vp, _vp, _vp, _i, _i, _i]),
     "mt_decode_plan": (_i, [_i, _i, _i, _i, _i, _sz, _i]),
     "mt_w8_pack": (_i, [_vp, _vp, _vp, _i, _i]),
     "mt_act_order_perm": (_i, [_vp, _vp, _vp, _vp, _i, _i]),

@@ -40,8 +40,9 @@ class FusedAllReduce:
         torch.cuda.synchronize()
         dist.barrier(group)   # every rank's buffer is zeroed before anyone's first kernel can raise a flag in it
 
-    def matmul(self, x, qweight, zeros, scales, groups, *, bits: int, bias=None, out=None, flags: int = 0):
-        """out = sum over ranks of x_r @ W_r (+ bias), identical on every rank, in one kernel per rank."""
+    def matmul(self, x, qweight, zeros, scales, groups, *, bits: int, bias=None, out=None, flags: int = 0, residual=None):
+        """out = sum over ranks of x_r @ W_r (+ bias) (+ residual, the same tensor on every rank), identical on
+        every rank, in one kernel per rank."""
         pack = 32 // bits
         *ms, k0 = x.shape
         n0 = qweight.shape[1]
@@ -52,15 +53,17 @@ class FusedAllReduce:
             raise ValueError("shape or dtype mismatch between x, qweight and scales")
         if m > self.m_max or n0 > self.n_max:
             raise ValueError(f"[{m},{n0}] exceeds the symmetric buffer ({self.m_max} x {self.n_max})")
-        dev = _lib.require_cuda(x, qweight, zeros, scales, groups, bias)
+        dev = _lib.require_cuda(x, qweight, zeros, scales, groups, bias, residual)
+        if residual is not None and (residual.dtype != x.dtype or residual.numel() != m * n0 or not residual.is_contiguous()):
+            raise ValueError("residual must be a contiguous [*ms, N] tensor in x.dtype")
         if out is None:
             out = torch.empty((*ms, n0), dtype=x.dtype, device=dev)
         stream = _lib.current_stream(dev)
         ws = _lib.workspace(dev, stream, _lib.lib.mt_workspace_bytes(m, n0, k0, bits))
         with torch.cuda.device(dev):
-            rc = _lib.lib.mt_qgemm_allreduce(stream, x.data_ptr(), qweight.data_ptr(), _lib.ptr(groups), _lib.ptr(zeros),
-                                             scales.data_ptr(), _lib.ptr(bias), out.data_ptr(), m, n0, k0, scales.shape[0],
-                                             bits, _lib.dtype_code(x.dtype), ws.data_ptr(), ws.numel(), flags,
-                                             self.peer_table.data_ptr(), self.rank, self.world, self.nbytes)
-        _lib.check(rc, "mt_qgemm_allreduce")
+            rc = _lib.lib.mt_qgemm_residual(stream, x.data_ptr(), qweight.data_ptr(), _lib.ptr(groups), _lib.ptr(zeros),
+                                            scales.data_ptr(), _lib.ptr(bias), _lib.ptr(residual), out.data_ptr(), m, n0, k0,
+                                            scales.shape[0], bits, _lib.dtype_code(x.dtype), ws.data_ptr(), ws.numel(), flags,
+                                            self.peer_table.data_ptr(), self.rank, self.world, self.nbytes)
+        _lib.check(rc, "mt_qgemm_residual")
         return out

@@ -95,15 +95,25 @@ class RowParallelQLinear(Module):
         size = world.size if size is None else size
         self.communicator = communicator
         self.size = size
+        self.rank = rank
         self.fused = fused   # a collective.fused.FusedAllReduce: GEMM and all-reduce become one kernel
         qw, qz, s, gi = shard_gptq_row(qweight, qzeros, scales, bits, rank, size, g_idx)
         self.shard = ShardedQuantized("row", qw, qz, s, gi, bits, bias if rank == 0 else None)
 
-    def forward(self, x, out=None, flags: int = 0, reduce: bool = True):
+    def forward(self, x, out=None, flags: int = 0, reduce: bool = True, residual=None):
+        """``residual`` (replicated, [*, N]): the block's ``x + linear(...)`` (examples/llama3_70b.py:160-162) folded into
+        this linear.  The fused kernel adds it to the reduced sum; on the NCCL path rank 0 adds it to its partial, like
+        the bias, so the sum counts it once."""
+        sh = self.shard
         if reduce and self.size > 1 and self.fused is not None:
-            sh = self.shard
-            return self.fused.matmul(x, sh.qweight, sh.qzeros, sh.scales, sh.g_idx, bits=sh.bits, bias=sh.bias, out=out, flags=flags)
-        partial = self.shard.local_matmul(x, out=out, flags=flags)
+            return self.fused.matmul(x, sh.qweight, sh.qzeros, sh.scales, sh.g_idx, bits=sh.bits, bias=sh.bias, out=out, flags=flags,
+                                     residual=residual)
+        if residual is not None and self.rank == 0:
+            from ..feedforward import quantized_matrix_multiply_residual
+            partial = quantized_matrix_multiply_residual(x, sh.qweight, sh.qzeros, sh.scales, sh.g_idx, residual, bits=sh.bits,
+                                                         bias=sh.bias, out=out, flags=flags)
+        else:
+            partial = self.shard.local_matmul(x, out=out, flags=flags)
         if reduce and self.size > 1:
             return self.all_reduce(partial)
         return partial

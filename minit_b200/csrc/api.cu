@@ -277,11 +277,11 @@ int mt_qgemm(void* stream, const void* x, const uint32_t* qweight, const int32_t
     return launch_small(st, a);
 }
 
-int mt_qgemm_allreduce(void* stream, const void* x, const uint32_t* qweight, const int32_t* g_idx,
-                       const uint32_t* qzeros, const void* scales, const void* bias, void* out,
-                       int m, int n, int k, int nr_groups, int bits, int dtype,
-                       void* workspace, size_t workspace_bytes, int flags,
-                       void* const* peer_buffers, int rank, int world, size_t buffer_bytes) {
+static int qgemm_allreduce_impl(void* stream, const void* x, const uint32_t* qweight, const int32_t* g_idx,
+                               const uint32_t* qzeros, const void* scales, const void* bias, const void* residual, void* out,
+                               int m, int n, int k, int nr_groups, int bits, int dtype,
+                               void* workspace, size_t workspace_bytes, int flags,
+                               void* const* peer_buffers, int rank, int world, size_t buffer_bytes) {
     int rc = validate_gptq(qweight, qzeros, scales, n, k, nr_groups, bits, dtype);
     if (rc != MT_OK) return rc;
     if (m < 0 || m > 64 || k == 0) return MT_ERR_SHAPE;          // one launch: the exchange is per launch
@@ -289,6 +289,7 @@ int mt_qgemm_allreduce(void* stream, const void* x, const uint32_t* qweight, con
     if (m == 0 || n == 0) return MT_OK;
     if (!x || !out || (world > 1 && !peer_buffers)) return MT_ERR_NULL;
     if (!aligned16(x) || !aligned16(out) || (bias && !aligned16(bias)) || (workspace && !aligned16(workspace))) return MT_ERR_ALIGN;
+    if (residual && !aligned16(residual)) return MT_ERR_ALIGN;
     if (!g_idx && (k / nr_groups) % (4 * (32 / bits)) != 0) return MT_ERR_SHAPE;
     if (world > 1 && buffer_bytes < kArDataOffset + 2 * (size_t)world * 256) return MT_ERR_WORKSPACE;
     if ((rc = check_device()) != MT_OK) return rc;
@@ -301,8 +302,101 @@ int mt_qgemm_allreduce(void* stream, const void* x, const uint32_t* qweight, con
         a.ar_rank = rank; a.ar_world = world; a.ar_bytes = buffer_bytes;
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (!(flags & MT_FLAG_FORCE_SMALL) && m <= 2 && vec_supported(a)) return launch_vec(st, a);
-    return launch_small(st, a);
+    if (!(flags & MT_FLAG_FORCE_SMALL) && m <= 2 && vec_supported(a)) {
+        a.residual = residual;                                   // the GEMV adds it to the reduced sum before its one rounding
+        return launch_vec(st, a);
+    }
+    rc = launch_small(st, a);
+    if (rc == MT_OK && residual) rc = launch_add_residual(st, out, residual, m, n, dtype);
+    return rc;
+}
+
+int mt_qgemm_allreduce(void* stream, const void* x, const uint32_t* qweight, const int32_t* g_idx,
+                       const uint32_t* qzeros, const void* scales, const void* bias, void* out,
+                       int m, int n, int k, int nr_groups, int bits, int dtype,
+                       void* workspace, size_t workspace_bytes, int flags,
+                       void* const* peer_buffers, int rank, int world, size_t buffer_bytes) {
+    return qgemm_allreduce_impl(stream, x, qweight, g_idx, qzeros, scales, bias, nullptr, out, m, n, k, nr_groups, bits, dtype,
+                                workspace, workspace_bytes, flags, peer_buffers, rank, world, buffer_bytes);
+}
+
+int mt_qgemm_residual(void* stream, const void* x, const uint32_t* qweight, const int32_t* g_idx,
+                      const uint32_t* qzeros, const void* scales, const void* bias, const void* residual, void* out,
+                      int m, int n, int k, int nr_groups, int bits, int dtype,
+                      void* workspace, size_t workspace_bytes, int flags,
+                      void* const* peer_buffers, int rank, int world, size_t buffer_bytes) {
+    if (world > 1)
+        return qgemm_allreduce_impl(stream, x, qweight, g_idx, qzeros, scales, bias, residual, out, m, n, k, nr_groups, bits, dtype,
+                                    workspace, workspace_bytes, flags, peer_buffers, rank, world, buffer_bytes);
+    if (!residual) return mt_qgemm(stream, x, qweight, g_idx, qzeros, scales, bias, out, m, n, k, nr_groups, bits, dtype, workspace, workspace_bytes, flags);
+    // one rank: any batch size.  The decode GEMV adds the residual in its epilogue; every other kernel is
+    // followed by one elementwise launch.
+    if (!aligned16(residual)) return MT_ERR_ALIGN;
+    const bool forced_other = (flags & (MT_FLAG_FORCE_SMALL | MT_FLAG_FORCE_TC | MT_FLAG_FORCE_DTC | MT_FLAG_FORCE_UMMA)) != 0;
+    if (m >= 1 && m <= 2 && !forced_other && !g_idx)
+        return qgemm_allreduce_impl(stream, x, qweight, g_idx, qzeros, scales, bias, residual, out, m, n, k, nr_groups, bits, dtype,
+                                    workspace, workspace_bytes, flags, nullptr, 0, 1, 0);
+    int rc = mt_qgemm(stream, x, qweight, g_idx, qzeros, scales, bias, out, m, n, k, nr_groups, bits, dtype, workspace, workspace_bytes, flags);
+    if (rc == MT_OK && m > 0 && n > 0) rc = launch_add_residual(static_cast<cudaStream_t>(stream), out, residual, m, n, dtype);
+    return rc;
+}
+
+int mt_qgemm_swiglu(void* stream, const void* x, const uint32_t* qweight, const uint32_t* qzeros, const void* scales,
+                    const void* bias, void* out, void* scratch, int m, int n, int k, int nr_groups, int bits, int dtype,
+                    void* workspace, size_t workspace_bytes, int flags) {
+    int rc = validate_gptq(qweight, qzeros, scales, n, k, nr_groups, bits, dtype);
+    if (rc != MT_OK) return rc;
+    if (m < 0 || n % 16 != 0) return MT_ERR_SHAPE;               // out rows of N/2 values keep the 16-byte alignment
+    if (m == 0 || n == 0) return MT_OK;
+    if (k == 0) return MT_ERR_SHAPE;
+    if (!x || !out) return MT_ERR_NULL;
+    if (!aligned16(x) || !aligned16(out) || (bias && !aligned16(bias)) || (workspace && !aligned16(workspace))) return MT_ERR_ALIGN;
+    if ((k / nr_groups) % (4 * (32 / bits)) != 0) return MT_ERR_SHAPE;
+    if ((rc = check_device()) != MT_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    QGemmArgs a = {};
+    a.x = x; a.qweight = qweight; a.qzeros = qzeros; a.scales = scales; a.bias = bias; a.out = out;
+    a.m = m; a.n = n; a.k = k; a.groups = nr_groups; a.bits = bits; a.dtype = dtype;
+    a.workspace = workspace; a.workspace_bytes = workspace_bytes; a.flags = flags;
+    const bool forced_other = (flags & (MT_FLAG_FORCE_SMALL | MT_FLAG_FORCE_TC | MT_FLAG_FORCE_DTC | MT_FLAG_FORCE_UMMA)) != 0;
+    if (m <= 2 && !forced_other && vec_supported(a)) {
+        a.epilogue = MT_EPILOGUE_SWIGLU;
+        return launch_vec(st, a);
+    }
+    if (!scratch) return MT_ERR_NULL;
+    if (!aligned16(scratch)) return MT_ERR_ALIGN;
+    rc = mt_qgemm(stream, x, qweight, nullptr, qzeros, scales, bias, scratch, m, n, k, nr_groups, bits, dtype, workspace, workspace_bytes, flags);
+    if (rc == MT_OK) rc = launch_swiglu_interleaved(st, scratch, out, m, n, dtype);
+    return rc;
+}
+
+int mt_interleave_gate_up(void* stream, const uint32_t* gate_qweight, const uint32_t* up_qweight,
+                          const uint32_t* gate_qzeros, const uint32_t* up_qzeros, const void* gate_scales, const void* up_scales,
+                          const void* gate_bias, const void* up_bias,
+                          uint32_t* qweight_out, uint32_t* qzeros_out, void* scales_out, void* bias_out,
+                          int n_half, int k, int nr_groups, int bits) {
+    if (bits != 4 && bits != 8) return MT_ERR_BITS;
+    if (n_half < 0 || k < 0 || nr_groups < 1 || n_half % 8 != 0 || k % 32 != 0) return MT_ERR_SHAPE;
+    if (n_half == 0 || k == 0) return MT_OK;
+    if (!gate_qweight || !up_qweight || !gate_scales || !up_scales || !qweight_out || !scales_out) return MT_ERR_NULL;
+    if ((gate_qzeros == nullptr) != (up_qzeros == nullptr) || (gate_qzeros == nullptr) != (qzeros_out == nullptr)) return MT_ERR_NULL;
+    if ((gate_bias == nullptr) != (up_bias == nullptr) || (gate_bias == nullptr) != (bias_out == nullptr)) return MT_ERR_NULL;
+    int rc = check_device();
+    if (rc != MT_OK) return rc;
+    return launch_interleave_gate_up(static_cast<cudaStream_t>(stream), gate_qweight, up_qweight, gate_qzeros, up_qzeros,
+                                     gate_scales, up_scales, gate_bias, up_bias, qweight_out, qzeros_out, scales_out, bias_out,
+                                     n_half, k, nr_groups, bits);
+}
+
+int mt_swiglu(void* stream, const void* gate_up, void* out, int m, int n, int dtype) {
+    if (dtype != MT_F16 && dtype != MT_BF16) return MT_ERR_DTYPE;
+    if (m < 0 || n < 0 || n % 16 != 0) return MT_ERR_SHAPE;
+    if (m == 0 || n == 0) return MT_OK;
+    if (!gate_up || !out) return MT_ERR_NULL;
+    if (!aligned16(gate_up) || !aligned16(out)) return MT_ERR_ALIGN;
+    int rc = check_device();
+    if (rc != MT_OK) return rc;
+    return launch_swiglu_interleaved(static_cast<cudaStream_t>(stream), gate_up, out, m, n, dtype);
 }
 
 int mt_decode_plan(int m, int n, int k, int nr_groups, int bits, size_t workspace_bytes, int flags) {

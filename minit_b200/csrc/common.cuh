@@ -42,6 +42,9 @@ template <> struct F16x2<__nv_bfloat16> {
         __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi); return *reinterpret_cast<uint32_t*>(&h); }
 };
 
+// silu(g) * u in fp32: the activation of a gated feed-forward (examples/llama3_70b.py:44-45, 127-129)
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + expf(-g)) * u; }
+
 // (a & b) | c in one LOP3
 __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d; asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
@@ -124,6 +127,9 @@ struct QGemmArgs {
     unsigned char* const* ar_peers;
     int ar_rank, ar_world;
     size_t ar_bytes;          // size of one symmetric buffer
+    // fused epilogues (decode GEMV only; other kernels are followed by an elementwise launch)
+    const void* residual;     // [M,N] T or null: out = residual + (x @ W + bias), added after the all-reduce
+    int epilogue;             // MT_EPILOGUE_*: SWIGLU = out[M,N/2] from the gate / up interleaved layout
 };
 
 // workspace layout: [0, kCounterBytes) tile counters (the last word is the error word) (kept zero between launches),
@@ -158,6 +164,11 @@ bool dtc_supported(const QGemmArgs& a);
 int launch_vec(cudaStream_t st, const QGemmArgs& a);            // CUDA-core decode GEMV, M <= 2, contiguous groups
 bool vec_supported(const QGemmArgs& a);
 int vec_plan(const QGemmArgs& a);                               // > 0 split-K factor, 0 stream-K, < 0 MT_ERR_*
+int launch_interleave_gate_up(cudaStream_t st, const uint32_t* qw_g, const uint32_t* qw_u, const uint32_t* qz_g, const uint32_t* qz_u,
+                              const void* s_g, const void* s_u, const void* b_g, const void* b_u,
+                              uint32_t* qw_out, uint32_t* qz_out, void* s_out, void* b_out, int half, int k, int groups, int bits);
+int launch_swiglu_interleaved(cudaStream_t st, const void* in, void* out, int m, int n, int dtype);   // [M,N] interleaved -> [M,N/2]
+int launch_add_residual(cudaStream_t st, void* io, const void* res, int m, int n, int dtype);        // io += res
 int launch_umma(cudaStream_t st, const QGemmArgs& a);           // tcgen05 with all-warp dequant, 2 < M <= 192, contiguous groups
 bool umma_supported(const QGemmArgs& a);
 size_t umma_workspace_bytes(int m, int n, int k);

@@ -54,6 +54,8 @@ struct VecParams {
     int pdl;
     int cluster;      // the `splits` CTAs of a column block form a thread-block cluster: split-K sums meet in CTA 0's shared memory
     ArParams ar;      // row-parallel use: all-reduce of the finished sums over peer memory (ar_mailbox.cuh)
+    const void* residual;   // [M,N] T or null, added to the finished (all-reduced) sum before the one rounding
+    int swiglu;       // columns are gate / up interleaved in blocks of 4 + 4: out[M,N/2] = silu(gate) * up
 };
 
 __device__ __forceinline__ float h2sum(uint32_t h) {
@@ -331,7 +333,13 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
         if (tid == 0) p.counters[tile] = 0;
     }
     if (active && bias) v += H::to_float(reinterpret_cast<const uint16_t*>(bias)[gc]);
-    if (!fused_ar) {
+    const uint16_t* resid = reinterpret_cast<const uint16_t*>(p.residual);
+    if (p.swiglu) {
+        // gate column cc (cc % 8 < 4) and its up column cc + 4 sit four lanes apart in the same warp
+        const float u = __shfl_xor_sync(0xffffffffu, v, 4);
+        if (active && !(cc & 4)) out[(size_t)mb_r * (p.n >> 1) + ((gc >> 3) << 2) + (gc & 3)] = H::from_float(silu_mul(v, u));
+    } else if (!fused_ar) {
+        if (active && resid) v += H::to_float(resid[(size_t)mb_r * p.n + gc]);
         if (active) out[(size_t)mb_r * p.n + gc] = H::from_float(v);
     } else {
         // four adjacent columns per thread for the exchange: regroup through shared memory
@@ -341,7 +349,12 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
         if (tid < 32 * MB && tid / 32 < p.m) {
             const int mb = tid / 32, c4 = (tid % 32) * 4;
             const float4 mine4 = *reinterpret_cast<const float4*>(red + mb * VEC_COLS + c4);
-            const float4 sum = ar_exchange(p.ar, epoch, (size_t)mb * p.n + tile * VEC_COLS + c4, mine4);
+            float4 sum = ar_exchange(p.ar, epoch, (size_t)mb * p.n + tile * VEC_COLS + c4, mine4);
+            if (resid) {
+                const uint2 rv = __ldg(reinterpret_cast<const uint2*>(resid + (size_t)mb * p.n + tile * VEC_COLS + c4));
+                sum.x += H::to_float(uint16_t(rv.x & 0xffff)); sum.y += H::to_float(uint16_t(rv.x >> 16));
+                sum.z += H::to_float(uint16_t(rv.y & 0xffff)); sum.w += H::to_float(uint16_t(rv.y >> 16));
+            }
             uint2 o; o.x = H::pack(sum.x, sum.y); o.y = H::pack(sum.z, sum.w);
             *reinterpret_cast<uint2*>(out + (size_t)mb * p.n + tile * VEC_COLS + c4) = o;
         }
@@ -380,6 +393,8 @@ struct StreamParams {
     int zp1_const;
     int pdl;
     ArParams ar;       // row-parallel use: all-reduce of the finished sums over peer memory (ar_mailbox.cuh)
+    const void* residual;   // [M,N] T or null, added to the finished (all-reduced) sum before the one rounding
+    int swiglu;        // columns are gate / up interleaved in blocks of 4 + 4: out[M,N/2] = silu(gate) * up
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
@@ -573,7 +588,22 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
         for (int mb = 0; mb < MB; ++mb)
             if (mb < p.m) {
                 float4 v = make_float4(r[mb].x + b0, r[mb].y + b1, r[mb].z + b2, r[mb].w + b3);
+                if (p.swiglu) {
+                    // an even lane holds four gate columns, the next lane their up columns (the whole warp is here)
+                    const float4 u = make_float4(__shfl_xor_sync(0xffffffffu, v.x, 1), __shfl_xor_sync(0xffffffffu, v.y, 1),
+                                                 __shfl_xor_sync(0xffffffffu, v.z, 1), __shfl_xor_sync(0xffffffffu, v.w, 1));
+                    if (!(lane & 1)) {
+                        uint2 o; o.x = H::pack(silu_mul(v.x, u.x), silu_mul(v.y, u.y)); o.y = H::pack(silu_mul(v.z, u.z), silu_mul(v.w, u.w));
+                        *reinterpret_cast<uint2*>(out + (size_t)mb * (p.n >> 1) + (colb >> 1)) = o;
+                    }
+                    continue;
+                }
                 if (fused_ar) v = ar_exchange(p.ar, epoch, (size_t)mb * p.n + colb, v);
+                if (p.residual) {
+                    const uint2 rv = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p.residual) + (size_t)mb * p.n + colb));
+                    v.x += H::to_float(uint16_t(rv.x & 0xffff)); v.y += H::to_float(uint16_t(rv.x >> 16));
+                    v.z += H::to_float(uint16_t(rv.y & 0xffff)); v.w += H::to_float(uint16_t(rv.y >> 16));
+                }
                 uint2 o; o.x = H::pack(v.x, v.y); o.y = H::pack(v.z, v.w);
                 *reinterpret_cast<uint2*>(out + (size_t)mb * p.n + colb) = o;
             }
@@ -863,6 +893,7 @@ int launch_stream_cfg(cudaStream_t st, const QGemmArgs& a, int ctas) {
     p.per = p.units / p.warps; p.rem = p.units % p.warps;
     p.ar = make_ar_params(a);
     if (p.ar.world > 1 && (size_t)a.m * a.n * 8 > p.ar.slot_bytes) return MT_ERR_TOO_LARGE;
+    p.residual = a.residual; p.swiglu = a.epilogue == MT_EPILOGUE_SWIGLU ? 1 : 0;
     p.zp1_const = 1 << (a.bits - 1);
     p.pdl = (a.flags & MT_FLAG_PDL) ? 1 : 0;
     const int grid = (p.warps + NW - 1) / NW;
@@ -982,6 +1013,7 @@ int launch_vec(cudaStream_t st, const QGemmArgs& a) {
     p.cluster = (splits >= 2 && splits <= 8 && !no_cluster) ? 1 : 0;
     p.ar = make_ar_params(a);
     if (p.ar.world > 1 && (size_t)a.m * a.n * 8 > p.ar.slot_bytes) return MT_ERR_TOO_LARGE;
+    p.residual = a.residual; p.swiglu = a.epilogue == MT_EPILOGUE_SWIGLU ? 1 : 0;
     const int mb = a.m == 1 ? 1 : 2;
     const size_t smem = (size_t)VEC_WARPS * mb * slice_ks * 16 + (size_t)VEC_WARPS * mb * (slice_ks / cks) * 8;
     if (smem > 160 * 1024) return MT_ERR_TOO_LARGE;

@@ -25,6 +25,14 @@ project root):
   ``examples/qwen1_5_int8.py:156-200``; fp32 accumulation from
   ``minit/cuda/kernel/cublas.py:122-127`` (``CUBLAS_COMPUTE_32F``); the bias add
   of ``QLinearWithBias.forward`` ``examples/qwen1_5_int8.py:311-317``.
+* ``sigmoid`` / ``silu`` / ``swiglu`` / ``add_residual`` -- the elementwise rules of
+  ``minit/cuda/dispatch.py:135-143`` (``{0} + {1}``, ``{0} * {1}`` in the tensor dtype;
+  sigmoid ``1.0 / (1.0 + expf((float)-{0}))`` cast to the tensor dtype), composed as
+  ``silu(x) = x * sigmoid(x)`` (``examples/llama3_70b.py:44-45``) and
+  ``down(silu(gate(x)) * up(x))`` (``examples/llama3_70b.py:126-130``); the residual add is
+  ``x + attention_output`` (``examples/llama3_70b.py:160-162``).  Every step rounds to the tensor dtype.
+* ``interleave_gate_up`` -- no counterpart in the reference: the column order this build's fused
+  gate / up linear uses (blocks of eight = four gate, four up columns), restated in numpy.
 * ``shard_*`` -- the tensor-parallel rules ``minit/collective/dispatch.py:26-37``
   and the local slice of ``minit/collective/tensor.py:88-94``.
 """
@@ -37,6 +45,7 @@ __all__ = [
     "pack_rows", "pack_cols", "unpack_rows", "unpack_cols", "dequantize",
     "dequantize_packed", "qlinear", "w8_perchannel_as_gptq", "w8_perchannel_linear",
     "shard_column", "shard_row", "make_gptq_case", "make_w8_case", "tolerance_ok",
+    "sigmoid", "silu", "swiglu", "add_residual", "interleave_columns", "interleave_gate_up",
 ]
 
 
@@ -166,6 +175,48 @@ def w8_perchannel_as_gptq(w_i8: np.ndarray, scales: torch.Tensor):
 def w8_perchannel_linear(x: torch.Tensor, w_i8: np.ndarray, scales: torch.Tensor, bias=None) -> torch.Tensor:
     qweight, g_idx, qzeros, s = w8_perchannel_as_gptq(w_i8, scales)
     return qlinear(x, dequantize_packed(qweight, g_idx, qzeros, s, 8), bias)
+
+
+# ---------------------------------------------------------------------------
+# the elementwise steps around the linears of a gated feed-forward
+# ---------------------------------------------------------------------------
+def sigmoid(x: torch.Tensor) -> torch.Tensor:
+    """T(1.0 / (1.0 + expf(float(-x)))): fp32 exp, the division in double (the literals are doubles)."""
+    e = torch.exp((-x).float()).double()
+    return (1.0 / (1.0 + e)).to(x.dtype)
+
+
+def silu(x: torch.Tensor) -> torch.Tensor:
+    return (x.float() * sigmoid(x).float()).to(x.dtype)          # one multiply in T: exact product, one rounding
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """T(silu(gate) * up), silu itself already rounded to T (three roundings after the linears)."""
+    return (silu(gate).float() * up.float()).to(gate.dtype)
+
+
+def add_residual(residual: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    return (residual.float() + y.float()).to(y.dtype)
+
+
+def interleave_columns(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """[R, H], [R, H] -> [R, 2H]: output column c = a[:, 4 (c // 8) + c % 8] if c % 8 < 4 else b[:, 4 (c // 8) + c % 8 - 4]."""
+    r, h = a.shape
+    out = np.empty((r, 2 * h), dtype=a.dtype)
+    o = out.reshape(r, h // 4, 8)
+    o[:, :, :4] = a.reshape(r, h // 4, 4)
+    o[:, :, 4:] = b.reshape(r, h // 4, 4)
+    return out
+
+
+def interleave_gate_up(gate, up, bits: int):
+    """(qweight, qzeros, scales) of the gate and up linears -> the same three for the fused linear."""
+    gq, gz, gs = (_np(t) for t in gate)
+    uq, uz, us = (_np(t) for t in up)
+    qw = interleave_columns(gq, uq)
+    sc = interleave_columns(gs.view(np.uint16) if gs.dtype != np.uint16 else gs, us.view(np.uint16) if us.dtype != np.uint16 else us)
+    z = interleave_columns(unpack_cols(gz, bits), unpack_cols(uz, bits))
+    return qw, pack_cols(z, bits), sc
 
 
 # ---------------------------------------------------------------------------

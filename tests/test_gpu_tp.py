@@ -43,6 +43,10 @@ def _worker(rank, size, port, results):
         ref = O.qlinear(h, w2, c2["bias"])
         ok, err, bound = O.tolerance_ok(y, ref, 2e-2)   # two chained linears + fp16 all-reduce: 2e-2 * rms
         assert ok, f"rank {rank}: err {err} > {bound}"
+        res = torch.randn((4, 1024), generator=torch.Generator().manual_seed(5)).half()
+        yr = row(h_local * 0.05, residual=res.to(dev))  # NCCL path: rank 0 folds the residual into its partial
+        ok, err, bound = O.tolerance_ok(yr, O.add_residual(res, ref), 2e-2)
+        assert ok, f"rank {rank} residual over NCCL: err {err} > {bound}"
         # the same row-parallel linear with the all-reduce fused into the GEMM epilogue (peer memory, no NCCL):
         # several calls in a row (alternating slots), two shapes, bit-identical on all ranks
         from minit_b200.collective import FusedAllReduce
@@ -75,6 +79,11 @@ def _worker(rank, size, port, results):
             g4 = [torch.empty_like(y4) for _ in range(size)]
             dist.all_gather(g4, y4)
             assert all(torch.equal(g4[0], t) for t in g4), "fused GEMV all-reduce results differ between ranks"
+            # the block's residual add folded into the same kernel (added once, to the reduced sum)
+            res4 = torch.randn((m4, 8192), generator=torch.Generator().manual_seed(seed4)).half()
+            y4r = rowf4(x4, flags=tune, residual=res4.to(dev))
+            ok, err, bound = O.tolerance_ok(y4r, O.add_residual(res4, ref4), 1e-2)
+            assert ok, f"rank {rank} fused GEMV + residual M={m4} tune={tune:#x}: err {err} > {bound}"
         # a captured graph of fused calls replays correctly: the call counter lives on the device
         xg = x4.clone(); yg = torch.empty_like(y4)
         side = torch.cuda.Stream()
