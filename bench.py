@@ -115,6 +115,71 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------
 # our arm
 # ---------------------------------------------------------------------------------------
+def run_mlp_block(args):
+    """The feed-forward block of a decode step, down(silu(gate(x)) * up(x)) + residual on the Llama-3-70B shapes,
+    timed with its elementwise steps as separate launches (gate/up linear, activation, down linear, residual add)
+    and fused into the two linears.  Distinct weights per layer (more than L2), one CUDA graph per form."""
+    import minit_b200 as M
+    from minit_b200 import _lib
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    m, nl = args.m, min(args.layers, 8)
+    gen = torch.Generator(device=dev).manual_seed(0)
+
+    def rnd_linear(k, n):
+        qw = torch.randint(-2**31, 2**31 - 1, (k // 8, n), device=dev, dtype=torch.int64, generator=gen).to(torch.int32)
+        qz = torch.randint(-2**31, 2**31 - 1, (k // GROUP, n // 8), device=dev, dtype=torch.int64, generator=gen).to(torch.int32)
+        sc = (0.002 + 0.018 * torch.rand((k // GROUP, n), device=dev, generator=gen)).half()
+        return qw, qz, sc
+    layers = [(rnd_linear(HIDDEN, 2 * INTER), rnd_linear(INTER, HIDDEN)) for _ in range(nl)]
+    x = torch.randn((m, HIDDEN), device=dev).half()
+    res = torch.randn((m, HIDDEN), device=dev).half()
+    y = torch.empty((m, 2 * INTER), device=dev, dtype=torch.float16)
+    h = torch.empty((m, INTER), device=dev, dtype=torch.float16)
+    o = torch.empty((m, HIDDEN), device=dev, dtype=torch.float16)
+    flags = _lib.FLAG_PDL if args.pdl else 0
+
+    def separate():
+        for (gq, gz, gs), (dq, dz, ds) in layers:
+            M.quantized_matrix_multiply(x, gq, gz, gs, None, bits=BITS, out=y, flags=flags)
+            hh = M.swiglu_interleaved(y)
+            M.quantized_matrix_multiply(hh, dq, dz, ds, None, bits=BITS, out=o, flags=flags)
+            torch.add(o, res, out=o)
+
+    def fused():
+        for (gq, gz, gs), (dq, dz, ds) in layers:
+            M.quantized_gate_up_swiglu(x, gq, gz, gs, bits=BITS, out=h, flags=flags)
+            M.quantized_matrix_multiply_residual(h, dq, dz, ds, None, res, bits=BITS, out=o, flags=flags)
+
+    def timed(fn):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(max(3, args.warmup)):
+                fn()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                fn()
+            graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(side)
+            for _ in range(args.steps):
+                graph.replay()
+            e1.record(side)
+            torch.cuda.synchronize()
+        torch.cuda.current_stream().wait_stream(side)
+        return e0.elapsed_time(e1) * 1e3 / (args.steps * nl)
+    us_sep, us_fused = timed(separate), timed(fused)
+    hbm_peak, kind = peaks()
+    wb = weight_bytes(HIDDEN, 2 * INTER) + weight_bytes(INTER, HIDDEN)
+    print(json.dumps({"mlp_block": "llama3-70b gate/up + silu*up + down + residual", "m": m, "layers": nl,
+                      "us_per_block_separate": us_sep, "launches_separate": 4, "us_per_block_fused": us_fused, "launches_fused": 2,
+                      "weight_GBps_fused": wb / us_fused / 1e3, "hbm_frac_fused": wb / us_fused / 1e3 / hbm_peak, "peak": kind,
+                      "note": "weights of %d layers in rotation (%.1f GB), CUDA graph, PDL %s" % (nl, wb * nl / 1e9, "on" if args.pdl else "off")}))
+
+
 def run_ours(args):
     import torch.distributed as dist
     import minit_b200 as M
@@ -390,6 +455,7 @@ def main():
                     help="row-parallel exchange: fused into the GEMM epilogue over peer memory, or an NCCL all-reduce after it")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--single-shape", default=None, help="K,N : time one linear instead of the workload (profiling aid)")
+    ap.add_argument("--mlp-block", action="store_true", help="time the feed-forward block with separate and with fused elementwise steps")
     ap.add_argument("--tune", type=lambda v: int(v, 0), default=0, help="single-shape mode: extra tuning bits ORed into the flags")
     ap.add_argument("--kernel", default="auto", choices=["auto", "ring", "dtc", "tc", "vec", "umma"])
     ap.add_argument("--bits", type=int, default=4)
@@ -397,6 +463,8 @@ def main():
     args = ap.parse_args()
     if args.single_shape:
         return run_single_shape(args)
+    if args.mlp_block:
+        return run_mlp_block(args)
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":

@@ -113,3 +113,45 @@ def test_tensor_parallel_sharding_identities(size):
         wr = O.dequantize_packed(qw.contiguous(), None, qz.contiguous(), s.contiguous(), 4)
         part += c["x"][:, ks * r:ks * (r + 1)].float() @ wr.float()
     assert torch.allclose(part, full, atol=1e-3)
+
+
+def test_elementwise_steps_of_the_feed_forward():
+    """sigmoid / silu / swiglu / add_residual follow the reference's elementwise rules (one rounding per step)."""
+    import numpy as np
+    import torch
+    from oracle import qlinear_oracle as O
+    x = torch.tensor([-20.0, -3.0, -0.5, 0.0, 0.25, 2.0, 11.0]).half()
+    s = O.sigmoid(x)
+    assert s.dtype == torch.float16
+    assert torch.equal(s, torch.sigmoid(x.double()).half())          # same value, rounded once
+    assert torch.equal(O.silu(x), (x.double() * s.double()).half())
+    u = torch.tensor([2.0, -1.0, 0.5, 3.0, -4.0, 1.5, 0.125]).half()
+    assert torch.equal(O.swiglu(x, u), (O.silu(x).double() * u.double()).half())
+    assert torch.equal(O.add_residual(x, u), (x.double() + u.double()).half())
+    for dtype in (torch.float16, torch.bfloat16):
+        g = (torch.randn(4096, generator=torch.Generator().manual_seed(0)) * 4).to(dtype)
+        exact = torch.nn.functional.silu(g.double())
+        ulp = 2.0 ** (-10 if dtype == torch.float16 else -7)
+        assert ((O.silu(g).double() - exact).abs() <= exact.abs() * ulp * 1.5 + 2e-6).all()      # 2e-6: fp16 sigmoid is subnormal below g = -10
+
+
+def test_gate_up_interleave_layout():
+    """Blocks of eight output columns = four gate columns, then the four up columns of the same indices; packed
+    zero points follow their columns."""
+    import numpy as np
+    from oracle import qlinear_oracle as O
+    a = np.arange(2 * 16).reshape(2, 16)
+    out = O.interleave_columns(a, a + 100)
+    assert out[0].tolist() == [0, 1, 2, 3, 100, 101, 102, 103, 4, 5, 6, 7, 104, 105, 106, 107,
+                               8, 9, 10, 11, 108, 109, 110, 111, 12, 13, 14, 15, 112, 113, 114, 115]
+    for bits in (4, 8):
+        g = O.make_gptq_case(256, 64, 1, bits=bits, seed=1)
+        u = O.make_gptq_case(256, 64, 1, bits=bits, seed=2)
+        qw, qz, sc = O.interleave_gate_up((g["qweight"], g["qzeros"], g["scales"].view(torch.int16)),
+                                          (u["qweight"], u["qzeros"], u["scales"].view(torch.int16)), bits)
+        # dequantizing the interleaved linear gives the interleaved dequantized weights
+        w = O.dequantize_packed(torch.from_numpy(qw), None, torch.from_numpy(qz), torch.from_numpy(sc.view(np.int16)).view(torch.float16), bits)
+        wg = O.dequantize_packed(g["qweight"], None, g["qzeros"], g["scales"], bits)
+        wu = O.dequantize_packed(u["qweight"], None, u["qzeros"], u["scales"], bits)
+        ref = O.interleave_columns(wg.view(torch.int16).numpy(), wu.view(torch.int16).numpy())
+        assert np.array_equal(w.view(torch.int16).numpy(), ref)
