@@ -180,6 +180,80 @@ def run_mlp_block(args):
                       "note": "weights of %d layers in rotation (%.1f GB), CUDA graph, PDL %s" % (nl, wb * nl / 1e9, "on" if args.pdl else "off")}))
 
 
+def run_decode_layer(args):
+    """One token through whole decoder layers of Llama-3-70B on one GPU (RMSNorm, fused qkv linear, rotary embedding + cache
+    append, attention over `--context` cached positions, o_proj + residual, RMSNorm, fused feed-forward + residual):
+    seven launches per layer.  Distinct weights and caches per layer, one CUDA graph over all of them."""
+    import minit_b200 as M
+    from minit_b200 import decoder as D
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    m, nl, ctx = args.m, min(args.layers, 16), args.context
+    gen = torch.Generator(device=dev).manual_seed(0)
+    HQ, HKV = Q_HEADS, KV_HEADS
+
+    def rnd_linear(k, n):
+        qw = torch.randint(-2**31, 2**31 - 1, (k // 8, n), device=dev, dtype=torch.int64, generator=gen).to(torch.int32)
+        qz = torch.randint(-2**31, 2**31 - 1, (k // GROUP, n // 8), device=dev, dtype=torch.int64, generator=gen).to(torch.int32)
+        sc = (0.0005 + 0.001 * torch.rand((k // GROUP, n), device=dev, generator=gen)).half()
+        return qw, qz, sc
+    cos, sin = D.rope_tables(HEAD_DIM, ctx + m, 5e5, torch.float16, dev)
+    layers = []
+    for _ in range(nl):
+        cache = D.KVCache(ctx + m, HKV, HEAD_DIM, torch.float16, dev)
+        cache.k.normal_(generator=gen); cache.v.normal_(generator=gen)
+        layers.append(dict(qkv=rnd_linear(HIDDEN, (HQ + 2 * HKV) * HEAD_DIM), o=rnd_linear(HQ * HEAD_DIM, HIDDEN),
+                           gu=rnd_linear(HIDDEN, 2 * INTER), dn=rnd_linear(INTER, HIDDEN), cache=cache,
+                           n1=torch.ones(HIDDEN, device=dev, dtype=torch.float16), n2=torch.ones(HIDDEN, device=dev, dtype=torch.float16)))
+    x0 = torch.randn((m, HIDDEN), device=dev).half()
+    flags = _flag_pdl() if args.pdl else 0
+
+    def step():
+        x = x0
+        for L in layers:
+            xn = D.rms_norm(x, L["n1"])
+            qkv = M.quantized_matrix_multiply(xn, *L["qkv"], None, bits=BITS, flags=flags)
+            q = D.rope_append(qkv, cos, sin, L["cache"], HQ, ctx)
+            a = D.attention_decode(q, L["cache"], ctx)
+            h = M.quantized_matrix_multiply_residual(a, *L["o"], None, x, bits=BITS, flags=flags)
+            hn = D.rms_norm(h, L["n2"])
+            g = M.quantized_gate_up_swiglu(hn, *L["gu"], bits=BITS, flags=flags)
+            x = M.quantized_matrix_multiply_residual(g, *L["dn"], None, h, bits=BITS, flags=flags)
+        return x
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(max(3, args.warmup)):
+            step()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            step()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(side)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(side)
+        torch.cuda.synchronize()
+    torch.cuda.current_stream().wait_stream(side)
+    us = e0.elapsed_time(e1) * 1e3 / (args.steps * nl)
+    hbm_peak, kind = peaks()
+    wb = sum(weight_bytes(k, n) for _, k, n, _ in layer_shapes(1))
+    kvb = 2 * ctx * HKV * HEAD_DIM * 2
+    print(json.dumps({"decode_layer": "llama3-70b, one GPU, int4 g128", "m": m, "context": ctx, "layers_timed": nl, "launches_per_layer": 7,
+                      "us_per_layer": us, "tokens_per_s_80_layers": m * 1e6 / (us * LAYERS),
+                      "bytes_per_layer": wb + kvb, "hbm_frac": (wb + kvb) / us / 1e3 / hbm_peak, "peak": kind,
+                      "note": "weights + KV cache of %d layers in rotation (%.1f GB), CUDA graph" % (nl, (wb + kvb) * nl / 1e9)}))
+
+
+def _flag_pdl():
+    from minit_b200 import _lib
+    return _lib.FLAG_PDL
+
+
 def run_ours(args):
     import torch.distributed as dist
     import minit_b200 as M
@@ -456,6 +530,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--single-shape", default=None, help="K,N : time one linear instead of the workload (profiling aid)")
     ap.add_argument("--mlp-block", action="store_true", help="time the feed-forward block with separate and with fused elementwise steps")
+    ap.add_argument("--decode-layer", action="store_true", help="time whole decoder layers (norms, rope, attention, fused linears) for one token")
+    ap.add_argument("--context", type=int, default=4096, help="--decode-layer: cached positions")
     ap.add_argument("--tune", type=lambda v: int(v, 0), default=0, help="single-shape mode: extra tuning bits ORed into the flags")
     ap.add_argument("--kernel", default="auto", choices=["auto", "ring", "dtc", "tc", "vec", "umma"])
     ap.add_argument("--bits", type=int, default=4)
@@ -465,6 +541,8 @@ def main():
         return run_single_shape(args)
     if args.mlp_block:
         return run_mlp_block(args)
+    if args.decode_layer:
+        return run_decode_layer(args)
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":

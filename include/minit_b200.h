@@ -178,6 +178,36 @@ int mt_qgemm_swiglu(void* stream, const void* x, const uint32_t* qweight, const 
 int mt_swiglu(void* stream, const void* gate_up, void* out, int m, int n, int dtype);
 
 /*
+ * The steps either side of the linears in a decoder layer, for decode-sized batches of ONE sequence
+ * (m new tokens at positions offset .. offset + m - 1, as in the reference's examples):
+ *
+ * mt_rms_norm: out[r, :] = T(float(x[r, :]) / sqrt(mean(x[r, :]^2) + eps) * float(weight)), the kernel of
+ *   minit/cuda/kernel/cuda/rms_norm.py:55-91 for the last axis.  h % 8 == 0.
+ *
+ * mt_rope_append: rotary embedding and cache append for one fused qkv row per token,
+ *   qkv[m, (hq + 2 hkv) * d] = [q heads | k heads | v heads].  Pairs (x[2i], x[2i+1]) of every q and k head are
+ *   rotated by (cos, sin)[position, i] in fp32 (minit/cuda/kernel/cuda/rope.py:58-73; tables fp32
+ *   [table_rows, d/2]); q goes to q_out[m, hq, d], k and v to k_cache / v_cache[capacity, hkv, d] at row
+ *   offset + token.  This replaces rope + F.tie of examples/llama3_70b.py:97-102: the cache is preallocated
+ *   and holds every kv head once (the reference stores it nr_groups times, :85-94).  d == 128.
+ *   offset_dev (device int32, may be NULL) overrides `offset` so that a captured graph can be replayed as
+ *   the sequence grows; rows beyond capacity are not written.
+ *
+ * mt_attention_decode: out[m, hq * d] = softmax(q k^T * scale + causal mask) v against the cache rows
+ *   0 .. offset + token (examples/llama3_70b.py:103-115), query head n reading kv head n / (hq / hkv).
+ *   One kernel, fp32 throughout, one rounding (the reference rounds scores, scaled scores, probabilities
+ *   and output separately).  max_len bounds offset + m (the grid is sized for it; pass the cache capacity
+ *   with offset_dev).  d == 128, hq / hkv <= 8.  workspace >= mt_attention_workspace_bytes(m, hkv, max_len),
+ *   zeroed once by the caller (the kernel leaves it zeroed).
+ */
+int mt_rms_norm(void* stream, const void* x, const void* weight, void* out, int rows, int h, float eps, int dtype);
+int mt_rope_append(void* stream, const void* qkv, const float* cos_table, const float* sin_table, void* q_out, void* k_cache, void* v_cache,
+                   int m, int hq, int hkv, int d, int offset, const int32_t* offset_dev, int capacity, int table_rows, int dtype);
+size_t mt_attention_workspace_bytes(int m, int hkv, int max_len);
+int mt_attention_decode(void* stream, const void* q, const void* k_cache, const void* v_cache, void* out, int m, int hq, int hkv, int d,
+                        int offset, const int32_t* offset_dev, int max_len, float scale, void* workspace, size_t workspace_bytes, int dtype);
+
+/*
  * Which schedule mt_qgemm would run a decode call (M <= 2, no g_idx) with: > 0 = split-K factor of the
  * CUDA-core GEMV, 0 = its stream-K schedule, MT_ERR_UNSUPPORTED = the request goes to another kernel.
  * Inspection only (no launch); no counterpart in the reference, whose launcher has one fixed grid

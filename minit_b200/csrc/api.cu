@@ -399,6 +399,52 @@ int mt_swiglu(void* stream, const void* gate_up, void* out, int m, int n, int dt
     return launch_swiglu_interleaved(static_cast<cudaStream_t>(stream), gate_up, out, m, n, dtype);
 }
 
+int mt_rms_norm(void* stream, const void* x, const void* weight, void* out, int rows, int h, float eps, int dtype) {
+    if (dtype != MT_F16 && dtype != MT_BF16) return MT_ERR_DTYPE;
+    if (rows < 0 || h < 0 || h % 8 != 0 || !(eps > 0.f)) return MT_ERR_SHAPE;
+    if (rows == 0 || h == 0) return MT_OK;
+    if (!x || !weight || !out) return MT_ERR_NULL;
+    if (!aligned16(x) || !aligned16(weight) || !aligned16(out)) return MT_ERR_ALIGN;
+    int rc = check_device();
+    if (rc != MT_OK) return rc;
+    return launch_rms_norm(static_cast<cudaStream_t>(stream), x, weight, out, rows, h, eps, dtype);
+}
+
+int mt_rope_append(void* stream, const void* qkv, const float* cos_table, const float* sin_table, void* q_out, void* k_cache, void* v_cache,
+                   int m, int hq, int hkv, int d, int offset, const int32_t* offset_dev, int capacity, int table_rows, int dtype) {
+    if (dtype != MT_F16 && dtype != MT_BF16) return MT_ERR_DTYPE;
+    if (m < 0 || hq < 1 || hkv < 1 || offset < 0 || capacity < 1 || table_rows < 1) return MT_ERR_SHAPE;
+    if (d != 128) return MT_ERR_UNSUPPORTED;
+    if (!offset_dev && (offset + m > capacity || offset + m > table_rows)) return MT_ERR_SHAPE;
+    if (m == 0) return MT_OK;
+    if (!qkv || !cos_table || !sin_table || !q_out || !k_cache || !v_cache) return MT_ERR_NULL;
+    int rc = check_device();
+    if (rc != MT_OK) return rc;
+    return launch_rope_append(static_cast<cudaStream_t>(stream), qkv, cos_table, sin_table, q_out, k_cache, v_cache, m, hq, hkv, offset,
+                              offset_dev, capacity, table_rows, dtype);
+}
+
+size_t mt_attention_workspace_bytes(int m, int hkv, int max_len) {
+    if (m < 1 || hkv < 1 || max_len < 1) return 0;
+    return attention_workspace_bytes(m, hkv, max_len);
+}
+
+int mt_attention_decode(void* stream, const void* q, const void* k_cache, const void* v_cache, void* out, int m, int hq, int hkv, int d,
+                        int offset, const int32_t* offset_dev, int max_len, float scale, void* workspace, size_t workspace_bytes, int dtype) {
+    if (dtype != MT_F16 && dtype != MT_BF16) return MT_ERR_DTYPE;
+    if (m < 0 || hq < 1 || hkv < 1 || offset < 0 || max_len < 1) return MT_ERR_SHAPE;
+    if (!offset_dev && offset + m > max_len) return MT_ERR_SHAPE;
+    if (m == 0) return MT_OK;
+    if (!q || !k_cache || !v_cache || !out) return MT_ERR_NULL;
+    if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out)) return MT_ERR_ALIGN;
+    if (!workspace) return MT_ERR_WORKSPACE;
+    if (!aligned16(workspace)) return MT_ERR_ALIGN;
+    int rc = check_device();
+    if (rc != MT_OK) return rc;
+    return launch_attention_decode(static_cast<cudaStream_t>(stream), q, k_cache, v_cache, out, m, hq, hkv, d, offset, offset_dev, max_len,
+                                   scale, workspace, workspace_bytes, dtype);
+}
+
 int mt_decode_plan(int m, int n, int k, int nr_groups, int bits, size_t workspace_bytes, int flags) {
     if ((bits != 4 && bits != 8) || m < 1 || n < 1 || k < 1 || nr_groups < 1 || k % nr_groups != 0) return MT_ERR_SHAPE;
     if (check_device() != MT_OK) return MT_ERR_DEVICE;

@@ -169,6 +169,13 @@ int launch_interleave_gate_up(cudaStream_t st, const uint32_t* qw_g, const uint3
                               uint32_t* qw_out, uint32_t* qz_out, void* s_out, void* b_out, int half, int k, int groups, int bits);
 int launch_swiglu_interleaved(cudaStream_t st, const void* in, void* out, int m, int n, int dtype);   // [M,N] interleaved -> [M,N/2]
 int launch_add_residual(cudaStream_t st, void* io, const void* res, int m, int n, int dtype);        // io += res
+int launch_rms_norm(cudaStream_t st, const void* x, const void* w, void* out, int rows, int h, float eps, int dtype);
+int launch_rope_append(cudaStream_t st, const void* qkv, const float* cosv, const float* sinv, void* q_out, void* k_cache, void* v_cache,
+                       int m, int hq, int hkv, int offset, const int* offset_dev, int capacity, int table_rows, int dtype);
+size_t attention_workspace_bytes(int m, int hkv, int max_len);
+int launch_attention_decode(cudaStream_t st, const void* q, const void* k_cache, const void* v_cache, void* out,
+                            int m, int hq, int hkv, int d, int offset, const int* offset_dev, int max_len, float scale,
+                            void* workspace, size_t workspace_bytes, int dtype);
 int launch_umma(cudaStream_t st, const QGemmArgs& a);           // tcgen05 with all-warp dequant, 2 < M <= 192, contiguous groups
 bool umma_supported(const QGemmArgs& a);
 size_t umma_workspace_bytes(int m, int n, int k);

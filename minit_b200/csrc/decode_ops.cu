@@ -1,0 +1,361 @@
+// The steps either side of the quantized linears in a decoder layer, for decode-sized batches:
+//
+//  * rms_norm      out = T(float(x) / sqrt(mean(x^2) + eps) * float(w)) per row
+//                  (minit/cuda/kernel/cuda/rms_norm.py:55-91: fp32 sum of squares, divide, multiply, one rounding).
+//  * rope_append   rotary embedding of the q and k parts of a fused qkv row, (x[2i], x[2i+1]) rotated by
+//                  (cos, sin)[position, i] in fp32 (minit/cuda/kernel/cuda/rope.py:58-73), q to its own tensor,
+//                  k and v straight into the preallocated cache at row offset + token: the reference grows
+//                  the cache by concatenation (examples/llama3_70b.py:99-102) and stores every kv head
+//                  nr_groups times (:85-94); here the cache holds each kv head once.
+//  * attention     softmax(q k^T / sqrt(d) + causal mask) v for the new tokens against the cache
+//                  (examples/llama3_70b.py:103-115), one kernel: a CTA takes one kv head, one token and a
+//                  range of cached positions for all query heads of the group (K and V are read once per
+//                  group), keeps scores, online softmax and the weighted sum in fp32, and the last CTA to
+//                  finish a (token, kv head) merges the ranges in order.  The reference rounds the scores,
+//                  the scaled scores, the probabilities and the output to the tensor dtype in separate
+//                  kernels (softmax: minit/cuda/kernel/cuda/softmax.py:55-106).
+//
+// All three are bound by HBM (the cache) or by launch latency (16 KB rows), so: 16-byte loads, the
+// cache streamed through shared memory once, grids of a few CTAs per SM, no tensor cores.
+#include "common.cuh"
+
+namespace mt {
+namespace {
+
+constexpr int ATT_D = 128;                 // head size
+constexpr int ATT_MAXG = 8;                // query heads per kv head
+constexpr int ATT_WARPS = 4;
+constexpr int ATT_TILE = 32;               // cached positions per warp tile: one per lane
+constexpr int ATT_ROW = ATT_D * 2 + 16;    // bytes of a K / V row in shared memory (padded: 16-byte reads of 8 rows hit 32 banks)
+constexpr int ATT_WARP_SMEM = 2 * ATT_TILE * ATT_ROW + ATT_MAXG * ATT_TILE * 4;   // K tile, V tile, probabilities
+constexpr int ATT_PART = ATT_D + 4;        // floats of a partial result per query head: 128 weighted sums, max, sum (+ pad: rows stay 16-byte aligned)
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) rms_norm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, uint4* __restrict__ out,
+                                                       int h8, float inv_h, float eps) {
+    using H = F16x2<T>;
+    __shared__ float red[8];
+    const uint4* xr = x + (size_t)blockIdx.x * h8;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < h8; i += 256) {
+        const uint4 v = xr[i];
+        const uint32_t* p = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float a = H::to_float(uint16_t(p[q] & 0xffff)), b = H::to_float(uint16_t(p[q] >> 16));
+            ss = fmaf(a, a, ss); ss = fmaf(b, b, ss);
+        }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) tot += red[q];
+    const float rms = sqrtf(tot * inv_h + eps);
+    for (int i = threadIdx.x; i < h8; i += 256) {
+        const uint4 v = xr[i], g = w[i];
+        const uint32_t* p = reinterpret_cast<const uint32_t*>(&v);
+        const uint32_t* pg = reinterpret_cast<const uint32_t*>(&g);
+        uint4 o; uint32_t* po = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            po[q] = H::pack(H::to_float(uint16_t(p[q] & 0xffff)) / rms * H::to_float(uint16_t(pg[q] & 0xffff)),
+                            H::to_float(uint16_t(p[q] >> 16)) / rms * H::to_float(uint16_t(pg[q] >> 16)));
+        out[(size_t)blockIdx.x * h8 + i] = o;
+    }
+}
+
+// one thread per (token, head of q | k | v, pair of values)
+template <typename T>
+__global__ void rope_append_kernel(const uint32_t* __restrict__ qkv, const float* __restrict__ cosv, const float* __restrict__ sinv,
+                                   uint32_t* __restrict__ q_out, uint32_t* __restrict__ k_cache, uint32_t* __restrict__ v_cache,
+                                   int m, int hq, int hkv, int offset, const int* __restrict__ offset_dev, int capacity, int table_rows) {
+    using H = F16x2<T>;
+    constexpr int HALF = ATT_D / 2;
+    const int heads = hq + 2 * hkv;
+    const long long total = (long long)m * heads * HALF;
+    const int off = offset_dev ? *offset_dev : offset;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int c = int(i % HALF); const int hd = int((i / HALF) % heads); const int tok = int(i / ((long long)HALF * heads));
+        const int pos = off + tok;
+        const uint32_t v = qkv[i];                                       // row layout [q heads | k heads | v heads] x [D]
+        if (hd >= hq + hkv) {                                            // v: copy
+            if (pos < capacity) v_cache[((size_t)pos * hkv + (hd - hq - hkv)) * HALF + c] = v;
+            continue;
+        }
+        const int tp = pos < table_rows ? pos : table_rows - 1;
+        const float re = H::to_float(uint16_t(v & 0xffff)), im = H::to_float(uint16_t(v >> 16));
+        const float cs = cosv[(size_t)tp * HALF + c], sn = sinv[(size_t)tp * HALF + c];
+        const uint32_t r = H::pack(re * cs - im * sn, im * cs + re * sn);
+        if (hd < hq) q_out[((size_t)tok * hq + hd) * HALF + c] = r;
+        else if (pos < capacity) k_cache[((size_t)pos * hkv + (hd - hq)) * HALF + c] = r;
+    }
+}
+
+struct AttParams {
+    const void* q; const void* k_cache; const void* v_cache; void* out;
+    float* partial; unsigned* counters;
+    const int* offset_dev;
+    int m, hq, hkv, group;      // group = hq / hkv
+    int offset;                 // cached positions before the first new token
+    int splits, chunk;          // CTAs per (token, kv head); positions per CTA (a multiple of 32 * ATT_WARPS)
+    int max_len;                // the caller's bound on offset + m: no cache row at or beyond it is read
+    float scale;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const AttParams p) {
+    using H = F16x2<T>;
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ __align__(16) float q_s[ATT_MAXG][ATT_D];                  // the group's queries, pre-scaled
+    __shared__ __align__(16) float part_s[ATT_WARPS][ATT_MAXG][ATT_PART];
+    __shared__ int s_last;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int split = blockIdx.x, kvh = blockIdx.y, tok = blockIdx.z;
+    const int G = p.group;
+    const int off = p.offset_dev ? *p.offset_dev : p.offset;
+    const int len = min(off + tok + 1, p.max_len);          // causal: the token sees the cache and itself
+    const int s0 = split * p.chunk, s1 = min(len, s0 + p.chunk);
+
+    const uint16_t* qg = reinterpret_cast<const uint16_t*>(p.q) + ((size_t)tok * p.hq + (size_t)kvh * G) * ATT_D;
+    for (int i = tid; i < G * ATT_D; i += ATT_WARPS * 32) q_s[i / ATT_D][i % ATT_D] = H::to_float(qg[i]) * p.scale;
+    __syncthreads();
+
+    unsigned char* ks = smem + warp * ATT_WARP_SMEM;
+    unsigned char* vs = ks + ATT_TILE * ATT_ROW;
+    float* ps = reinterpret_cast<float*>(vs + ATT_TILE * ATT_ROW);      // [G][32]
+    const uint32_t ks_a = (uint32_t)__cvta_generic_to_shared(ks), vs_a = (uint32_t)__cvta_generic_to_shared(vs);
+    const unsigned char* kc = static_cast<const unsigned char*>(p.k_cache);
+    const unsigned char* vc = static_cast<const unsigned char*>(p.v_cache);
+    const size_t row_bytes = (size_t)p.hkv * ATT_D * 2;
+
+    float mx[ATT_MAXG], ls[ATT_MAXG], acc[ATT_MAXG][4];
+#pragma unroll
+    for (int h = 0; h < ATT_MAXG; ++h) { mx[h] = -INFINITY; ls[h] = 0.f; acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.f; }
+
+    for (int t0 = s0 + warp * ATT_TILE; t0 < s1; t0 += ATT_WARPS * ATT_TILE) {
+        // ---- the tile's K and V rows -> shared memory (16 lanes copy one 256-byte row) ----
+        __syncwarp();
+#pragma unroll
+        for (int r = 0; r < ATT_TILE / 2; ++r) {
+            const int row = 2 * r + (lane >> 4), pos = t0 + row;
+            const bool live = pos < s1;
+            const size_t g = (live ? (size_t)pos : 0) * row_bytes + (size_t)kvh * ATT_D * 2 + (lane & 15) * 16;
+            const int sz = live ? 16 : 0;                   // rows past the range: zeros
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(ks_a + row * ATT_ROW + (lane & 15) * 16), "l"(kc + g), "r"(sz) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vs_a + row * ATT_ROW + (lane & 15) * 16), "l"(vc + g), "r"(sz) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
+        // ---- scores: lane = cached position ----
+        float s[ATT_MAXG];
+#pragma unroll
+        for (int h = 0; h < ATT_MAXG; ++h) s[h] = 0.f;
+        const unsigned char* krow = ks + lane * ATT_ROW;
+#pragma unroll 4
+        for (int d8 = 0; d8 < ATT_D / 8; ++d8) {
+            const uint4 kv = *reinterpret_cast<const uint4*>(krow + d8 * 16);
+            const uint32_t* kp = reinterpret_cast<const uint32_t*>(&kv);
+            float kf[8];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { kf[2 * q] = H::to_float(uint16_t(kp[q] & 0xffff)); kf[2 * q + 1] = H::to_float(uint16_t(kp[q] >> 16)); }
+#pragma unroll
+            for (int h = 0; h < ATT_MAXG; ++h) {
+                if (h < G) {
+                    const float4 qa = *reinterpret_cast<const float4*>(&q_s[h][d8 * 8]);
+                    const float4 qb = *reinterpret_cast<const float4*>(&q_s[h][d8 * 8 + 4]);
+                    s[h] = fmaf(qa.x, kf[0], s[h]); s[h] = fmaf(qa.y, kf[1], s[h]); s[h] = fmaf(qa.z, kf[2], s[h]); s[h] = fmaf(qa.w, kf[3], s[h]);
+                    s[h] = fmaf(qb.x, kf[4], s[h]); s[h] = fmaf(qb.y, kf[5], s[h]); s[h] = fmaf(qb.z, kf[6], s[h]); s[h] = fmaf(qb.w, kf[7], s[h]);
+                }
+            }
+        }
+        const bool live = t0 + lane < s1;
+        // ---- online softmax: new running maximum, rescale, probabilities to shared memory ----
+#pragma unroll
+        for (int h = 0; h < ATT_MAXG; ++h) {
+            if (h < G) {
+                const float sv = live ? s[h] : -INFINITY;
+                const float mn = fmaxf(mx[h], warp_max(sv));            // finite: position t0 is live
+                const float resc = __expf(mx[h] - mn);                   // 0 on the first tile (mx = -inf)
+                const float pv = live ? __expf(sv - mn) : 0.f;
+                mx[h] = mn;
+                ls[h] = ls[h] * resc + pv;                              // per-lane partial sums, reduced at the end
+                acc[h][0] *= resc; acc[h][1] *= resc; acc[h][2] *= resc; acc[h][3] *= resc;
+                ps[h * ATT_TILE + lane] = pv;
+            }
+        }
+        __syncwarp();
+        // ---- weighted sum of V: lane = four of the 128 dimensions ----
+#pragma unroll 2
+        for (int t4 = 0; t4 < ATT_TILE; t4 += 4) {
+            float vf[4][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint2 vv = *reinterpret_cast<const uint2*>(vs + (t4 + j) * ATT_ROW + lane * 8);
+                vf[j][0] = H::to_float(uint16_t(vv.x & 0xffff)); vf[j][1] = H::to_float(uint16_t(vv.x >> 16));
+                vf[j][2] = H::to_float(uint16_t(vv.y & 0xffff)); vf[j][3] = H::to_float(uint16_t(vv.y >> 16));
+            }
+#pragma unroll
+            for (int h = 0; h < ATT_MAXG; ++h) {
+                if (h < G) {
+                    const float4 pp = *reinterpret_cast<const float4*>(ps + h * ATT_TILE + t4);
+                    const float pj[4] = {pp.x, pp.y, pp.z, pp.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) acc[h][e] = fmaf(pj[j], vf[j][e], acc[h][e]);
+                }
+            }
+        }
+    }
+
+    // ---- the CTA's warps -> one partial per query head (merged in warp order) ----
+#pragma unroll
+    for (int h = 0; h < ATT_MAXG; ++h) {
+        if (h < G) {
+            const float l = warp_sum(ls[h]);
+            if (lane == 0) { part_s[warp][h][ATT_D] = mx[h]; part_s[warp][h][ATT_D + 1] = l; }
+            *reinterpret_cast<float4*>(&part_s[warp][h][lane * 4]) = make_float4(acc[h][0], acc[h][1], acc[h][2], acc[h][3]);
+        }
+    }
+    __syncthreads();
+    // thread -> (query head, dimension): 8 x 128 values over 128 threads
+    const size_t slot = ((size_t)tok * p.hkv + kvh) * p.splits;
+    auto merge_store = [&](int h, int d, float m_all, float l_all, float a_all) {
+        const uint16_t o = H::from_float(l_all > 0.f ? a_all / l_all : 0.f);
+        reinterpret_cast<uint16_t*>(p.out)[((size_t)tok * p.hq + (size_t)kvh * G + h) * ATT_D + d] = o;
+        (void)m_all;
+    };
+    for (int h = 0; h < G; ++h) {
+        const int d = tid;                                  // 128 threads = 128 dimensions
+        float m_all = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) m_all = fmaxf(m_all, part_s[w][h][ATT_D]);
+        float l_all = 0.f, a_all = 0.f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) {
+            const float f = part_s[w][h][ATT_D] == -INFINITY ? 0.f : __expf(part_s[w][h][ATT_D] - m_all);
+            l_all = fmaf(part_s[w][h][ATT_D + 1], f, l_all);
+            a_all = fmaf(part_s[w][h][d], f, a_all);
+        }
+        if (p.splits == 1) {
+            merge_store(h, d, m_all, l_all, a_all);
+        } else {
+            float* dst = p.partial + ((slot + split) * ATT_MAXG + h) * ATT_PART;
+            if (d == 0) { __stcg(dst + ATT_D, m_all); __stcg(dst + ATT_D + 1, l_all); }
+            __stcg(dst + d, a_all);
+        }
+    }
+    if (p.splits == 1) return;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = (atomicAdd(p.counters + tok * p.hkv + kvh, 1u) == unsigned(p.splits - 1));
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const int nsplit = (len + p.chunk - 1) / p.chunk;       // ranges that hold positions; the rest wrote (-inf, 0, 0)
+    for (int h = 0; h < G; ++h) {
+        const int d = tid;
+        const float* src = p.partial + (slot * ATT_MAXG + h) * ATT_PART;
+        float m_all = -INFINITY;
+        for (int sp = 0; sp < nsplit; ++sp) m_all = fmaxf(m_all, __ldcg(src + (size_t)sp * ATT_MAXG * ATT_PART + ATT_D));
+        float l_all = 0.f, a_all = 0.f;
+        for (int sp = 0; sp < nsplit; ++sp) {
+            const float* s2 = src + (size_t)sp * ATT_MAXG * ATT_PART;
+            const float ms = __ldcg(s2 + ATT_D);
+            const float f = ms == -INFINITY ? 0.f : __expf(ms - m_all);
+            l_all = fmaf(__ldcg(s2 + ATT_D + 1), f, l_all);
+            a_all = fmaf(__ldcg(s2 + d), f, a_all);
+        }
+        merge_store(h, d, m_all, l_all, a_all);
+    }
+    if (tid == 0) p.counters[tok * p.hkv + kvh] = 0;
+}
+
+void attention_plan(int max_len, int& splits, int& chunk) {
+    // one 32-position tile per warp and CTA while that gives at most 64 CTAs per (token, kv head); beyond, longer ranges
+    const int tile = ATT_WARPS * ATT_TILE;
+    int tiles = (max_len + tile - 1) / tile;
+    if (tiles < 1) tiles = 1;
+    const int per = (tiles + 63) / 64;
+    chunk = per * tile;
+    splits = (tiles + per - 1) / per;
+}
+
+}  // namespace
+
+int launch_rms_norm(cudaStream_t st, const void* x, const void* w, void* out, int rows, int h, float eps, int dtype) {
+    if (dtype == MT_F16) rms_norm_kernel<__half><<<rows, 256, 0, st>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(w), static_cast<uint4*>(out), h / 8, 1.f / h, eps);
+    else rms_norm_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(w), static_cast<uint4*>(out), h / 8, 1.f / h, eps);
+    return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_CUDA;
+}
+
+int launch_rope_append(cudaStream_t st, const void* qkv, const float* cosv, const float* sinv, void* q_out, void* k_cache, void* v_cache,
+                       int m, int hq, int hkv, int offset, const int* offset_dev, int capacity, int table_rows, int dtype) {
+    const long long total = (long long)m * (hq + 2 * hkv) * (ATT_D / 2);
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (dtype == MT_F16)
+        rope_append_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const uint32_t*>(qkv), cosv, sinv, static_cast<uint32_t*>(q_out),
+                                                                     static_cast<uint32_t*>(k_cache), static_cast<uint32_t*>(v_cache), m, hq, hkv, offset, offset_dev, capacity, table_rows);
+    else
+        rope_append_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const uint32_t*>(qkv), cosv, sinv, static_cast<uint32_t*>(q_out),
+                                                                            static_cast<uint32_t*>(k_cache), static_cast<uint32_t*>(v_cache), m, hq, hkv, offset, offset_dev, capacity, table_rows);
+    return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_CUDA;
+}
+
+size_t attention_workspace_bytes(int m, int hkv, int max_len) {
+    int splits, chunk;
+    attention_plan(max_len, splits, chunk);
+    const size_t counters = (((size_t)m * hkv * 4) + 255) & ~(size_t)255;
+    return counters + (size_t)m * hkv * splits * ATT_MAXG * ATT_PART * 4;
+}
+
+int launch_attention_decode(cudaStream_t st, const void* q, const void* k_cache, const void* v_cache, void* out,
+                            int m, int hq, int hkv, int d, int offset, const int* offset_dev, int max_len, float scale,
+                            void* workspace, size_t workspace_bytes, int dtype) {
+    if (d != ATT_D || hkv < 1 || hq % hkv != 0 || hq / hkv > ATT_MAXG) return MT_ERR_UNSUPPORTED;
+    AttParams p;
+    p.q = q; p.k_cache = k_cache; p.v_cache = v_cache; p.out = out;
+    p.m = m; p.hq = hq; p.hkv = hkv; p.group = hq / hkv; p.offset = offset; p.offset_dev = offset_dev; p.scale = scale;
+    attention_plan(max_len, p.splits, p.chunk);
+    p.max_len = max_len;
+    if (attention_workspace_bytes(m, hkv, max_len) > workspace_bytes) return MT_ERR_WORKSPACE;
+    const size_t counters = (((size_t)m * hkv * 4) + 255) & ~(size_t)255;
+    p.counters = static_cast<unsigned*>(workspace);
+    p.partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + counters);
+    const dim3 grid(p.splits, hkv, m);
+    const size_t smem = (size_t)ATT_WARPS * ATT_WARP_SMEM;
+    static bool configured[64][2] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return MT_ERR_CUDA; }
+    if (dtype == MT_F16) {
+        if (!configured[dev][0]) {
+            if (cudaFuncSetAttribute(attention_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
+            configured[dev][0] = true;
+        }
+        attention_decode_kernel<__half><<<grid, ATT_WARPS * 32, smem, st>>>(p);
+    } else {
+        if (!configured[dev][1]) {
+            if (cudaFuncSetAttribute(attention_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
+            configured[dev][1] = true;
+        }
+        attention_decode_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, smem, st>>>(p);
+    }
+    return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_CUDA;
+}
+
+}  // namespace mt

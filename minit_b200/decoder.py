@@ -1,0 +1,175 @@
+"""The decoder layer around the quantized linears, for decode-sized batches of one sequence.
+
+Reference (examples/llama3_70b.py): ``RMSNorm`` :133-141, ``Attention`` :58-115, ``TransformerBlock``
+:144-162, rotary tables :206-212.  Differences a caller must know: the KV cache is preallocated
+(``KVCache(capacity, ...)``) and appended in place instead of growing by ``F.tie``; it stores each kv head
+once, not ``nr_groups`` times; q, k and v come from ONE linear over the concatenated columns; the
+residual adds are folded into the output linears.  Every step is one call into the C ABI.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from .feedforward import QFeedForward, quantized_matrix_multiply_residual
+from .module import Module
+from .qlinear import QLinear, QLinearWithBias, quantized_matrix_multiply
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``F.rms_norm(x, weight, axis=-1, eps)`` (minit/functional/special.py:11-16)."""
+    dev = _lib.require_cuda(x, weight)
+    h = x.shape[-1]
+    if weight.shape != (h,) or weight.dtype != x.dtype or not x.is_contiguous():
+        raise ValueError("weight must be [H] in x.dtype and x contiguous")
+    rows = x.numel() // max(h, 1)
+    if out is None:
+        out = torch.empty_like(x)
+    with torch.cuda.device(dev):
+        rc = _lib.lib.mt_rms_norm(_lib.current_stream(dev), x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, h, eps,
+                                  _lib.dtype_code(x.dtype))
+    _lib.check(rc, "mt_rms_norm")
+    return out
+
+
+def rope_tables(head_size: int, size: int, theta: float = 5e5, dtype: torch.dtype = torch.float16, device="cuda"):
+    """cos / sin of position * theta^(-2i/d), rounded to ``dtype`` as the reference stores them
+    (examples/llama3_70b.py:206-212) and kept as fp32 for the kernel."""
+    freqs = (1.0 / theta) ** (torch.arange(0, head_size // 2, dtype=torch.float32) * (2.0 / head_size))
+    ang = torch.arange(0, size, dtype=torch.float32)[:, None] * freqs[None, :]
+    return (ang.cos().to(dtype).float().to(device).contiguous(), ang.sin().to(dtype).float().to(device).contiguous())
+
+
+class KVCache:
+    """Preallocated cache of one layer: k, v [capacity, kv_heads, head_size]; ``length`` rows are valid."""
+
+    def __init__(self, capacity: int, kv_heads: int, head_size: int, dtype: torch.dtype = torch.float16, device="cuda") -> None:
+        self.k = torch.zeros((capacity, kv_heads, head_size), dtype=dtype, device=device)
+        self.v = torch.zeros((capacity, kv_heads, head_size), dtype=dtype, device=device)
+        self.capacity, self.kv_heads, self.head_size = capacity, kv_heads, head_size
+        self.length = 0
+
+
+def rope_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, cache: KVCache, nr_querys: int, offset: int,
+                offset_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rotate the q and k heads of fused qkv rows [M, (hq + 2 hkv) d] and append k, v to the cache at rows
+    offset .. offset + M - 1; returns q [M, hq, d]."""
+    dev = _lib.require_cuda(qkv, cos, sin, cache.k, cache.v, offset_dev)
+    m = qkv.shape[0]
+    hkv, d = cache.kv_heads, cache.head_size
+    if qkv.shape != (m, (nr_querys + 2 * hkv) * d) or not qkv.is_contiguous() or cos.dtype != torch.float32 or cos.shape != sin.shape:
+        raise ValueError("qkv must be [M, (hq + 2 hkv) d] contiguous and the tables fp32 of one shape")
+    q = torch.empty((m, nr_querys, d), dtype=qkv.dtype, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib.mt_rope_append(_lib.current_stream(dev), qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), q.data_ptr(),
+                                     cache.k.data_ptr(), cache.v.data_ptr(), m, nr_querys, hkv, d, offset, _lib.ptr(offset_dev),
+                                     cache.capacity, cos.shape[0], _lib.dtype_code(qkv.dtype))
+    _lib.check(rc, "mt_rope_append")
+    return q
+
+
+_att_ws = {}
+
+
+def attention_decode(q: torch.Tensor, cache: KVCache, offset: int, offset_dev: Optional[torch.Tensor] = None,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """softmax(q k^T / sqrt(d) + causal mask) v for M new tokens (q [M, hq, d]) at positions offset .. against the
+    cache rows 0 .. offset + token; returns [M, hq * d]."""
+    dev = _lib.require_cuda(q, cache.k, cache.v, offset_dev)
+    m, hq, d = q.shape
+    max_len = cache.capacity if offset_dev is not None else offset + m
+    need = _lib.lib.mt_attention_workspace_bytes(m, cache.kv_heads, max_len)
+    stream = _lib.current_stream(dev)
+    key = (dev.index, stream)
+    ws = _att_ws.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=dev)       # zeroed once; the kernel leaves it zeroed
+        _att_ws[key] = ws
+    if out is None:
+        out = torch.empty((m, hq * d), dtype=q.dtype, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib.mt_attention_decode(stream, q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), out.data_ptr(), m, hq,
+                                          cache.kv_heads, d, offset, _lib.ptr(offset_dev), max_len, 1.0 / math.sqrt(d),
+                                          ws.data_ptr(), ws.numel(), _lib.dtype_code(q.dtype))
+    _lib.check(rc, "mt_attention_decode")
+    return out
+
+
+def fuse_columns(linears) -> Tuple[torch.Tensor, Optional[torch.Tensor], torch.Tensor, Optional[torch.Tensor]]:
+    """Load-time: GPTQ linears with the same K, groups and bits side by side as one linear (q | k | v)."""
+    qw = torch.cat([l.qweight for l in linears], dim=1).contiguous()
+    qz = torch.cat([l.qzeros for l in linears], dim=1).contiguous()
+    sc = torch.cat([l.scales for l in linears], dim=1).contiguous()
+    biases = [getattr(l, "bias", None) for l in linears]
+    bi = torch.cat(biases).contiguous() if all(isinstance(b, torch.Tensor) for b in biases) else None
+    return qw, qz, sc, bi
+
+
+class RMSNorm(Module):
+    def __init__(self, size: int, eps: float = 1e-5, dtype: str = "float16") -> None:
+        super().__init__()
+        self.eps = eps
+        self.weight = self.register_buffer("weight", (size,), dtype)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return rms_norm(x, self.weight, self.eps)
+
+
+class QAttention(Module):
+    """``Attention(hidden_size, nr_querys, nr_groups, head_size)`` of the reference on GPTQ linears
+    (``nr_groups`` = query heads per kv head, as there).  ``forward`` takes the M new tokens of one sequence
+    [M, hidden], the layer's cache and the position of the first token."""
+
+    def __init__(self, hidden_size: int, nr_querys: int, nr_groups: int, head_size: int, quant_groups: int, bits: int = 8,
+                 bias: bool = False, dtype: str = "float16") -> None:
+        super().__init__()
+        cls = QLinearWithBias if bias else QLinear
+        self.nr_querys, self.nr_kv, self.head_size, self.bits = nr_querys, nr_querys // nr_groups, head_size, bits
+        self.q_proj = self.register_module("q_proj", cls(hidden_size, nr_querys * head_size, quant_groups, bits, dtype))
+        self.k_proj = self.register_module("k_proj", cls(hidden_size, self.nr_kv * head_size, quant_groups, bits, dtype))
+        self.v_proj = self.register_module("v_proj", cls(hidden_size, self.nr_kv * head_size, quant_groups, bits, dtype))
+        self.o_proj = self.register_module("o_proj", QLinear(nr_querys * head_size, hidden_size,
+                                                             quant_groups * (nr_querys * head_size) // hidden_size, bits, dtype))
+        self._qkv = None
+
+    def update_buffer(self, name: str, value: torch.Tensor) -> None:
+        super().update_buffer(name, value)
+        self._qkv = None
+
+    def forward(self, x: torch.Tensor, cache: KVCache, cos: torch.Tensor, sin: torch.Tensor, offset: int,
+                residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self._qkv is None:
+            for lin in (self.q_proj, self.k_proj, self.v_proj):
+                if lin._groups() is not None:
+                    raise ValueError("act-order q / k / v projections are not fused")
+            self._qkv = fuse_columns((self.q_proj, self.k_proj, self.v_proj))
+        qw, qz, sc, bi = self._qkv
+        qkv = quantized_matrix_multiply(x, qw, qz, sc, None, bits=self.bits, bias=bi)
+        q = rope_append(qkv, cos, sin, cache, self.nr_querys, offset)
+        a = attention_decode(q, cache, offset)
+        cache.length = max(cache.length, offset + x.shape[0])
+        o = self.o_proj
+        if residual is None:
+            return o._matmul(a, None)
+        return quantized_matrix_multiply_residual(a, o.qweight, o.qzeros, o.scales, o._groups(), residual, bits=self.bits)
+
+
+class QDecoderLayer(Module):
+    """``TransformerBlock`` of the reference (examples/llama3_70b.py:144-162) with the same child names."""
+
+    def __init__(self, hidden_size: int, nr_querys: int, nr_groups: int, head_size: int, internal_size: int, bits: int = 4,
+                 group_size: int = 128, eps: float = 1e-5, dtype: str = "float16") -> None:
+        super().__init__()
+        self.self_attn = self.register_module("self_attn", QAttention(hidden_size, nr_querys, nr_groups, head_size,
+                                                                      hidden_size // group_size, bits, False, dtype))
+        self.mlp = self.register_module("mlp", QFeedForward(hidden_size, internal_size, hidden_size // group_size,
+                                                            internal_size // group_size, bits, False, dtype=dtype))
+        self.input_layernorm = self.register_module("input_layernorm", RMSNorm(hidden_size, eps, dtype))
+        self.post_attention_layernorm = self.register_module("post_attention_layernorm", RMSNorm(hidden_size, eps, dtype))
+
+    def forward(self, x: torch.Tensor, cache: KVCache, cos: torch.Tensor, sin: torch.Tensor, offset: int) -> torch.Tensor:
+        h = self.self_attn(self.input_layernorm(x), cache, cos, sin, offset, residual=x)      # x + attention_output
+        return self.mlp(self.post_attention_layernorm(h), residual=h)                           # + ffn_output

@@ -33,6 +33,13 @@ project root):
   ``x + attention_output`` (``examples/llama3_70b.py:160-162``).  Every step rounds to the tensor dtype.
 * ``interleave_gate_up`` -- no counterpart in the reference: the column order this build's fused
   gate / up linear uses (blocks of eight = four gate, four up columns), restated in numpy.
+* ``rms_norm`` -- ``minit/cuda/kernel/cuda/rms_norm.py:55-91``: fp32 sum of squares, ``sqrt(mean + eps)``,
+  ``value / rms * weight`` in fp32, one rounding.
+* ``rope`` -- ``minit/cuda/kernel/cuda/rope.py:58-73``: pairs ``(x[2i], x[2i+1])`` rotated by fp32
+  ``(cos, sin)[position, i]``; tables as built at ``examples/llama3_70b.py:206-212`` (rounded to the tensor dtype).
+* ``attention`` -- ``examples/llama3_70b.py:85-115`` step by step, each step rounded to the tensor dtype:
+  scores (fp32 accumulate), ``/ sqrt(d)``, ``+ mask``, softmax (``minit/cuda/kernel/cuda/softmax.py:55-106``:
+  fp32 max, exp, sum, divide), weighted sum of v; query head n reads kv head ``n // nr_groups``.
 * ``shard_*`` -- the tensor-parallel rules ``minit/collective/dispatch.py:26-37``
   and the local slice of ``minit/collective/tensor.py:88-94``.
 """
@@ -46,6 +53,7 @@ __all__ = [
     "dequantize_packed", "qlinear", "w8_perchannel_as_gptq", "w8_perchannel_linear",
     "shard_column", "shard_row", "make_gptq_case", "make_w8_case", "tolerance_ok",
     "sigmoid", "silu", "swiglu", "add_residual", "interleave_columns", "interleave_gate_up",
+    "rms_norm", "rope_tables", "rope", "attention",
 ]
 
 
@@ -217,6 +225,52 @@ def interleave_gate_up(gate, up, bits: int):
     sc = interleave_columns(gs.view(np.uint16) if gs.dtype != np.uint16 else gs, us.view(np.uint16) if us.dtype != np.uint16 else us)
     z = interleave_columns(unpack_cols(gz, bits), unpack_cols(uz, bits))
     return qw, pack_cols(z, bits), sc
+
+
+# ---------------------------------------------------------------------------
+# the steps either side of the linears in a decoder layer
+# ---------------------------------------------------------------------------
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    xf = x.float()
+    rms = torch.sqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps)
+    return (xf / rms * weight.float()).to(x.dtype)
+
+
+def rope_tables(head_size: int, size: int, theta: float = 5e5, dtype=torch.float16):
+    freqs = (1.0 / theta) ** (torch.arange(0, head_size // 2, dtype=torch.float32) * (2.0 / head_size))
+    ang = torch.arange(0, size, dtype=torch.float32)[:, None] * freqs[None, :]
+    return ang.cos().to(dtype).float(), ang.sin().to(dtype).float()
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, offset: int) -> torch.Tensor:
+    """x [S, heads, D]; token s is at position offset + s."""
+    s_len, _, d = x.shape
+    xf = x.float().reshape(s_len, -1, d // 2, 2)
+    re, im = xf[..., 0], xf[..., 1]
+    c = cos[offset:offset + s_len][:, None, :]
+    sn = sin[offset:offset + s_len][:, None, :]
+    out = torch.stack((re * c - im * sn, im * c + re * sn), dim=-1)
+    return out.reshape(x.shape).to(x.dtype)
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, offset: int) -> torch.Tensor:
+    """q [S, hq, D] (rotated), k / v [offset + S, hkv, D] (the cache including the new tokens) -> [S, hq * D]."""
+    T = q.dtype
+    s_len, hq, d = q.shape
+    hkv = k.shape[1]
+    r = hq // hkv
+    kk = k.repeat_interleave(r, dim=1).float()                       # "bs(hd)->bs(hr)d"
+    vv = v.repeat_interleave(r, dim=1).float()
+    qk = torch.einsum("snd,tnd->nst", q.float(), kk).to(T)
+    qk = (qk.float() / float(np.sqrt(d))).to(T)
+    t_len = k.shape[0]
+    mask = torch.zeros((s_len, t_len))
+    for i in range(s_len):
+        mask[i, offset + i + 1:] = -np.inf
+    qk = (qk.float() + mask[None]).to(T)
+    p = torch.softmax(qk.float(), dim=-1).to(T)
+    out = torch.einsum("nst,tnd->snd", p.float(), vv).to(T)
+    return out.reshape(s_len, hq * d)
 
 
 # ---------------------------------------------------------------------------
