@@ -28,6 +28,8 @@ constexpr int ATT_WARPS = 4;
 constexpr int ATT_TILE = 32;               // cached positions per warp tile: one per lane
 constexpr int ATT_ROW = ATT_D * 2 + 16;    // bytes of a K / V row in shared memory (padded: 16-byte reads of 8 rows hit 32 banks)
 constexpr int ATT_WARP_SMEM = 2 * ATT_TILE * ATT_ROW + ATT_MAXG * ATT_TILE * 4;   // K tile, V tile, probabilities
+constexpr int ATT_CLUSTER = 4;               // CTAs of one (token, kv head) that merge through shared memory
+constexpr int ATT_MAXCL = 10;                // clusters per (token, kv head) at most: merged through global memory
 constexpr int ATT_PART = ATT_D + 4;        // floats of a partial result per query head: 128 weighted sums, max, sum (+ pad: rows stay 16-byte aligned)
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -111,6 +113,7 @@ struct AttParams {
     int m, hq, hkv, group;      // group = hq / hkv
     int offset;                 // cached positions before the first new token
     int splits, chunk;          // CTAs per (token, kv head); positions per CTA (a multiple of 32 * ATT_WARPS)
+    int cluster;                // CTAs per thread-block cluster (divides splits)
     int max_len;                // the caller's bound on offset + m: no cache row at or beyond it is read
     float scale;
 };
@@ -125,6 +128,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, kvh = blockIdx.y, tok = blockIdx.z;
     const int G = p.group;
+    if (p.cluster > 1) cluster_arrive_relaxed();            // phase 0: "this CTA runs, its shared memory exists"
     const int off = p.offset_dev ? *p.offset_dev : p.offset;
     const int len = min(off + tok + 1, p.max_len);          // causal: the token sees the cache and itself
     const int s0 = split * p.chunk, s1 = min(len, s0 + p.chunk);
@@ -232,67 +236,120 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const 
         }
     }
     __syncthreads();
-    // thread -> (query head, dimension): 8 x 128 values over 128 threads
-    const size_t slot = ((size_t)tok * p.hkv + kvh) * p.splits;
-    auto merge_store = [&](int h, int d, float m_all, float l_all, float a_all) {
-        const uint16_t o = H::from_float(l_all > 0.f ? a_all / l_all : 0.f);
-        reinterpret_cast<uint16_t*>(p.out)[((size_t)tok * p.hq + (size_t)kvh * G + h) * ATT_D + d] = o;
-        (void)m_all;
+    // thread -> dimension d of every query head: first the CTA's four warps, then (through the cluster's shared
+    // memory) the CTAs of the cluster, then (through global memory, last CTA to arrive) the clusters
+    const int d = tid;                                      // 128 threads = 128 dimensions
+    const int C = p.cluster;
+    const int crank = C > 1 ? split % C : 0, cl = split / C, ncl = p.splits / C;
+    float* xred = reinterpret_cast<float*>(smem + ATT_WARPS * ATT_WARP_SMEM);      // [C][G][ATT_PART], used in cluster rank 0
+    auto merge_store = [&](int h, float l_all, float a_all) {
+        reinterpret_cast<uint16_t*>(p.out)[((size_t)tok * p.hq + (size_t)kvh * G + h) * ATT_D + d] = H::from_float(l_all > 0.f ? a_all / l_all : 0.f);
     };
-    for (int h = 0; h < G; ++h) {
-        const int d = tid;                                  // 128 threads = 128 dimensions
-        float m_all = -INFINITY;
+    float m_c[ATT_MAXG], l_c[ATT_MAXG], a_c[ATT_MAXG];
 #pragma unroll
-        for (int w = 0; w < ATT_WARPS; ++w) m_all = fmaxf(m_all, part_s[w][h][ATT_D]);
-        float l_all = 0.f, a_all = 0.f;
+    for (int h = 0; h < ATT_MAXG; ++h) {
+        m_c[h] = -INFINITY; l_c[h] = 0.f; a_c[h] = 0.f;
+        if (h < G) {
 #pragma unroll
-        for (int w = 0; w < ATT_WARPS; ++w) {
-            const float f = part_s[w][h][ATT_D] == -INFINITY ? 0.f : __expf(part_s[w][h][ATT_D] - m_all);
-            l_all = fmaf(part_s[w][h][ATT_D + 1], f, l_all);
-            a_all = fmaf(part_s[w][h][d], f, a_all);
-        }
-        if (p.splits == 1) {
-            merge_store(h, d, m_all, l_all, a_all);
-        } else {
-            float* dst = p.partial + ((slot + split) * ATT_MAXG + h) * ATT_PART;
-            if (d == 0) { __stcg(dst + ATT_D, m_all); __stcg(dst + ATT_D + 1, l_all); }
-            __stcg(dst + d, a_all);
+            for (int w = 0; w < ATT_WARPS; ++w) m_c[h] = fmaxf(m_c[h], part_s[w][h][ATT_D]);
+#pragma unroll
+            for (int w = 0; w < ATT_WARPS; ++w) {
+                const float f = part_s[w][h][ATT_D] == -INFINITY ? 0.f : __expf(part_s[w][h][ATT_D] - m_c[h]);
+                l_c[h] = fmaf(part_s[w][h][ATT_D + 1], f, l_c[h]);
+                a_c[h] = fmaf(part_s[w][h][d], f, a_c[h]);
+            }
         }
     }
-    if (p.splits == 1) return;
+    if (C > 1) {
+        cluster_wait_acquire();                             // phase 0 complete: rank 0 of the cluster is resident
+#pragma unroll
+        for (int h = 0; h < ATT_MAXG; ++h) {
+            if (h < G) {
+                float* row = xred + ((size_t)crank * ATT_MAXG + h) * ATT_PART;
+                st_cluster_f32(row + d, 0u, a_c[h]);
+                if (d == 0) { st_cluster_f32(row + ATT_D, 0u, m_c[h]); st_cluster_f32(row + ATT_D + 1, 0u, l_c[h]); }
+            }
+        }
+        cluster_arrive_release();
+        cluster_wait_acquire();
+        if (crank != 0) return;
+#pragma unroll
+        for (int h = 0; h < ATT_MAXG; ++h) {
+            if (h < G) {
+                float mm = -INFINITY;
+                for (int r = 0; r < C; ++r) mm = fmaxf(mm, xred[((size_t)r * ATT_MAXG + h) * ATT_PART + ATT_D]);
+                float ll = 0.f, aa = 0.f;
+                for (int r = 0; r < C; ++r) {               // in rank order: the result does not depend on arrival order
+                    const float* row = xred + ((size_t)r * ATT_MAXG + h) * ATT_PART;
+                    const float f = row[ATT_D] == -INFINITY ? 0.f : __expf(row[ATT_D] - mm);
+                    ll = fmaf(row[ATT_D + 1], f, ll);
+                    aa = fmaf(row[d], f, aa);
+                }
+                m_c[h] = mm; l_c[h] = ll; a_c[h] = aa;
+            }
+        }
+    }
+    if (ncl == 1) {
+#pragma unroll
+        for (int h = 0; h < ATT_MAXG; ++h)
+            if (h < G) merge_store(h, l_c[h], a_c[h]);
+        return;
+    }
+    const size_t slot = ((size_t)tok * p.hkv + kvh) * ncl;
+#pragma unroll
+    for (int h = 0; h < ATT_MAXG; ++h) {
+        if (h < G) {
+            float* dst = p.partial + ((slot + cl) * ATT_MAXG + h) * ATT_PART;
+            if (d == 0) { __stcg(dst + ATT_D, m_c[h]); __stcg(dst + ATT_D + 1, l_c[h]); }
+            __stcg(dst + d, a_c[h]);
+        }
+    }
     __threadfence();
     __syncthreads();
-    if (tid == 0) s_last = (atomicAdd(p.counters + tok * p.hkv + kvh, 1u) == unsigned(p.splits - 1));
+    if (tid == 0) s_last = (atomicAdd(p.counters + tok * p.hkv + kvh, 1u) == unsigned(ncl - 1));
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    const int nsplit = (len + p.chunk - 1) / p.chunk;       // ranges that hold positions; the rest wrote (-inf, 0, 0)
+#pragma unroll 1
     for (int h = 0; h < G; ++h) {
-        const int d = tid;
         const float* src = p.partial + (slot * ATT_MAXG + h) * ATT_PART;
-        float m_all = -INFINITY;
-        for (int sp = 0; sp < nsplit; ++sp) m_all = fmaxf(m_all, __ldcg(src + (size_t)sp * ATT_MAXG * ATT_PART + ATT_D));
-        float l_all = 0.f, a_all = 0.f;
-        for (int sp = 0; sp < nsplit; ++sp) {
-            const float* s2 = src + (size_t)sp * ATT_MAXG * ATT_PART;
-            const float ms = __ldcg(s2 + ATT_D);
-            const float f = ms == -INFINITY ? 0.f : __expf(ms - m_all);
-            l_all = fmaf(__ldcg(s2 + ATT_D + 1), f, l_all);
-            a_all = fmaf(__ldcg(s2 + d), f, a_all);
+        float ms[ATT_MAXCL], lv[ATT_MAXCL], av[ATT_MAXCL];
+#pragma unroll
+        for (int c = 0; c < ATT_MAXCL; ++c) {               // all loads in flight at once
+            const bool on = c < ncl;
+            const float* s2 = src + (size_t)(on ? c : 0) * ATT_MAXG * ATT_PART;
+            ms[c] = on ? __ldcg(s2 + ATT_D) : -INFINITY;
+            lv[c] = on ? __ldcg(s2 + ATT_D + 1) : 0.f;
+            av[c] = on ? __ldcg(s2 + d) : 0.f;
         }
-        merge_store(h, d, m_all, l_all, a_all);
+        float mm = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < ATT_MAXCL; ++c) mm = fmaxf(mm, ms[c]);
+        float ll = 0.f, aa = 0.f;
+#pragma unroll
+        for (int c = 0; c < ATT_MAXCL; ++c) {               // in cluster order
+            const float f = ms[c] == -INFINITY ? 0.f : __expf(ms[c] - mm);
+            ll = fmaf(lv[c], f, ll);
+            aa = fmaf(av[c], f, aa);
+        }
+        merge_store(h, ll, aa);
     }
     if (tid == 0) p.counters[tok * p.hkv + kvh] = 0;
 }
 
-void attention_plan(int max_len, int& splits, int& chunk) {
-    // one 32-position tile per warp and CTA while that gives at most 64 CTAs per (token, kv head); beyond, longer ranges
+// CTAs per (token, kv head) = clusters x cluster size; positions per CTA.  One 32-position tile per warp while
+// that gives at most ATT_MAXCL clusters of ATT_CLUSTER CTAs (two CTAs per SM with 8 kv heads); beyond, longer ranges.
+void attention_plan(int max_len, int& splits, int& chunk, int& cluster) {
     const int tile = ATT_WARPS * ATT_TILE;
     int tiles = (max_len + tile - 1) / tile;
     if (tiles < 1) tiles = 1;
-    const int per = (tiles + 63) / 64;
+    if (tiles <= ATT_CLUSTER) { cluster = tiles; splits = tiles; chunk = tile; return; }
+    cluster = ATT_CLUSTER;
+    int ncl = (tiles + ATT_CLUSTER - 1) / ATT_CLUSTER;
+    if (ncl > ATT_MAXCL) ncl = ATT_MAXCL;
+    splits = ncl * ATT_CLUSTER;
+    const int per = (tiles + splits - 1) / splits;
     chunk = per * tile;
-    splits = (tiles + per - 1) / per;
 }
 
 }  // namespace
@@ -318,10 +375,27 @@ int launch_rope_append(cudaStream_t st, const void* qkv, const float* cosv, cons
 }
 
 size_t attention_workspace_bytes(int m, int hkv, int max_len) {
-    int splits, chunk;
-    attention_plan(max_len, splits, chunk);
+    int splits, chunk, cluster;
+    attention_plan(max_len, splits, chunk, cluster);
     const size_t counters = (((size_t)m * hkv * 4) + 255) & ~(size_t)255;
-    return counters + (size_t)m * hkv * splits * ATT_MAXG * ATT_PART * 4;
+    return counters + (size_t)m * hkv * (splits / cluster) * ATT_MAXG * ATT_PART * 4;
+}
+
+template <typename T>
+static int launch_attention_inst(cudaStream_t st, const AttParams& p, dim3 grid, size_t smem, bool& configured) {
+    auto kern = attention_decode_kernel<T>;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(ATT_WARPS * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = p.cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = p.cluster > 1 ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
+    return MT_OK;
 }
 
 int launch_attention_decode(cudaStream_t st, const void* q, const void* k_cache, const void* v_cache, void* out,
@@ -331,31 +405,20 @@ int launch_attention_decode(cudaStream_t st, const void* q, const void* k_cache,
     AttParams p;
     p.q = q; p.k_cache = k_cache; p.v_cache = v_cache; p.out = out;
     p.m = m; p.hq = hq; p.hkv = hkv; p.group = hq / hkv; p.offset = offset; p.offset_dev = offset_dev; p.scale = scale;
-    attention_plan(max_len, p.splits, p.chunk);
+    attention_plan(max_len, p.splits, p.chunk, p.cluster);
     p.max_len = max_len;
     if (attention_workspace_bytes(m, hkv, max_len) > workspace_bytes) return MT_ERR_WORKSPACE;
     const size_t counters = (((size_t)m * hkv * 4) + 255) & ~(size_t)255;
     p.counters = static_cast<unsigned*>(workspace);
     p.partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + counters);
     const dim3 grid(p.splits, hkv, m);
-    const size_t smem = (size_t)ATT_WARPS * ATT_WARP_SMEM;
+    // the K / V tiles of the four warps, then the cluster's merge rows (always ATT_CLUSTER of them: one attribute value)
+    const size_t smem = (size_t)ATT_WARPS * ATT_WARP_SMEM + (size_t)ATT_CLUSTER * ATT_MAXG * ATT_PART * 4;
     static bool configured[64][2] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return MT_ERR_CUDA; }
-    if (dtype == MT_F16) {
-        if (!configured[dev][0]) {
-            if (cudaFuncSetAttribute(attention_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
-            configured[dev][0] = true;
-        }
-        attention_decode_kernel<__half><<<grid, ATT_WARPS * 32, smem, st>>>(p);
-    } else {
-        if (!configured[dev][1]) {
-            if (cudaFuncSetAttribute(attention_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
-            configured[dev][1] = true;
-        }
-        attention_decode_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, smem, st>>>(p);
-    }
-    return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_CUDA;
+    if (dtype == MT_F16) return launch_attention_inst<__half>(st, p, grid, smem, configured[dev][0]);
+    return launch_attention_inst<__nv_bfloat16>(st, p, grid, smem, configured[dev][1]);
 }
 
 }  // namespace mt
