@@ -43,16 +43,36 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// One CTA per row; a thread keeps its (up to RMS_NV) 16-byte pieces of the row in registers between the two passes,
+// so the row is read once, and the weight load overlaps the reduction.
+constexpr int RMS_NV = 4;
 template <typename T>
-__global__ void __launch_bounds__(256) rms_norm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, uint4* __restrict__ out,
-                                                       int h8, float inv_h, float eps) {
+__global__ void __launch_bounds__(1024) rms_norm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, uint4* __restrict__ out,
+                                                        int h8, float inv_h, float eps) {
     using H = F16x2<T>;
-    __shared__ float red[8];
+    __shared__ float red[32];
     const uint4* xr = x + (size_t)blockIdx.x * h8;
+    const int nt = blockDim.x;
+    uint4 v[RMS_NV], g[RMS_NV];
     float ss = 0.f;
-    for (int i = threadIdx.x; i < h8; i += 256) {
-        const uint4 v = xr[i];
-        const uint32_t* p = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+    for (int j = 0; j < RMS_NV; ++j) {
+        const int i = threadIdx.x + j * nt;
+        v[j] = make_uint4(0u, 0u, 0u, 0u); g[j] = v[j];
+        if (i < h8) { v[j] = xr[i]; g[j] = __ldg(w + i); }
+    }
+#pragma unroll
+    for (int j = 0; j < RMS_NV; ++j) {
+        const uint32_t* p = reinterpret_cast<const uint32_t*>(&v[j]);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float a = H::to_float(uint16_t(p[q] & 0xffff)), b = H::to_float(uint16_t(p[q] >> 16));
+            ss = fmaf(a, a, ss); ss = fmaf(b, b, ss);
+        }
+    }
+    for (int i = threadIdx.x + RMS_NV * nt; i < h8; i += nt) {          // rows longer than RMS_NV * 8 * threads values
+        const uint4 t = xr[i];
+        const uint32_t* p = reinterpret_cast<const uint32_t*>(&t);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const float a = H::to_float(uint16_t(p[q] & 0xffff)), b = H::to_float(uint16_t(p[q] >> 16));
@@ -63,20 +83,24 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const uint4* __restrict__
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
     __syncthreads();
     float tot = 0.f;
-#pragma unroll
-    for (int q = 0; q < 8; ++q) tot += red[q];
+    for (int q = 0; q < (nt >> 5); ++q) tot += red[q];
     const float rms = sqrtf(tot * inv_h + eps);
-    for (int i = threadIdx.x; i < h8; i += 256) {
-        const uint4 v = xr[i], g = w[i];
-        const uint32_t* p = reinterpret_cast<const uint32_t*>(&v);
-        const uint32_t* pg = reinterpret_cast<const uint32_t*>(&g);
+    auto scale_store = [&](const uint4& xv, const uint4& gv, int i) {
+        const uint32_t* p = reinterpret_cast<const uint32_t*>(&xv);
+        const uint32_t* pg = reinterpret_cast<const uint32_t*>(&gv);
         uint4 o; uint32_t* po = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
         for (int q = 0; q < 4; ++q)
             po[q] = H::pack(H::to_float(uint16_t(p[q] & 0xffff)) / rms * H::to_float(uint16_t(pg[q] & 0xffff)),
                             H::to_float(uint16_t(p[q] >> 16)) / rms * H::to_float(uint16_t(pg[q] >> 16)));
         out[(size_t)blockIdx.x * h8 + i] = o;
+    };
+#pragma unroll
+    for (int j = 0; j < RMS_NV; ++j) {
+        const int i = threadIdx.x + j * nt;
+        if (i < h8) scale_store(v[j], g[j], i);
     }
+    for (int i = threadIdx.x + RMS_NV * nt; i < h8; i += nt) scale_store(xr[i], __ldg(w + i), i);
 }
 
 // one thread per (token, head of q | k | v, pair of values)
@@ -310,29 +334,32 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const 
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    // warp w merges query heads w and w + 4, a lane four dimensions: every load of a head is in flight at once
 #pragma unroll 1
-    for (int h = 0; h < G; ++h) {
+    for (int h = warp; h < G; h += ATT_WARPS) {
         const float* src = p.partial + (slot * ATT_MAXG + h) * ATT_PART;
-        float ms[ATT_MAXCL], lv[ATT_MAXCL], av[ATT_MAXCL];
+        float ms[ATT_MAXCL], lv[ATT_MAXCL]; float4 av[ATT_MAXCL];
 #pragma unroll
-        for (int c = 0; c < ATT_MAXCL; ++c) {               // all loads in flight at once
+        for (int c = 0; c < ATT_MAXCL; ++c) {
             const bool on = c < ncl;
             const float* s2 = src + (size_t)(on ? c : 0) * ATT_MAXG * ATT_PART;
             ms[c] = on ? __ldcg(s2 + ATT_D) : -INFINITY;
             lv[c] = on ? __ldcg(s2 + ATT_D + 1) : 0.f;
-            av[c] = on ? __ldcg(s2 + d) : 0.f;
+            av[c] = on ? __ldcg(reinterpret_cast<const float4*>(s2) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
         float mm = -INFINITY;
 #pragma unroll
         for (int c = 0; c < ATT_MAXCL; ++c) mm = fmaxf(mm, ms[c]);
-        float ll = 0.f, aa = 0.f;
+        float ll = 0.f; float4 aa = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int c = 0; c < ATT_MAXCL; ++c) {               // in cluster order
             const float f = ms[c] == -INFINITY ? 0.f : __expf(ms[c] - mm);
             ll = fmaf(lv[c], f, ll);
-            aa = fmaf(av[c], f, aa);
+            aa.x = fmaf(av[c].x, f, aa.x); aa.y = fmaf(av[c].y, f, aa.y); aa.z = fmaf(av[c].z, f, aa.z); aa.w = fmaf(av[c].w, f, aa.w);
         }
-        merge_store(h, ll, aa);
+        const float inv = ll > 0.f ? 1.f / ll : 0.f;
+        uint2 o; o.x = H::pack(aa.x * inv, aa.y * inv); o.y = H::pack(aa.z * inv, aa.w * inv);
+        *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.out) + ((size_t)tok * p.hq + (size_t)kvh * G + h) * ATT_D + lane * 4) = o;
     }
     if (tid == 0) p.counters[tok * p.hkv + kvh] = 0;
 }
@@ -355,8 +382,11 @@ void attention_plan(int max_len, int& splits, int& chunk, int& cluster) {
 }  // namespace
 
 int launch_rms_norm(cudaStream_t st, const void* x, const void* w, void* out, int rows, int h, float eps, int dtype) {
-    if (dtype == MT_F16) rms_norm_kernel<__half><<<rows, 256, 0, st>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(w), static_cast<uint4*>(out), h / 8, 1.f / h, eps);
-    else rms_norm_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(w), static_cast<uint4*>(out), h / 8, 1.f / h, eps);
+    const int h8 = h / 8;
+    int threads = (h8 + 31) / 32 * 32;                      // one 16-byte piece per thread up to 8192 values
+    if (threads > 1024) threads = 1024;
+    if (dtype == MT_F16) rms_norm_kernel<__half><<<rows, threads, 0, st>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(w), static_cast<uint4*>(out), h8, 1.f / h, eps);
+    else rms_norm_kernel<__nv_bfloat16><<<rows, threads, 0, st>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(w), static_cast<uint4*>(out), h8, 1.f / h, eps);
     return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_CUDA;
 }
 
