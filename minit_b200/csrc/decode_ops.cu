@@ -10,13 +10,17 @@
 //  * attention     softmax(q k^T / sqrt(d) + causal mask) v for the new tokens against the cache
 //                  (examples/llama3_70b.py:103-115), one kernel: a CTA takes one kv head, one token and a
 //                  range of cached positions for all query heads of the group (K and V are read once per
-//                  group), keeps scores, online softmax and the weighted sum in fp32, and the last CTA to
-//                  finish a (token, kv head) merges the ranges in order.  The reference rounds the scores,
+//                  group), keeps scores, online softmax and the weighted sum in fp32 (mma.sync m16n8k16 with
+//                  the group's query heads as the rows: 64 tensor instructions per 32 positions instead of
+//                  ~2300 FMAs), merges the ranges of a cluster through shared memory and the clusters through
+//                  global memory, always in order.  The reference rounds the scores,
 //                  the scaled scores, the probabilities and the output to the tensor dtype in separate
 //                  kernels (softmax: minit/cuda/kernel/cuda/softmax.py:55-106).
 //
 // All three are bound by HBM (the cache) or by launch latency (16 KB rows), so: 16-byte loads, the
-// cache streamed through shared memory once, grids of a few CTAs per SM, no tensor cores.
+// cache streamed through shared memory once, grids of a few CTAs per SM.  The batch (8 query heads per
+// kv head) is far too small for tcgen05's 128-row tiles; the warp-level tensor path is enough to keep
+// the arithmetic well under the memory time.
 #include "common.cuh"
 
 namespace mt {
@@ -27,7 +31,7 @@ constexpr int ATT_MAXG = 8;                // query heads per kv head
 constexpr int ATT_WARPS = 4;
 constexpr int ATT_TILE = 32;               // cached positions per warp tile: one per lane
 constexpr int ATT_ROW = ATT_D * 2 + 16;    // bytes of a K / V row in shared memory (padded: 16-byte reads of 8 rows hit 32 banks)
-constexpr int ATT_WARP_SMEM = 2 * ATT_TILE * ATT_ROW + ATT_MAXG * ATT_TILE * 4;   // K tile, V tile, probabilities
+constexpr int ATT_WARP_SMEM = 2 * ATT_TILE * ATT_ROW;   // K tile, V tile
 constexpr int ATT_CLUSTER = 4;               // CTAs of one (token, kv head) that merge through shared memory
 constexpr int ATT_MAXCL = 10;                // clusters per (token, kv head) at most: merged through global memory
 constexpr int ATT_PART = ATT_D + 4;        // floats of a partial result per query head: 128 weighted sums, max, sum (+ pad: rows stay 16-byte aligned)
@@ -35,11 +39,6 @@ constexpr int ATT_PART = ATT_D + 4;        // floats of a partial result per que
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
 
@@ -146,7 +145,6 @@ template <typename T>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const AttParams p) {
     using H = F16x2<T>;
     extern __shared__ __align__(16) unsigned char smem[];
-    __shared__ __align__(16) float q_s[ATT_MAXG][ATT_D];                  // the group's queries, pre-scaled
     __shared__ __align__(16) float part_s[ATT_WARPS][ATT_MAXG][ATT_PART];
     __shared__ int s_last;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -157,107 +155,116 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const 
     const int len = min(off + tok + 1, p.max_len);          // causal: the token sees the cache and itself
     const int s0 = split * p.chunk, s1 = min(len, s0 + p.chunk);
 
-    const uint16_t* qg = reinterpret_cast<const uint16_t*>(p.q) + ((size_t)tok * p.hq + (size_t)kvh * G) * ATT_D;
-    for (int i = tid; i < G * ATT_D; i += ATT_WARPS * 32) q_s[i / ATT_D][i % ATT_D] = H::to_float(qg[i]) * p.scale;
-    __syncthreads();
-
     unsigned char* ks = smem + warp * ATT_WARP_SMEM;
     unsigned char* vs = ks + ATT_TILE * ATT_ROW;
-    float* ps = reinterpret_cast<float*>(vs + ATT_TILE * ATT_ROW);      // [G][32]
     const uint32_t ks_a = (uint32_t)__cvta_generic_to_shared(ks), vs_a = (uint32_t)__cvta_generic_to_shared(vs);
     const unsigned char* kc = static_cast<const unsigned char*>(p.k_cache);
     const unsigned char* vc = static_cast<const unsigned char*>(p.v_cache);
     const size_t row_bytes = (size_t)p.hkv * ATT_D * 2;
-
-    float mx[ATT_MAXG], ls[ATT_MAXG], acc[ATT_MAXG][4];
-#pragma unroll
-    for (int h = 0; h < ATT_MAXG; ++h) { mx[h] = -INFINITY; ls[h] = 0.f; acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.f; }
-
-    for (int t0 = s0 + warp * ATT_TILE; t0 < s1; t0 += ATT_WARPS * ATT_TILE) {
-        // ---- the tile's K and V rows -> shared memory (16 lanes copy one 256-byte row) ----
-        __syncwarp();
+    // the tile's K and V rows -> shared memory (16 lanes copy one 256-byte row; rows past the range: zeros)
+    auto issue = [&](int t0) {
 #pragma unroll
         for (int r = 0; r < ATT_TILE / 2; ++r) {
             const int row = 2 * r + (lane >> 4), pos = t0 + row;
             const bool live = pos < s1;
-            const size_t g = (live ? (size_t)pos : 0) * row_bytes + (size_t)kvh * ATT_D * 2 + (lane & 15) * 16;
-            const int sz = live ? 16 : 0;                   // rows past the range: zeros
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(ks_a + row * ATT_ROW + (lane & 15) * 16), "l"(kc + g), "r"(sz) : "memory");
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vs_a + row * ATT_ROW + (lane & 15) * 16), "l"(vc + g), "r"(sz) : "memory");
+            const size_t go = (live ? (size_t)pos : 0) * row_bytes + (size_t)kvh * ATT_D * 2 + (lane & 15) * 16;
+            const int sz = live ? 16 : 0;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(ks_a + row * ATT_ROW + (lane & 15) * 16), "l"(kc + go), "r"(sz) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vs_a + row * ATT_ROW + (lane & 15) * 16), "l"(vc + go), "r"(sz) : "memory");
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    int t0 = s0 + warp * ATT_TILE;
+    if (t0 < s1) issue(t0);
+
+    // Tensor-core formulation (mma.sync m16n8k16, fp32 accumulate): rows = the group's query heads (8 of 16 rows
+    // used), scores S = Q K^T with K rows as the col-major B operand, output O = P V with P re-used from the score
+    // accumulators as the A operand and V read through ldmatrix.trans.  gq = lane / 4 is this lane's head,
+    // tq = lane % 4 its column pair.
+    const int gq = lane >> 2, tq = lane & 3;
+    uint32_t qa[ATT_D / 16][2];                             // A fragments of Q: (head gq, d = 16 ks + 2 tq, +1) and (.., d + 8)
+    {
+        const uint32_t* q32 = reinterpret_cast<const uint32_t*>(p.q) + ((size_t)tok * p.hq + (size_t)kvh * G + gq) * (ATT_D / 2);
+#pragma unroll
+        for (int ks2 = 0; ks2 < ATT_D / 16; ++ks2) {
+            qa[ks2][0] = gq < G ? __ldg(q32 + 8 * ks2 + tq) : 0u;
+            qa[ks2][1] = gq < G ? __ldg(q32 + 8 * ks2 + 4 + tq) : 0u;
+        }
+    }
+    float mx = -INFINITY, ls = 0.f;                         // running maximum and (this lane's share of) the sum of head gq
+    float oc[ATT_D / 8][4];                                 // O accumulators: [jd][0..1] = (head gq, d = 8 jd + 2 tq, +1)
+#pragma unroll
+    for (int jd = 0; jd < ATT_D / 8; ++jd) oc[jd][0] = oc[jd][1] = oc[jd][2] = oc[jd][3] = 0.f;
+    const int lm = lane >> 3, lr = lane & 7;                // ldmatrix: this lane supplies row lr of matrix lm
+
+    for (; t0 < s1; t0 += ATT_WARPS * ATT_TILE) {
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncwarp();
-        // ---- scores: lane = cached position ----
-        float s[ATT_MAXG];
+        // ---- scores ----
+        float sc[ATT_TILE / 8][4];
 #pragma unroll
-        for (int h = 0; h < ATT_MAXG; ++h) s[h] = 0.f;
-        const unsigned char* krow = ks + lane * ATT_ROW;
-#pragma unroll 4
-        for (int d8 = 0; d8 < ATT_D / 8; ++d8) {
-            const uint4 kv = *reinterpret_cast<const uint4*>(krow + d8 * 16);
-            const uint32_t* kp = reinterpret_cast<const uint32_t*>(&kv);
-            float kf[8];
+        for (int j = 0; j < ATT_TILE / 8; ++j) {
+            sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) { kf[2 * q] = H::to_float(uint16_t(kp[q] & 0xffff)); kf[2 * q + 1] = H::to_float(uint16_t(kp[q] >> 16)); }
-#pragma unroll
-            for (int h = 0; h < ATT_MAXG; ++h) {
-                if (h < G) {
-                    const float4 qa = *reinterpret_cast<const float4*>(&q_s[h][d8 * 8]);
-                    const float4 qb = *reinterpret_cast<const float4*>(&q_s[h][d8 * 8 + 4]);
-                    s[h] = fmaf(qa.x, kf[0], s[h]); s[h] = fmaf(qa.y, kf[1], s[h]); s[h] = fmaf(qa.z, kf[2], s[h]); s[h] = fmaf(qa.w, kf[3], s[h]);
-                    s[h] = fmaf(qb.x, kf[4], s[h]); s[h] = fmaf(qb.y, kf[5], s[h]); s[h] = fmaf(qb.z, kf[6], s[h]); s[h] = fmaf(qb.w, kf[7], s[h]);
-                }
+            for (int kk = 0; kk < ATT_D / 32; ++kk) {       // matrices: d 32 kk + (0, 8, 16, 24) of keys 8 j .. 8 j + 7
+                uint32_t b0, b1, b2, b3;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(ks_a + (8 * j + lr) * ATT_ROW + 64 * kk + 16 * lm));
+                mma16816<T>(sc[j], qa[2 * kk][0], 0u, qa[2 * kk][1], 0u, b0, b1);
+                mma16816<T>(sc[j], qa[2 * kk + 1][0], 0u, qa[2 * kk + 1][1], 0u, b2, b3);
             }
         }
-        const bool live = t0 + lane < s1;
-        // ---- online softmax: new running maximum, rescale, probabilities to shared memory ----
+        // ---- online softmax of head gq over the tile's 32 positions (8 in this lane, the rest in its quad) ----
+        float mloc = -INFINITY;
 #pragma unroll
-        for (int h = 0; h < ATT_MAXG; ++h) {
-            if (h < G) {
-                const float sv = live ? s[h] : -INFINITY;
-                const float mn = fmaxf(mx[h], warp_max(sv));            // finite: position t0 is live
-                const float resc = __expf(mx[h] - mn);                   // 0 on the first tile (mx = -inf)
-                const float pv = live ? __expf(sv - mn) : 0.f;
-                mx[h] = mn;
-                ls[h] = ls[h] * resc + pv;                              // per-lane partial sums, reduced at the end
-                acc[h][0] *= resc; acc[h][1] *= resc; acc[h][2] *= resc; acc[h][3] *= resc;
-                ps[h * ATT_TILE + lane] = pv;
+        for (int j = 0; j < ATT_TILE / 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const bool live = t0 + 8 * j + 2 * tq + e < s1;
+                sc[j][e] = live ? sc[j][e] * p.scale : -INFINITY;
+                mloc = fmaxf(mloc, sc[j][e]);
+            }
+        mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, 1));
+        mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, 2));
+        const float mn = fmaxf(mx, mloc);                   // finite: position t0 is live
+        const float resc = __expf(mx - mn);                 // 0 on the first tile (mx = -inf)
+        mx = mn;
+        float lsum = 0.f;
+        uint32_t pa[ATT_TILE / 16][2];                      // A fragments of P for the two 16-position steps
+#pragma unroll
+        for (int j = 0; j < ATT_TILE / 8; ++j) {
+            const float p0 = __expf(sc[j][0] - mn), p1 = __expf(sc[j][1] - mn);      // exp(-inf) = 0 for dead positions
+            lsum += p0 + p1;
+            pa[j >> 1][j & 1] = H::pack(p0, p1);
+        }
+        ls = ls * resc + lsum;
+#pragma unroll
+        for (int jd = 0; jd < ATT_D / 8; ++jd) { oc[jd][0] *= resc; oc[jd][1] *= resc; }
+        // ---- O += P V ----
+#pragma unroll
+        for (int ks2 = 0; ks2 < ATT_TILE / 16; ++ks2) {
+#pragma unroll
+            for (int jp = 0; jp < ATT_D / 16; ++jp) {       // matrices: (keys 16 ks, d 16 jp), (keys + 8, d), (keys, d + 8), (keys + 8, d + 8)
+                uint32_t b0, b1, b2, b3;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                             : "r"(vs_a + (16 * ks2 + 8 * (lm & 1) + lr) * ATT_ROW + 32 * jp + 16 * (lm >> 1)));
+                mma16816<T>(oc[2 * jp], pa[ks2][0], 0u, pa[ks2][1], 0u, b0, b1);
+                mma16816<T>(oc[2 * jp + 1], pa[ks2][0], 0u, pa[ks2][1], 0u, b2, b3);
             }
         }
-        __syncwarp();
-        // ---- weighted sum of V: lane = four of the 128 dimensions ----
-#pragma unroll 2
-        for (int t4 = 0; t4 < ATT_TILE; t4 += 4) {
-            float vf[4][4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint2 vv = *reinterpret_cast<const uint2*>(vs + (t4 + j) * ATT_ROW + lane * 8);
-                vf[j][0] = H::to_float(uint16_t(vv.x & 0xffff)); vf[j][1] = H::to_float(uint16_t(vv.x >> 16));
-                vf[j][2] = H::to_float(uint16_t(vv.y & 0xffff)); vf[j][3] = H::to_float(uint16_t(vv.y >> 16));
-            }
-#pragma unroll
-            for (int h = 0; h < ATT_MAXG; ++h) {
-                if (h < G) {
-                    const float4 pp = *reinterpret_cast<const float4*>(ps + h * ATT_TILE + t4);
-                    const float pj[4] = {pp.x, pp.y, pp.z, pp.w};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) acc[h][e] = fmaf(pj[j], vf[j][e], acc[h][e]);
-                }
-            }
-        }
+        __syncwarp();                                       // every lane is done with the tile before it is overwritten
+        if (t0 + ATT_WARPS * ATT_TILE < s1) issue(t0 + ATT_WARPS * ATT_TILE);
     }
 
     // ---- the CTA's warps -> one partial per query head (merged in warp order) ----
+    ls += __shfl_xor_sync(0xffffffffu, ls, 1);
+    ls += __shfl_xor_sync(0xffffffffu, ls, 2);
+    if (gq < G) {
+        if (tq == 0) { part_s[warp][gq][ATT_D] = mx; part_s[warp][gq][ATT_D + 1] = ls; }
 #pragma unroll
-    for (int h = 0; h < ATT_MAXG; ++h) {
-        if (h < G) {
-            const float l = warp_sum(ls[h]);
-            if (lane == 0) { part_s[warp][h][ATT_D] = mx[h]; part_s[warp][h][ATT_D + 1] = l; }
-            *reinterpret_cast<float4*>(&part_s[warp][h][lane * 4]) = make_float4(acc[h][0], acc[h][1], acc[h][2], acc[h][3]);
-        }
+        for (int jd = 0; jd < ATT_D / 8; ++jd)
+            *reinterpret_cast<float2*>(&part_s[warp][gq][8 * jd + 2 * tq]) = make_float2(oc[jd][0], oc[jd][1]);
     }
     __syncthreads();
     // thread -> dimension d of every query head: first the CTA's four warps, then (through the cluster's shared
