@@ -32,7 +32,8 @@ constexpr int ATT_WARPS = 4;
 constexpr int ATT_TILE = 32;               // cached positions per warp tile: one per lane
 constexpr int ATT_ROW = ATT_D * 2 + 16;    // bytes of a K / V row in shared memory (padded: 16-byte reads of 8 rows hit 32 banks)
 constexpr int ATT_WARP_SMEM = 2 * ATT_TILE * ATT_ROW;   // K tile, V tile
-constexpr int ATT_CLUSTER = 4;               // CTAs of one (token, kv head) that merge through shared memory
+constexpr int ATT_CLUSTER = 8;               // CTAs of one (token, kv head) that merge through shared memory
+constexpr int ATT_PER_SINGLE = 6;            // tiles per warp up to which one cluster takes the whole sequence (no global stage)
 constexpr int ATT_MAXCL = 10;                // clusters per (token, kv head) at most: merged through global memory
 constexpr int ATT_PART = ATT_D + 4;        // floats of a partial result per query head: 128 weighted sums, max, sum (+ pad: rows stay 16-byte aligned)
 
@@ -145,7 +146,6 @@ template <typename T>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const AttParams p) {
     using H = F16x2<T>;
     extern __shared__ __align__(16) unsigned char smem[];
-    __shared__ __align__(16) float part_s[ATT_WARPS][ATT_MAXG][ATT_PART];
     __shared__ int s_last;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, kvh = blockIdx.y, tok = blockIdx.z;
@@ -161,21 +161,24 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const 
     const unsigned char* kc = static_cast<const unsigned char*>(p.k_cache);
     const unsigned char* vc = static_cast<const unsigned char*>(p.v_cache);
     const size_t row_bytes = (size_t)p.hkv * ATT_D * 2;
-    // the tile's K and V rows -> shared memory (16 lanes copy one 256-byte row; rows past the range: zeros)
-    auto issue = [&](int t0) {
+    // a tile's K (or V) rows -> shared memory (16 lanes copy one 256-byte row; rows past the range: zeros); one
+    // cp.async group per call, also when there is nothing to copy, so that the group count stays uniform
+    auto issue = [&](int t0, const unsigned char* src, uint32_t dst) {
+        if (t0 < s1) {
 #pragma unroll
-        for (int r = 0; r < ATT_TILE / 2; ++r) {
-            const int row = 2 * r + (lane >> 4), pos = t0 + row;
-            const bool live = pos < s1;
-            const size_t go = (live ? (size_t)pos : 0) * row_bytes + (size_t)kvh * ATT_D * 2 + (lane & 15) * 16;
-            const int sz = live ? 16 : 0;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(ks_a + row * ATT_ROW + (lane & 15) * 16), "l"(kc + go), "r"(sz) : "memory");
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vs_a + row * ATT_ROW + (lane & 15) * 16), "l"(vc + go), "r"(sz) : "memory");
+            for (int r = 0; r < ATT_TILE / 2; ++r) {
+                const int row = 2 * r + (lane >> 4), pos = t0 + row;
+                const bool live = pos < s1;
+                const size_t go = (live ? (size_t)pos : 0) * row_bytes + (size_t)kvh * ATT_D * 2 + (lane & 15) * 16;
+                const int sz = live ? 16 : 0;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + row * ATT_ROW + (lane & 15) * 16), "l"(src + go), "r"(sz) : "memory");
+            }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     int t0 = s0 + warp * ATT_TILE;
-    if (t0 < s1) issue(t0);
+    issue(t0, kc, ks_a);
+    issue(t0, vc, vs_a);
 
     // Tensor-core formulation (mma.sync m16n8k16, fp32 accumulate): rows = the group's query heads (8 of 16 rows
     // used), scores S = Q K^T with K rows as the col-major B operand, output O = P V with P re-used from the score
@@ -198,7 +201,9 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const 
     const int lm = lane >> 3, lr = lane & 7;                // ldmatrix: this lane supplies row lr of matrix lm
 
     for (; t0 < s1; t0 += ATT_WARPS * ATT_TILE) {
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        // groups in flight: K of this tile, V of this tile.  K of the next tile is requested as soon as the scores are
+        // done, V of the next after the weighted sum, so each copy overlaps the other half of the arithmetic.
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncwarp();
         // ---- scores ----
         float sc[ATT_TILE / 8][4];
@@ -238,8 +243,12 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const 
             pa[j >> 1][j & 1] = H::pack(p0, p1);
         }
         ls = ls * resc + lsum;
+        __syncwarp();                                       // every lane has read its K fragments
+        issue(t0 + ATT_WARPS * ATT_TILE, kc, ks_a);
 #pragma unroll
         for (int jd = 0; jd < ATT_D / 8; ++jd) { oc[jd][0] *= resc; oc[jd][1] *= resc; }
+        asm volatile("cp.async.wait_group 1;" ::: "memory"); // V of this tile (the next K may still be in flight)
+        __syncwarp();
         // ---- O += P V ----
 #pragma unroll
         for (int ks2 = 0; ks2 < ATT_TILE / 16; ++ks2) {
@@ -253,18 +262,22 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const 
                 mma16816<T>(oc[2 * jp + 1], pa[ks2][0], 0u, pa[ks2][1], 0u, b2, b3);
             }
         }
-        __syncwarp();                                       // every lane is done with the tile before it is overwritten
-        if (t0 + ATT_WARPS * ATT_TILE < s1) issue(t0 + ATT_WARPS * ATT_TILE);
+        __syncwarp();                                       // every lane is done with the V tile before it is overwritten
+        issue(t0 + ATT_WARPS * ATT_TILE, vc, vs_a);
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 
-    // ---- the CTA's warps -> one partial per query head (merged in warp order) ----
+    // ---- the CTA's warps -> one partial per query head (merged in warp order); a warp parks its partial in its own
+    //      (now idle) tile buffer ----
+    auto part = [&](int w, int h) -> float* { return reinterpret_cast<float*>(smem + w * ATT_WARP_SMEM) + h * ATT_PART; };
+    __syncwarp();
     ls += __shfl_xor_sync(0xffffffffu, ls, 1);
     ls += __shfl_xor_sync(0xffffffffu, ls, 2);
     if (gq < G) {
-        if (tq == 0) { part_s[warp][gq][ATT_D] = mx; part_s[warp][gq][ATT_D + 1] = ls; }
+        if (tq == 0) { part(warp, gq)[ATT_D] = mx; part(warp, gq)[ATT_D + 1] = ls; }
 #pragma unroll
         for (int jd = 0; jd < ATT_D / 8; ++jd)
-            *reinterpret_cast<float2*>(&part_s[warp][gq][8 * jd + 2 * tq]) = make_float2(oc[jd][0], oc[jd][1]);
+            *reinterpret_cast<float2*>(&part(warp, gq)[8 * jd + 2 * tq]) = make_float2(oc[jd][0], oc[jd][1]);
     }
     __syncthreads();
     // thread -> dimension d of every query head: first the CTA's four warps, then (through the cluster's shared
@@ -282,12 +295,12 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const 
         m_c[h] = -INFINITY; l_c[h] = 0.f; a_c[h] = 0.f;
         if (h < G) {
 #pragma unroll
-            for (int w = 0; w < ATT_WARPS; ++w) m_c[h] = fmaxf(m_c[h], part_s[w][h][ATT_D]);
+            for (int w = 0; w < ATT_WARPS; ++w) m_c[h] = fmaxf(m_c[h], part(w, h)[ATT_D]);
 #pragma unroll
             for (int w = 0; w < ATT_WARPS; ++w) {
-                const float f = part_s[w][h][ATT_D] == -INFINITY ? 0.f : __expf(part_s[w][h][ATT_D] - m_c[h]);
-                l_c[h] = fmaf(part_s[w][h][ATT_D + 1], f, l_c[h]);
-                a_c[h] = fmaf(part_s[w][h][d], f, a_c[h]);
+                const float f = part(w, h)[ATT_D] == -INFINITY ? 0.f : __expf(part(w, h)[ATT_D] - m_c[h]);
+                l_c[h] = fmaf(part(w, h)[ATT_D + 1], f, l_c[h]);
+                a_c[h] = fmaf(part(w, h)[d], f, a_c[h]);
             }
         }
     }
@@ -371,15 +384,16 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const 
     if (tid == 0) p.counters[tok * p.hkv + kvh] = 0;
 }
 
-// CTAs per (token, kv head) = clusters x cluster size; positions per CTA.  One 32-position tile per warp while
-// that gives at most ATT_MAXCL clusters of ATT_CLUSTER CTAs (two CTAs per SM with 8 kv heads); beyond, longer ranges.
+// CTAs per (token, kv head) = clusters x cluster size; positions per CTA.  Up to ATT_CLUSTER * ATT_PER_SINGLE tiles
+// one cluster takes the whole sequence, its CTAs a few tiles per warp, and everything merges through shared memory
+// (the global stage costs ~7 us: partials, fence, counter, read back); longer sequences use up to ATT_MAXCL clusters.
 void attention_plan(int max_len, int& splits, int& chunk, int& cluster) {
     const int tile = ATT_WARPS * ATT_TILE;
     int tiles = (max_len + tile - 1) / tile;
     if (tiles < 1) tiles = 1;
     if (tiles <= ATT_CLUSTER) { cluster = tiles; splits = tiles; chunk = tile; return; }
     cluster = ATT_CLUSTER;
-    int ncl = (tiles + ATT_CLUSTER - 1) / ATT_CLUSTER;
+    int ncl = (tiles + ATT_CLUSTER * ATT_PER_SINGLE - 1) / (ATT_CLUSTER * ATT_PER_SINGLE);
     if (ncl > ATT_MAXCL) ncl = ATT_MAXCL;
     splits = ncl * ATT_CLUSTER;
     const int per = (tiles + splits - 1) / splits;
