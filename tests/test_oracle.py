@@ -155,3 +155,37 @@ def test_gate_up_interleave_layout():
         wu = O.dequantize_packed(u["qweight"], None, u["qzeros"], u["scales"], bits)
         ref = O.interleave_columns(wg.view(torch.int16).numpy(), wu.view(torch.int16).numpy())
         assert np.array_equal(w.view(torch.int16).numpy(), ref)
+
+
+def test_decoder_step_restatements():
+    """rms_norm / rope / attention of the oracle: properties the reference's kernels have by construction (their CUDA
+    sources cannot run without a GPU, so these restatements are pinned by properties, not by vectors)."""
+    import math
+    gen = torch.Generator().manual_seed(0)
+    # rms_norm: unit weight gives rows of unit mean square; scaling the input leaves the output unchanged
+    x = torch.randn((3, 256), generator=gen).half()
+    y = O.rms_norm(x, torch.ones(256).half(), 1e-5).float()
+    assert torch.allclose(y.pow(2).mean(dim=-1), torch.ones(3), atol=2e-3)
+    assert torch.allclose(O.rms_norm(x * 4, torch.ones(256).half(), 1e-5).float(), y, atol=2e-3)
+    # rope: position 0 is the identity, a rotation keeps the length of every (even, odd) pair
+    cos, sin = O.rope_tables(128, 64)
+    q = torch.randn((4, 2, 128), generator=gen).half()
+    assert torch.equal(O.rope(q[:1], cos, sin, 0), q[:1])
+    r = O.rope(q, cos, sin, 7).float().reshape(4, 2, 64, 2)
+    assert torch.allclose(r.pow(2).sum(-1), q.float().reshape(4, 2, 64, 2).pow(2).sum(-1), atol=2e-2)
+    # relative position: <rope(a, m), rope(b, n)> depends on m - n only
+    a, b = q[:1, :1], q[1:2, :1]
+    d1 = (O.rope(a, cos, sin, 5).float() * O.rope(b, cos, sin, 2).float()).sum()
+    d2 = (O.rope(a, cos, sin, 25).float() * O.rope(b, cos, sin, 22).float()).sum()
+    assert abs(d1 - d2) < 0.05 * (abs(d1) + 1)
+    # attention: one cached position returns its v; causal: the first new token ignores the second
+    k = torch.randn((6, 2, 128), generator=gen).half(); v = torch.randn((6, 2, 128), generator=gen).half()
+    qq = torch.randn((2, 4, 128), generator=gen).half()
+    one = O.attention(qq[:1], k[:1], v[:1], 0)
+    assert torch.equal(one.reshape(4, 128)[0], v[0, 0]) and torch.equal(one.reshape(4, 128)[3], v[0, 1])   # heads 0-1 -> kv 0, 2-3 -> kv 1
+    both = O.attention(qq, k, v, 4)
+    first = O.attention(qq[:1], k[:5], v[:5], 4)
+    assert torch.equal(both[0], first[0])
+    ref = torch.softmax(torch.einsum("snd,tnd->nst", qq[1:].float(), k.repeat_interleave(2, 1).float()) / math.sqrt(128), -1)
+    out = torch.einsum("nst,tnd->snd", ref, v.repeat_interleave(2, 1).float()).reshape(1, -1)
+    assert torch.allclose(both[1:].float(), out, atol=2e-2)
