@@ -181,16 +181,28 @@ def run_mlp_block(args):
 
 
 def run_decode_layer(args):
-    """One token through whole decoder layers of Llama-3-70B on one GPU (RMSNorm, fused qkv linear, rotary embedding + cache
-    append, attention over `--context` cached positions, o_proj + residual, RMSNorm, fused feed-forward + residual):
-    seven launches per layer.  Distinct weights and caches per layer, one CUDA graph over all of them."""
+    """One token through whole decoder layers of Llama-3-70B (RMSNorm, fused qkv linear, rotary embedding + cache append,
+    attention over `--context` cached positions, o_proj + residual, RMSNorm, fused feed-forward + residual): seven
+    launches per layer.  Distinct weights and caches per layer, one CUDA graph over all of them.  Under torchrun the
+    layer is tensor parallel: heads and the feed-forward's inner dimension are split over the ranks, o_proj and
+    down_proj run with the all-reduce and the residual add in the GEMV kernel."""
+    import torch.distributed as dist
     import minit_b200 as M
     from minit_b200 import decoder as D
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(0)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(local_rank)
+    far = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        from minit_b200.collective import FusedAllReduce
+        far = FusedAllReduce(m_max=max(16, args.m), n_max=HIDDEN)
     m, nl, ctx = args.m, min(args.layers, 16), args.context
-    gen = torch.Generator(device=dev).manual_seed(0)
-    HQ, HKV = Q_HEADS, KV_HEADS
+    gen = torch.Generator(device=dev).manual_seed(rank)
+    HQ, HKV = Q_HEADS // world, KV_HEADS // world
+    inter = INTER // world
 
     def rnd_linear(k, n):
         qw = torch.randint(-2**31, 2**31 - 1, (k // 8, n), device=dev, dtype=torch.int64, generator=gen).to(torch.int32)
@@ -203,10 +215,15 @@ def run_decode_layer(args):
         cache = D.KVCache(ctx + m, HKV, HEAD_DIM, torch.float16, dev)
         cache.k.normal_(generator=gen); cache.v.normal_(generator=gen)
         layers.append(dict(qkv=rnd_linear(HIDDEN, (HQ + 2 * HKV) * HEAD_DIM), o=rnd_linear(HQ * HEAD_DIM, HIDDEN),
-                           gu=rnd_linear(HIDDEN, 2 * INTER), dn=rnd_linear(INTER, HIDDEN), cache=cache,
+                           gu=rnd_linear(HIDDEN, 2 * inter), dn=rnd_linear(inter, HIDDEN), cache=cache,
                            n1=torch.ones(HIDDEN, device=dev, dtype=torch.float16), n2=torch.ones(HIDDEN, device=dev, dtype=torch.float16)))
-    x0 = torch.randn((m, HIDDEN), device=dev).half()
+    x0 = torch.randn((m, HIDDEN), generator=torch.Generator().manual_seed(5)).half().to(dev)     # replicated
     flags = _flag_pdl() if args.pdl else 0
+
+    def row_parallel(a, lin, residual):
+        if far is not None:
+            return far.matmul(a, *lin, None, bits=BITS, flags=flags, residual=residual)       # GEMV + all-reduce + residual, one kernel
+        return M.quantized_matrix_multiply_residual(a, *lin, None, residual, bits=BITS, flags=flags)
 
     def step():
         x = x0
@@ -215,12 +232,16 @@ def run_decode_layer(args):
             qkv = M.quantized_matrix_multiply(xn, *L["qkv"], None, bits=BITS, flags=flags)
             q = D.rope_append(qkv, cos, sin, L["cache"], HQ, ctx)
             a = D.attention_decode(q, L["cache"], ctx)
-            h = M.quantized_matrix_multiply_residual(a, *L["o"], None, x, bits=BITS, flags=flags)
+            h = row_parallel(a, L["o"], x)
             hn = D.rms_norm(h, L["n2"])
             g = M.quantized_gate_up_swiglu(hn, *L["gu"], bits=BITS, flags=flags)
-            x = M.quantized_matrix_multiply_residual(g, *L["dn"], None, h, bits=BITS, flags=flags)
+            x = row_parallel(g, L["dn"], h)
         return x
 
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
@@ -231,22 +252,31 @@ def run_decode_layer(args):
         with torch.cuda.graph(graph, stream=side):
             step()
         graph.replay()
-        torch.cuda.synchronize()
+        barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(side)
         for _ in range(args.steps):
             graph.replay()
         e1.record(side)
-        torch.cuda.synchronize()
+        barrier()
     torch.cuda.current_stream().wait_stream(side)
-    us = e0.elapsed_time(e1) * 1e3 / (args.steps * nl)
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    us = ms.item() * 1e3 / (args.steps * nl)
     hbm_peak, kind = peaks()
-    wb = sum(weight_bytes(k, n) for _, k, n, _ in layer_shapes(1))
+    wb = sum(weight_bytes(k, n) for _, k, n, _ in layer_shapes(world))
     kvb = 2 * ctx * HKV * HEAD_DIM * 2
-    print(json.dumps({"decode_layer": "llama3-70b, one GPU, int4 g128", "m": m, "context": ctx, "layers_timed": nl, "launches_per_layer": 7,
-                      "us_per_layer": us, "tokens_per_s_80_layers": m * 1e6 / (us * LAYERS),
-                      "bytes_per_layer": wb + kvb, "hbm_frac": (wb + kvb) / us / 1e3 / hbm_peak, "peak": kind,
-                      "note": "weights + KV cache of %d layers in rotation (%.1f GB), CUDA graph" % (nl, (wb + kvb) * nl / 1e9)}))
+    if rank == 0:
+        print(json.dumps({"decode_layer": "llama3-70b, int4 g128, tp%d" % world, "n_gpus": world, "m": m, "context": ctx, "layers_timed": nl,
+                          "launches_per_layer": 7, "us_per_layer": us, "tokens_per_s_80_layers": m * 1e6 / (us * LAYERS),
+                          "bytes_per_layer_per_gpu": wb + kvb, "hbm_frac": (wb + kvb) / us / 1e3 / hbm_peak, "peak": kind,
+                          "note": "weights + KV cache of %d layers in rotation (%.1f GB per GPU), CUDA graph, max over ranks" % (nl, (wb + kvb) * nl / 1e9)}))
+    if world > 1:
+        from minit_b200 import _lib
+        for ws in _lib._workspaces.values():
+            assert _lib.workspace_error_word(ws) == 0, "a bounded wait of the fused all-reduce expired"
+        dist.destroy_process_group()
 
 
 def _flag_pdl():
