@@ -180,6 +180,42 @@ def run_mlp_block(args):
                       "note": "weights of %d layers in rotation (%.1f GB), CUDA graph, PDL %s" % (nl, wb * nl / 1e9, "on" if args.pdl else "off")}))
 
 
+def run_attention(args):
+    """Decode attention alone (one token, Llama-3-70B heads) over `--context` cached positions: device time per call and
+    the cache bytes it streams against the HBM peak.  Several caches in rotation, eager launches."""
+    from minit_b200 import decoder as D
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    ctx, m = args.context, args.m
+    kvb = 2 * (ctx + m) * KV_HEADS * HEAD_DIM * 2
+    copies = max(2, min(16, int(400e6 // kvb) + 1))
+    caches = []
+    for _ in range(copies):
+        c = D.KVCache(ctx + m, KV_HEADS, HEAD_DIM, torch.float16, dev)
+        c.k.normal_(); c.v.normal_()
+        caches.append(c)
+    q = torch.randn((m, Q_HEADS, HEAD_DIM), device=dev).half()
+    out = torch.empty((m, Q_HEADS * HEAD_DIM), device=dev, dtype=torch.float16)
+
+    def one():
+        for c in caches:
+            D.attention_decode(q, c, ctx, out=out)
+    for _ in range(max(3, args.warmup)):
+        one()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        one()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (args.steps * copies)
+    hbm_peak, kind = peaks()
+    print(json.dumps({"attention_decode": "64 query / 8 kv heads x 128", "m": m, "context": ctx, "us_per_call": us,
+                      "cache_GBps": kvb / us / 1e3, "hbm_frac": kvb / us / 1e3 / hbm_peak, "peak": kind,
+                      "launch": "eager, %d caches in rotation (%.0f MB)" % (copies, kvb * copies / 1e6)}))
+
+
 def run_decode_layer(args):
     """One token through whole decoder layers of Llama-3-70B (RMSNorm, fused qkv linear, rotary embedding + cache append,
     attention over `--context` cached positions, o_proj + residual, RMSNorm, fused feed-forward + residual): seven
@@ -561,6 +597,7 @@ def main():
     ap.add_argument("--single-shape", default=None, help="K,N : time one linear instead of the workload (profiling aid)")
     ap.add_argument("--mlp-block", action="store_true", help="time the feed-forward block with separate and with fused elementwise steps")
     ap.add_argument("--decode-layer", action="store_true", help="time whole decoder layers (norms, rope, attention, fused linears) for one token")
+    ap.add_argument("--attention", action="store_true", help="time decode attention alone over --context cached positions")
     ap.add_argument("--context", type=int, default=4096, help="--decode-layer: cached positions")
     ap.add_argument("--tune", type=lambda v: int(v, 0), default=0, help="single-shape mode: extra tuning bits ORed into the flags")
     ap.add_argument("--kernel", default="auto", choices=["auto", "ring", "dtc", "tc", "vec", "umma"])
@@ -573,6 +610,8 @@ def main():
         return run_mlp_block(args)
     if args.decode_layer:
         return run_decode_layer(args)
+    if args.attention:
+        return run_attention(args)
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
