@@ -217,8 +217,8 @@ def run_attention(args):
 
 
 def run_decode_layer(args):
-    """One token through whole decoder layers of Llama-3-70B (RMSNorm, fused qkv linear, rotary embedding + cache append,
-    attention over `--context` cached positions, o_proj + residual, RMSNorm, fused feed-forward + residual): seven
+    """One token through whole decoder layers of Llama-3-70B (RMSNorm, fused qkv linear with rotary embedding + cache
+    append, attention over `--context` cached positions, o_proj + residual, RMSNorm, fused feed-forward + residual): six
     launches per layer.  Distinct weights and caches per layer, one CUDA graph over all of them.  Under torchrun the
     layer is tensor parallel: heads and the feed-forward's inner dimension are split over the ranks, o_proj and
     down_proj run with the all-reduce and the residual add in the GEMV kernel."""
@@ -265,8 +265,7 @@ def run_decode_layer(args):
         x = x0
         for L in layers:
             xn = D.rms_norm(x, L["n1"])
-            qkv = M.quantized_matrix_multiply(xn, *L["qkv"], None, bits=BITS, flags=flags)
-            q = D.rope_append(qkv, cos, sin, L["cache"], HQ, ctx)
+            q = D.qkv_rope_append(xn, *L["qkv"], cos, sin, L["cache"], HQ, ctx, bits=BITS, flags=flags)
             a = D.attention_decode(q, L["cache"], ctx)
             h = row_parallel(a, L["o"], x)
             hn = D.rms_norm(h, L["n2"])
@@ -305,7 +304,7 @@ def run_decode_layer(args):
     kvb = 2 * ctx * HKV * HEAD_DIM * 2
     if rank == 0:
         print(json.dumps({"decode_layer": "llama3-70b, int4 g128, tp%d" % world, "n_gpus": world, "m": m, "context": ctx, "layers_timed": nl,
-                          "launches_per_layer": 7, "us_per_layer": us, "tokens_per_s_80_layers": m * 1e6 / (us * LAYERS),
+                          "launches_per_layer": 6, "us_per_layer": us, "tokens_per_s_80_layers": m * 1e6 / (us * LAYERS),
                           "bytes_per_layer_per_gpu": wb + kvb, "hbm_frac": (wb + kvb) / us / 1e3 / hbm_peak, "peak": kind,
                           "note": "weights + KV cache of %d layers in rotation (%.1f GB per GPU), CUDA graph, max over ranks" % (nl, (wb + kvb) * nl / 1e9)}))
     if world > 1:

@@ -203,6 +203,17 @@ int mt_swiglu(void* stream, const void* gate_up, void* out, int m, int n, int dt
 int mt_rms_norm(void* stream, const void* x, const void* weight, void* out, int rows, int h, float eps, int dtype);
 int mt_rope_append(void* stream, const void* qkv, const float* cos_table, const float* sin_table, void* q_out, void* k_cache, void* v_cache,
                    int m, int hq, int hkv, int d, int offset, const int32_t* offset_dev, int capacity, int table_rows, int dtype);
+/*
+ * mt_qgemm_rope_append: the fused q/k/v linear of a decode step with mt_rope_append as its epilogue:
+ * qkv = x @ W (+ bias) with W[K, (hq + 2 hkv) * d], rotated and scattered to q_out / k_cache / v_cache without ever
+ * being stored as a row.  At M <= 2 (decode GEMV) the rotation runs on the fp32 sums, one rounding; otherwise the
+ * GEMM writes the row into scratch ([M, (hq + 2 hkv) d], required then) and mt_rope_append follows.  No act-order.
+ */
+int mt_qgemm_rope_append(void* stream, const void* x, const uint32_t* qweight, const uint32_t* qzeros, const void* scales, const void* bias,
+                         const float* cos_table, const float* sin_table, void* q_out, void* k_cache, void* v_cache, void* scratch,
+                         int m, int hq, int hkv, int d, int k, int nr_groups, int bits, int dtype,
+                         int offset, const int32_t* offset_dev, int capacity, int table_rows,
+                         void* workspace, size_t workspace_bytes, int flags);
 size_t mt_attention_workspace_bytes(int m, int hkv, int max_len);
 int mt_attention_decode(void* stream, const void* q, const void* k_cache, const void* v_cache, void* out, int m, int hq, int hkv, int d,
                         int offset, const int32_t* offset_dev, int max_len, float scale, void* workspace, size_t workspace_bytes, int dtype);

@@ -424,6 +424,44 @@ int mt_rope_append(void* stream, const void* qkv, const float* cos_table, const 
                               offset_dev, capacity, table_rows, dtype);
 }
 
+int mt_qgemm_rope_append(void* stream, const void* x, const uint32_t* qweight, const uint32_t* qzeros, const void* scales, const void* bias,
+                         const float* cos_table, const float* sin_table, void* q_out, void* k_cache, void* v_cache, void* scratch,
+                         int m, int hq, int hkv, int d, int k, int nr_groups, int bits, int dtype,
+                         int offset, const int32_t* offset_dev, int capacity, int table_rows,
+                         void* workspace, size_t workspace_bytes, int flags) {
+    if (hq < 1 || hkv < 1 || offset < 0 || capacity < 1 || table_rows < 1) return MT_ERR_SHAPE;
+    if (d != 128) return MT_ERR_UNSUPPORTED;
+    const int n = (hq + 2 * hkv) * d;
+    int rc = validate_gptq(qweight, qzeros, scales, n, k, nr_groups, bits, dtype);
+    if (rc != MT_OK) return rc;
+    if (m < 0 || k == 0) return MT_ERR_SHAPE;
+    if (!offset_dev && (offset + m > capacity || offset + m > table_rows)) return MT_ERR_SHAPE;
+    if (m == 0) return MT_OK;
+    if (!x || !cos_table || !sin_table || !q_out || !k_cache || !v_cache) return MT_ERR_NULL;
+    if (!aligned16(x) || !aligned16(q_out) || !aligned16(k_cache) || !aligned16(v_cache) || (bias && !aligned16(bias)) ||
+        (workspace && !aligned16(workspace))) return MT_ERR_ALIGN;
+    if ((k / nr_groups) % (4 * (32 / bits)) != 0) return MT_ERR_SHAPE;
+    if ((rc = check_device()) != MT_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    QGemmArgs a = {};
+    a.x = x; a.qweight = qweight; a.qzeros = qzeros; a.scales = scales; a.bias = bias; a.out = q_out;
+    a.m = m; a.n = n; a.k = k; a.groups = nr_groups; a.bits = bits; a.dtype = dtype;
+    a.workspace = workspace; a.workspace_bytes = workspace_bytes; a.flags = flags;
+    const bool forced_other = (flags & (MT_FLAG_FORCE_SMALL | MT_FLAG_FORCE_TC | MT_FLAG_FORCE_DTC | MT_FLAG_FORCE_UMMA)) != 0;
+    if (m <= 2 && !forced_other && vec_supported(a)) {
+        RopeArgs r;
+        r.cosv = cos_table; r.sinv = sin_table; r.q_out = q_out; r.k_cache = k_cache; r.v_cache = v_cache; r.offset_dev = offset_dev;
+        r.hq = hq; r.hkv = hkv; r.offset = offset; r.capacity = capacity; r.table_rows = table_rows;
+        a.rope = &r;
+        return launch_vec(st, a);
+    }
+    if (!scratch) return MT_ERR_NULL;
+    if (!aligned16(scratch)) return MT_ERR_ALIGN;
+    rc = mt_qgemm(stream, x, qweight, nullptr, qzeros, scales, bias, scratch, m, n, k, nr_groups, bits, dtype, workspace, workspace_bytes, flags);
+    if (rc == MT_OK) rc = launch_rope_append(st, scratch, cos_table, sin_table, q_out, k_cache, v_cache, m, hq, hkv, offset, offset_dev, capacity, table_rows, dtype);
+    return rc;
+}
+
 size_t mt_attention_workspace_bytes(int m, int hkv, int max_len) {
     if (m < 1 || hkv < 1 || max_len < 1) return 0;
     return attention_workspace_bytes(m, hkv, max_len);

@@ -109,6 +109,32 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
 // ----------------------------------------------------------------------------------
 // host-side launch plumbing shared by the .cu files
 // ----------------------------------------------------------------------------------
+// Epilogue of the fused q/k/v linear at decode: rotary embedding of the q and k heads, q to its own tensor, k and v
+// straight into the cache (what rope_append_kernel does as a separate launch).  cosv == nullptr: off.
+struct RopeArgs {
+    const float* cosv; const float* sinv;     // fp32 [table_rows, 64]
+    void* q_out;                              // [M, hq, 128] T
+    void* k_cache; void* v_cache;             // [capacity, hkv, 128] T
+    const int* offset_dev;                    // device int32 or null: overrides offset
+    int hq, hkv, offset, capacity, table_rows;
+};
+
+// One (even column, odd column) pair of a fused qkv row: rotate (q, k heads) or copy (v heads) and store.
+template <typename T>
+__device__ __forceinline__ void rope_store_pair(const RopeArgs& r, int off, int tok, int col, float re, float im) {
+    using H = F16x2<T>;
+    const int head = col >> 7, d = col & 127, pos = off + tok;
+    if (head >= r.hq + r.hkv) {
+        if (pos < r.capacity) reinterpret_cast<uint32_t*>(r.v_cache)[(((size_t)pos * r.hkv + (head - r.hq - r.hkv)) * 128 + d) >> 1] = H::pack(re, im);
+        return;
+    }
+    const int tp = pos < r.table_rows ? pos : r.table_rows - 1;
+    const float cs = __ldg(r.cosv + (size_t)tp * 64 + (d >> 1)), sn = __ldg(r.sinv + (size_t)tp * 64 + (d >> 1));
+    const uint32_t o = H::pack(re * cs - im * sn, im * cs + re * sn);
+    if (head < r.hq) reinterpret_cast<uint32_t*>(r.q_out)[(((size_t)tok * r.hq + head) * 128 + d) >> 1] = o;
+    else if (pos < r.capacity) reinterpret_cast<uint32_t*>(r.k_cache)[(((size_t)pos * r.hkv + (head - r.hq)) * 128 + d) >> 1] = o;
+}
+
 struct QGemmArgs {
     const void* x;            // [M,K] T
     const uint32_t* qweight;  // [K/pack, N]
@@ -130,6 +156,7 @@ struct QGemmArgs {
     // fused epilogues (decode GEMV only; other kernels are followed by an elementwise launch)
     const void* residual;     // [M,N] T or null: out = residual + (x @ W + bias), added after the all-reduce
     int epilogue;             // MT_EPILOGUE_*: SWIGLU = out[M,N/2] from the gate / up interleaved layout
+    const RopeArgs* rope;     // non-null: the output row is a fused q/k/v row, rotated and scattered (out unused)
 };
 
 // workspace layout: [0, kCounterBytes) tile counters (the last word is the error word) (kept zero between launches),

@@ -56,6 +56,7 @@ struct VecParams {
     ArParams ar;      // row-parallel use: all-reduce of the finished sums over peer memory (ar_mailbox.cuh)
     const void* residual;   // [M,N] T or null, added to the finished (all-reduced) sum before the one rounding
     int swiglu;       // columns are gate / up interleaved in blocks of 4 + 4: out[M,N/2] = silu(gate) * up
+    RopeArgs rope;    // rope.cosv != null: rotary embedding + cache append of a fused q/k/v row instead of the store
 };
 
 __device__ __forceinline__ float h2sum(uint32_t h) {
@@ -334,7 +335,11 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
     }
     if (active && bias) v += H::to_float(reinterpret_cast<const uint16_t*>(bias)[gc]);
     const uint16_t* resid = reinterpret_cast<const uint16_t*>(p.residual);
-    if (p.swiglu) {
+    if (p.rope.cosv) {
+        // the pair (even column, odd column) sits in neighbouring lanes; the even one rotates and stores both
+        const float im = __shfl_xor_sync(0xffffffffu, v, 1);
+        if (active && !(cc & 1)) rope_store_pair<T>(p.rope, p.rope.offset_dev ? *p.rope.offset_dev : p.rope.offset, mb_r, gc, v, im);
+    } else if (p.swiglu) {
         // gate column cc (cc % 8 < 4) and its up column cc + 4 sit four lanes apart in the same warp
         const float u = __shfl_xor_sync(0xffffffffu, v, 4);
         if (active && !(cc & 4)) out[(size_t)mb_r * (p.n >> 1) + ((gc >> 3) << 2) + (gc & 3)] = H::from_float(silu_mul(v, u));
@@ -395,6 +400,7 @@ struct StreamParams {
     ArParams ar;       // row-parallel use: all-reduce of the finished sums over peer memory (ar_mailbox.cuh)
     const void* residual;   // [M,N] T or null, added to the finished (all-reduced) sum before the one rounding
     int swiglu;        // columns are gate / up interleaved in blocks of 4 + 4: out[M,N/2] = silu(gate) * up
+    RopeArgs rope;     // rope.cosv != null: rotary embedding + cache append of a fused q/k/v row instead of the store
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
@@ -588,6 +594,12 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
         for (int mb = 0; mb < MB; ++mb)
             if (mb < p.m) {
                 float4 v = make_float4(r[mb].x + b0, r[mb].y + b1, r[mb].z + b2, r[mb].w + b3);
+                if (p.rope.cosv) {
+                    const int off = p.rope.offset_dev ? *p.rope.offset_dev : p.rope.offset;
+                    rope_store_pair<T>(p.rope, off, mb, colb, v.x, v.y);
+                    rope_store_pair<T>(p.rope, off, mb, colb + 2, v.z, v.w);
+                    continue;
+                }
                 if (p.swiglu) {
                     // an even lane holds four gate columns, the next lane their up columns (the whole warp is here)
                     const float4 u = make_float4(__shfl_xor_sync(0xffffffffu, v.x, 1), __shfl_xor_sync(0xffffffffu, v.y, 1),
@@ -894,6 +906,7 @@ int launch_stream_cfg(cudaStream_t st, const QGemmArgs& a, int ctas) {
     p.ar = make_ar_params(a);
     if (p.ar.world > 1 && (size_t)a.m * a.n * 8 > p.ar.slot_bytes) return MT_ERR_TOO_LARGE;
     p.residual = a.residual; p.swiglu = a.epilogue == MT_EPILOGUE_SWIGLU ? 1 : 0;
+    if (a.rope) p.rope = *a.rope; else p.rope.cosv = nullptr;
     p.zp1_const = 1 << (a.bits - 1);
     p.pdl = (a.flags & MT_FLAG_PDL) ? 1 : 0;
     const int grid = (p.warps + NW - 1) / NW;
@@ -1014,6 +1027,7 @@ int launch_vec(cudaStream_t st, const QGemmArgs& a) {
     p.ar = make_ar_params(a);
     if (p.ar.world > 1 && (size_t)a.m * a.n * 8 > p.ar.slot_bytes) return MT_ERR_TOO_LARGE;
     p.residual = a.residual; p.swiglu = a.epilogue == MT_EPILOGUE_SWIGLU ? 1 : 0;
+    if (a.rope) p.rope = *a.rope; else p.rope.cosv = nullptr;
     const int mb = a.m == 1 ? 1 : 2;
     const size_t smem = (size_t)VEC_WARPS * mb * slice_ks * 16 + (size_t)VEC_WARPS * mb * (slice_ks / cks) * 8;
     if (smem > 160 * 1024) return MT_ERR_TOO_LARGE;

@@ -71,6 +71,31 @@ def rope_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, cache: 
     return q
 
 
+def qkv_rope_append(x: torch.Tensor, qweight: torch.Tensor, zeros: Optional[torch.Tensor], scales: torch.Tensor,
+                    cos: torch.Tensor, sin: torch.Tensor, cache: KVCache, nr_querys: int, offset: int, *, bits: int = 8,
+                    bias: Optional[torch.Tensor] = None, offset_dev: Optional[torch.Tensor] = None, flags: int = 0) -> torch.Tensor:
+    """The fused q/k/v linear with the rotary embedding and the cache append as its epilogue (one kernel at M <= 2):
+    returns q [M, hq, d]; k and v of the M tokens land in the cache at rows offset .. offset + M - 1."""
+    dev = _lib.require_cuda(x, qweight, zeros, scales, cos, sin, cache.k, cache.v, bias, offset_dev)
+    pack = 32 // bits
+    m, k0 = x.shape
+    hkv, d = cache.kv_heads, cache.head_size
+    n0 = (nr_querys + 2 * hkv) * d
+    if qweight.shape != (k0 // pack, n0) or scales.shape[1] != n0 or scales.dtype != x.dtype or cos.dtype != torch.float32:
+        raise ValueError("shape or dtype mismatch between x, qweight, scales and the tables")
+    q = torch.empty((m, nr_querys, d), dtype=x.dtype, device=dev)
+    scratch = torch.empty((m, n0), dtype=x.dtype, device=dev) if m > 2 else None
+    stream = _lib.current_stream(dev)
+    ws = _lib.workspace(dev, stream, _lib.lib.mt_workspace_bytes(m, n0, k0, bits))
+    with torch.cuda.device(dev):
+        rc = _lib.lib.mt_qgemm_rope_append(stream, x.data_ptr(), qweight.data_ptr(), _lib.ptr(zeros), scales.data_ptr(), _lib.ptr(bias),
+                                           cos.data_ptr(), sin.data_ptr(), q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+                                           _lib.ptr(scratch), m, nr_querys, hkv, d, k0, scales.shape[0], bits, _lib.dtype_code(x.dtype),
+                                           offset, _lib.ptr(offset_dev), cache.capacity, cos.shape[0], ws.data_ptr(), ws.numel(), flags)
+    _lib.check(rc, "mt_qgemm_rope_append")
+    return q
+
+
 _att_ws = {}
 
 
@@ -147,8 +172,7 @@ class QAttention(Module):
                     raise ValueError("act-order q / k / v projections are not fused")
             self._qkv = fuse_columns((self.q_proj, self.k_proj, self.v_proj))
         qw, qz, sc, bi = self._qkv
-        qkv = quantized_matrix_multiply(x, qw, qz, sc, None, bits=self.bits, bias=bi)
-        q = rope_append(qkv, cos, sin, cache, self.nr_querys, offset)
+        q = qkv_rope_append(x, qw, qz, sc, cos, sin, cache, self.nr_querys, offset, bits=self.bits, bias=bi)
         a = attention_decode(q, cache, offset)
         cache.length = max(cache.length, offset + x.shape[0])
         o = self.o_proj

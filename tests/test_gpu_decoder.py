@@ -68,6 +68,30 @@ def test_rope_append(D, dtype, m, hq, hkv, offset):
     assert torch.equal(c2.cpu(), cos) and torch.equal(s2.cpu(), sin)
 
 
+@pytest.mark.parametrize("variant", [0, 1 << 24, 2 << 24], ids=["auto", "split", "stream"])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,hq,hkv,offset,bias", [(1, 8, 2, 0, False), (1, 16, 4, 300, True), (2, 8, 2, 41, False), (3, 8, 2, 7, True)])
+def test_qkv_linear_with_rope_epilogue(D, variant, dtype, m, hq, hkv, offset, bias):
+    """The fused q/k/v linear with rotary embedding + cache append as its epilogue, against the oracle's linear followed
+    by its rope; M = 3 takes the two-launch path (GEMM into scratch, then mt_rope_append)."""
+    d, k, bits = 128, 1024, 4
+    n = (hq + 2 * hkv) * d
+    c = O.make_gptq_case(k, n, m, bits=bits, dtype=dtype, seed=hq + offset + m, bias=bias, scale_lo=0.001, scale_hi=0.004)
+    cos, sin = O.rope_tables(d, 512, 5e5, dtype)
+    cache = D.KVCache(512, hkv, d, dtype, DEV)
+    cache.k.fill_(7.0); cache.v.fill_(7.0)
+    dv = lambda t: t.to(DEV)
+    q = D.qkv_rope_append(dv(c["x"]), dv(c["qweight"]), dv(c["qzeros"]), dv(c["scales"]), dv(cos), dv(sin), cache, hq, offset,
+                          bits=bits, bias=dv(c["bias"]) if bias else None, flags=variant).cpu()
+    w = O.dequantize_packed(c["qweight"], None, c["qzeros"], c["scales"], bits)
+    y = O.qlinear(c["x"], w, c["bias"] if bias else None).reshape(m, hq + 2 * hkv, d)
+    assert_close(q.reshape(m, -1), O.rope(y[:, :hq], cos, sin, offset).reshape(m, -1), "q")
+    assert_close(cache.k[offset:offset + m].cpu().reshape(m, -1), O.rope(y[:, hq:hq + hkv], cos, sin, offset).reshape(m, -1), "k")
+    assert_close(cache.v[offset:offset + m].cpu().reshape(m, -1), y[:, hq + hkv:].reshape(m, -1), "v")
+    assert (cache.k[:offset] == 7).all() and (cache.k[offset + m:] == 7).all()
+    assert (cache.v[:offset] == 7).all() and (cache.v[offset + m:] == 7).all()
+
+
 def attention_fp32(q, k, v, offset):
     s_len, hq, d = q.shape
     r = hq // k.shape[1]
@@ -186,3 +210,5 @@ def test_status_codes(D):
     assert lib.mt_attention_decode(None, p, p, p, p, 1, 24, 2, 128, 0, None, 8, 0.1, p, 1 << 18, 0) == -8   # 12 query heads per kv head
     assert lib.mt_attention_decode(None, p, p, p, p, 1, 8, 2, 128, 0, None, 8, 0.1, p, 16, 0) == -6         # workspace too small
     assert lib.mt_attention_workspace_bytes(1, 8, 4096) > 0
+    assert lib.mt_qgemm_rope_append(None, p, p, p, p, None, p, p, p, p, p, None, 1, 8, 2, 64, 256, 2, 4, 0, 0, None, 16, 16, p, 1 << 18, 0) == -8
+    assert lib.mt_qgemm_rope_append(None, p, p, p, p, None, p, p, p, p, p, None, 4, 8, 2, 128, 256, 2, 4, 0, 0, None, 16, 16, p, 1 << 18, 0) == -1   # scratch at M > 2
