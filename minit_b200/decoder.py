@@ -84,7 +84,7 @@ def qkv_rope_append(x: torch.Tensor, qweight: torch.Tensor, zeros: Optional[torc
     if qweight.shape != (k0 // pack, n0) or scales.shape[1] != n0 or scales.dtype != x.dtype or cos.dtype != torch.float32:
         raise ValueError("shape or dtype mismatch between x, qweight, scales and the tables")
     q = torch.empty((m, nr_querys, d), dtype=x.dtype, device=dev)
-    scratch = torch.empty((m, n0), dtype=x.dtype, device=dev) if m > 2 else None
+    scratch = torch.empty((m, n0), dtype=x.dtype, device=dev) if (m > 2 or (k0 // scales.shape[0]) % 32) else None
     stream = _lib.current_stream(dev)
     ws = _lib.workspace(dev, stream, _lib.lib.mt_workspace_bytes(m, n0, k0, bits))
     with torch.cuda.device(dev):

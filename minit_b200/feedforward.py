@@ -72,7 +72,8 @@ def quantized_gate_up_swiglu(x: torch.Tensor, qweight: torch.Tensor, zeros: Opti
         m *= d
     if out is None:
         out = torch.empty((*ms, n0 // 2), dtype=x.dtype, device=dev)
-    scratch = torch.empty((m, n0), dtype=x.dtype, device=dev) if m > 2 else None
+    # the GEMV has the epilogue at M <= 2 (N % 128 == 0, group size % 32 == 0); otherwise the GEMM writes a scratch row first
+    scratch = torch.empty((m, n0), dtype=x.dtype, device=dev) if (m > 2 or n0 % 128 or (k0 // scales.shape[0]) % 32) else None
     stream = _lib.current_stream(dev)
     ws = _lib.workspace(dev, stream, _lib.lib.mt_workspace_bytes(m, n0, k0, bits))
     with torch.cuda.device(dev):

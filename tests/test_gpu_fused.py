@@ -223,6 +223,26 @@ def test_feed_forward_module(M, m, names, bias):
     assert_close(ff(x.to(DEV), residual=res.to(DEV)), O.add_residual(res, y_ref), "feed-forward + residual")
 
 
+@pytest.mark.parametrize("m", [1, 2])
+def test_shapes_the_gemv_does_not_take_fall_back(M, m):
+    """N not a multiple of 128 (the GEMV's column block): the two-launch path serves M <= 2 as well; empty batches are a no-op."""
+    bits = 4
+    g, u = gate_up_case(512, 200, m, bits, torch.float16, seed=3)                   # N = 400
+    qw, qz, sc, _ = interleaved_on_device(M, g, u, bits)
+    out = M.quantized_gate_up_swiglu(g["x"].to(DEV), qw, qz, sc, bits=bits)
+    assert_swiglu_close(out, g, u, bits, what="swiglu N=400")
+    c = O.make_gptq_case(512, 200, m, bits=bits, seed=5)
+    res = torch.randn((m, 200), generator=torch.Generator().manual_seed(1)).half()
+    d = lambda t: t.to(DEV)
+    out = M.quantized_matrix_multiply_residual(d(c["x"]), d(c["qweight"]), d(c["qzeros"]), d(c["scales"]), None, d(res), bits=bits)
+    w = O.dequantize_packed(c["qweight"], None, c["qzeros"], c["scales"], bits)
+    assert_close(out, O.add_residual(res, O.qlinear(c["x"], w)), "residual N=200")
+    empty = M.quantized_gate_up_swiglu(g["x"][:0].to(DEV), qw, qz, sc, bits=bits)
+    assert empty.shape == (0, 200)
+    empty = M.quantized_matrix_multiply_residual(d(c["x"][:0]), d(c["qweight"]), d(c["qzeros"]), d(c["scales"]), None, d(res[:0]), bits=bits)
+    assert empty.shape == (0, 200)
+
+
 def test_status_codes(M):
     from minit_b200 import _lib
     lib = _lib.lib
