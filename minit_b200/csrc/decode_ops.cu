@@ -28,7 +28,6 @@ namespace {
 
 constexpr int ATT_D = 128;                 // head size
 constexpr int ATT_MAXG = 8;                // query heads per kv head
-constexpr int ATT_WARPS = 4;
 constexpr int ATT_TILE = 32;               // cached positions per warp tile: one per lane
 constexpr int ATT_ROW = ATT_D * 2 + 16;    // bytes of a K / V row in shared memory (padded: 16-byte reads of 8 rows hit 32 banks)
 constexpr int ATT_WARP_SMEM = 2 * ATT_TILE * ATT_ROW;   // K tile, V tile
@@ -138,14 +137,16 @@ struct AttParams {
     const int* offset_dev;
     int m, hq, hkv, group;      // group = hq / hkv
     int offset;                 // cached positions before the first new token
-    int splits, chunk;          // CTAs per (token, kv head); positions per CTA (a multiple of 32 * ATT_WARPS)
+    int splits, chunk;          // CTAs per (token, kv head); positions per CTA (a multiple of 32 x warps per CTA)
     int cluster;                // CTAs per thread-block cluster (divides splits)
     int max_len;                // the caller's bound on offset + m: no cache row at or beyond it is read
     float scale;
 };
 
-template <typename T>
-__global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const AttParams p) {
+// NW warps per CTA: 8 (one CTA per SM, eight tiles in flight) while one cluster takes the whole sequence, 4 (two CTAs
+// per SM, more and shorter ranges) beyond
+template <typename T, int NW>
+__global__ void __launch_bounds__(NW * 32) attention_decode_kernel(const AttParams p) {
     using H = F16x2<T>;
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ int s_last;
@@ -203,7 +204,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const 
     for (int jd = 0; jd < ATT_D / 8; ++jd) oc[jd][0] = oc[jd][1] = oc[jd][2] = oc[jd][3] = 0.f;
     const int lm = lane >> 3, lr = lane & 7;                // ldmatrix: this lane supplies row lr of matrix lm
 
-    for (; t0 < s1; t0 += ATT_WARPS * ATT_TILE) {
+    for (; t0 < s1; t0 += NW * ATT_TILE) {
         // groups in flight: K of this tile, V of this tile.  K of the next tile is requested as soon as the scores are
         // done, V of the next after the weighted sum, so each copy overlaps the other half of the arithmetic.
         asm volatile("cp.async.wait_group 1;" ::: "memory");
@@ -247,7 +248,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const 
         }
         ls = ls * resc + lsum;
         __syncwarp();                                       // every lane has read its K fragments
-        issue(t0 + ATT_WARPS * ATT_TILE, kc, ks_a);
+        issue(t0 + NW * ATT_TILE, kc, ks_a);
 #pragma unroll
         for (int jd = 0; jd < ATT_D / 8; ++jd) { oc[jd][0] *= resc; oc[jd][1] *= resc; }
         asm volatile("cp.async.wait_group 1;" ::: "memory"); // V of this tile (the next K may still be in flight)
@@ -266,7 +267,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const 
             }
         }
         __syncwarp();                                       // every lane is done with the V tile before it is overwritten
-        issue(t0 + ATT_WARPS * ATT_TILE, vc, vs_a);
+        issue(t0 + NW * ATT_TILE, vc, vs_a);
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 
@@ -283,45 +284,50 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const 
             *reinterpret_cast<float2*>(&part(warp, gq)[8 * jd + 2 * tq]) = make_float2(oc[jd][0], oc[jd][1]);
     }
     __syncthreads();
-    // thread -> dimension d of every query head: first the CTA's four warps, then (through the cluster's shared
+    // thread -> dimension d of every ATT_HS-th query head: first the CTA's warps, then (through the cluster's shared
     // memory) the CTAs of the cluster, then (through global memory, last CTA to arrive) the clusters
-    const int d = tid;                                      // 128 threads = 128 dimensions
+    constexpr int ATT_HS = NW * 32 / ATT_D;          // threads per dimension: each takes the heads hh, hh + ATT_HS, ...
+    constexpr int NH = ATT_MAXG / ATT_HS;
+    const int d = tid & (ATT_D - 1), hh = tid / ATT_D;
     const int C = p.cluster;
     const int crank = C > 1 ? split % C : 0, cl = split / C, ncl = p.splits / C;
-    float* xred = reinterpret_cast<float*>(smem + ATT_WARPS * ATT_WARP_SMEM);      // [C][G][ATT_PART], used in cluster rank 0
+    float* xred = reinterpret_cast<float*>(smem + NW * ATT_WARP_SMEM);      // [C][G][ATT_PART], used in cluster rank 0
     auto merge_store = [&](int h, float l_all, float a_all) {
         reinterpret_cast<uint16_t*>(p.out)[((size_t)tok * p.hq + (size_t)kvh * G + h) * ATT_D + d] = H::from_float(l_all > 0.f ? a_all / l_all : 0.f);
     };
-    float m_c[ATT_MAXG], l_c[ATT_MAXG], a_c[ATT_MAXG];
+    float m_c[NH], l_c[NH], a_c[NH];
 #pragma unroll
-    for (int h = 0; h < ATT_MAXG; ++h) {
-        m_c[h] = -INFINITY; l_c[h] = 0.f; a_c[h] = 0.f;
+    for (int hi = 0; hi < NH; ++hi) {
+        const int h = hi * ATT_HS + hh;
+        m_c[hi] = -INFINITY; l_c[hi] = 0.f; a_c[hi] = 0.f;
         if (h < G) {
 #pragma unroll
-            for (int w = 0; w < ATT_WARPS; ++w) m_c[h] = fmaxf(m_c[h], part(w, h)[ATT_D]);
+            for (int w = 0; w < NW; ++w) m_c[hi] = fmaxf(m_c[hi], part(w, h)[ATT_D]);
 #pragma unroll
-            for (int w = 0; w < ATT_WARPS; ++w) {
-                const float f = part(w, h)[ATT_D] == -INFINITY ? 0.f : __expf(part(w, h)[ATT_D] - m_c[h]);
-                l_c[h] = fmaf(part(w, h)[ATT_D + 1], f, l_c[h]);
-                a_c[h] = fmaf(part(w, h)[d], f, a_c[h]);
+            for (int w = 0; w < NW; ++w) {
+                const float f = part(w, h)[ATT_D] == -INFINITY ? 0.f : __expf(part(w, h)[ATT_D] - m_c[hi]);
+                l_c[hi] = fmaf(part(w, h)[ATT_D + 1], f, l_c[hi]);
+                a_c[hi] = fmaf(part(w, h)[d], f, a_c[hi]);
             }
         }
     }
     if (C > 1) {
         cluster_wait_acquire();                             // phase 0 complete: rank 0 of the cluster is resident
 #pragma unroll
-        for (int h = 0; h < ATT_MAXG; ++h) {
+        for (int hi = 0; hi < NH; ++hi) {
+            const int h = hi * ATT_HS + hh;
             if (h < G) {
                 float* row = xred + ((size_t)crank * ATT_MAXG + h) * ATT_PART;
-                st_cluster_f32(row + d, 0u, a_c[h]);
-                if (d == 0) { st_cluster_f32(row + ATT_D, 0u, m_c[h]); st_cluster_f32(row + ATT_D + 1, 0u, l_c[h]); }
+                st_cluster_f32(row + d, 0u, a_c[hi]);
+                if (d == 0) { st_cluster_f32(row + ATT_D, 0u, m_c[hi]); st_cluster_f32(row + ATT_D + 1, 0u, l_c[hi]); }
             }
         }
         cluster_arrive_release();
         cluster_wait_acquire();
         if (crank != 0) return;
 #pragma unroll
-        for (int h = 0; h < ATT_MAXG; ++h) {
+        for (int hi = 0; hi < NH; ++hi) {
+            const int h = hi * ATT_HS + hh;
             if (h < G) {
                 float mm = -INFINITY;
                 for (int r = 0; r < C; ++r) mm = fmaxf(mm, xred[((size_t)r * ATT_MAXG + h) * ATT_PART + ATT_D]);
@@ -332,23 +338,24 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const 
                     ll = fmaf(row[ATT_D + 1], f, ll);
                     aa = fmaf(row[d], f, aa);
                 }
-                m_c[h] = mm; l_c[h] = ll; a_c[h] = aa;
+                m_c[hi] = mm; l_c[hi] = ll; a_c[hi] = aa;
             }
         }
     }
     if (ncl == 1) {
 #pragma unroll
-        for (int h = 0; h < ATT_MAXG; ++h)
-            if (h < G) merge_store(h, l_c[h], a_c[h]);
+        for (int hi = 0; hi < NH; ++hi)
+            if (hi * ATT_HS + hh < G) merge_store(hi * ATT_HS + hh, l_c[hi], a_c[hi]);
         return;
     }
     const size_t slot = ((size_t)tok * p.hkv + kvh) * ncl;
 #pragma unroll
-    for (int h = 0; h < ATT_MAXG; ++h) {
+    for (int hi = 0; hi < NH; ++hi) {
+        const int h = hi * ATT_HS + hh;
         if (h < G) {
             float* dst = p.partial + ((slot + cl) * ATT_MAXG + h) * ATT_PART;
-            if (d == 0) { __stcg(dst + ATT_D, m_c[h]); __stcg(dst + ATT_D + 1, l_c[h]); }
-            __stcg(dst + d, a_c[h]);
+            if (d == 0) { __stcg(dst + ATT_D, m_c[hi]); __stcg(dst + ATT_D + 1, l_c[hi]); }
+            __stcg(dst + d, a_c[hi]);
         }
     }
     __threadfence();
@@ -357,9 +364,9 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const 
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // warp w merges query heads w and w + 4, a lane four dimensions: every load of a head is in flight at once
+    // warp w merges query head w (w + NW, ...), a lane four dimensions: every load of a head is in flight at once
 #pragma unroll 1
-    for (int h = warp; h < G; h += ATT_WARPS) {
+    for (int h = warp; h < G; h += NW) {
         const float* src = p.partial + (slot * ATT_MAXG + h) * ATT_PART;
         float ms[ATT_MAXCL], lv[ATT_MAXCL]; float4 av[ATT_MAXCL];
 #pragma unroll
@@ -390,12 +397,17 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_decode_kernel(const 
 // CTAs per (token, kv head) = clusters x cluster size; positions per CTA.  Up to ATT_CLUSTER * ATT_PER_SINGLE tiles
 // one cluster takes the whole sequence, its CTAs a few tiles per warp, and everything merges through shared memory
 // (the global stage costs ~7 us: partials, fence, counter, read back); longer sequences use up to ATT_MAXCL clusters.
-void attention_plan(int max_len, int& splits, int& chunk, int& cluster) {
-    const int tile = ATT_WARPS * ATT_TILE;
+void attention_plan(int max_len, int& splits, int& chunk, int& cluster, int& warps) {
+    warps = 8;
+    int tile = warps * ATT_TILE;
     int tiles = (max_len + tile - 1) / tile;
     if (tiles < 1) tiles = 1;
     if (tiles <= ATT_CLUSTER) { cluster = tiles; splits = tiles; chunk = tile; return; }
     cluster = ATT_CLUSTER;
+    if (tiles <= ATT_CLUSTER * ATT_PER_SINGLE) { splits = ATT_CLUSTER; chunk = (tiles + splits - 1) / splits * tile; return; }
+    warps = 4;
+    tile = warps * ATT_TILE;
+    tiles = (max_len + tile - 1) / tile;
     int ncl = (tiles + ATT_CLUSTER * ATT_PER_SINGLE - 1) / (ATT_CLUSTER * ATT_PER_SINGLE);
     if (ncl > ATT_MAXCL) ncl = ATT_MAXCL;
     splits = ncl * ATT_CLUSTER;
@@ -442,21 +454,26 @@ int launch_rope_append(cudaStream_t st, const void* qkv, const float* cosv, cons
 }
 
 size_t attention_workspace_bytes(int m, int hkv, int max_len) {
-    int splits, chunk, cluster;
-    attention_plan(max_len, splits, chunk, cluster);
+    int splits, chunk, cluster, warps;
+    attention_plan(max_len, splits, chunk, cluster, warps);
     const size_t counters = (((size_t)m * hkv * 4) + 255) & ~(size_t)255;
     return counters + (size_t)m * hkv * (splits / cluster) * ATT_MAXG * ATT_PART * 4;
 }
 
-template <typename T>
-static int launch_attention_inst(cudaStream_t st, const AttParams& p, dim3 grid, size_t smem, bool& configured) {
-    auto kern = attention_decode_kernel<T>;
-    if (!configured) {
+template <typename T, int NW>
+static int launch_attention_inst(cudaStream_t st, const AttParams& p, dim3 grid) {
+    auto kern = attention_decode_kernel<T, NW>;
+    // the K / V tiles of the warps, then the cluster's merge rows (always ATT_CLUSTER of them: one attribute value)
+    const size_t smem = (size_t)NW * ATT_WARP_SMEM + (size_t)ATT_CLUSTER * ATT_MAXG * ATT_PART * 4;
+    static bool configured[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return MT_ERR_CUDA; }
+    if (!configured[dev]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
-        configured = true;
+        configured[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid; cfg.blockDim = dim3(ATT_WARPS * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cfg.gridDim = grid; cfg.blockDim = dim3(NW * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = p.cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
@@ -472,20 +489,16 @@ int launch_attention_decode(cudaStream_t st, const void* q, const void* k_cache,
     AttParams p;
     p.q = q; p.k_cache = k_cache; p.v_cache = v_cache; p.out = out;
     p.m = m; p.hq = hq; p.hkv = hkv; p.group = hq / hkv; p.offset = offset; p.offset_dev = offset_dev; p.scale = scale;
-    attention_plan(max_len, p.splits, p.chunk, p.cluster);
+    int warps;
+    attention_plan(max_len, p.splits, p.chunk, p.cluster, warps);
     p.max_len = max_len;
     if (attention_workspace_bytes(m, hkv, max_len) > workspace_bytes) return MT_ERR_WORKSPACE;
     const size_t counters = (((size_t)m * hkv * 4) + 255) & ~(size_t)255;
     p.counters = static_cast<unsigned*>(workspace);
     p.partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + counters);
     const dim3 grid(p.splits, hkv, m);
-    // the K / V tiles of the four warps, then the cluster's merge rows (always ATT_CLUSTER of them: one attribute value)
-    const size_t smem = (size_t)ATT_WARPS * ATT_WARP_SMEM + (size_t)ATT_CLUSTER * ATT_MAXG * ATT_PART * 4;
-    static bool configured[64][2] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return MT_ERR_CUDA; }
-    if (dtype == MT_F16) return launch_attention_inst<__half>(st, p, grid, smem, configured[dev][0]);
-    return launch_attention_inst<__nv_bfloat16>(st, p, grid, smem, configured[dev][1]);
+    if (dtype == MT_F16) return warps == 8 ? launch_attention_inst<__half, 8>(st, p, grid) : launch_attention_inst<__half, 4>(st, p, grid);
+    return warps == 8 ? launch_attention_inst<__nv_bfloat16, 8>(st, p, grid) : launch_attention_inst<__nv_bfloat16, 4>(st, p, grid);
 }
 
 }  // namespace mt

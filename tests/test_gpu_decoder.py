@@ -104,7 +104,8 @@ def attention_fp32(q, k, v, offset):
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("m,hq,hkv,offset", [(1, 64, 8, 0), (1, 64, 8, 5), (1, 64, 8, 127), (1, 64, 8, 128), (1, 64, 8, 1500),
-                                             (1, 32, 8, 4095), (4, 64, 8, 300), (2, 8, 8, 40), (3, 4, 1, 257), (1, 16, 2, 9000)])
+                                             (1, 32, 8, 4095), (4, 64, 8, 300), (2, 8, 8, 40), (3, 4, 1, 257), (1, 16, 2, 9000),
+                                             (1, 16, 2, 13000), (2, 8, 1, 40000)])    # beyond 12288: four-warp CTAs, several clusters
 def test_attention_decode(D, dtype, m, hq, hkv, offset):
     d = 128
     gen = torch.Generator().manual_seed(m + hq + offset)
