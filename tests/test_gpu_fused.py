@@ -254,3 +254,38 @@ def test_status_codes(M):
     assert lib.mt_interleave_gate_up(None, p, p, None, None, p, p, None, None, p, None, p, None, 12, 256, 2, 4) == -3
     assert lib.mt_swiglu(None, p, p, 1, 24, 0) == -3
     assert lib.mt_swiglu(None, p, p, 1, 32, 7) == -4
+
+
+def test_full_size_feed_forward_block(M):
+    """Llama-3-70B feed-forward at full size (8192 -> 2 x 28672 -> 8192), M = 1: the fused two-kernel form against the
+    separate launches of the same library (same weights), and a column slice of the first stage against the oracle."""
+    hidden, inner, bits = 8192, 28672, 4
+    gen = torch.Generator(device=DEV).manual_seed(0)
+
+    def rnd(k, n):
+        qw = torch.randint(-2**31, 2**31 - 1, (k // 8, n), device=DEV, dtype=torch.int64, generator=gen).to(torch.int32)
+        qz = torch.randint(-2**31, 2**31 - 1, (k // 128, n // 8), device=DEV, dtype=torch.int64, generator=gen).to(torch.int32)
+        sc = (0.0005 + 0.001 * torch.rand((k // 128, n), device=DEV, generator=gen)).half()
+        return qw, qz, sc
+    gq, gz, gs = rnd(hidden, inner)
+    uq, uz, us = rnd(hidden, inner)
+    dq, dz, ds = rnd(inner, hidden)
+    x = torch.randn((1, hidden), device=DEV, generator=gen).half()
+    res = torch.randn((1, hidden), device=DEV, generator=gen).half()
+    qw, qz, sc, _ = M.interleave_gate_up((gq, gz, gs, None), (uq, uz, us, None), bits=bits)
+    h = M.quantized_gate_up_swiglu(x, qw, qz, sc, bits=bits)
+    out = M.quantized_matrix_multiply_residual(h, dq, dz, ds, None, res, bits=bits)
+    # the same block as four launches
+    yg = M.quantized_matrix_multiply(x, gq, gz, gs, None, bits=bits)
+    yu = M.quantized_matrix_multiply(x, uq, uz, us, None, bits=bits)
+    h2 = (torch.nn.functional.silu(yg.float()) * yu.float()).half()
+    assert_close(h, h2, "fused activation vs separate linears")
+    out2 = (M.quantized_matrix_multiply(h2, dq, dz, ds, None, bits=bits).float() + res.float()).half()
+    assert_close(out, out2, "fused block vs separate launches")
+    # oracle on gate / up columns 20000 .. 20063
+    lo, hi = 20000, 20064
+    cpu = lambda t: t.cpu()
+    wg = O.dequantize_packed(cpu(gq[:, lo:hi]).contiguous(), None, cpu(gz[:, lo // 8:hi // 8]).contiguous(), cpu(gs[:, lo:hi]).contiguous(), bits)
+    wu = O.dequantize_packed(cpu(uq[:, lo:hi]).contiguous(), None, cpu(uz[:, lo // 8:hi // 8]).contiguous(), cpu(us[:, lo:hi]).contiguous(), bits)
+    ref = O.swiglu(O.qlinear(cpu(x), wg), O.qlinear(cpu(x), wu))
+    assert_close(h[:, lo:hi].cpu(), ref, "fused activation vs oracle slice")
