@@ -319,6 +319,39 @@ def _flag_pdl():
     return _lib.FLAG_PDL
 
 
+def prefill_m4096(dev):
+    """The other half of the headline metric: TFLOP/s of the int4 GEMM at M = 4096 on the prefill shapes
+    (K, N) = (4096, 28672), (14336, 4096), (4096, 6144), against the measured dense bf16 tensor peak.
+    Three weight sets in rotation, 3 warm-up and 10 timed launches per shape, CUDA events."""
+    import minit_b200 as M
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak, kind = (float(json.load(open(path))["bf16_tflops"]), "measured cuBLAS bf16 burst") if os.path.exists(path) else (1590.0, "fallback")
+    gen = torch.Generator(device=dev).manual_seed(99)
+    mrows, shapes = 4096, []
+    for k, n in [(4096, 28672), (14336, 4096), (4096, 6144)]:
+        sets = []
+        for _ in range(3):
+            qw = torch.randint(-2**31, 2**31 - 1, (k // 8, n), device=dev, dtype=torch.int64, generator=gen).to(torch.int32)
+            qz = torch.randint(-2**31, 2**31 - 1, (k // GROUP, n // 8), device=dev, dtype=torch.int64, generator=gen).to(torch.int32)
+            sc = (0.002 + 0.018 * torch.rand((k // GROUP, n), device=dev, generator=gen)).half()
+            sets.append((qw, qz, sc))
+        x = torch.randn((mrows, k), device=dev, generator=gen).half()
+        out = torch.empty((mrows, n), device=dev, dtype=torch.float16)
+        for i in range(3):
+            M.quantized_matrix_multiply(x, *sets[i % 3], None, bits=BITS, out=out)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(10):
+            M.quantized_matrix_multiply(x, *sets[i % 3], None, bits=BITS, out=out)
+        e1.record()
+        torch.cuda.synchronize()
+        tf = 2.0 * mrows * n * k * 10 / (e0.elapsed_time(e1) * 1e-3) / 1e12
+        shapes.append({"k": k, "n": n, "tflops": tf, "frac": tf / peak})
+        del sets, x, out
+    return {"m": mrows, "bound": "tensor", "unit": "TFLOP/s", "peak": peak, "peak_source": kind, "shapes": shapes}
+
+
 def run_ours(args):
     import torch.distributed as dist
     import minit_b200 as M
@@ -456,6 +489,8 @@ def run_ours(args):
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }
+    if rank == 0 and world == 1 and m == 1 and not args.no_prefill:
+        line["prefill_m4096"] = prefill_m4096(dev)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(budget_s=20.0)
     if world > 1:
@@ -593,6 +628,7 @@ def main():
     ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
                     help="row-parallel exchange: fused into the GEMM epilogue over peer memory, or an NCCL all-reduce after it")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the M = 4096 TFLOP/s measurement of the default one-GPU run")
     ap.add_argument("--single-shape", default=None, help="K,N : time one linear instead of the workload (profiling aid)")
     ap.add_argument("--mlp-block", action="store_true", help="time the feed-forward block with separate and with fused elementwise steps")
     ap.add_argument("--decode-layer", action="store_true", help="time whole decoder layers (norms, rope, attention, fused linears) for one token")
