@@ -520,10 +520,26 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
         it_ptr += rstride;
         if (--it_rows == 0) { ++it_tile; it_ptr = qbase + (size_t)it_tile * (VEC_COLS / 4); it_rows = p.nchunks * CRW; }
     };
+    // RG consecutive rows at once: when they lie in one column block and are all valid (almost always) the
+    // addresses are base + r * stride and the bookkeeping runs once per group instead of once per row
+    const uint32_t rstride_b = uint32_t(p.n) * 4u;        // bytes between packed rows
+    auto issue_group = [&](int slot0) {
+        if (it_rows > RG && issued + RG <= total_rows) {
+            const char* base = reinterpret_cast<const char*>(it_ptr);
+#pragma unroll
+            for (int r = 0; r < RG; ++r)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ring_s + uint32_t(slot0 + r) * SLOT_BYTES),
+                             "l"(base + (unsigned long long)(uint32_t(r) * rstride_b)) : "memory");
+            issued += RG; it_rows -= RG;
+            it_ptr = reinterpret_cast<const uint4*>(base + (unsigned long long)(uint32_t(RG) * rstride_b));
+        } else {
+#pragma unroll
+            for (int r = 0; r < RG; ++r) issue(slot0 + r);
+        }
+    };
 #pragma unroll
     for (int gq = 0; gq < NG; ++gq) {
-#pragma unroll
-        for (int r = 0; r < RG; ++r) issue(gq * RG + r);
+        issue_group(gq * RG);
         cp_async_commit();
     }
 
@@ -708,8 +724,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
             }
             if (rb % RG == RG - 1) {
                 // the four rows of this group are in registers: refill their slots
-#pragma unroll
-                for (int r = 0; r < RG; ++r) issue((rb - (RG - 1) + r) % D);
+                issue_group((rb - (RG - 1)) % D);
                 cp_async_commit();
             }
             if (rr == RPK - 1 && (kj + 1) % CKS == 0) {
