@@ -352,6 +352,64 @@ def prefill_m4096(dev):
     return {"m": mrows, "bound": "tensor", "unit": "TFLOP/s", "peak": peak, "peak_source": kind, "shapes": shapes}
 
 
+def parity_check(world, rank, dev, far, comm, ms=(1, 8)):
+    """Outside the timed region, at every N: one row-parallel linear of each kind (o, down) of the workload at
+    M = 1 and M = 8 through the same call the timed step makes (the fused GEMM + all-reduce, the NCCL all-reduce
+    after the GEMM, or the plain GEMM on one GPU), on seeded UNSHARDED weights that every rank generates
+    identically on the host and slices on K by rank (minit/collective/dispatch.py:33-37,
+    minit/collective/tensor.py:72-73).  A 512-column slice of every rank's output is compared with the oracle's
+    dequantize-then-matmul of the unsharded weight (max |err| <= 1e-2 * rms, the test suite's bound), and the
+    outputs of all ranks must be bit-identical.  The oracle is only the checker here."""
+    import torch.distributed as dist
+    import minit_b200 as M
+    from minit_b200.collective.quantized import shard_gptq_row
+    from oracle import qlinear_oracle as O
+    cols = slice(1024, 1536)
+    res = {"cases": [], "ok": True, "bound": "max|out - ref| <= 1e-2 * rms(ref) on 512 columns; outputs identical on all ranks"}
+    for name, k, n in (("o", HIDDEN, HIDDEN), ("down", INTER, HIDDEN)):
+        gen = torch.Generator().manual_seed(4242 + k)
+        g = k // GROUP
+        qw = torch.randint(-2**31, 2**31 - 1, (k // 8, n), generator=gen, dtype=torch.int64).to(torch.int32)
+        qz = torch.randint(-2**31, 2**31 - 1, (g, n // 8), generator=gen, dtype=torch.int64).to(torch.int32)
+        sc = (0.002 + 0.018 * torch.rand((g, n), generator=gen)).half()
+        w_ref = O.dequantize_packed(qw[:, cols].contiguous(), None, qz[:, cols.start // 8:cols.stop // 8].contiguous(),
+                                    sc[:, cols].contiguous(), BITS)
+        sqw, sqz, ssc, _ = shard_gptq_row(qw, qz, sc, BITS, rank, world)
+        sqw, sqz, ssc = sqw.to(dev), sqz.to(dev), ssc.to(dev)
+        for m in ms:
+            x = torch.randn((m, k), generator=gen).half()
+            ref = O.qlinear(x, w_ref)
+            xs = x[:, k // world * rank:k // world * (rank + 1)].contiguous().to(dev)
+            if world > 1 and far is not None:
+                out = far.matmul(xs, sqw, sqz, ssc, None, bits=BITS)
+            else:
+                out = M.quantized_matrix_multiply(xs, sqw, sqz, ssc, None, bits=BITS)
+                if world > 1:
+                    from minit_b200.nccl.dispatch import all_reduce_
+                    all_reduce_(comm.version, out)
+            torch.cuda.synchronize()
+            ok, err, bound = O.tolerance_ok(out[:, cols], ref, 1e-2)
+            same = True
+            if world > 1:
+                gathered = [torch.empty_like(out) for _ in range(world)]
+                dist.all_gather(gathered, out)
+                same = all(torch.equal(gathered[0], t) for t in gathered[1:])
+                flag = torch.tensor([0 if (ok and same) else 1], device=dev)
+                dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+                ok = ok and int(flag.item()) == 0
+            res["cases"].append({"linear": name, "k": k, "n": n, "m": m, "max_err": err, "bound": bound, "ranks_identical": same})
+            res["ok"] = res["ok"] and ok and same
+        del sqw, sqz, ssc
+    return res
+
+
+def error_words():
+    """Non-zero error words of this process's workspaces: a bounded wait inside a kernel expired."""
+    from minit_b200 import _lib
+    torch.cuda.synchronize()
+    return [w for w in (_lib.workspace_error_word(ws) for ws in _lib._workspaces.values()) if w != 0]
+
+
 def run_ours(args):
     import torch.distributed as dist
     import minit_b200 as M
@@ -460,6 +518,20 @@ def run_ours(args):
     e2e_runner, e2e_mode = make_runner(one_pass_e2e)
     ms_e2e, _ = timed(e2e_runner, args.steps, args.warmup)
 
+    # correctness evidence beside the timing, at every N: no bounded wait expired during the timed steps, and the
+    # row-parallel linears (with their all-reduce) reproduce the oracle on unsharded weights
+    words_timed = error_words()
+    parity = parity_check(world, rank, dev, far, comm)
+    parity["error_words_after_timed_steps"] = words_timed
+    bad_words = words_timed + error_words()
+    if world > 1:
+        t = torch.tensor([len(bad_words)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        parity["error_word_any_rank"] = int(t.item())
+        parity["ok"] = parity["ok"] and int(t.item()) == 0
+    else:
+        parity["ok"] = parity["ok"] and not bad_words
+
     per_rank_wbytes = args.layers * sum(weight_bytes(k, n) for _, k, n, _ in shapes)
     per_rank_abytes = args.layers * sum(algorithmic_bytes(m, k, n) for _, k, n, _ in shapes)
     total_wbytes = per_rank_wbytes * world
@@ -488,6 +560,7 @@ def run_ours(args):
                 "note": "weights stay resident (loaded once, like model parameters); activations cross PCIe every step"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
+        "parity_check": parity,
     }
     if rank == 0 and world == 1 and m == 1 and not args.no_prefill:
         line["prefill_m4096"] = prefill_m4096(dev)
@@ -498,6 +571,8 @@ def run_ours(args):
         dist.destroy_process_group()
     if rank == 0:
         print(json.dumps(line))
+    if not parity["ok"]:
+        raise SystemExit("parity check failed: " + json.dumps(parity))
 
 
 # ---------------------------------------------------------------------------------------

@@ -31,6 +31,10 @@
 #include "tma.cuh"
 #include "tcgen05.cuh"
 
+#ifndef MT_UM_PSTAGES4
+#define MT_UM_PSTAGES4 8
+#endif
+
 namespace mt {
 namespace {
 
@@ -85,7 +89,7 @@ __device__ __forceinline__ bool um_wait(uint32_t bar, uint32_t parity, volatile 
 template <int BITS, int BM> struct UmSmem {
     static constexpr int PROWS = 64 / (32 / BITS);                    // packed rows per k-block: 8 | 16
     static constexpr int P_BYTES = PROWS * UM_COLS * 4;               // packed words of one k-block of the CTA tile: 8 | 16 KB
-    static constexpr int PSTAGES = BITS == 4 ? 8 : 4;                 // 64 KB of packed weights in flight per SM
+    static constexpr int PSTAGES = BITS == 4 ? MT_UM_PSTAGES4 : 4;                 // 64 KB of packed weights in flight per SM
     static constexpr int B_BYTES = BM * 128;                          // one B tile: BM rows x 64 k
     static constexpr int OFF_P = 0;
     static constexpr int OFF_B = OFF_P + PSTAGES * P_BYTES;

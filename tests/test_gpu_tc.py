@@ -58,3 +58,33 @@ def test_tc_prefill_shape_4096(M):
     w = O.dequantize_packed(c["qweight"], None, c["qzeros"], c["scales"], 4)
     for r0 in (0, 2000, 3968):
         assert_close(out[r0:r0 + 128], O.qlinear(c["x"][r0:r0 + 128], w), f"prefill rows {r0}")
+
+
+# The prefill config's other shapes at every batch size it names, in both dtypes.  One case per
+# (shape, dtype) is built at the largest M and its leading rows serve the smaller ones; the oracle
+# checks three 128-row blocks of each output to bound CPU time.
+_PREFILL_CASES = {}
+
+
+def _prefill_case(k, n, dtype):
+    key = (k, n, dtype)
+    if key not in _PREFILL_CASES:
+        _PREFILL_CASES.clear()                      # one resident case at a time (hundreds of MB each)
+        c = O.make_gptq_case(k, n, 8192, bits=4, dtype=dtype, seed=k + n)
+        c.pop("q"); c.pop("z")
+        c["w"] = O.dequantize_packed(c["qweight"], None, c["qzeros"], c["scales"], 4)
+        _PREFILL_CASES[key] = c
+    return _PREFILL_CASES[key]
+
+
+@pytest.mark.parametrize("m", [2048, 4096, 8192])       # the top decorator varies fastest: a case is built once
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("k,n", [(4096, 28672), (14336, 4096)])
+def test_tc_prefill_config_shapes(M, k, n, dtype, m):
+    c = _prefill_case(k, n, dtype)
+    d = {key: val for key, val in c.items() if key != "w"}
+    d["x"] = c["x"][:m].contiguous()
+    out = run(M, d, 4, flags=0).cpu()                 # default dispatch: what a caller of this config gets
+    assert tuple(out.shape) == (m, n)
+    for r0 in (0, m // 2 - 64, m - 128):
+        assert_close(out[r0:r0 + 128], O.qlinear(d["x"][r0:r0 + 128], c["w"]), f"prefill {k}x{n} M={m} {dtype} rows {r0}")
