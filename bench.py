@@ -664,7 +664,7 @@ def run_single_shape(args):
         sets.append((qw, qz, sc))
     x = torch.randn((m, k), device=dev, dtype=torch.float32).to(dtype)
     out = torch.empty((m, n), device=dev, dtype=dtype)
-    flags = {"auto": 0, "ring": 1, "tc": 2, "dtc": 8, "vec": 16, "umma": 32}[args.kernel] | (4 if args.pdl and args.kernel in ("auto", "ring", "vec") else 0) | args.tune
+    flags = {"auto": 0, "ring": 1, "tc": 2, "vec": 16, "umma": 32}[args.kernel] | (4 if args.pdl and args.kernel in ("auto", "ring", "vec") else 0)
 
     def one():
         for qw, qz, sc in sets:
@@ -709,8 +709,7 @@ def main():
     ap.add_argument("--decode-layer", action="store_true", help="time whole decoder layers (norms, rope, attention, fused linears) for one token")
     ap.add_argument("--attention", action="store_true", help="time decode attention alone over --context cached positions")
     ap.add_argument("--context", type=int, default=4096, help="--decode-layer: cached positions")
-    ap.add_argument("--tune", type=lambda v: int(v, 0), default=0, help="single-shape mode: extra tuning bits ORed into the flags")
-    ap.add_argument("--kernel", default="auto", choices=["auto", "ring", "dtc", "tc", "vec", "umma"])
+    ap.add_argument("--kernel", default="auto", choices=["auto", "ring", "tc", "vec", "umma"])
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--bf16", action="store_true")
     args = ap.parse_args()

@@ -32,6 +32,7 @@ extern "C" {
 #define MT_ERR_DEVICE        -9  /* the current device is not compute capability 10.x */
 #define MT_ERR_TOO_LARGE    -10  /* request exceeds a fixed built-in capacity */
 #define MT_ERR_NCCL         -11  /* the NCCL library reported an error or could not be loaded */
+#define MT_ERR_PEER_TIMEOUT -12  /* read back from a workspace error word: a bounded device-side wait expired, the output is not valid */
 
 /* dtype of x / scales / bias / out */
 #define MT_F16   0
@@ -41,13 +42,14 @@ extern "C" {
 #define MT_FLAG_NONE         0
 #define MT_FLAG_FORCE_SMALL  1   /* always use the register-ring streaming kernel (tiles M by 64) */
 #define MT_FLAG_FORCE_TC     2   /* always use the tcgen05 kernel */
-#define MT_FLAG_FORCE_DTC    8   /* always use the tcgen05 decode kernel (M <= 16, contiguous groups) */
 #define MT_FLAG_FORCE_UMMA  32   /* always use the mid-batch tcgen05 kernel (all warps dequantize; contiguous groups, group size % 64 == 0) */
 #define MT_FLAG_FORCE_VEC   16   /* always use the CUDA-core decode GEMV (M <= 2, contiguous groups, N % 128 == 0) */
 #define MT_FLAG_SPLITS(s)   (((s) & 0xff) << 16)   /* tuning: force the split-K factor of the decode GEMV */
 #define MT_FLAG_PDL          4   /* launch with programmatic stream serialization: the kernel starts
                                     fetching weights before the previous kernel in the stream ends and
                                     waits for it only before touching x / out / workspace */
+#define MT_FLAG_AR_SHORT_WAIT 64 /* fused all-reduce: give up on a peer after ~4 thousand polls (a fraction of a
+                                    millisecond) instead of ~4 million; for tests of the time-out path */
 
 /* Library version: major*10000 + minor*100 + patch. */
 int mt_version(void);
@@ -238,8 +240,13 @@ int mt_decode_plan(int m, int n, int k, int nr_groups, int bits, size_t workspac
  * a decode loop.  Every GPU that loads the library holds the array until the process exits.
  *   - Limit: refused with MT_ERR_TOO_LARGE when mt_workspace_bytes(m, n, k, bits) exceeds
  *     MT_STATIC_SCRATCH_BYTES (e.g. int4 K = N = 8192 fits, K = 8192 x N = 57344 does not).
- *   - The first call on a device looks up the array's device address; make that first call
- *     before starting any stream capture on that device.
+ *   - The first call on a device looks up the array's device address.  With CUDA's default lazy
+ *     module loading that look-up is also the moment the driver loads the module that holds the
+ *     array and reserves its MT_STATIC_SCRATCH_BYTES on that device (under
+ *     CUDA_MODULE_LOADING=EAGER this happens when the library is loaded instead).  So make one
+ *     call per device at start-up: BEFORE the host claims the remaining device memory for its
+ *     own pool (afterwards the reservation would fail and the call returns MT_ERR_CUDA) and
+ *     before starting any stream capture on that device.  Later calls reserve nothing.
  *   - All calls on a device share the one array (it keeps the previous call's contents; the
  *     part that must start at zero is cleared on `stream` by each call).  Two calls that can
  *     overlap on the GPU -- different streams, no dependency -- race on it: serialise them.

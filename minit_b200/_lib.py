@@ -22,7 +22,8 @@ if not os.path.exists(LIB_PATH):
 lib = ctypes.CDLL(LIB_PATH)
 
 MT_F16, MT_BF16 = 0, 1
-FLAG_FORCE_SMALL, FLAG_FORCE_TC, FLAG_PDL, FLAG_FORCE_DTC, FLAG_FORCE_VEC, FLAG_FORCE_UMMA = 1, 2, 4, 8, 16, 32
+FLAG_FORCE_SMALL, FLAG_FORCE_TC, FLAG_PDL, FLAG_FORCE_VEC, FLAG_FORCE_UMMA, FLAG_AR_SHORT_WAIT = 1, 2, 4, 16, 32, 64
+ERR_PEER_TIMEOUT = -12
 COUNTER_BYTES = 16384
 STATIC_SCRATCH_BYTES = 8 << 20
 
@@ -131,5 +132,25 @@ def workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
 
 
 def workspace_error_word(ws: torch.Tensor) -> int:
-    """Error word the tcgen05 kernel sets when one of its bounded waits expires (test aid)."""
+    """Error word a kernel sets when one of its bounded waits expires (4: a peer's all-reduce cells never arrived,
+    5: an mbarrier wait of a tensor-core kernel).  Reading it synchronises with the device."""
     return int(ws[COUNTER_BYTES - 4:COUNTER_BYTES].view(torch.int32).item())
+
+
+def raise_on_error_words(clear: bool = True) -> None:
+    """Check the error word of every workspace of this process and raise ``MinitError`` (status
+    ``ERR_PEER_TIMEOUT``) if a bounded device-side wait expired since the last check: the outputs of the
+    calls in between are not valid (after an expired all-reduce wait the ranks no longer hold the same
+    values).  It reads device memory, so call it where the host synchronises anyway -- after the read-back
+    of a step's result, at the end of a benchmark step -- not per linear."""
+    bad = []
+    for key, ws in _workspaces.items():
+        word = workspace_error_word(ws)
+        if word:
+            bad.append((key, word))
+            if clear:
+                ws[COUNTER_BYTES - 4:COUNTER_BYTES].zero_()
+    if bad:
+        err = MinitError(ERR_PEER_TIMEOUT, "bounded device-side wait")
+        err.words = bad
+        raise err

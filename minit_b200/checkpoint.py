@@ -87,13 +87,19 @@ def save_safetensors(path: str, tensors: Dict[str, torch.Tensor], metadata: Opti
 
 
 def _assign(model: Module, name: str, array: torch.Tensor, epilogue, device) -> None:
+    """Cast to the buffer's dtype, check the FULL checkpoint shape against the buffer, then hand the tensor to the
+    epilogue and store whatever it returns -- the order of the reference (minit/module/checkpoint.py:30-36), whose
+    tensor-parallel servers shard inside the epilogue (examples/llama3_70b.py:298-310): the result may be a
+    ``CollectiveTensor`` or a torch shard whose shape differs from the declared buffer."""
     spec_shape, spec_dtype = _buffer_spec(model, name)
     from .module import _DTYPES
     array = array.to(_DTYPES[spec_dtype])
-    array = epilogue(name, array)
     if tuple(array.shape) != tuple(spec_shape):
         raise ValueError(f"{name}: checkpoint shape {tuple(array.shape)} vs buffer {tuple(spec_shape)}")
-    model.update_buffer(name, array.to(device))
+    value = epilogue(name, array)
+    if isinstance(value, torch.Tensor):
+        value = value.to(device)
+    model.update_buffer(name, value, sharded=not (isinstance(value, torch.Tensor) and tuple(value.shape) == tuple(spec_shape)))
 
 
 def _buffer_spec(model: Module, name: str):

@@ -40,6 +40,13 @@ class FusedAllReduce:
         torch.cuda.synchronize()
         dist.barrier(group)   # every rank's buffer is zeroed before anyone's first kernel can raise a flag in it
 
+    @staticmethod
+    def check() -> None:
+        """Raise ``MinitError`` (``MT_ERR_PEER_TIMEOUT``) if a fused all-reduce since the last check gave up waiting
+        for a peer: its output, and everything computed from it, is not valid and differs between ranks.  Reads
+        device memory (synchronises): call it where the host waits for the step anyway."""
+        _lib.raise_on_error_words()
+
     def matmul(self, x, qweight, zeros, scales, groups, *, bits: int, bias=None, out=None, flags: int = 0, residual=None):
         """out = sum over ranks of x_r @ W_r (+ bias) (+ residual, the same tensor on every rank), identical on
         every rank, in one kernel per rank."""

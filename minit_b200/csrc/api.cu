@@ -172,6 +172,7 @@ const char* mt_strerror(int status) {
         case MT_ERR_DEVICE: return "the current device is not compute capability 10.x (B200)";
         case MT_ERR_TOO_LARGE: return "the request exceeds a fixed built-in capacity";
         case MT_ERR_NCCL: return "NCCL reported an error or could not be loaded";
+        case MT_ERR_PEER_TIMEOUT: return "a bounded wait inside a kernel expired (a peer rank was late or absent); the output is not valid";
     }
     return "unknown status";
 }
@@ -256,7 +257,6 @@ int mt_qgemm(void* stream, const void* x, const uint32_t* qweight, const int32_t
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (flags & MT_FLAG_FORCE_TC) return tc_supported(a) ? launch_tc(st, a) : MT_ERR_UNSUPPORTED;
     if (flags & MT_FLAG_FORCE_SMALL) return launch_small(st, a);
-    if (flags & MT_FLAG_FORCE_DTC) return dtc_supported(a) ? launch_dtc(st, a) : MT_ERR_UNSUPPORTED;
     if (flags & MT_FLAG_FORCE_VEC) return vec_supported(a) ? launch_vec(st, a) : MT_ERR_UNSUPPORTED;
     if (flags & MT_FLAG_FORCE_UMMA) return umma_supported(a) ? launch_umma(st, a) : MT_ERR_UNSUPPORTED;
     // Mid-size batches: the tcgen05 kernel with sixteen converting warps holds 0.24-0.31 of HBM peak up to
@@ -332,7 +332,7 @@ int mt_qgemm_residual(void* stream, const void* x, const uint32_t* qweight, cons
     // one rank: any batch size.  The decode GEMV adds the residual in its epilogue; every other kernel is
     // followed by one elementwise launch.
     if (!aligned16(residual)) return MT_ERR_ALIGN;
-    const bool forced_other = (flags & (MT_FLAG_FORCE_SMALL | MT_FLAG_FORCE_TC | MT_FLAG_FORCE_DTC | MT_FLAG_FORCE_UMMA)) != 0;
+    const bool forced_other = (flags & (MT_FLAG_FORCE_SMALL | MT_FLAG_FORCE_TC | MT_FLAG_FORCE_UMMA)) != 0;
     if (m >= 1 && m <= 2 && !forced_other && !g_idx)
         return qgemm_allreduce_impl(stream, x, qweight, g_idx, qzeros, scales, bias, residual, out, m, n, k, nr_groups, bits, dtype,
                                     workspace, workspace_bytes, flags, nullptr, 0, 1, 0);
@@ -358,7 +358,7 @@ int mt_qgemm_swiglu(void* stream, const void* x, const uint32_t* qweight, const 
     a.x = x; a.qweight = qweight; a.qzeros = qzeros; a.scales = scales; a.bias = bias; a.out = out;
     a.m = m; a.n = n; a.k = k; a.groups = nr_groups; a.bits = bits; a.dtype = dtype;
     a.workspace = workspace; a.workspace_bytes = workspace_bytes; a.flags = flags;
-    const bool forced_other = (flags & (MT_FLAG_FORCE_SMALL | MT_FLAG_FORCE_TC | MT_FLAG_FORCE_DTC | MT_FLAG_FORCE_UMMA)) != 0;
+    const bool forced_other = (flags & (MT_FLAG_FORCE_SMALL | MT_FLAG_FORCE_TC | MT_FLAG_FORCE_UMMA)) != 0;
     if (m <= 2 && !forced_other && vec_supported(a)) {
         a.epilogue = MT_EPILOGUE_SWIGLU;
         return launch_vec(st, a);
@@ -447,7 +447,7 @@ int mt_qgemm_rope_append(void* stream, const void* x, const uint32_t* qweight, c
     a.x = x; a.qweight = qweight; a.qzeros = qzeros; a.scales = scales; a.bias = bias; a.out = q_out;
     a.m = m; a.n = n; a.k = k; a.groups = nr_groups; a.bits = bits; a.dtype = dtype;
     a.workspace = workspace; a.workspace_bytes = workspace_bytes; a.flags = flags;
-    const bool forced_other = (flags & (MT_FLAG_FORCE_SMALL | MT_FLAG_FORCE_TC | MT_FLAG_FORCE_DTC | MT_FLAG_FORCE_UMMA)) != 0;
+    const bool forced_other = (flags & (MT_FLAG_FORCE_SMALL | MT_FLAG_FORCE_TC | MT_FLAG_FORCE_UMMA)) != 0;
     if (m <= 2 && !forced_other && vec_supported(a)) {
         RopeArgs r;
         r.cosv = cos_table; r.sinv = sin_table; r.q_out = q_out; r.k_cache = k_cache; r.v_cache = v_cache; r.offset_dev = offset_dev;
@@ -561,7 +561,7 @@ int mt_qgemm_ordered(void* stream, const void* x, const int32_t* x_perm, void* x
     a.m = m; a.n = n; a.k = k; a.groups = nr_groups; a.bits = bits; a.dtype = dtype;
     a.workspace = workspace; a.workspace_bytes = workspace_bytes; a.flags = flags;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const bool forced_other = (flags & (MT_FLAG_FORCE_SMALL | MT_FLAG_FORCE_TC | MT_FLAG_FORCE_DTC)) != 0;
+    const bool forced_other = (flags & (MT_FLAG_FORCE_SMALL | MT_FLAG_FORCE_TC | MT_FLAG_FORCE_UMMA)) != 0;
     if (m <= 2 && !forced_other && vec_supported(a)) {          // the GEMV gathers while it stages the activations
         a.x_perm = x_perm;
         return launch_vec(st, a);

@@ -33,6 +33,7 @@ struct ArParams {
     unsigned* err;                 // error word: set to 4 when a peer's cells never arrive
     int rank, world;
     size_t slot_bytes;             // bytes of one (parity, sender) mailbox
+    int spin_limit;                // polls per peer before the wait gives up (2^22: 0.1 s to a few seconds)
 };
 
 __device__ __forceinline__ bool ar_active(const ArParams& a) { return a.world > 1; }
@@ -64,7 +65,7 @@ __device__ __forceinline__ float4 ar_exchange(const ArParams& a, unsigned epoch,
             asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(c0.x), "=r"(c0.y), "=r"(c0.z), "=r"(c0.w) : "l"(src) : "memory");
             asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(c1.x), "=r"(c1.y), "=r"(c1.z), "=r"(c1.w) : "l"(src + 16) : "memory");
             if (c0.y == epoch && c0.w == epoch && c1.y == epoch && c1.w == epoch) break;
-            if (++spins > (1 << 22)) { if (a.err) atomicExch(a.err, 4u); break; }   // a peer never arrived: give up, flag the error
+            if (++spins > a.spin_limit) { if (a.err) atomicExch(a.err, 4u); break; }   // a peer never arrived: give up, flag the error (the host must read it)
             if (spins > 32) __nanosleep(32);
         }
         sum.x += __uint_as_float(c0.x); sum.y += __uint_as_float(c0.z); sum.z += __uint_as_float(c1.x); sum.w += __uint_as_float(c1.z);

@@ -170,6 +170,7 @@ inline ArParams make_ar_params(const QGemmArgs& a) {
     r.peers = a.ar_peers; r.rank = a.ar_rank; r.world = a.ar_peers ? a.ar_world : 1;
     r.err = a.workspace ? static_cast<unsigned*>(a.workspace) + (kMaxTiles - 1) : nullptr;
     r.slot_bytes = (a.ar_peers && a.ar_world > 0) ? ((a.ar_bytes - kArDataOffset) / (2 * (size_t)a.ar_world)) & ~(size_t)255 : 0;
+    r.spin_limit = (a.flags & MT_FLAG_AR_SHORT_WAIT) ? (1 << 12) : (1 << 22);
     return r;
 }
 
@@ -186,8 +187,6 @@ int launch_small(cudaStream_t st, const QGemmArgs& a);          // GPTQ layout, 
 int launch_small_w8(cudaStream_t st, const QGemmArgs& a);       // int8 [K,N] per-channel, M <= 64 per launch
 int launch_w8vec(cudaStream_t st, const QGemmArgs& a);          // int8 [K,N] per-channel, CUDA-core GEMV, M <= 2, N % 256 == 0
 bool w8vec_supported(const QGemmArgs& a);
-int launch_dtc(cudaStream_t st, const QGemmArgs& a);            // tcgen05 decode kernel, M <= 32, contiguous groups
-bool dtc_supported(const QGemmArgs& a);
 int launch_vec(cudaStream_t st, const QGemmArgs& a);            // CUDA-core decode GEMV, M <= 2, contiguous groups
 bool vec_supported(const QGemmArgs& a);
 int vec_plan(const QGemmArgs& a);                               // > 0 split-K factor, 0 stream-K, < 0 MT_ERR_*

@@ -6,8 +6,11 @@
 // device synchronisation cudaMalloc/cudaFree bring with them.  Such a caller can still own
 // x, the weights and out (they come from its pool) but has no way to size and allocate the
 // split-K scratch mt_qgemm asks for.  Here that scratch is a fixed array inside this library:
-// every GPU that loads the library carries MT_STATIC_SCRATCH_BYTES of it until the process
-// exits, whether or not this entry point is ever called.
+// every GPU on which the module of this file is loaded carries MT_STATIC_SCRATCH_BYTES of it
+// until the process exits.  The driver loads that module at library load under
+// CUDA_MODULE_LOADING=EAGER and, with the default lazy loading, at the first call of this
+// entry point on the device (the symbol look-up below): that first call is the one that
+// reserves the bytes, so it belongs at start-up, before the host's pool takes what is left.
 //
 // How the array is addressed: in host code the name `g_static_scratch` is only the host-side
 // handle of the device symbol, not a device address.  The device address is obtained once

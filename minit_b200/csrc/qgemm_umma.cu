@@ -31,10 +31,6 @@
 #include "tma.cuh"
 #include "tcgen05.cuh"
 
-#ifndef MT_UM_PSTAGES4
-#define MT_UM_PSTAGES4 8
-#endif
-
 namespace mt {
 namespace {
 
@@ -64,17 +60,6 @@ struct UmParams {
 // Bounded wait that does not poll: mbarrier.try_wait with a suspend-time hint parks the thread until the
 // phase completes or the hint expires, so waiting warps leave the issue slots to the converters.
 __device__ __forceinline__ bool um_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-#ifdef UM_SPIN
-    for (int i = 0; i < (1 << 26); ++i) {
-        uint32_t ok;
-        asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}"
-                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if ((i & 4095) == 4095 && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    return false;
-#endif
     for (int i = 0; i < (1 << 20); ++i) {                // ~1 us per turn: gives up after about a second
         uint32_t ok;
         asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.b32 %0, 1, 0, p;\n}"
@@ -89,7 +74,7 @@ __device__ __forceinline__ bool um_wait(uint32_t bar, uint32_t parity, volatile 
 template <int BITS, int BM> struct UmSmem {
     static constexpr int PROWS = 64 / (32 / BITS);                    // packed rows per k-block: 8 | 16
     static constexpr int P_BYTES = PROWS * UM_COLS * 4;               // packed words of one k-block of the CTA tile: 8 | 16 KB
-    static constexpr int PSTAGES = BITS == 4 ? MT_UM_PSTAGES4 : 4;                 // 64 KB of packed weights in flight per SM
+    static constexpr int PSTAGES = BITS == 4 ? 8 : 4;                 // 64 KB of packed weights in flight per SM
     static constexpr int B_BYTES = BM * 128;                          // one B tile: BM rows x 64 k
     static constexpr int OFF_P = 0;
     static constexpr int OFF_B = OFF_P + PSTAGES * P_BYTES;
@@ -151,21 +136,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_a = tmem_base + S::D_COLS;
-#ifdef MT_UMMA_TIMING
-    long long tw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    int tslot = 0;
-    const long long t_begin = clock64();
-    auto wait = [&](uint32_t bar, uint32_t parity) {
-        const long long t0 = clock64();
-        const bool r = um_wait(bar, parity, &abort_flag);
-        tw[tslot] += clock64() - t0;
-        return r;
-    };
-#define UM_SLOT(n) tslot = n
-#else
     auto wait = [&](uint32_t bar, uint32_t parity) { return um_wait(bar, parity, &abort_flag); };
-#define UM_SLOT(n)
-#endif
 
     // first / last CTA with a unit in column tile t
     auto owner = [&](int u) -> int {
@@ -185,7 +156,6 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
 #pragma unroll
                 for (int pr = 0; pr < UM_NPAIR; ++pr) {          // slot indices are static: addresses and descriptors fold to constants
                     if (i0 + 2 * pr >= nrun || !ok) break;
-                    UM_SLOT(2);
                     if (!wait(bar_afull(pr), aph)) { ok = false; break; }
                     tc_fence_after();
 #pragma unroll
@@ -196,11 +166,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
                         const bool first = (i == 0) || (kb == 0);
                         const bool last = (i == nrun - 1) || (kb == p.kbt - 1);
                         kb = (kb + 1 == p.kbt) ? 0 : kb + 1;
-                        UM_SLOT(0);
                         if (first) { if (!wait(bar_dempty, (seg & 1) ^ 1)) { ok = false; break; } tc_fence_after(); }
-#ifdef MT_UMMA_TIMING
-                        const long long t_m0 = clock64();
-#endif
                         const uint64_t bdesc = tc_desc_sw128(sbase + S::OFF_B + as * S::B_BYTES);
 #pragma unroll
                         for (int k4 = 0; k4 < 4; ++k4)
@@ -208,19 +174,10 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
                             for (int nt = 0; nt < UM_NT; ++nt)
                                 tc_mma_ts(tmem_base + (uint32_t)(nt * BM), tmem_a + (uint32_t)((as * UM_NT + nt) * 32 + k4 * 8),
                                           bdesc + (uint64_t)(k4 * 2), idesc, (first && k4 == 0) ? 0u : 1u);
-#ifdef MT_UMMA_TIMING
-                        tw[3] += clock64() - t_m0;
-#endif
                         if (last) { tc_commit(bar_dfull); ++seg; }
                     }
                     if (!ok) break;
-#ifdef MT_UMMA_TIMING
-                    const long long t_m1 = clock64();
-#endif
                     tc_commit(bar_aempty(pr));           // frees the A and B slots of both k-blocks
-#ifdef MT_UMMA_TIMING
-                    tw[4] += clock64() - t_m1;
-#endif
                 }
             }
         }
@@ -279,7 +236,6 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
             asm volatile("cp.async.wait_group %0;" ::"n"(AHEAD - 1) : "memory");
             const int bs = i % UM_BSTAGES; const uint32_t bph = (i / UM_BSTAGES) & 1;
             const int pr = bs >> 1;
-            UM_SLOT(0);
             if (!wait(bar_aempty(pr), bph ^ 1)) { ok = false; break; }
             if (i >= nrun) { __syncwarp(); if (lane == 0) mbar_arrive(bar_afull(pr)); continue; }
             unsigned char* tile_s = smem + S::OFF_B + bs * S::B_BYTES;
@@ -359,7 +315,6 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
         // the finished part of a column tile: stored, or handed over as an fp32 partial tile.  The sixteen warps
         // split the accumulator: group -> (128-column tile, half of the batch rows).
         auto epilogue = [&](int tile) {
-            UM_SLOT(1);
             if (!wait(bar_dfull, seg & 1)) { ok = false; return; }
             tc_fence_after();
             const int nt = grp & 1;
@@ -439,7 +394,6 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
                 for (int nt = 0; nt < UM_NT; ++nt) { sr_n[d][nt] = sr_n[d + 1][nt]; zr_n[d][nt] = zr_n[d + 1][nt]; }
             fetch(sr_n[SZ - 1], zr_n[SZ - 1]);
             const int ps = i % S::PSTAGES; const uint32_t pph = (i / S::PSTAGES) & 1;
-            UM_SLOT(3);
             if (!wait(bar_pfull(ps), pph)) { ok = false; break; }
             const uint32_t* pk = reinterpret_cast<const uint32_t*>(smem + S::OFF_P + ps * S::P_BYTES) + cl;
             uint32_t wq[UM_NT][PROWS];
@@ -485,7 +439,6 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
                     }
                 }
                 if (!waited) {
-                    UM_SLOT(0);
                     if (!wait(bar_aempty(pr), aph ^ 1)) { ok = false; break; }
                     tc_fence_after();
                     waited = true;
@@ -506,13 +459,6 @@ __global__ void __launch_bounds__(UM_THREADS, 1) qgemm_umma_kernel(const __grid_
         drain_until(nrun);
     }
 
-#ifdef MT_UMMA_TIMING
-    if (blockIdx.x == 1 && lane == 0) {
-        long long* dst = reinterpret_cast<long long*>(p.counters + 2048) + warp * 8;
-        dst[0] = clock64() - t_begin;
-        for (int q = 0; q < 7; ++q) dst[1 + q] = tw[q];
-    }
-#endif
     tc_fence_before();
     __syncthreads();
     if (warp == UM_W_MMA) {

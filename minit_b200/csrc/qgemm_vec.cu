@@ -31,15 +31,6 @@ constexpr int VEC_WARPS = 8;
 constexpr int VEC_COLS = 128;   // columns per CTA
 constexpr int VEC_D = 8;        // packed rows in flight per thread
 
-// Optional phase timeline for tuning (compile with -DMT_VEC_TIMING): lane 0 of every warp stores
-// the global timer at eight points into the tail of the workspace.
-#ifdef MT_VEC_TIMING
-#define MT_TL(buf, idx, i) do { if ((threadIdx.x & 31) == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
-    reinterpret_cast<unsigned long long*>(buf)[(1 << 17) + (size_t)(idx) * 8 + (i)] = t_; } } while (0)
-#else
-#define MT_TL(buf, idx, i) do { } while (0)
-#endif
-
 struct VecParams {
     const void* x; const uint32_t* qw; const uint32_t* qz; const void* scales; const void* bias; void* out;
     const int32_t* xperm;   // act-order: activations are read as x[perm[k]] (null: in order)
@@ -69,9 +60,12 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
 // Eight consecutive activations of a row, optionally read through the act-order permutation
 // (x[perm[k0 .. k0+7]]): the weights' rows were sorted by group once, the activations follow here.
 template <typename T>
-__device__ __forceinline__ uint4 load_x8(const T* __restrict__ xrow, const int32_t* __restrict__ perm, size_t k0) {
+__device__ __forceinline__ uint4 load_x8(const T* __restrict__ xrow, const int32_t* __restrict__ perm, size_t k0, int kmax) {
     if (!perm) return __ldg(reinterpret_cast<const uint4*>(xrow + k0));
-    const int4 i0 = __ldg(reinterpret_cast<const int4*>(perm + k0)), i1 = __ldg(reinterpret_cast<const int4*>(perm + k0 + 4));
+    int4 i0 = __ldg(reinterpret_cast<const int4*>(perm + k0)), i1 = __ldg(reinterpret_cast<const int4*>(perm + k0 + 4));
+    // a permutation entry outside [0, K) is clamped, like every other index this library reads from the caller
+    i0.x = min(max(i0.x, 0), kmax); i0.y = min(max(i0.y, 0), kmax); i0.z = min(max(i0.z, 0), kmax); i0.w = min(max(i0.w, 0), kmax);
+    i1.x = min(max(i1.x, 0), kmax); i1.y = min(max(i1.y, 0), kmax); i1.z = min(max(i1.z, 0), kmax); i1.w = min(max(i1.w, 0), kmax);
     const unsigned short* xs = reinterpret_cast<const unsigned short*>(xrow);
     uint4 r;
     r.x = uint32_t(__ldg(xs + i0.x)) | (uint32_t(__ldg(xs + i0.y)) << 16);
@@ -105,8 +99,6 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
 
     // this warp's run of chunks
     const int u = split * VEC_WARPS + warp;
-    const int tl_id = (blockIdx.y * gridDim.x + blockIdx.x) * VEC_WARPS + warp; (void)tl_id;
-    MT_TL(p.partial, tl_id, 0);
     const int c_lo = int((long long)u * p.nchunks / p.units);
     const int c_hi = int((long long)(u + 1) * p.nchunks / p.units);
     const int nks = (c_hi - c_lo) * CKS;
@@ -137,9 +129,7 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
     uint2 s0 = load_s(g), s1 = load_s(g + 1), s2 = load_s(g + 2);
     uint32_t z0 = load_z(g), z1 = load_z(g + 1), z2 = load_z(g + 2);
 
-    MT_TL(p.partial, tl_id, 1);
     if (p.pdl) { griddep_launch_dependents(); griddep_wait(); }
-    MT_TL(p.partial, tl_id, 2);
 
     // ---- stage the activations of this warp's run: block-scale, permute, fp16 ----
     unsigned char* xs_base = smem + (size_t)warp * MB * p.slice_ks * 16;
@@ -151,7 +141,7 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
         for (int i = 0; i < p.slice_ks; i += 32) {
             const int ks = i + lane;
             uint4 raw = make_uint4(0, 0, 0, 0);
-            if (row_ok && ks < nks) raw = load_x8(xg + (size_t)mb * p.k, p.xperm, ((size_t)c_lo * CKS + ks) * 8);
+            if (row_ok && ks < nks) raw = load_x8(xg + (size_t)mb * p.k, p.xperm, ((size_t)c_lo * CKS + ks) * 8, p.k - 1);
             float f[8];
             const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
@@ -188,7 +178,6 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
         }
     }
     __syncwarp();
-    MT_TL(p.partial, tl_id, 3);
 
     // ---- main loop ----
     float sf[4], zf[4];
@@ -282,12 +271,10 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
     }
 
     // ---- reduce the 8 warps of the CTA, then the splits ----
-    MT_TL(p.partial, tl_id, 4);
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb)
         *reinterpret_cast<float4*>(red + ((size_t)warp * MB + mb) * VEC_COLS + lane * 4) = make_float4(acc[mb][0], acc[mb][1], acc[mb][2], acc[mb][3]);
     __syncthreads();
-    MT_TL(p.partial, tl_id, 5);
     const int mb_r = tid / VEC_COLS, cc = tid % VEC_COLS;
     const bool active = mb_r < MB && mb_r < p.m;
     float v = 0.f;
@@ -321,7 +308,6 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
         __syncthreads();
         if (tid == 0) s_last = (atomicAdd(p.counters + tile, 1u) == unsigned(p.splits - 1));
         __syncthreads();
-        MT_TL(p.partial, tl_id, 6);
         if (!s_last) {
             if (fused_ar && tid == 0) ar_leave(p.ar, epoch, gridDim.x * gridDim.y);
             return;
@@ -366,7 +352,6 @@ __global__ void __launch_bounds__(VEC_THREADS, 2) qgemm_vec_kernel(const VecPara
         __syncthreads();
         if (tid == 0) ar_leave(p.ar, epoch, gridDim.x * gridDim.y);
     }
-    MT_TL(p.partial, tl_id, 7);
 }
 
 
@@ -437,7 +422,6 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
     if (p.pdl) griddep_launch_dependents();
     const int j = blockIdx.x * NW + warp;
     const bool idle = j >= p.warps;
-    MT_TL(p.partial, j, 0);
 
     const int u0 = idle ? 0 : j * p.per + (j < p.rem ? j : p.rem);
     const int nun = idle ? 0 : p.per + (j < p.rem ? 1 : 0);   // chunks of this warp's run (0: no run, the warp only joins the CTA's combine step)
@@ -462,7 +446,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
         const size_t k = (size_t)cl * CK + (size_t)(ks % CKS) * 8;
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb)
-            xr[mb] = (ok && mb < p.m) ? load_x8(xg + (size_t)mb * p.k, p.xperm, k) : make_uint4(0, 0, 0, 0);
+            xr[mb] = (ok && mb < p.m) ? load_x8(xg + (size_t)mb * p.k, p.xperm, k, p.k - 1) : make_uint4(0, 0, 0, 0);
     };
     auto stage_x = [&](int b, const uint4 (&xr)[MB]) {
         const int buf = b & 1;
@@ -563,14 +547,11 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
     uint2 s1 = load_s(); uint32_t z1 = load_z(); pf_advance();
     uint2 s2 = load_s(); uint32_t z2 = load_z();
 
-    MT_TL(p.partial, j, 1);
     if (p.pdl) griddep_wait();
     load_x(0, xr0);
     load_x(1, xr);
-    MT_TL(p.partial, j, 2);
 
     stage_x(0, xr0);
-    MT_TL(p.partial, j, 3);
 
     float sf[4], zf[4];
     auto convert = [&](uint2 s, uint32_t z) {
@@ -758,7 +739,6 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
             }
         }
     }
-    MT_TL(p.partial, j, 4);
     cp_async_wait<0>();
 
     // ---- combine the shared partial rows: CTA first, then across CTAs ----
@@ -766,11 +746,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
         if (nseg < 1) seg_tile[warp * 2] = -1;
         if (nseg < 2) seg_tile[warp * 2 + 1] = -1;
     }
-#ifdef MT_VEC_TIMING
-    if (lane == 0) { unsigned smid_; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid_)); reinterpret_cast<unsigned long long*>(p.partial)[(1 << 17) + (size_t)j * 8 + 5] = smid_ + 1; }
-#endif
     __syncthreads();
-    MT_TL(p.partial, j, 6);
     const int cta = blockIdx.x;
     for (int q = 0; q < 2; ++q) {
         const int slot = warp * 2 + q;
@@ -831,7 +807,6 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
         __syncthreads();
         if (tid == 0) ar_leave(p.ar, epoch, gridDim.x);
     }
-    MT_TL(p.partial, j, 7);
 }
 
 template <int BITS, typename T, int MB, int CK>

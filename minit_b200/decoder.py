@@ -160,8 +160,8 @@ class QAttention(Module):
                                                              quant_groups * (nr_querys * head_size) // hidden_size, bits, dtype))
         self._qkv = None
 
-    def update_buffer(self, name: str, value: torch.Tensor) -> None:
-        super().update_buffer(name, value)
+    def update_buffer(self, name: str, value, sharded: bool = False) -> None:
+        super().update_buffer(name, value, sharded)
         self._qkv = None
 
     def forward(self, x: torch.Tensor, cache: KVCache, cos: torch.Tensor, sin: torch.Tensor, offset: int,

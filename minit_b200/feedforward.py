@@ -132,8 +132,8 @@ class QFeedForward(Module):
             setattr(self, name, child)                       # children are looked up by their registered names
         self._fused = None
 
-    def update_buffer(self, name: str, value: torch.Tensor) -> None:
-        super().update_buffer(name, value)
+    def update_buffer(self, name: str, value, sharded: bool = False) -> None:
+        super().update_buffer(name, value, sharded)
         self._fused = None                                   # the interleaved copy is rebuilt on the next call
 
     def _gate_up(self):

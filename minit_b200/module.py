@@ -57,16 +57,18 @@ class Module:
         assert name in self.buffers
         return getattr(self, name)
 
-    def update_buffer(self, name: str, value: torch.Tensor) -> None:
+    def update_buffer(self, name: str, value, sharded: bool = False) -> None:
+        """``sharded``: the value is a rank's part of the buffer (a ``CollectiveTensor`` or a torch shard produced by a
+        loader epilogue): the dtype is still checked, the shape is the shard's own."""
         if "." in name:
             prefix, suffix = name.split(".", maxsplit=1)
-            self.get_child(prefix).update_buffer(suffix, value)
+            self.get_child(prefix).update_buffer(suffix, value, sharded)
             return
         assert name in self.buffers, f"{name} is not a buffer of {type(self).__name__}"
         shape, dtype = self.buffers[name]
-        if tuple(value.shape) != shape or value.dtype != _DTYPES[dtype]:
+        if value.dtype != _DTYPES[dtype] or (not sharded and tuple(value.shape) != shape):
             raise ValueError(f"buffer {name}: expected {shape} {dtype}, got {tuple(value.shape)} {value.dtype}")
-        setattr(self, name, value.contiguous())
+        setattr(self, name, value.contiguous() if isinstance(value, torch.Tensor) else value)
 
     def __call__(self, *args, **kwargs):
         return self.forward(*args, **kwargs)

@@ -32,9 +32,17 @@ def _matmul_quantized(op: MatrixMultiply, a: torch.Tensor, b) -> tuple:
     if b.packed is not None:
         qweight, qzeros, bits = b.packed
         return (quantized_matrix_multiply(a, qweight, qzeros, b._scale, b._group, bits=bits),)
-    # operands exist only unpacked: dequantize (own kernel), then a plain library GEMM; the
-    # quantized operand is [K,N] (orientation of the fused kernel, examples/qwen1_5_int8.py:156-200)
-    w = b.dequantize()
+    # operands exist only unpacked (one element per byte, what the reference's ``unpack`` produces): four bytes
+    # along K are one word of the 8-bit layout (little-endian, examples/qwen1_5_int8.py:40-50 read backwards), so
+    # the fused 8-bit kernel takes them after two view-and-copy steps; 4-bit values are 8-bit values below 16.
+    # The quantized operand is [K,N] (orientation of the fused kernel, examples/qwen1_5_int8.py:156-200).
+    data, zero = b._data, b._zero
+    k, n = data.shape
+    if data.dtype == torch.uint8 and zero.dtype == torch.uint8 and k % 32 == 0 and n % 8 == 0:
+        qweight = data.view(k // 4, 4, n).permute(0, 2, 1).contiguous().view(torch.int32).view(k // 4, n)
+        qzeros = zero.contiguous().view(torch.int32)
+        return (quantized_matrix_multiply(a, qweight, qzeros, b._scale, b._group, bits=8),)
+    w = b.dequantize()          # ragged shapes: dequantize (own kernel), then a plain library GEMM
     return (torch.matmul(a, w),)
 
 

@@ -230,8 +230,8 @@ class QLinear(Module):
         self._groups_arg = "unchecked"
         self._sorted = None       # (qweight_sorted, perm) of an act-order layer, built on first use
 
-    def update_buffer(self, name: str, value: torch.Tensor) -> None:
-        super().update_buffer(name, value)
+    def update_buffer(self, name: str, value, sharded: bool = False) -> None:
+        super().update_buffer(name, value, sharded)
         if name in ("g_idx", "qweight"):
             self._groups_arg = "unchecked"
             self._sorted = None
@@ -289,8 +289,8 @@ class W8Linear(Module):
         self.bias = self.register_buffer("bias", (out_features,), dtype) if bias else None
         self._packed = None       # the weights in the GPTQ word layout, built on first use
 
-    def update_buffer(self, name: str, value: torch.Tensor) -> None:
-        super().update_buffer(name, value)
+    def update_buffer(self, name: str, value, sharded: bool = False) -> None:
+        super().update_buffer(name, value, sharded)
         if name == "weight":
             self._packed = None
 

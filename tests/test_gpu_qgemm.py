@@ -1,6 +1,5 @@
 """mt_qgemm decode kernels through the C ABI against the oracle: flags=1 forces the register-ring
-kernel (mma.sync), flags=8 the tcgen05 decode kernel (M <= 16, contiguous groups), flags=0 lets
-the library choose.
+kernel (mma.sync), flags=0 lets the library choose.
 Tolerance from the north star: max|out - ref| <= 1e-2 * rms(ref), ref = T(float(x) @ float(W_oracle))."""
 import numpy as np
 import pytest
@@ -25,7 +24,7 @@ def run(M, c, act, bits, bias=None, flags=1):
                                        bits=bits, bias=None if bias is None else bias.to(DEV), flags=flags)
 
 
-KERNELS = [0, 1, 8]
+KERNELS = [0, 1]
 
 
 @pytest.mark.parametrize("flags", KERNELS)
@@ -134,13 +133,12 @@ def test_pdl_launch_flag(M, flags):
 
 
 def test_large_scales_and_small_x_stay_inside_tolerance(M):
-    """The tcgen05 decode kernel cancels a per-group offset in fp32; scales up to 1 and x values that
-    underflow when divided by 16 must not break the bound."""
+    """Scales up to 1 and x values that underflow when divided by 16 must not break the bound."""
     c = O.make_gptq_case(4096, 256, 3, bits=4, seed=31, scale_lo=0.5, scale_hi=1.0)
-    assert_close(run(M, c, False, 4, flags=8), oracle_out(c, False), "large scales")
+    assert_close(run(M, c, False, 4, flags=0), oracle_out(c, False), "large scales")
     c = O.make_gptq_case(4096, 256, 3, bits=4, seed=32)
     c["x"] = (c["x"].float() * 1e-4).half()
-    assert_close(run(M, c, False, 4, flags=8), oracle_out(c, False), "tiny x")
+    assert_close(run(M, c, False, 4, flags=0), oracle_out(c, False), "tiny x")
 
 
 def test_full_size_linearity_property(M):

@@ -96,6 +96,33 @@ def _worker(rank, size, port, results):
         pa = ca["x"][:, 256 // size * rank:256 // size * (rank + 1)].float() @ O.dequantize_packed(qw, gi, qz, s, 4).float()
         assert torch.allclose(comm.all_reduce(pa), ca["x"].float() @ wa.float(), atol=1e-3)
 
+        # 7. a checkpoint loaded through a sharding epilogue (examples/llama3_70b.py:298-310): the full shape is
+        # checked first, then the epilogue's result is stored, a CollectiveTensor or a torch shard
+        import tempfile
+        from minit_b200 import checkpoint as C
+        from minit_b200.module import Module
+
+        class Net(Module):
+            def __init__(self):
+                super().__init__()
+                self.w_col = self.register_buffer("w_col", (8, 6), "float16")
+                self.w_row = self.register_buffer("w_row", (8, 6), "float16")
+        full_w = {"w_col": torch.arange(48, dtype=torch.float16).reshape(8, 6), "w_row": -torch.arange(48, dtype=torch.float16).reshape(8, 6)}
+        with tempfile.TemporaryDirectory() as tmp:
+            path = os.path.join(tmp, f"net{rank}.safetensors")
+            C.save_safetensors(path, full_w)
+
+            def epilogue(key, value):
+                ct = CollectiveTensor.from_broadcast(comm, value)
+                return ct.to_split(0) if key == "w_col" else ct.to_split(1)._local       # a CollectiveTensor and a plain shard
+            net = C.load_from_safetensors(Net(), [path], epilogue, device="cpu")
+            assert isinstance(net.w_col, CollectiveTensor) and net.w_col.shape == (8, 6)
+            assert torch.equal(net.w_col._local, full_w["w_col"][4 * rank:4 * rank + 4])
+            assert torch.equal(net.w_row, full_w["w_row"][:, 3 * rank:3 * rank + 3])
+            C.save_safetensors(path, {"w_col": torch.zeros(4, 6, dtype=torch.float16)})    # wrong full shape: refused before the epilogue
+            with pytest.raises(ValueError):
+                C.load_from_safetensors(Net(), [path], epilogue, device="cpu")
+
         # 6. shapes that do not split are refused
         with pytest.raises(ValueError):
             shard_gptq_column(c["qweight"][:, :24], c["qzeros"][:, :3], c["scales"][:, :24], 4, rank, size * 2 if size == 2 else 5)
