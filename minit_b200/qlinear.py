@@ -35,6 +35,35 @@ def unpack(x: torch.Tensor, axis: int, bits: int = 8) -> torch.Tensor:
     return out
 
 
+def _validate_gptq_call(x, qweight, zeros, scales, groups, bias, bits: int):
+    """Shape and dtype contract shared by every wrapper of the fused kernel (examples/qwen1_5_int8.py:247-254, plus the
+    integer dtypes the kernels index with): raises ValueError before anything reaches the C call.  Returns (ms, m, k, n, g)."""
+    if bits not in (4, 8):
+        raise ValueError("bits must be 4 or 8")
+    pack = 32 // bits
+    *ms, k0 = x.shape
+    if qweight.dim() != 2 or scales.dim() != 2:
+        raise ValueError("qweight and scales must be 2-D")
+    pk1, n0 = qweight.shape
+    g1, n2 = scales.shape
+    if not (k0 == pk1 * pack and n0 == n2):
+        raise ValueError(f"shape mismatch: x[..,{k0}] qweight[{pk1}*{pack},{n0}] scales[{g1},{n2}]")
+    if qweight.dtype != torch.int32:
+        raise ValueError("qweight must be int32 (packed words)")
+    if zeros is not None and (tuple(zeros.shape) != (g1, n0 // pack) or zeros.dtype != torch.int32):
+        raise ValueError(f"zeros must be int32 [{g1},{n0 // pack}], got {zeros.dtype} {tuple(zeros.shape)}")
+    if groups is not None and (tuple(groups.shape) != (k0,) or groups.dtype != torch.int32):
+        raise ValueError(f"groups must be int32 [{k0}], got {groups.dtype} {tuple(groups.shape)}")
+    if scales.dtype != x.dtype:
+        raise ValueError("scales.dtype must equal x.dtype")
+    if bias is not None and (bias.dtype != x.dtype or tuple(bias.shape) != (n0,)):
+        raise ValueError("bias must be [N] in x.dtype")
+    m = 1
+    for d in ms:
+        m *= d
+    return ms, m, k0, n0, g1
+
+
 def quantized_matrix_multiply(x: torch.Tensor, qweight: torch.Tensor, zeros: Optional[torch.Tensor],
                               scales: torch.Tensor, groups: Optional[torch.Tensor], *, bits: int = 8,
                               bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
@@ -46,26 +75,8 @@ def quantized_matrix_multiply(x: torch.Tensor, qweight: torch.Tensor, zeros: Opt
     the per-k group index (g_idx) or None for contiguous groups; ``zeros`` None means the
     symmetric midpoint.  The shape contract is the reference's (examples/qwen1_5_int8.py:247-254).
     """
-    if bits not in (4, 8):
-        raise ValueError("bits must be 4 or 8")
-    pack = 32 // bits
-    *ms, k0 = x.shape
-    pk1, n0 = qweight.shape
-    g1, n2 = scales.shape
-    if not (k0 == pk1 * pack and n0 == n2):
-        raise ValueError(f"shape mismatch: x[..,{k0}] qweight[{pk1}*{pack},{n0}] scales[{g1},{n2}]")
-    if zeros is not None and tuple(zeros.shape) != (g1, n0 // pack):
-        raise ValueError(f"zeros must be [{g1},{n0 // pack}], got {tuple(zeros.shape)}")
-    if groups is not None and tuple(groups.shape) != (k0,):
-        raise ValueError(f"groups must be [{k0}], got {tuple(groups.shape)}")
-    if scales.dtype != x.dtype:
-        raise ValueError("scales.dtype must equal x.dtype")
-    if bias is not None and (bias.dtype != x.dtype or tuple(bias.shape) != (n0,)):
-        raise ValueError("bias must be [N] in x.dtype")
+    ms, m, k0, n0, g1 = _validate_gptq_call(x, qweight, zeros, scales, groups, bias, bits)
     dev = _lib.require_cuda(x, qweight, zeros, scales, groups, bias)
-    m = 1
-    for d in ms:
-        m *= d
     if out is None:
         out = torch.empty((*ms, n0), dtype=x.dtype, device=dev)
     else:
@@ -159,17 +170,10 @@ def quantized_matrix_multiply_noalloc(x: torch.Tensor, qweight: torch.Tensor, ze
     call under it allocates.  Shapes whose scratch would not fit raise (status -10); calls share
     the array, so do not let two of them overlap on the GPU.  Call it once before any stream
     capture on a device: the first call looks up the array's address."""
-    pack = 32 // bits
-    *ms, k0 = x.shape
-    n0 = qweight.shape[1]
-    if k0 != qweight.shape[0] * pack or tuple(scales.shape) != (scales.shape[0], n0) or scales.dtype != x.dtype:
-        raise ValueError("shape or dtype mismatch between x, qweight and scales")
+    ms, m, k0, n0, _ = _validate_gptq_call(x, qweight, zeros, scales, groups, bias, bits)
     if tuple(out.shape) != (*ms, n0) or out.dtype != x.dtype:
         raise ValueError("out has the wrong shape or dtype")
     dev = _lib.require_cuda(x, qweight, zeros, scales, groups, bias, out)
-    m = 1
-    for d in ms:
-        m *= d
     with torch.cuda.device(dev):
         rc = _lib.lib.mt_qgemm_static(_lib.current_stream(dev), x.data_ptr(), qweight.data_ptr(), _lib.ptr(groups),
                                       _lib.ptr(zeros), scales.data_ptr(), _lib.ptr(bias), out.data_ptr(), m, n0, k0,

@@ -17,8 +17,15 @@ the reference CUDA kernels (gather along one axis, C cast, elementwise arithmeti
 evaluated in the tensor's own dtype).  ``nvtx`` (a hard import of the reference,
 absent here) is replaced by a no-op stub.
 
+  * ``unpack(x, axis)`` of examples/qwen1_5_int8.py:40-50: the function's own source is cut out of the
+    example file (importing the whole example would compile its CUDA runtime shims) and executed
+    unmodified; its Reinterpret / Expand / AddAxis / Transpose / RemoveAxis / Fold steps run through the
+    reference's functional wrappers and dispatch, with torch-CPU rules that restate the view / copy
+    semantics of minit/cuda/dispatch.py:210-245, 356-380, 482-490.
+
 The fixture stores inputs (packed GPTQ tensors) and the reference's W bit pattern
-(int16 view) for several small cases.  The reference has no 4-bit instantiation of
+(int16 view) for several small cases, and two int32 matrices with the reference's unpack(x, 0) and
+unpack(x, 1) of each.  The reference has no 4-bit instantiation of
 its unpack(); 4-bit data is unpacked here with the reference's accessor formula
 (examples/qwen1_5_int8.py:97-138) before entering the reference dequantize.
 """
@@ -51,6 +58,7 @@ def _load_reference(root):
         from minit.core.dispatch import register_dispatch
         from minit.operator.arith import Add, Subtract, Multiply, Cast
         from minit.operator.index import Index
+        from minit.operator.shape import AddAxis, Expand, Fold, Reinterpret, RemoveAxis, Transpose
         import minit.quantize.dispatch  # noqa: F401  registers dispatch_dequantize
         from minit.quantize.tensor import QuantizedTensor
 
@@ -106,19 +114,64 @@ def _load_reference(root):
         def _mul(op: Multiply, x: CPUTensor, y: CPUTensor):
             return (CPUTensor(x.t * y.t),)
 
+        def _dim(v):
+            return int(v.item()) if isinstance(v, CPUTensor) else int(v.value())
+
+        @register_dispatch()
+        def _reinterpret(op: Reinterpret, x: CPUTensor):
+            return (CPUTensor(x.t.contiguous().view(tdt[op.target])),)
+
+        @register_dispatch()
+        def _expand(op: Expand, x: CPUTensor, *sizes: Tensor):
+            dims = tuple(_dim(v) for v in sizes)
+            shape = tuple(x.t.shape)
+            return (CPUTensor(x.t.contiguous().reshape(shape[:op.axis] + dims + shape[op.axis + 1:])),)
+
+        @register_dispatch()
+        def _add_axis(op: AddAxis, x: CPUTensor):
+            return (CPUTensor(x.t.contiguous().unsqueeze(op.axis)),)
+
+        @register_dispatch()
+        def _remove_axis(op: RemoveAxis, x: CPUTensor):
+            assert x.t.shape[op.axis] == 1
+            return (CPUTensor(x.t.contiguous().squeeze(op.axis)),)
+
+        @register_dispatch()
+        def _fold(op: Fold, x: CPUTensor):
+            shape = tuple(x.t.shape)
+            size = 1
+            for d in shape[op.start:op.stop]:
+                size *= d
+            return (CPUTensor(x.t.contiguous().reshape(shape[:op.start] + (size,) + shape[op.stop:])),)
+
+        @register_dispatch()
+        def _transpose(op: Transpose, x: CPUTensor):
+            return (CPUTensor(x.t.transpose(op.axis_a, op.axis_b).contiguous()),)     # the reference's copy kernel
+
+    # the reference's unpack(), source text taken from the example file as it is
+    import ast
+    example = os.path.join(root, "examples", "qwen1_5_int8.py")
+    src = open(example).read()
+    node = next(n for n in ast.parse(src).body if isinstance(n, ast.FunctionDef) and n.name == "unpack")
+    ns = {"Tensor": Tensor}
+    exec(compile(ast.Module(body=[node], type_ignores=[]), example, "exec"), ns)
+
+    def ref_unpack(x_i32, axis):
+        return ns["unpack"](CPUTensor(torch.from_numpy(x_i32)), axis).t.numpy()
+
     def ref_dequantize(q_u8, g_idx, z_u8, scales):
         qt = QuantizedTensor(CPUTensor(torch.from_numpy(q_u8)), CPUTensor(torch.from_numpy(g_idx)),
                              CPUTensor(torch.from_numpy(z_u8)), CPUTensor(scales))
         return qt.dequantize().t
 
-    return ref_dequantize
+    return ref_dequantize, ref_unpack
 
 
 def main():
     if len(sys.argv) < 2 and "MINIT_REFERENCE" not in os.environ:
         raise SystemExit("usage: make_golden.py <path to a checkout of the reference project>  (or set MINIT_REFERENCE)")
     root = sys.argv[1] if len(sys.argv) > 1 else os.environ["MINIT_REFERENCE"]
-    ref_dequantize = _load_reference(root)
+    ref_dequantize, ref_unpack = _load_reference(root)
     from oracle import qlinear_oracle as O
 
     cases = {}
@@ -157,9 +210,17 @@ def main():
     cases["w8pc.w_i8"] = c["w"].numpy()
     cases["w8pc.scales_bits"] = c["scales"].view(torch.int16).numpy()
     cases["w8pc.w_bits"] = w.view(torch.int16).numpy()
+    # the reference's own unpack() (8-bit, the only width it has) on two packed matrices, both axes
+    rng = np.random.default_rng(5)
+    for name, shape in (("unpack_a", (8, 12)), ("unpack_b", (32, 16))):
+        x = rng.integers(-2**31, 2**31 - 1, size=shape, dtype=np.int64).astype(np.int32)
+        x[0, 0], x[0, 1] = np.int32(0x04030201), np.int32(-1)        # byte order and the sign bit at a glance
+        cases[f"{name}.x"] = x
+        cases[f"{name}.axis0"] = ref_unpack(x, 0)
+        cases[f"{name}.axis1"] = ref_unpack(x, 1)
     out = os.path.join(HERE, "dequant_golden.npz")
     np.savez_compressed(out, **cases)
-    print("wrote", out, os.path.getsize(out), "bytes;", len(specs) + 1, "cases")
+    print("wrote", out, os.path.getsize(out), "bytes;", len(specs) + 1, "dequantize cases, 2 unpack cases")
 
 
 if __name__ == "__main__":

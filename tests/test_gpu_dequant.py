@@ -78,3 +78,12 @@ def test_dequant_full_size_config1_roundtrip_property(M):
     assert torch.equal(w.cpu().view(torch.int16), ref.view(torch.int16))
     w2 = dequantize_packed(d["qweight"], None, d["qzeros"], d["scales"] * 2, 4)
     assert torch.equal(w2, w * 2)
+
+
+@pytest.mark.parametrize("name", ["unpack_a", "unpack_b"])
+def test_unpack_matches_the_reference_unpack(M, name):
+    """mt_unpack against the bytes the reference's own unpack() produced (tests/golden/make_golden.py)."""
+    g = np.load(GOLDEN)
+    x = torch.from_numpy(g[f"{name}.x"]).to(DEV)
+    assert np.array_equal(M.unpack(x, 0, 8).cpu().numpy(), g[f"{name}.axis0"])
+    assert np.array_equal(M.unpack(x, 1, 8).cpu().numpy(), g[f"{name}.axis1"])

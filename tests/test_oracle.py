@@ -189,3 +189,14 @@ def test_decoder_step_restatements():
     ref = torch.softmax(torch.einsum("snd,tnd->nst", qq[1:].float(), k.repeat_interleave(2, 1).float()) / math.sqrt(128), -1)
     out = torch.einsum("nst,tnd->snd", ref, v.repeat_interleave(2, 1).float()).reshape(1, -1)
     assert torch.allclose(both[1:].float(), out, atol=2e-2)
+
+
+@pytest.mark.parametrize("name", ["unpack_a", "unpack_b"])
+def test_oracle_unpack_matches_the_reference_unpack(name):
+    """unpack(x, 0) / unpack(x, 1) as the reference's own function computed them (examples/qwen1_5_int8.py:40-50,
+    executed by tests/golden/make_golden.py): the oracle's 8-bit accessors give the same bytes."""
+    g = np.load(GOLDEN)
+    x = g[f"{name}.x"]
+    assert np.array_equal(O.unpack_rows(x, 8), g[f"{name}.axis0"])
+    assert np.array_equal(O.unpack_cols(x, 8), g[f"{name}.axis1"])
+    assert g[f"{name}.axis0"].shape == (x.shape[0] * 4, x.shape[1]) and g[f"{name}.axis1"].shape == (x.shape[0], x.shape[1] * 4)
