@@ -352,6 +352,151 @@ def prefill_m4096(dev):
     return {"m": mrows, "bound": "tensor", "unit": "TFLOP/s", "peak": peak, "peak_source": kind, "shapes": shapes}
 
 
+# ---------------------------------------------------------------------------------------
+# the other configs of the metric, as compact extra keys of the one-GPU line
+# ---------------------------------------------------------------------------------------
+def _graph_time_us(calls, reps=3):
+    """Device time per call of a list of closures: warmed up and captured as ONE CUDA graph on a side stream (the calls
+    rotate over weight sets larger than L2), replayed `reps` times between two CUDA events."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            for fn in calls:
+                fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for fn in calls:
+                fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(side)
+        for _ in range(reps):
+            graph.replay()
+        e1.record(side)
+        torch.cuda.synchronize()
+    torch.cuda.current_stream().wait_stream(side)
+    return e0.elapsed_time(e1) * 1e3 / (reps * len(calls))
+
+
+def _entry(k, n, m, us, nbytes, hbm_peak, tensor_peak, **extra):
+    """{shape, m, us, frac, bound}: frac against the roofline that bounds the call (the longer of bytes / HBM peak
+    and flops / tensor peak)."""
+    t_hbm = nbytes / (hbm_peak * 1e3)                   # us
+    t_tc = 2.0 * m * n * k / (tensor_peak * 1e6)         # us
+    e = {"shape": [k, n], "m": m, "us": round(us, 2), "bound": "hbm" if t_hbm >= t_tc else "tensor",
+         "frac": round(max(t_hbm, t_tc) / us, 4)}
+    e.update(extra)
+    return e
+
+
+def extra_configs(dev):
+    """cfg1 (one 4096x4096 int4 linear), cfg2 (int8 per-channel, both routes), cfg3 (a Mistral-7B layer with act-order)
+    and the prefill config at all its batch sizes and both dtypes.  Weight sets rotate (> 2x L2 per measurement)."""
+    import minit_b200 as M
+    hbm_peak, _ = peaks()
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    tensor_peak = float(json.load(open(path))["bf16_tflops"]) if os.path.exists(path) else 1590.0
+    gen = torch.Generator(device=dev).manual_seed(321)
+    out = {}
+
+    def gptq(k, n, dtype=torch.float16):
+        qw = torch.randint(-2**31, 2**31 - 1, (k // 8, n), device=dev, dtype=torch.int64, generator=gen).to(torch.int32)
+        qz = torch.randint(-2**31, 2**31 - 1, (k // GROUP, n // 8), device=dev, dtype=torch.int64, generator=gen).to(torch.int32)
+        sc = (0.002 + 0.018 * torch.rand((k // GROUP, n), device=dev, generator=gen)).to(dtype)
+        return qw, qz, sc
+
+    def nsets(nbytes):
+        return max(2, min(40, int(300e6 // nbytes) + 1))
+
+    # ---- cfg1 ----
+    k = n = 4096
+    sets = [gptq(k, n) for _ in range(nsets(weight_bytes(k, n)))]
+    rows = []
+    for m in (1, 16):
+        x = torch.randn((m, k), device=dev, generator=gen).half()
+        o = torch.empty((m, n), device=dev, dtype=torch.float16)
+        calls = [(lambda s=s_: M.quantized_matrix_multiply(x, s[0], s[1], s[2], None, bits=4, out=o, flags=4)) for s_ in sets]
+        rows.append(_entry(k, n, m, _graph_time_us(calls), algorithmic_bytes(m, k, n), hbm_peak, tensor_peak))
+    out["cfg1_int4_4096"] = rows
+    del sets
+
+    # ---- cfg2: int8, one scale per output channel; plain [K,N] layout and packed once into the 8-bit word layout ----
+    rows = []
+    for k, n in ((4096, 4096), (4096, 11008), (11008, 4096)):
+        cnt = nsets(k * n)
+        ws = [torch.randint(-127, 128, (k, n), device=dev, dtype=torch.int32, generator=gen).to(torch.int8) for _ in range(cnt)]
+        scs = [(0.001 + 0.009 * torch.rand((n,), device=dev, generator=gen)).half() for _ in range(cnt)]
+        packed = [M.pack_w8(w) for w in ws]
+        for m in (1, 8, 32, 128, 512):
+            x = torch.randn((m, k), device=dev, generator=gen).half()
+            o = torch.empty((m, n), device=dev, dtype=torch.float16)
+            nb = k * n + 2 * n + 2 * m * k + 2 * m * n
+            plain = [(lambda w=w_, sc=sc_: M.w8_perchannel_matrix_multiply(x, w, sc, out=o)) for w_, sc_ in zip(ws, scs)]
+            pk = [(lambda q=q_, sc=sc_: M.quantized_matrix_multiply(x, q, None, sc.view(1, -1), None, bits=8, out=o)) for q_, sc_ in zip(packed, scs)]
+            rows.append(_entry(k, n, m, _graph_time_us(pk), nb, hbm_peak, tensor_peak, route="packed (mt_w8_pack + mt_qgemm)",
+                               us_plain_layout=round(_graph_time_us(plain), 2)))
+        del ws, scs, packed
+    out["cfg2_int8_perchannel"] = rows
+
+    # ---- cfg3: the seven linears of a Mistral-7B layer, act-order g_idx, rows sorted by group once at load ----
+    lin = [("q", 4096, 4096), ("k", 4096, 1024), ("v", 4096, 1024), ("o", 4096, 4096), ("gate", 4096, 14336), ("up", 4096, 14336),
+           ("down", 14336, 4096)]
+    layers = []
+    for _ in range(3):
+        layer = []
+        for _, k, n in lin:
+            qw, qz, sc = gptq(k, n)
+            g_idx = (torch.arange(k, device=dev) // GROUP)[torch.randperm(k, device=dev, generator=gen)].to(torch.int32)
+            qs, perm = M.sort_act_order(qw, g_idx, k // GROUP, 4)
+            layer.append((qs, qz, sc, perm))
+            del qw
+        layers.append(layer)
+    rows = []
+    for m in (1, 4, 16, 64):
+        xs = {k: torch.randn((m, k), device=dev, generator=gen).half() for k in (4096, 14336)}
+        os_ = {n: torch.empty((m, n), device=dev, dtype=torch.float16) for n in (4096, 1024, 14336)}
+        calls = []
+        for layer in layers:
+            for (_, k, n), (qs, qz, sc, perm) in zip(lin, layer):
+                calls.append(lambda qs=qs, qz=qz, sc=sc, perm=perm, k=k, n=n: M.quantized_matrix_multiply_ordered(xs[k], qs, qz, sc, perm, bits=4, out=os_[n]))
+        us_layer = _graph_time_us(calls) * len(lin)
+        nb = sum(algorithmic_bytes(m, k, n) + 4 * k for _, k, n in lin)
+        rows.append({"m": m, "us_per_layer": round(us_layer, 2), "bound": "hbm", "frac": round(nb / (hbm_peak * 1e3) / us_layer, 4),
+                     "launches_per_layer": len(lin) if m <= 2 else 2 * len(lin)})
+    out["cfg3_mistral7b_layer_actorder"] = rows
+    del layers
+
+    # ---- cfg5: prefill, every batch size and both dtypes ----
+    rows = []
+    for dtype, name in ((torch.float16, "f16"), (torch.bfloat16, "bf16")):
+        for k, n in ((4096, 6144), (4096, 28672), (14336, 4096)):
+            sets = [gptq(k, n, dtype) for _ in range(2)]
+            for m in (2048, 4096, 8192):
+                x = torch.randn((m, k), device=dev, generator=gen).to(dtype)
+                o = torch.empty((m, n), device=dev, dtype=dtype)
+                for i in range(2):
+                    M.quantized_matrix_multiply(x, *sets[i % 2], None, bits=4, out=o)
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for i in range(4):
+                    M.quantized_matrix_multiply(x, *sets[i % 2], None, bits=4, out=o)
+                e1.record()
+                torch.cuda.synchronize()
+                us = e0.elapsed_time(e1) * 1e3 / 4
+                rows.append(_entry(k, n, m, us, algorithmic_bytes(m, k, n), hbm_peak, tensor_peak, dtype=name,
+                                   tflops=round(2.0 * m * n * k / us / 1e6, 1)))
+                del x, o
+            del sets
+    out["cfg5_prefill"] = rows
+    out["note"] = ("CUDA-graph loops over weight sets in rotation (> 2x L2), device time per call; frac is against the measured HBM "
+                   "peak (%.0f GB/s) or the measured dense bf16 burst peak (%.0f TFLOP/s), whichever bounds the call" % (hbm_peak, tensor_peak))
+    return out
+
+
 def parity_check(world, rank, dev, far, comm, ms=(1, 8)):
     """Outside the timed region, at every N: one row-parallel linear of each kind (o, down) of the workload at
     M = 1 and M = 8 through the same call the timed step makes (the fused GEMM + all-reduce, the NCCL all-reduce
@@ -517,6 +662,11 @@ def run_ours(args):
     ms_step, clocks = timed(runner, args.steps, args.warmup, sample_clocks=True)
     e2e_runner, e2e_mode = make_runner(one_pass_e2e)
     ms_e2e, _ = timed(e2e_runner, args.steps, args.warmup)
+    # the same end-to-end step without the CUDA graph: one eager call of the Python wrapper per linear, which is the
+    # seam the reference has (examples/qwen1_5_int8.py:244-267); its per-call host cost shows here
+    ms_e2e_eager = None
+    if mode == "cuda_graph" and not args.no_extra:
+        ms_e2e_eager, _ = timed(one_pass_e2e, 5, 2)
 
     # correctness evidence beside the timing, at every N: no bounded wait expired during the timed steps, and the
     # row-parallel linears (with their all-reduce) reproduce the oracle on unsharded weights
@@ -558,12 +708,16 @@ def run_ours(args):
         "e2e": {"value": total_wbytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e, "launch": e2e_mode,
                 "h2d_bytes_per_step": sum(x.numel() * 2 for x in xs_host), "d2h_bytes_per_step": out_host.numel() * 2,
                 "note": "weights stay resident (loaded once, like model parameters); activations cross PCIe every step"},
+        "e2e_eager": None if ms_e2e_eager is None else {"value": total_wbytes / (ms_e2e_eager * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e_eager,
+                                                          "launch": "eager: one Python call per linear, %d per step" % launches_per_step},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
         "parity_check": parity,
     }
     if rank == 0 and world == 1 and m == 1 and not args.no_prefill:
         line["prefill_m4096"] = prefill_m4096(dev)
+    if rank == 0 and world == 1 and m == 1 and not args.no_extra:
+        line["other_configs"] = extra_configs(dev)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(budget_s=20.0)
     if world > 1:
@@ -704,6 +858,7 @@ def main():
                     help="row-parallel exchange: fused into the GEMM epilogue over peer memory, or an NCCL all-reduce after it")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the M = 4096 TFLOP/s measurement of the default one-GPU run")
+    ap.add_argument("--no-extra", action="store_true", help="skip the other configs (cfg1, cfg2 int8, cfg3 act-order, all prefill sizes) and the eager e2e figure")
     ap.add_argument("--single-shape", default=None, help="K,N : time one linear instead of the workload (profiling aid)")
     ap.add_argument("--mlp-block", action="store_true", help="time the feed-forward block with separate and with fused elementwise steps")
     ap.add_argument("--decode-layer", action="store_true", help="time whole decoder layers (norms, rope, attention, fused linears) for one token")

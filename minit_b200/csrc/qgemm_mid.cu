@@ -1,0 +1,621 @@
+// Mid-size batches (2 < M <= 64 per pass) for GPTQ weights with contiguous groups of a multiple of 128:
+// the packed integers go to the tensor core AS INTEGERS.
+//
+// Replaces the per-thread dequantize-and-multiply loop of examples/qwen1_5_int8.py:156-200 (and the
+// dequantize-then-matmul of minit/quantize/dispatch.py:8-20) for the batch sizes where the product is
+// still a stream of the packed weights.  Turning every weight into fp16 costs more issue slots than the
+// stream leaves at 6.5 TB/s, so this kernel does not dequantize at all:
+//
+//   * tcgen05.mma.kind::i8 multiplies unsigned 8-bit by signed 8-bit with exact 32-bit sums.  A packed
+//     nibble masked in place IS the unsigned byte q (word & 0x0f0f0f0f: the even nibbles of a word,
+//     (word >> 4) & 0x0f0f0f0f: the odd ones): three integer instructions per eight weights, written
+//     straight to tensor memory (tcgen05.st) as the A operand (M = 128 output columns per tile).  An
+//     8-bit weight needs no instruction at all.
+//   * the activations are split once per call by a small pre-pass (xprep_kernel): per row and per 128
+//     values of k a power-of-two block scale 2^e brings the largest |x| into [2^13, 2^14), x' = rint(x 2^e)
+//     is written as two signed bytes x' = 256 h + l, and sum(x') and 2^-e are kept.  The B operand of a
+//     128-k block is the 2 BM x 128 byte tile [h rows | l rows], stored by the pre-pass in the
+//     shared-memory image the tensor core reads (K-major, 128-byte swizzle, k-slots in the order the
+//     nibble masks produce), so the main kernel fetches it with one bulk copy.
+//   * per 128 values of k the integer sums V = 256 D_h + D_l = sum_k q x' leave tensor memory
+//     (tcgen05.ld) and are folded in fp32 with the scale and zero point of that block's group:
+//         out[m, n] += s[g, n] * 2^-e[m] * (V - (z[g, n] + 1) * sum_k x')
+//     which is the GPTQ formula (q - (z + 1)) * s applied to x' 2^-e.  The only approximation is the
+//     14-bit block-fixed-point x' (relative output error ~1e-4 of rms, far inside the 1e-2 bound).
+//
+// Roles (18 warps, one CTA per SM): 16 worker warps = (tile, TMEM lane quarter, split): a thread owns
+// one output column, converts its share of a k-block's words, and folds its share of the batch rows of
+// the PREVIOUS k-block while the tensor core works on the current one (two accumulator buffers);
+// 1 producer lane (TMA of the packed rows, scales and zero words of a k-block: 17 KB per stage, 8 stages;
+// one bulk copy of the B tile); 1 MMA lane.  Stream-K over (column tile, k-block) units as in the other
+// kernels; a tile shared by several CTAs is finished, slice by slice, by the last warp to arrive.
+// Every wait is bounded and reports through the workspace error word.
+#include "tma.cuh"
+#include "tcgen05.cuh"
+
+namespace mt {
+namespace {
+
+constexpr int MD_WORKERS = 16;
+constexpr int MD_W_PROD = 16, MD_W_MMA = 17;
+constexpr int MD_THREADS = 18 * 32;
+constexpr int MD_KB = 128;                         // values of k per unit
+
+template <int BITS, int BM> struct MdCfg {
+    static constexpr int PACK = 32 / BITS;
+    static constexpr int PROWS = MD_KB / PACK;     // packed rows per k-block: 16 | 32
+    static constexpr int NT = BM <= 32 ? 2 : 1;    // 128-column tiles per CTA tile
+    static constexpr int COLS = NT * 128;
+    static constexpr int RS = 16 / (4 * NT);       // splits of the rows (fold) and of the k-block (conversion) per tile quarter: 2 | 4
+    static constexpr int RW = BM / RS;             // batch rows a worker folds: 8 | 16
+    static constexpr int WPW = PROWS / RS;         // packed words a worker converts per k-block
+    static constexpr int AREGS = 32 / RS;          // 32-bit TMEM columns a worker writes per k-block: 16 | 8
+    static constexpr int NB = 2 * BM;              // MMA N: h rows then l rows
+    static constexpr int D_COLS = 2 * NT * NB;     // two accumulator buffers
+    static constexpr int A_STAGE = NT * 32;        // TMEM columns of one k-block of the A operand
+    static constexpr int AST = (512 - D_COLS) / A_STAGE >= 8 ? 8 : (512 - D_COLS) / A_STAGE;
+    static constexpr int W_BYTES = PROWS * COLS * 4;
+    static constexpr int S_BYTES = COLS * 2;
+    static constexpr int Z_BYTES = COLS / PACK * 4;
+    static constexpr int P_STAGE = (W_BYTES + S_BYTES + Z_BYTES + 127) / 128 * 128;
+    static constexpr int PST = (136 * 1024) / P_STAGE;                 // ~136 KB of packed weights in flight per SM
+    static constexpr int B_TILE = NB * 128;
+    static constexpr int B_COPY = B_TILE + BM * 8;                    // tile + sum(x') [BM] int32 + 2^-e [BM] fp32
+    static constexpr int B_STAGE = B_TILE + 1024;
+    static constexpr int BST = 4;
+    static constexpr int OFF_P = 0;
+    static constexpr int OFF_B = OFF_P + PST * P_STAGE;
+    static constexpr int OFF_BAR = OFF_B + BST * B_STAGE;
+    static constexpr int NBARS = 2 * PST + 2 * BST + 2 * AST + 4;
+    static constexpr int TOTAL = OFF_BAR + NBARS * 8 + 64 + 1024;
+    static_assert(D_COLS + AST * A_STAGE <= 512 && AST >= 3, "TMEM budget");
+    static_assert(OFF_B % 1024 == 0, "B tiles need 1024-byte alignment");
+    static_assert(TOTAL <= 227 * 1024, "shared memory budget");
+};
+
+struct MdParams {
+    const unsigned char* xl;      // pre-pass output: per k-block [B tile | sum(x') | 2^-e]
+    const void* bias; void* out;
+    float* partial; unsigned* counters; unsigned* err;
+    int m, n, k;
+    int has_zeros;
+    int tiles, kbt;               // column tiles, k-blocks per tile
+    int kpg;                      // k-blocks per scale group
+    int units, per, rem;
+    int zp1_const;
+    int pdl;
+    ArParams ar;                  // row-parallel use: all-reduce of the finished sums over peer memory
+    const void* residual;         // [M,N] T or null: added to the finished (all-reduced) sum before the one rounding
+};
+
+__device__ __forceinline__ bool md_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (int i = 0; i < (1 << 20); ++i) {                // parked, not polling; gives up after about a second
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.b32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
+        if (ok) return true;
+        if ((i & 63) == 63 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void md_mma_i8(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n}"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void md_bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+template <int NR>
+__device__ __forceinline__ void md_st(uint32_t taddr, const uint32_t (&r)[NR]) {
+    static_assert(NR == 8 || NR == 16, "tcgen05.st width");
+    if constexpr (NR == 8) {
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                     ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+    } else {
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                     ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                       "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+    }
+}
+
+// ----------------------------------------------------------------------------------------------
+// pre-pass: activations -> two-limb block-fixed-point B tiles (one block per k-block of 128 values)
+// ----------------------------------------------------------------------------------------------
+// grid = K / 128 blocks of 256 threads; warp w handles batch rows w, w + 8, ...; lane = 4 consecutive k.
+template <typename T, int BITS>
+__global__ void __launch_bounds__(256) xprep_kernel(const T* __restrict__ x, unsigned char* __restrict__ xl, int m, int k, int bm, int pdl) {
+    using H = F16x2<T>;
+    const int kb = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb = 2 * bm;
+    unsigned char* tile = xl + (size_t)kb * (nb * 128 + bm * 8);
+    int* sums = reinterpret_cast<int*>(tile + nb * 128);
+    float* pes = reinterpret_cast<float*>(tile + nb * 128 + bm * 4);
+    if (pdl) { griddep_launch_dependents(); griddep_wait(); }
+    for (int r = warp; r < bm; r += 8) {
+        float f[4] = {0.f, 0.f, 0.f, 0.f};
+        if (r < m) {
+            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + (size_t)r * k + (size_t)kb * MD_KB) + lane);
+            f[0] = H::to_float(uint16_t(raw.x & 0xffff)); f[1] = H::to_float(uint16_t(raw.x >> 16));
+            f[2] = H::to_float(uint16_t(raw.y & 0xffff)); f[3] = H::to_float(uint16_t(raw.y >> 16));
+        }
+        float amax = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3])));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        int e = 0;                                           // x' = x * 2^e has its block maximum in [2^13, 2^14)
+        if (amax > 0.f && amax < 3.0e38f) e = 13 - (int((__float_as_uint(amax) >> 23) & 0xff) - 127);
+        e = e < -100 ? -100 : (e > 100 ? 100 : e);
+        const float up = __uint_as_float(uint32_t(127 + e) << 23);
+        int xi[4], sum = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float v = fminf(fmaxf(f[j] * up, -16384.f), 16384.f);   // NaN -> -16384: garbage in, bounded garbage out
+            xi[j] = __float2int_rn(v);
+            sum += xi[j];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        int lo[4], hi[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { lo[j] = ((xi[j] + 128) & 255) - 128; hi[j] = (xi[j] - lo[j]) >> 8; }
+        const int rh = r, rl = bm + r;                        // tile rows of the two limbs
+        auto row_base = [&](int R) { return tile + (R >> 3) * 1024 + (R & 7) * 128; };
+        auto slot_addr = [&](unsigned char* base, int R, int p) { return base + ((((p >> 4) ^ (R & 7)) << 4) | (p & 15)); };
+        if constexpr (BITS == 4) {
+            // k = 4 lane + j sits in word rw = lane / 2 at nibble i = (lane % 2) * 4 + j; slot = 8 rw + i / 2 (+ 4 for odd i)
+            const int rw = lane >> 1, i0 = (lane & 1) * 4;
+            const int pe_ = 8 * rw + i0 / 2, po = pe_ + 4;
+            *reinterpret_cast<uint16_t*>(slot_addr(row_base(rh), rh, pe_)) = uint16_t((hi[0] & 255) | ((hi[2] & 255) << 8));
+            *reinterpret_cast<uint16_t*>(slot_addr(row_base(rh), rh, po)) = uint16_t((hi[1] & 255) | ((hi[3] & 255) << 8));
+            *reinterpret_cast<uint16_t*>(slot_addr(row_base(rl), rl, pe_)) = uint16_t((lo[0] & 255) | ((lo[2] & 255) << 8));
+            *reinterpret_cast<uint16_t*>(slot_addr(row_base(rl), rl, po)) = uint16_t((lo[1] & 255) | ((lo[3] & 255) << 8));
+        } else {
+            const int p = 4 * lane;                           // bytes of a word are consecutive k: slot = k
+            *reinterpret_cast<uint32_t*>(slot_addr(row_base(rh), rh, p)) =
+                uint32_t(hi[0] & 255) | (uint32_t(hi[1] & 255) << 8) | (uint32_t(hi[2] & 255) << 16) | (uint32_t(hi[3] & 255) << 24);
+            *reinterpret_cast<uint32_t*>(slot_addr(row_base(rl), rl, p)) =
+                uint32_t(lo[0] & 255) | (uint32_t(lo[1] & 255) << 8) | (uint32_t(lo[2] & 255) << 16) | (uint32_t(lo[3] & 255) << 24);
+        }
+        if (lane == 0) {
+            sums[r] = sum;
+            pes[r] = r < m ? __uint_as_float(uint32_t(127 - e) << 23) : 0.f;
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------------------------
+// main kernel
+// ----------------------------------------------------------------------------------------------
+template <int BITS, typename T, int BM>
+__global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_s,
+                                                                  const __grid_constant__ CUtensorMap tmap_z, const MdParams p) {
+    using C = MdCfg<BITS, BM>;
+    using H = F16x2<T>;
+
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar0 = sbase + C::OFF_BAR;
+    auto bar_pfull = [&](int s) { return bar0 + 8u * s; };
+    auto bar_pempty = [&](int s) { return bar0 + 8u * (C::PST + s); };
+    auto bar_bfull = [&](int s) { return bar0 + 8u * (2 * C::PST + s); };
+    auto bar_bempty = [&](int s) { return bar0 + 8u * (2 * C::PST + C::BST + s); };
+    auto bar_afull = [&](int s) { return bar0 + 8u * (2 * C::PST + 2 * C::BST + s); };
+    auto bar_aempty = [&](int s) { return bar0 + 8u * (2 * C::PST + 2 * C::BST + C::AST + s); };
+    auto bar_dfull = [&](int s) { return bar0 + 8u * (2 * C::PST + 2 * C::BST + 2 * C::AST + s); };
+    auto bar_dempty = [&](int s) { return bar0 + 8u * (2 * C::PST + 2 * C::BST + 2 * C::AST + 2 + s); };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::NBARS * 8);
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int cta = blockIdx.x;
+    const int x0 = cta * p.per + (cta < p.rem ? cta : p.rem);
+    const int nrun = p.per + (cta < p.rem ? 1 : 0);
+
+    if (tid == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < C::PST; ++s) { mbar_init(bar_pfull(s), 1); mbar_init(bar_pempty(s), MD_WORKERS); }
+        for (int s = 0; s < C::BST; ++s) { mbar_init(bar_bfull(s), 1); mbar_init(bar_bempty(s), MD_WORKERS); }
+        for (int s = 0; s < C::AST; ++s) { mbar_init(bar_afull(s), MD_WORKERS); mbar_init(bar_aempty(s), 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(bar_dfull(s), 1); mbar_init(bar_dempty(s), MD_WORKERS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == MD_W_MMA) tc_alloc<512>(smem_u32(tmem_slot));
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_a = tmem_base + C::D_COLS;
+    auto wait = [&](uint32_t bar, uint32_t parity) { return md_wait(bar, parity, &abort_flag); };
+
+    // first / last CTA with a unit of column tile t
+    auto owner = [&](int u) -> int {
+        const int big = p.rem * (p.per + 1);
+        return u < big ? u / (p.per + 1) : p.rem + (u - big) / p.per;
+    };
+
+    if (warp == MD_W_PROD) {
+        // ------------------------------ producer: one lane ------------------------------
+        if (lane == 0) {
+            int tile = x0 / p.kbt, kb = x0 - tile * p.kbt;
+            bool ok = true;
+            const uint32_t ptx = (uint32_t)(C::W_BYTES + C::S_BYTES + (p.has_zeros ? C::Z_BYTES : 0));
+            // The packed weights, scales and zero words do not depend on the previous kernel in the stream: the first
+            // stages are requested before the wait for it (programmatic dependent launch).  The B tiles do (the pre-pass writes them).
+            int issued_p = 0;
+            auto issue_p = [&](int i, int t, int b) {
+                const int ps = i % C::PST;
+                const uint32_t dst = sbase + C::OFF_P + ps * C::P_STAGE;
+                mbar_expect_tx(bar_pfull(ps), ptx);
+                tma_load_2d(dst, &tmap_q, t * C::COLS, b * C::PROWS, bar_pfull(ps));
+                tma_load_2d(dst + C::W_BYTES, &tmap_s, t * C::COLS, b / p.kpg, bar_pfull(ps));
+                if (p.has_zeros) tma_load_2d(dst + C::W_BYTES + C::S_BYTES, &tmap_z, t * C::COLS / C::PACK, b / p.kpg, bar_pfull(ps));
+            };
+            int pt = tile, pb = kb;
+            if (p.pdl) {
+                for (; issued_p < nrun && issued_p < C::PST; ++issued_p) {
+                    issue_p(issued_p, pt, pb);
+                    if (++pb == p.kbt) { pb = 0; ++pt; }
+                }
+                griddep_launch_dependents();
+                griddep_wait();
+            }
+            for (int i = 0; i < nrun && ok; ++i) {
+                if (i >= issued_p) {
+                    const int ps = i % C::PST;
+                    if (!wait(bar_pempty(ps), ((i / C::PST) & 1) ^ 1)) { ok = false; break; }
+                    issue_p(i, pt, pb);
+                    ++issued_p;
+                    if (++pb == p.kbt) { pb = 0; ++pt; }
+                }
+                const int bs = i % C::BST;
+                if (!wait(bar_bempty(bs), ((i / C::BST) & 1) ^ 1)) { ok = false; break; }
+                mbar_expect_tx(bar_bfull(bs), (uint32_t)C::B_COPY);
+                md_bulk_load(sbase + C::OFF_B + bs * C::B_STAGE, p.xl + (size_t)kb * C::B_COPY, (uint32_t)C::B_COPY, bar_bfull(bs));
+                if (++kb == p.kbt) { kb = 0; ++tile; }
+            }
+        }
+    } else if (warp == MD_W_MMA) {
+        // ------------------------------ MMA issuer: one lane ------------------------------
+        if (lane == 0) {
+            // kind::i8: D s32 (2 << 4), A unsigned 8-bit (0 << 7), B signed 8-bit (1 << 10), K-major both, N = 2 BM, M = 128
+            const uint32_t idesc = (2u << 4) | (1u << 10) | ((uint32_t)(C::NB >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+            bool ok = true;
+            for (int i = 0; i < nrun && ok; ++i) {
+                const int as = i % C::AST, bs = i % C::BST, db = i & 1;
+                if (!wait(bar_afull(as), (i / C::AST) & 1)) { ok = false; break; }
+                if (!wait(bar_bfull(bs), (i / C::BST) & 1)) { ok = false; break; }
+                if (!wait(bar_dempty(db), ((i >> 1) & 1) ^ 1)) { ok = false; break; }
+                tc_fence_after();
+                const uint64_t bdesc = tc_desc_sw128(sbase + C::OFF_B + bs * C::B_STAGE);
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4)
+#pragma unroll
+                    for (int nt = 0; nt < C::NT; ++nt)
+                        md_mma_i8(tmem_base + (uint32_t)((db * C::NT + nt) * C::NB), tmem_a + (uint32_t)((as * C::NT + nt) * 32 + k4 * 8),
+                                  bdesc + (uint64_t)(k4 * 2), idesc, k4 ? 1u : 0u);
+                tc_commit(bar_aempty(as));
+                tc_commit(bar_dfull(db));
+            }
+        }
+    } else {
+        // ------------------------------ workers ------------------------------
+        const int q4 = warp & 3;                              // TMEM lane quarter (= warp % 4)
+        const int jj = warp >> 2;
+        const int nt = C::NT == 2 ? (jj & 1) : 0;
+        const int rs = C::NT == 2 ? (jj >> 1) : jj;           // which split of the k-block (conversion) and of the rows (fold)
+        const int cl = nt * 128 + q4 * 32 + lane;             // column inside the CTA tile
+        const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
+        const int r0 = rs * C::RW;
+        constexpr uint32_t ZMASK = (1u << BITS) - 1u;
+        const T* __restrict__ bias = reinterpret_cast<const T*>(p.bias);
+        uint16_t* __restrict__ out = reinterpret_cast<uint16_t*>(p.out);
+        const uint16_t* __restrict__ resid = reinterpret_cast<const uint16_t*>(p.residual);
+        const bool fused_ar = ar_active(p.ar);
+        unsigned epoch = 0u;
+        bool epoch_read = false;
+
+        float acc[C::RW];
+#pragma unroll
+        for (int r = 0; r < C::RW; ++r) acc[r] = 0.f;
+        float s_prev = 0.f; int zp1_prev = 0;
+        bool ok = true;
+
+        // the finished part of column tile `tile`: stored, or left as an fp32 partial slice that the last warp to arrive sums
+        auto flush = [&](int tile) {
+            const int col = tile * C::COLS + cl;
+            const bool okc = col < p.n;
+            const int cf = owner(tile * p.kbt), cla = owner(tile * p.kbt + p.kbt - 1);
+            const int nparts = cla - cf + 1;
+            bool write = true;
+            if (nparts > 1) {
+                float* part = p.partial + (size_t)(cta + tile) * BM * C::COLS;
+#pragma unroll
+                for (int r = 0; r < C::RW; ++r) __stcg(part + (size_t)(r0 + r) * C::COLS + cl, acc[r]);
+                __threadfence();
+                __syncwarp();
+                const int cidx = tile * MD_WORKERS + warp;     // one 16-bit counter per (tile, worker warp), two per word
+                const int sh = (cidx & 1) * 16;
+                unsigned old = 0;
+                if (lane == 0) old = (atomicAdd(p.counters + (cidx >> 1), 1u << sh) >> sh) & 0xffffu;
+                old = __shfl_sync(0xffffffffu, old, 0);
+                write = old == unsigned(nparts - 1);
+                if (write) {
+                    __threadfence();
+#pragma unroll
+                    for (int r = 0; r < C::RW; ++r) acc[r] = 0.f;
+                    for (int c = cf; c <= cla; ++c) {           // CTA order: the same sum whoever arrives last
+                        const float* src = p.partial + (size_t)(c + tile) * BM * C::COLS + (size_t)r0 * C::COLS + cl;
+#pragma unroll
+                        for (int r = 0; r < C::RW; ++r) acc[r] += __ldcg(src + (size_t)r * C::COLS);
+                    }
+                    if (lane == 0) atomicSub(p.counters + (cidx >> 1), unsigned(nparts) << sh);
+                }
+            }
+            if (write && okc) {
+                const float bv = bias ? H::to_float(reinterpret_cast<const uint16_t*>(bias)[col]) : 0.f;
+                if (fused_ar && !epoch_read) { epoch = ar_epoch(p.ar); epoch_read = true; }
+#pragma unroll
+                for (int r = 0; r < C::RW; ++r) {
+                    const int row = r0 + r;
+                    if (row < p.m) {
+                        float v = acc[r] + bv;
+                        if (fused_ar) v = ar_exchange1(p.ar, epoch, (size_t)row * p.n + col, v);
+                        if (resid) v += H::to_float(resid[(size_t)row * p.n + col]);
+                        out[(size_t)row * p.n + col] = H::from_float(v);
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < C::RW; ++r) acc[r] = 0.f;
+        };
+
+        int tile = x0 / p.kbt, kb = x0 - tile * p.kbt;        // of the unit being CONVERTED
+        int f_tile = tile, f_kb = kb;                          // of the unit being FOLDED (one behind)
+        if (p.pdl) griddep_wait();                              // before the first read of anything an earlier kernel wrote (out / partial / x tiles)
+        for (int i = 0; i <= nrun && ok; ++i) {
+            float s_cur = 0.f; int zp1_cur = 0;
+            if (i < nrun) {
+                const int ps = i % C::PST;
+                if (!wait(bar_pfull(ps), (i / C::PST) & 1)) { ok = false; break; }
+                const unsigned char* st = smem + C::OFF_P + ps * C::P_STAGE;
+                const uint32_t* pk = reinterpret_cast<const uint32_t*>(st) + (size_t)(rs * C::WPW) * C::COLS + cl;
+                uint32_t wq[C::WPW];
+#pragma unroll
+                for (int r = 0; r < C::WPW; ++r) wq[r] = pk[r * C::COLS];
+                s_cur = H::to_float(reinterpret_cast<const uint16_t*>(st + C::W_BYTES)[cl]);
+                zp1_cur = p.has_zeros ? int((reinterpret_cast<const uint32_t*>(st + C::W_BYTES + C::S_BYTES)[cl / C::PACK] >> ((cl % C::PACK) * BITS)) & ZMASK) + 1
+                                      : p.zp1_const;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_pempty(ps));   // the stage is in registers
+                uint32_t a[C::AREGS];
+                if constexpr (BITS == 4) {
+#pragma unroll
+                    for (int r = 0; r < C::WPW; ++r) {
+                        a[2 * r] = wq[r] & 0x0f0f0f0fu;              // nibbles 0, 2, 4, 6 as bytes
+                        a[2 * r + 1] = (wq[r] >> 4) & 0x0f0f0f0fu;   // nibbles 1, 3, 5, 7
+                    }
+                } else {
+#pragma unroll
+                    for (int r = 0; r < C::WPW; ++r) a[r] = wq[r];
+                }
+                const int as = i % C::AST;
+                if (!wait(bar_aempty(as), ((i / C::AST) & 1) ^ 1)) { ok = false; break; }
+                tc_fence_after();
+                md_st<C::AREGS>(tmem_a + lane_base + (uint32_t)((as * C::NT + nt) * 32 + rs * C::AREGS), a);
+                tc_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_afull(as));
+                if (++kb == p.kbt) { kb = 0; ++tile; }
+            }
+            if (i >= 1) {
+                const int j = i - 1, db = j & 1, bs = j % C::BST;
+                if (!wait(bar_dfull(db), (j >> 1) & 1)) { ok = false; break; }
+                if (!wait(bar_bfull(bs), (j / C::BST) & 1)) { ok = false; break; }     // completed long ago: makes the bulk copy's bytes visible here
+                tc_fence_after();
+                uint32_t dh[C::RW], dl[C::RW];
+                const uint32_t dbase = tmem_base + lane_base + (uint32_t)((db * C::NT + nt) * C::NB + r0);
+                tc_ld<C::RW>(dbase, dh);
+                tc_ld<C::RW>(dbase + BM, dl);
+                const unsigned char* bst = smem + C::OFF_B + bs * C::B_STAGE + C::B_TILE;
+                int sx[C::RW]; float pe[C::RW];
+#pragma unroll
+                for (int r = 0; r < C::RW; r += 4) {
+                    const int4 sv = *reinterpret_cast<const int4*>(bst + (r0 + r) * 4);
+                    const float4 pv = *reinterpret_cast<const float4*>(bst + BM * 4 + (r0 + r) * 4);
+                    sx[r] = sv.x; sx[r + 1] = sv.y; sx[r + 2] = sv.z; sx[r + 3] = sv.w;
+                    pe[r] = pv.x; pe[r + 1] = pv.y; pe[r + 2] = pv.z; pe[r + 3] = pv.w;
+                }
+                tc_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) { mbar_arrive(bar_dempty(db)); mbar_arrive(bar_bempty(bs)); }
+#pragma unroll
+                for (int r = 0; r < C::RW; ++r) {
+                    const int v = int(dh[r]) * 256 + int(dl[r]) - zp1_prev * sx[r];   // sum_k (q - (z + 1)) x'
+                    acc[r] = fmaf(s_prev * pe[r], __int2float_rn(v), acc[r]);
+                }
+                const bool tile_ends = (f_kb == p.kbt - 1) || (j == nrun - 1);
+                if (tile_ends) flush(f_tile);
+                if (++f_kb == p.kbt) { f_kb = 0; ++f_tile; }
+            }
+            s_prev = s_cur; zp1_prev = zp1_cur;
+        }
+        if (fused_ar) {
+            // every CTA of the grid reports when its exchanges are done; the last one publishes the epoch for the next call
+            asm volatile("bar.sync 1, %0;" ::"n"(MD_WORKERS * 32) : "memory");
+            if (tid == 0) ar_leave(p.ar, epoch_read ? epoch : ar_epoch(p.ar), gridDim.x);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == MD_W_MMA) {
+        tc_fence_after();
+        tc_dealloc<512>(tmem_base);
+    }
+    if (tid == 0 && abort_flag && p.err) atomicExch(p.err, 5u);
+}
+
+template <int BITS, typename T, int BM>
+int launch_inst(cudaStream_t st, const CUtensorMap& mq, const CUtensorMap& ms, const CUtensorMap& mz, const MdParams& p, int grid) {
+    using C = MdCfg<BITS, BM>;
+    auto kern = qgemm_mid_kernel<BITS, T, BM>;
+    static bool configured[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return MT_ERR_CUDA; }
+    if (!configured[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL) != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
+        configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(MD_THREADS); cfg.dynamicSmemBytes = C::TOTAL; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = p.pdl ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, kern, mq, ms, mz, p) != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
+    return MT_OK;
+}
+
+template <int BITS, typename T>
+int launch_bm(cudaStream_t st, const CUtensorMap& mq, const CUtensorMap& ms, const CUtensorMap& mz, const MdParams& p, int grid, int bm) {
+    if (bm == 16) return launch_inst<BITS, T, 16>(st, mq, ms, mz, p, grid);
+    if (bm == 32) return launch_inst<BITS, T, 32>(st, mq, ms, mz, p, grid);
+    return launch_inst<BITS, T, 64>(st, mq, ms, mz, p, grid);
+}
+
+template <typename T>
+int launch_prep(cudaStream_t st, const void* x, unsigned char* xl, int m, int k, int bm, int bits, int pdl) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(k / MD_KB); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+    const T* xt = static_cast<const T*>(x);
+    cudaError_t e = bits == 4 ? cudaLaunchKernelEx(&cfg, xprep_kernel<T, 4>, xt, xl, m, k, bm, pdl)
+                              : cudaLaunchKernelEx(&cfg, xprep_kernel<T, 8>, xt, xl, m, k, bm, pdl);
+    if (e != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
+    return MT_OK;
+}
+
+struct MdPlan { int bm, cols, tiles, kbt, grid; size_t partial_bytes, xl_bytes; };
+
+MdPlan plan(int m, int n, int k) {
+    MdPlan pl;
+    pl.bm = m <= 16 ? 16 : m <= 32 ? 32 : 64;
+    pl.cols = pl.bm <= 32 ? 256 : 128;
+    pl.tiles = (n + pl.cols - 1) / pl.cols;
+    pl.kbt = k / MD_KB;
+    const long long units = (long long)pl.tiles * pl.kbt;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    long long g = units / 4;                            // at least 4 k-blocks per CTA
+    if (g < 1) g = 1;
+    if (g > sms) g = sms;
+    pl.grid = (int)g;
+    pl.partial_bytes = (size_t)(pl.grid + pl.tiles) * pl.bm * pl.cols * 4;
+    pl.xl_bytes = (size_t)pl.kbt * (2 * pl.bm * 128 + pl.bm * 8);
+    return pl;
+}
+
+}  // namespace
+
+bool mid_supported(const QGemmArgs& a) {
+    if (a.g_idx != nullptr || a.m < 1 || a.groups < 1 || a.k % a.groups != 0) return false;
+    const int gs = a.k / a.groups;
+    if (gs % MD_KB != 0 || a.n % 32 != 0 || a.n < 32) return false;
+    if (a.workspace == nullptr || a.workspace_bytes < kCounterBytes) return false;
+    if (!get_tensor_map_encoder()) return false;
+    const MdPlan pl = plan(a.m < 64 ? a.m : 64, a.n, a.k);
+    if ((long long)pl.tiles * MD_WORKERS >= 2LL * (kMaxTiles - 1)) return false;   // 16-bit counters, two per word, the last word is the error word
+    if ((long long)pl.tiles * pl.kbt > (1LL << 30)) return false;
+    return pl.partial_bytes + pl.xl_bytes <= a.workspace_bytes - kCounterBytes;
+}
+
+size_t mid_workspace_bytes(int m, int n, int k) {
+    if (k % MD_KB != 0) return 0;
+    const MdPlan pl = plan(m < 64 ? m : 64, n, k);
+    return pl.partial_bytes + pl.xl_bytes + 256;
+}
+
+int launch_mid(cudaStream_t st, const QGemmArgs& a) {
+    if (!mid_supported(a)) return MT_ERR_UNSUPPORTED;
+    EncodeTiledFn enc = get_tensor_map_encoder();
+    const int pack = 32 / a.bits;
+    const int m0 = a.m < 64 ? a.m : 64;
+    const MdPlan pl0 = plan(m0, a.n, a.k);
+    CUtensorMap mq, ms, mz;
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)a.n, (cuuint64_t)(a.k / pack)};
+        cuuint64_t strides[1] = {(cuuint64_t)a.n * 4};
+        cuuint32_t box[2] = {(cuuint32_t)pl0.cols, (cuuint32_t)(MD_KB / pack)};
+        cuuint32_t es[2] = {1, 1};
+        if (enc(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(a.qweight), dims, strides, box, es,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return MT_ERR_CUDA;
+    }
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)a.n, (cuuint64_t)a.groups};
+        cuuint64_t strides[1] = {(cuuint64_t)a.n * 2};
+        cuuint32_t box[2] = {(cuuint32_t)pl0.cols, 1};
+        cuuint32_t es[2] = {1, 1};
+        if (enc(&ms, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(a.scales), dims, strides, box, es,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return MT_ERR_CUDA;
+    }
+    mz = ms;
+    if (a.qzeros) {
+        cuuint64_t dims[2] = {(cuuint64_t)(a.n / pack), (cuuint64_t)a.groups};
+        cuuint64_t strides[1] = {(cuuint64_t)(a.n / pack) * 4};
+        cuuint32_t box[2] = {(cuuint32_t)(pl0.cols / pack), 1};
+        cuuint32_t es[2] = {1, 1};
+        if (enc(&mz, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(a.qzeros), dims, strides, box, es,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return MT_ERR_CUDA;
+    }
+    for (int r0 = 0; r0 < a.m; r0 += 64) {
+        const int m = a.m - r0 < 64 ? a.m - r0 : 64;
+        MdPlan pl = plan(m, a.n, a.k);
+        if (pl.cols != pl0.cols) {                       // a last pass with fewer rows keeps the first pass's tile width (one set of tensor maps)
+            pl.bm = pl0.cols == 128 ? 64 : pl.bm;
+            pl.cols = pl0.cols; pl.tiles = pl0.tiles; pl.grid = pl0.grid;
+            pl.partial_bytes = (size_t)(pl.grid + pl.tiles) * pl.bm * pl.cols * 4;
+            pl.xl_bytes = (size_t)pl.kbt * (2 * pl.bm * 128 + pl.bm * 8);
+        }
+        MdParams p;
+        unsigned char* base = static_cast<unsigned char*>(a.workspace) + kCounterBytes;
+        p.partial = reinterpret_cast<float*>(base);
+        unsigned char* xl = base + ((pl.partial_bytes + 255) & ~(size_t)255);
+        p.xl = xl;
+        p.bias = a.bias;
+        p.out = static_cast<char*>(a.out) + (size_t)r0 * a.n * 2;
+        p.residual = a.residual ? static_cast<const char*>(a.residual) + (size_t)r0 * a.n * 2 : nullptr;
+        p.counters = static_cast<unsigned*>(a.workspace);
+        p.err = p.counters + (kMaxTiles - 1);
+        p.m = m; p.n = a.n; p.k = a.k;
+        p.has_zeros = a.qzeros ? 1 : 0;
+        p.tiles = pl.tiles; p.kbt = pl.kbt; p.kpg = (a.k / a.groups) / MD_KB;
+        p.units = pl.tiles * pl.kbt; p.per = p.units / pl.grid; p.rem = p.units % pl.grid;
+        p.zp1_const = 1 << (a.bits - 1);
+        p.pdl = (a.flags & MT_FLAG_PDL) ? 1 : 0;
+        p.ar = make_ar_params(a);
+        if (p.ar.world > 1 && (a.m > 64 || (size_t)a.m * a.n * 8 > p.ar.slot_bytes)) return MT_ERR_TOO_LARGE;
+        const void* xrow = static_cast<const char*>(a.x) + (size_t)r0 * a.k * 2;
+        int rc = a.dtype == MT_F16 ? launch_prep<__half>(st, xrow, xl, m, a.k, pl.bm, a.bits, p.pdl)
+                                   : launch_prep<__nv_bfloat16>(st, xrow, xl, m, a.k, pl.bm, a.bits, p.pdl);
+        if (rc != MT_OK) return rc;
+        if (a.bits == 4) rc = a.dtype == MT_F16 ? launch_bm<4, __half>(st, mq, ms, mz, p, pl.grid, pl.bm) : launch_bm<4, __nv_bfloat16>(st, mq, ms, mz, p, pl.grid, pl.bm);
+        else rc = a.dtype == MT_F16 ? launch_bm<8, __half>(st, mq, ms, mz, p, pl.grid, pl.bm) : launch_bm<8, __nv_bfloat16>(st, mq, ms, mz, p, pl.grid, pl.bm);
+        if (rc != MT_OK) return rc;
+    }
+    return MT_OK;
+}
+
+}  // namespace mt
