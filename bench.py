@@ -818,26 +818,29 @@ def run_single_shape(args):
         sets.append((qw, qz, sc))
     x = torch.randn((m, k), device=dev, dtype=torch.float32).to(dtype)
     out = torch.empty((m, n), device=dev, dtype=dtype)
-    flags = {"auto": 0, "ring": 1, "tc": 2, "vec": 16, "umma": 32}[args.kernel] | (4 if args.pdl and args.kernel in ("auto", "ring", "vec") else 0)
+    flags = {"auto": 0, "ring": 1, "tc": 2, "vec": 16, "umma": 32, "mid": 128}[args.kernel] | (4 if args.pdl and args.kernel in ("auto", "ring", "vec") else 0)
 
     def one():
         for qw, qz, sc in sets:
             M.quantized_matrix_multiply(x, qw, qz, sc, None, bits=bits, out=out, flags=flags)
-    for _ in range(args.warmup):
-        one()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        one()
-    e1.record()
-    torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) * 1e3 / (args.steps * copies)
+    if args.no_graph:
+        for _ in range(args.warmup):
+            one()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            one()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (args.steps * copies)
+    else:
+        us = _graph_time_us([one], reps=max(1, args.steps)) / copies
     hbm_peak, kind = peaks()
     ab = k * n * bits // 8 + (k // GROUP) * n * 2 + (k // GROUP) * n * bits // 8 + 2 * m * k + 2 * m * n
     line = {"single_shape": [k, n], "m": m, "bits": bits, "kernel": args.kernel, "us_per_launch": us,
             "weight_GBps": weight_bytes(k, n, bits) / us / 1e3, "TFLOPs": 2.0 * m * n * k / us / 1e6,
-            "hbm_frac": ab / us / 1e3 / hbm_peak, "launch": "eager, %d weight sets in rotation" % copies}
+            "hbm_frac": ab / us / 1e3 / hbm_peak, "launch": "%s, %d weight sets in rotation" % ("eager" if args.no_graph else "cuda graph", copies)}
     ppath = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(ppath):
         line["tensor_frac_of_burst"] = line["TFLOPs"] / float(json.load(open(ppath))["bf16_tflops"])
@@ -864,7 +867,7 @@ def main():
     ap.add_argument("--decode-layer", action="store_true", help="time whole decoder layers (norms, rope, attention, fused linears) for one token")
     ap.add_argument("--attention", action="store_true", help="time decode attention alone over --context cached positions")
     ap.add_argument("--context", type=int, default=4096, help="--decode-layer: cached positions")
-    ap.add_argument("--kernel", default="auto", choices=["auto", "ring", "tc", "vec", "umma"])
+    ap.add_argument("--kernel", default="auto", choices=["auto", "ring", "tc", "vec", "umma", "mid"])
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--bf16", action="store_true")
     args = ap.parse_args()

@@ -22,7 +22,7 @@ if not os.path.exists(LIB_PATH):
 lib = ctypes.CDLL(LIB_PATH)
 
 MT_F16, MT_BF16 = 0, 1
-FLAG_FORCE_SMALL, FLAG_FORCE_TC, FLAG_PDL, FLAG_FORCE_VEC, FLAG_FORCE_UMMA, FLAG_AR_SHORT_WAIT = 1, 2, 4, 16, 32, 64
+FLAG_FORCE_SMALL, FLAG_FORCE_TC, FLAG_PDL, FLAG_FORCE_VEC, FLAG_FORCE_UMMA, FLAG_AR_SHORT_WAIT, FLAG_FORCE_MID = 1, 2, 4, 16, 32, 64, 128
 ERR_PEER_TIMEOUT = -12
 COUNTER_BYTES = 16384
 STATIC_SCRATCH_BYTES = 8 << 20

@@ -186,6 +186,10 @@ size_t mt_workspace_bytes(int m, int n, int k, int bits) {
         const size_t mid = umma_workspace_bytes(m, n, k);
         if (mid > bytes) bytes = mid;
     }
+    if (m > 2 && k % 128 == 0) {                                // partial tiles and the two-limb activation tiles of the integer kernel
+        const size_t mid = mid_workspace_bytes(m, n, k);
+        if (mid > bytes) bytes = mid;
+    }
     return kCounterBytes + bytes;
 }
 
@@ -259,12 +263,15 @@ int mt_qgemm(void* stream, const void* x, const uint32_t* qweight, const int32_t
     if (flags & MT_FLAG_FORCE_SMALL) return launch_small(st, a);
     if (flags & MT_FLAG_FORCE_VEC) return vec_supported(a) ? launch_vec(st, a) : MT_ERR_UNSUPPORTED;
     if (flags & MT_FLAG_FORCE_UMMA) return umma_supported(a) ? launch_umma(st, a) : MT_ERR_UNSUPPORTED;
-    // Mid-size batches: the tcgen05 kernel with sixteen converting warps holds 0.24-0.31 of HBM peak up to
-    // M = 64 on large weights, where the register-ring kernel falls from 0.25 (M = 16) to 0.13 (M = 64) with
-    // the legacy mma.sync rate; it costs ~12 us of set-up, so small weights stay on the ring kernel until
-    // M > 32.  Between 64 and 128 rows two passes of it beat the prefill kernels when K is deep (their
-    // grid has no split along K).
+    if (flags & MT_FLAG_FORCE_MID) return mid_supported(a) ? launch_mid(st, a) : MT_ERR_UNSUPPORTED;
+    // Mid-size batches.  Up to 32 rows on weights of at least 32 M elements the integer tensor-core kernel (packed
+    // nibbles as unsigned bytes, two-limb activations, scale and zero point folded per 128 values of k) holds
+    // 0.35-0.5 of HBM peak; it pays ~10 us of set-up (a pre-pass launch, tensor maps, tensor-memory allocation), so
+    // small weights stay on the register-ring kernel.  From 33 to 64 rows its fold costs more than dequantizing, and
+    // the tcgen05 kernel whose sixteen warps rebuild fp16 weights takes over; between 64 and 128 rows two passes of
+    // that one beat the prefill kernels when K is deep (their grid has no split along K).
     const long long weights = (long long)k * n;
+    if (m > 2 && m <= 32 && weights >= (32LL << 20) && mid_supported(a)) return launch_mid(st, a);
     if (umma_supported(a)) {
         if (m > 32 && m <= 64) return launch_umma(st, a);
         if (m > 8 && m <= 32 && weights >= (128LL << 20)) return launch_umma(st, a);
@@ -305,6 +312,10 @@ static int qgemm_allreduce_impl(void* stream, const void* x, const uint32_t* qwe
     if (!(flags & MT_FLAG_FORCE_SMALL) && m <= 2 && vec_supported(a)) {
         a.residual = residual;                                   // the GEMV adds it to the reduced sum before its one rounding
         return launch_vec(st, a);
+    }
+    if (!(flags & MT_FLAG_FORCE_SMALL) && m > 2 && m <= 32 && (long long)k * n >= (32LL << 20) && mid_supported(a)) {
+        a.residual = residual;                                   // the integer kernel exchanges and adds it in its epilogue too
+        return launch_mid(st, a);
     }
     rc = launch_small(st, a);
     if (rc == MT_OK && residual) rc = launch_add_residual(st, out, residual, m, n, dtype);

@@ -73,6 +73,38 @@ __device__ __forceinline__ float4 ar_exchange(const ArParams& a, unsigned epoch,
     return sum;
 }
 
+// The same exchange for ONE value at a time (a thread that owns a column, not four adjacent ones): one 8-byte cell per
+// peer.  Split in two so that a thread with several values first pushes them all and then collects them all: the
+// NVLink round trip is paid once, not once per value.
+__device__ __forceinline__ void ar_push1(const ArParams& a, unsigned epoch, size_t cell, float v) {
+    const int slot = int(epoch & 1u);
+    const unsigned u = __float_as_uint(v);
+    for (int r = 0; r < a.world; ++r) {
+        if (r == a.rank) continue;
+        unsigned char* dst = a.peers[r] + kArDataOffset + ((size_t)slot * a.world + a.rank) * a.slot_bytes + cell * 8;
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(u), "r"(epoch) : "memory");
+    }
+}
+__device__ __forceinline__ float ar_pull1(const ArParams& a, unsigned epoch, size_t cell, float v) {
+    const int slot = int(epoch & 1u);
+    const unsigned char* mine = a.peers[a.rank];
+    float sum = 0.f;
+    for (int r = 0; r < a.world; ++r) {
+        if (r == a.rank) { sum += v; continue; }
+        const unsigned char* src = mine + kArDataOffset + ((size_t)slot * a.world + r) * a.slot_bytes + cell * 8;
+        uint2 c;
+        int spins = 0;
+        for (;;) {
+            asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(c.x), "=r"(c.y) : "l"(src) : "memory");
+            if (c.y == epoch) break;
+            if (++spins > a.spin_limit) { if (a.err) atomicExch(a.err, 4u); break; }   // a peer never arrived: give up, flag the error (the host must read it)
+            if (spins > 32) __nanosleep(32);
+        }
+        sum += __uint_as_float(c.x);
+    }
+    return sum;
+}
+
 // Called by ONE thread of every CTA of the grid, after the CTA's last exchange: the last CTA to
 // leave publishes the epoch for the next call.
 __device__ __forceinline__ void ar_leave(const ArParams& a, unsigned epoch, unsigned total_ctas) {

@@ -35,7 +35,7 @@ def _nvcc() -> str:
 
 def _units():
     units = [("dequant.cu", "dequant.o", []), ("api.cu", "api.o", []), ("qgemm_tc.cu", "qgemm_tc.o", []),
-             ("qgemm_w8.cu", "qgemm_w8.o", []), ("qgemm_vec.cu", "qgemm_vec.o", []), ("repack.cu", "repack.o", []), ("qgemm_umma.cu", "qgemm_umma.o", []), ("qgemm_w8vec.cu", "qgemm_w8vec.o", []), ("decode_ops.cu", "decode_ops.o", []), ("noalloc.cu", "noalloc.o", []), ("nccl_shim.cc", "nccl_shim.o", [])]
+             ("qgemm_w8.cu", "qgemm_w8.o", []), ("qgemm_vec.cu", "qgemm_vec.o", []), ("repack.cu", "repack.o", []), ("qgemm_umma.cu", "qgemm_umma.o", []), ("qgemm_mid.cu", "qgemm_mid.o", []), ("qgemm_w8vec.cu", "qgemm_w8vec.o", []), ("decode_ops.cu", "decode_ops.o", []), ("noalloc.cu", "noalloc.o", []), ("nccl_shim.cc", "nccl_shim.o", [])]
     for bits in (4, 8):
         for bf in (0, 1):
             units.append(("qgemm_small_inst.cu", f"qgemm_small_i{bits}_{'bf16' if bf else 'f16'}.o",

@@ -205,6 +205,9 @@ int launch_attention_decode(cudaStream_t st, const void* q, const void* k_cache,
 int launch_umma(cudaStream_t st, const QGemmArgs& a);           // tcgen05 with all-warp dequant, 2 < M <= 192, contiguous groups
 bool umma_supported(const QGemmArgs& a);
 size_t umma_workspace_bytes(int m, int n, int k);
+int launch_mid(cudaStream_t st, const QGemmArgs& a);            // integer tensor-core kernel, 2 < M (passes of 64), contiguous groups of a multiple of 128
+bool mid_supported(const QGemmArgs& a);
+size_t mid_workspace_bytes(int m, int n, int k);
 int launch_tc(cudaStream_t st, const QGemmArgs& a);             // tcgen05 path (any M), GPTQ layout without g_idx
 bool tc_supported(const QGemmArgs& a);
 

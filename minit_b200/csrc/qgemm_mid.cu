@@ -23,11 +23,12 @@
 //     which is the GPTQ formula (q - (z + 1)) * s applied to x' 2^-e.  The only approximation is the
 //     14-bit block-fixed-point x' (relative output error ~1e-4 of rms, far inside the 1e-2 bound).
 //
-// Roles (18 warps, one CTA per SM): 16 worker warps = (tile, TMEM lane quarter, split): a thread owns
-// one output column, converts its share of a k-block's words, and folds its share of the batch rows of
-// the PREVIOUS k-block while the tensor core works on the current one (two accumulator buffers);
-// 1 producer lane (TMA of the packed rows, scales and zero words of a k-block: 17 KB per stage, 8 stages;
-// one bulk copy of the B tile); 1 MMA lane.  Stream-K over (column tile, k-block) units as in the other
+// Roles (19 warps, one CTA per SM): two groups of 4 converter warps (a thread = one column of each 128-column tile: reads
+// the packed words from the stage, masks, one tcgen05.st per tile); 8 fold warps = (tile, TMEM lane quarter)
+// or (TMEM lane quarter, half of the batch rows): a thread owns one output column and folds the k-block the tensor core finished
+// while it works on the next one (two accumulator buffers), scale and zero word read straight from global
+// memory one k-block ahead; 6 producer lanes (TMA of the packed rows of a k-block, 16 KB per stage, 8 stages;
+// one bulk copy of the B tile; one lane cannot issue the copies fast enough); one MMA lane per tile.  Stream-K over (column tile, k-block) units as in the other
 // kernels; a tile shared by several CTAs is finished, slice by slice, by the last warp to arrive.
 // Every wait is bounded and reports through the workspace error word.
 #include "tma.cuh"
@@ -36,9 +37,19 @@
 namespace mt {
 namespace {
 
-constexpr int MD_WORKERS = 16;
-constexpr int MD_W_PROD = 16, MD_W_MMA = 17;
-constexpr int MD_THREADS = 18 * 32;
+#ifndef MD_FOLD_WARPS
+#define MD_FOLD_WARPS 8
+#endif
+constexpr int MD_FOLD = MD_FOLD_WARPS;             // fold warps: 0 .. MD_FOLD - 1
+#ifndef MD_FAST_NS
+#define MD_FAST_NS 20
+#endif
+#ifndef MD_SLOW_NS
+#define MD_SLOW_NS 400
+#endif
+constexpr int MD_CGROUPS = 2;                      // converter groups of four warps, alternating k-blocks
+constexpr int MD_W_CONV = MD_FOLD, MD_W_PROD = MD_FOLD + 4 * MD_CGROUPS, MD_W_MMA = MD_W_PROD + 1;   // then the producer warp and two MMA warps (column tile 0 and 1)
+constexpr int MD_THREADS = (MD_W_MMA + 2) * 32;
 constexpr int MD_KB = 128;                         // values of k per unit
 
 template <int BITS, int BM> struct MdCfg {
@@ -46,39 +57,45 @@ template <int BITS, int BM> struct MdCfg {
     static constexpr int PROWS = MD_KB / PACK;     // packed rows per k-block: 16 | 32
     static constexpr int NT = BM <= 32 ? 2 : 1;    // 128-column tiles per CTA tile
     static constexpr int COLS = NT * 128;
-    static constexpr int RS = 16 / (4 * NT);       // splits of the rows (fold) and of the k-block (conversion) per tile quarter: 2 | 4
-    static constexpr int RW = BM / RS;             // batch rows a worker folds: 8 | 16
-    static constexpr int WPW = PROWS / RS;         // packed words a worker converts per k-block
-    static constexpr int AREGS = 32 / RS;          // 32-bit TMEM columns a worker writes per k-block: 16 | 8
+    static constexpr int RS = MD_FOLD / (4 * NT);  // fold warps that share a (tile, lane quarter) split the batch rows: 1 | 2
+    static constexpr int RW = BM / RS;             // batch rows a fold warp handles: 16 | 32
+    static constexpr int RC = RW < 16 ? RW : 16;   // rows per tcgen05.ld
     static constexpr int NB = 2 * BM;              // MMA N: h rows then l rows
     static constexpr int D_COLS = 2 * NT * NB;     // two accumulator buffers
     static constexpr int A_STAGE = NT * 32;        // TMEM columns of one k-block of the A operand
-    static constexpr int AST = (512 - D_COLS) / A_STAGE >= 8 ? 8 : (512 - D_COLS) / A_STAGE;
+    static constexpr int AST = BM == 64 ? 4 : (512 - D_COLS) / A_STAGE;   // slots of the A operand, and of the activation stage: 6 | 4 | 4
     static constexpr int W_BYTES = PROWS * COLS * 4;
-    static constexpr int S_BYTES = COLS * 2;
-    static constexpr int Z_BYTES = COLS / PACK * 4;
-    static constexpr int P_STAGE = (W_BYTES + S_BYTES + Z_BYTES + 127) / 128 * 128;
-    static constexpr int PST = (136 * 1024) / P_STAGE;                 // ~136 KB of packed weights in flight per SM
+    static constexpr int P_STAGE = W_BYTES;
+    static constexpr int PST = (128 * 1024) / P_STAGE;                 // 128 KB of packed weights in flight per SM
     static constexpr int B_TILE = NB * 128;
     static constexpr int B_COPY = B_TILE + BM * 8;                    // tile + sum(x') [BM] int32 + 2^-e [BM] fp32
-    static constexpr int B_STAGE = B_TILE + 1024;
-    static constexpr int BST = 4;
+    static constexpr int S_BYTES = COLS * 2;                          // scales of the stage's group, this CTA tile's columns
+    static constexpr int Z_BYTES = COLS / PACK * 4;                   // zero words
+    static constexpr int OFF_S = B_TILE + 512, OFF_Z = B_TILE + 1024;
+    static constexpr int B_STAGE = B_TILE + 2048;
     static constexpr int OFF_P = 0;
     static constexpr int OFF_B = OFF_P + PST * P_STAGE;
-    static constexpr int OFF_BAR = OFF_B + BST * B_STAGE;
-    static constexpr int NBARS = 2 * PST + 2 * BST + 2 * AST + 4;
+    static constexpr int OFF_BAR = OFF_B + AST * B_STAGE;
+    static constexpr int NBARS = 2 * PST + 3 * AST;
     static constexpr int TOTAL = OFF_BAR + NBARS * 8 + 64 + 1024;
+    static_assert(BM * 8 <= 512 && S_BYTES <= 512 && Z_BYTES <= 1024, "activation stage layout");
     static_assert(D_COLS + AST * A_STAGE <= 512 && AST >= 3, "TMEM budget");
     static_assert(OFF_B % 1024 == 0, "B tiles need 1024-byte alignment");
     static_assert(TOTAL <= 227 * 1024, "shared memory budget");
 };
 
+#ifdef MD_TL
+#define MD_STAMP(slot, unit) do { if (blockIdx.x == 3 && (unit) < 64) reinterpret_cast<long long*>(p.counters + (30 << 18))[(unit) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define MD_STAMP(slot, unit) do { } while (0)
+#endif
+
 struct MdParams {
     const unsigned char* xl;      // pre-pass output: per k-block [B tile | sum(x') | 2^-e]
+    const void* scales; const uint32_t* qz;   // [G, N] T; [G, N / pack] or null (symmetric midpoint)
     const void* bias; void* out;
     float* partial; unsigned* counters; unsigned* err;
     int m, n, k;
-    int has_zeros;
     int tiles, kbt;               // column tiles, k-blocks per tile
     int kpg;                      // k-blocks per scale group
     int units, per, rem;
@@ -88,13 +105,20 @@ struct MdParams {
     const void* residual;         // [M,N] T or null: added to the finished (all-reduced) sum before the one rounding
 };
 
+// Bounded wait with an explicit poll rate.  Every poll of an mbarrier is an instruction for the unit that serves all of
+// them and an issue slot taken from the warps that do arithmetic, so a role that runs ahead of the pipeline (producers,
+// converters) sleeps long between polls and only the roles on the critical path (MMA lanes, fold warps) poll closely.
+// Gives up after about a second and raises the CTA's abort flag.
+template <int SLEEP_NS>
 __device__ __forceinline__ bool md_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (int i = 0; i < (1 << 20); ++i) {                // parked, not polling; gives up after about a second
+    constexpr int LIMIT = 1000000000 / (SLEEP_NS + 50);
+    for (int i = 0; i < LIMIT; ++i) {
         uint32_t ok;
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.b32 %0, 1, 0, p;\n}"
-                     : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
+        asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return true;
-        if ((i & 63) == 63 && *abort_flag) return false;
+        if ((i & 255) == 255 && *abort_flag) return false;
+        __nanosleep(SLEEP_NS);
     }
     *abort_flag = 1;
     return false;
@@ -189,6 +213,15 @@ __global__ void __launch_bounds__(256) xprep_kernel(const T* __restrict__ x, uns
 // ----------------------------------------------------------------------------------------------
 // main kernel
 // ----------------------------------------------------------------------------------------------
+// Barriers.  Every mbarrier operation costs its thread 200-350 cycles even when the phase is long complete, so the
+// protocol is built to give the busiest roles ONE wait per k-block:
+//   pfull[PST] / pempty[PST]   packed rows in the stage (copy engine)            / read by the converter group (4 warps)
+//   full[AST]                  everything the MMAs of a k-block need: the A operand in tensor memory (4 converter warps),
+//                              the activation tile with its scales / zero words (copy engine, one arrival of a producer
+//                              lane) and a free accumulator buffer (the MD_FOLD fold warps, two k-blocks earlier)
+//   done[AST]                  the MMAs of a k-block have completed (one commit per MMA lane): frees the A slot for the
+//                              converters and hands the accumulators to the fold warps
+//   bempty[AST]                the fold warps are done with the activation stage (sum(x'), 2^-e, scales, zero words)
 template <int BITS, typename T, int BM>
 __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_s,
                                                                   const __grid_constant__ CUtensorMap tmap_z, const MdParams p) {
@@ -201,12 +234,9 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
     const uint32_t bar0 = sbase + C::OFF_BAR;
     auto bar_pfull = [&](int s) { return bar0 + 8u * s; };
     auto bar_pempty = [&](int s) { return bar0 + 8u * (C::PST + s); };
-    auto bar_bfull = [&](int s) { return bar0 + 8u * (2 * C::PST + s); };
-    auto bar_bempty = [&](int s) { return bar0 + 8u * (2 * C::PST + C::BST + s); };
-    auto bar_afull = [&](int s) { return bar0 + 8u * (2 * C::PST + 2 * C::BST + s); };
-    auto bar_aempty = [&](int s) { return bar0 + 8u * (2 * C::PST + 2 * C::BST + C::AST + s); };
-    auto bar_dfull = [&](int s) { return bar0 + 8u * (2 * C::PST + 2 * C::BST + 2 * C::AST + s); };
-    auto bar_dempty = [&](int s) { return bar0 + 8u * (2 * C::PST + 2 * C::BST + 2 * C::AST + 2 + s); };
+    auto bar_full = [&](int s) { return bar0 + 8u * (2 * C::PST + s); };
+    auto bar_done = [&](int s) { return bar0 + 8u * (2 * C::PST + C::AST + s); };
+    auto bar_bempty = [&](int s) { return bar0 + 8u * (2 * C::PST + 2 * C::AST + s); };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::NBARS * 8);
     __shared__ int abort_flag;
 
@@ -217,11 +247,12 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
 
     if (tid == 0) {
         abort_flag = 0;
-        for (int s = 0; s < C::PST; ++s) { mbar_init(bar_pfull(s), 1); mbar_init(bar_pempty(s), MD_WORKERS); }
-        for (int s = 0; s < C::BST; ++s) { mbar_init(bar_bfull(s), 1); mbar_init(bar_bempty(s), MD_WORKERS); }
-        for (int s = 0; s < C::AST; ++s) { mbar_init(bar_afull(s), MD_WORKERS); mbar_init(bar_aempty(s), 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(bar_dfull(s), 1); mbar_init(bar_dempty(s), MD_WORKERS); }
+        for (int s = 0; s < C::PST; ++s) { mbar_init(bar_pfull(s), 1); mbar_init(bar_pempty(s), 4); }
+        for (int s = 0; s < C::AST; ++s) { mbar_init(bar_full(s), 4 + 1 + MD_FOLD); mbar_init(bar_done(s), C::NT); mbar_init(bar_bempty(s), MD_FOLD); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // the first two k-blocks find both accumulator buffers free: stand in for the fold warps' arrivals
+        for (int s = 0; s < 2; ++s)
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(bar_full(s)), "r"((uint32_t)MD_FOLD) : "memory");
     }
     if (warp == MD_W_MMA) tc_alloc<512>(smem_u32(tmem_slot));
     tc_fence_before();
@@ -229,7 +260,32 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_a = tmem_base + C::D_COLS;
-    auto wait = [&](uint32_t bar, uint32_t parity) { return md_wait(bar, parity, &abort_flag); };
+#ifdef MD_TL
+    long long tw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    int tslot = 0;
+    const long long t_begin = clock64();
+    auto wait = [&](uint32_t bar, uint32_t parity) {
+        const long long t0 = clock64();
+        const bool r = md_wait<MD_FAST_NS>(bar, parity, &abort_flag);
+        tw[tslot] += clock64() - t0;
+        return r;
+    };
+    auto lazy_wait = [&](uint32_t bar, uint32_t parity) {
+        const long long t0 = clock64();
+        const bool r = md_wait<MD_SLOW_NS>(bar, parity, &abort_flag);
+        tw[tslot] += clock64() - t0;
+        return r;
+    };
+#define MD_SLOT(n) tslot = n
+#define MD_T0() const long long t_x0 = clock64()
+#define MD_T1(n) tw[n] += clock64() - t_x0
+#else
+    auto wait = [&](uint32_t bar, uint32_t parity) { return md_wait<MD_FAST_NS>(bar, parity, &abort_flag); };        // critical path
+    auto lazy_wait = [&](uint32_t bar, uint32_t parity) { return md_wait<MD_SLOW_NS>(bar, parity, &abort_flag); };   // roles that run ahead
+#define MD_SLOT(n)
+#define MD_T0()
+#define MD_T1(n)
+#endif
 
     // first / last CTA with a unit of column tile t
     auto owner = [&](int u) -> int {
@@ -238,79 +294,121 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
     };
 
     if (warp == MD_W_PROD) {
-        // ------------------------------ producer: one lane ------------------------------
-        if (lane == 0) {
-            int tile = x0 / p.kbt, kb = x0 - tile * p.kbt;
-            bool ok = true;
-            const uint32_t ptx = (uint32_t)(C::W_BYTES + C::S_BYTES + (p.has_zeros ? C::Z_BYTES : 0));
-            // The packed weights, scales and zero words do not depend on the previous kernel in the stream: the first
-            // stages are requested before the wait for it (programmatic dependent launch).  The B tiles do (the pre-pass writes them).
-            int issued_p = 0;
-            auto issue_p = [&](int i, int t, int b) {
+        // ------------------------------ producers: eight lanes, each with its own stream of copies ------------------------------
+        // One thread completes only about four asynchronous copies per microsecond (each wait / expect / issue step is a
+        // long-latency instruction and they depend on one another).  Lanes 0-3 fetch the packed rows of every fourth
+        // k-block, lanes 4-7 the activation tile, scales and zero words of every fourth one.
+        if (lane < 4) {
+            // The packed weights do not depend on the previous kernel in the stream: the first ring of stages is requested
+            // at once; every later stage waits for the converters to have read its previous content.
+            for (int i = lane; i < nrun; i += 4) {
                 const int ps = i % C::PST;
-                const uint32_t dst = sbase + C::OFF_P + ps * C::P_STAGE;
-                mbar_expect_tx(bar_pfull(ps), ptx);
-                tma_load_2d(dst, &tmap_q, t * C::COLS, b * C::PROWS, bar_pfull(ps));
-                tma_load_2d(dst + C::W_BYTES, &tmap_s, t * C::COLS, b / p.kpg, bar_pfull(ps));
-                if (p.has_zeros) tma_load_2d(dst + C::W_BYTES + C::S_BYTES, &tmap_z, t * C::COLS / C::PACK, b / p.kpg, bar_pfull(ps));
-            };
-            int pt = tile, pb = kb;
-            if (p.pdl) {
-                for (; issued_p < nrun && issued_p < C::PST; ++issued_p) {
-                    issue_p(issued_p, pt, pb);
-                    if (++pb == p.kbt) { pb = 0; ++pt; }
-                }
-                griddep_launch_dependents();
-                griddep_wait();
+                if (i >= C::PST && !lazy_wait(bar_pempty(ps), ((i / C::PST) & 1) ^ 1)) break;
+                const int u = x0 + i, t = u / p.kbt, b = u - t * p.kbt;
+                mbar_expect_tx(bar_pfull(ps), (uint32_t)C::W_BYTES);
+                tma_load_2d(sbase + C::OFF_P + ps * C::P_STAGE, &tmap_q, t * C::COLS, b * C::PROWS, bar_pfull(ps));
+                MD_STAMP(0, i);
             }
-            for (int i = 0; i < nrun && ok; ++i) {
-                if (i >= issued_p) {
-                    const int ps = i % C::PST;
-                    if (!wait(bar_pempty(ps), ((i / C::PST) & 1) ^ 1)) { ok = false; break; }
-                    issue_p(i, pt, pb);
-                    ++issued_p;
-                    if (++pb == p.kbt) { pb = 0; ++pt; }
-                }
-                const int bs = i % C::BST;
-                if (!wait(bar_bempty(bs), ((i / C::BST) & 1) ^ 1)) { ok = false; break; }
-                mbar_expect_tx(bar_bfull(bs), (uint32_t)C::B_COPY);
-                md_bulk_load(sbase + C::OFF_B + bs * C::B_STAGE, p.xl + (size_t)kb * C::B_COPY, (uint32_t)C::B_COPY, bar_bfull(bs));
-                if (++kb == p.kbt) { kb = 0; ++tile; }
+        } else if (lane < 8) {
+            if (p.pdl) griddep_wait();                           // the activation tiles are written by the pre-pass
+            const uint32_t btx = (uint32_t)(C::B_COPY + C::S_BYTES + (p.qz ? C::Z_BYTES : 0));
+            for (int i = lane - 4; i < nrun; i += 4) {
+                const int as = i % C::AST;
+                if (i >= C::AST && !lazy_wait(bar_bempty(as), ((i / C::AST) & 1) ^ 1)) break;
+                const int u = x0 + i, t = u / p.kbt, kb = u - t * p.kbt;
+                const uint32_t dst = sbase + C::OFF_B + as * C::B_STAGE;
+                mbar_expect_tx(bar_full(as), btx);
+                md_bulk_load(dst, p.xl + (size_t)kb * C::B_COPY, (uint32_t)C::B_COPY, bar_full(as));
+                tma_load_2d(dst + C::OFF_S, &tmap_s, t * C::COLS, kb / p.kpg, bar_full(as));
+                if (p.qz) tma_load_2d(dst + C::OFF_Z, &tmap_z, t * C::COLS / C::PACK, kb / p.kpg, bar_full(as));
+                MD_STAMP(1, i);
             }
+        } else if (lane == 31 && p.pdl) {
+            griddep_launch_dependents();
         }
-    } else if (warp == MD_W_MMA) {
-        // ------------------------------ MMA issuer: one lane ------------------------------
-        if (lane == 0) {
+    } else if (warp >= MD_W_MMA) {
+        // ------------------------------ MMA issuers: one lane per column tile ------------------------------
+        const int nt = warp - MD_W_MMA;
+        if (lane == 0 && nt < C::NT) {
             // kind::i8: D s32 (2 << 4), A unsigned 8-bit (0 << 7), B signed 8-bit (1 << 10), K-major both, N = 2 BM, M = 128
             const uint32_t idesc = (2u << 4) | (1u << 10) | ((uint32_t)(C::NB >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-            bool ok = true;
-            for (int i = 0; i < nrun && ok; ++i) {
-                const int as = i % C::AST, bs = i % C::BST, db = i & 1;
-                if (!wait(bar_afull(as), (i / C::AST) & 1)) { ok = false; break; }
-                if (!wait(bar_bfull(bs), (i / C::BST) & 1)) { ok = false; break; }
-                if (!wait(bar_dempty(db), ((i >> 1) & 1) ^ 1)) { ok = false; break; }
+            for (int i = 0; i < nrun; ++i) {
+                const int as = i % C::AST, db = i & 1;
+                MD_SLOT(0);
+                if (!wait(bar_full(as), (i / C::AST) & 1)) break;
                 tc_fence_after();
-                const uint64_t bdesc = tc_desc_sw128(sbase + C::OFF_B + bs * C::B_STAGE);
+                if (nt == 0) MD_STAMP(6, i);
+                const uint64_t bdesc = tc_desc_sw128(sbase + C::OFF_B + as * C::B_STAGE);
+                const uint32_t d = tmem_base + (uint32_t)((db * C::NT + nt) * C::NB), a = tmem_a + (uint32_t)((as * C::NT + nt) * 32);
+                { MD_T0();
 #pragma unroll
-                for (int k4 = 0; k4 < 4; ++k4)
-#pragma unroll
-                    for (int nt = 0; nt < C::NT; ++nt)
-                        md_mma_i8(tmem_base + (uint32_t)((db * C::NT + nt) * C::NB), tmem_a + (uint32_t)((as * C::NT + nt) * 32 + k4 * 8),
-                                  bdesc + (uint64_t)(k4 * 2), idesc, k4 ? 1u : 0u);
-                tc_commit(bar_aempty(as));
-                tc_commit(bar_dfull(db));
+                for (int k4 = 0; k4 < 4; ++k4) md_mma_i8(d, a + (uint32_t)(k4 * 8), bdesc + (uint64_t)(k4 * 2), idesc, k4 ? 1u : 0u);
+                tc_commit(bar_done(as));
+                MD_T1(3); }
+                if (nt == 0) MD_STAMP(7, i);
             }
         }
+    } else if (warp >= MD_W_CONV) {
+        // ------------------------------ converters: two groups of four warps, a thread = one column of every tile ------------------------------
+        // Few, fat warps: what a warp pays per k-block for waits, barrier traffic and addresses is paid four times per
+        // k-block.  Group g takes the k-blocks i = g, g + 2, ...  A thread reads the PROWS packed words of its column from
+        // the stage, masks the nibbles into bytes and stores the 128 bytes of its TMEM lane with one tcgen05.st per tile.
+        const int q4 = warp & 3;
+        const int grp = (warp - MD_W_CONV) >> 2;
+        const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
+        const int cq = q4 * 32 + lane;                          // column inside a 128-column tile
+        for (int i = grp; i < nrun; i += MD_CGROUPS) {
+            const int ps = i % C::PST, as = i % C::AST;
+            MD_SLOT(0);
+            if (!lazy_wait(bar_pfull(ps), (i / C::PST) & 1)) break;
+            MD_SLOT(1);
+            if (tid == MD_W_CONV * 32) MD_STAMP(2, i);
+            const uint32_t* pk = reinterpret_cast<const uint32_t*>(smem + C::OFF_P + ps * C::P_STAGE) + cq;
+            bool ok = true;
+#pragma unroll
+            for (int nt = 0; nt < C::NT; ++nt) {
+                uint32_t a[32];
+                if constexpr (BITS == 4) {
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) {
+                        const uint32_t w = pk[r * C::COLS + nt * 128];
+                        a[2 * r] = w & 0x0f0f0f0fu;              // nibbles 0, 2, 4, 6 as bytes
+                        a[2 * r + 1] = (w >> 4) & 0x0f0f0f0fu;   // nibbles 1, 3, 5, 7
+                    }
+                } else {
+#pragma unroll
+                    for (int r = 0; r < 32; ++r) a[r] = pk[r * C::COLS + nt * 128];
+                }
+                if (nt == C::NT - 1) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_pempty(ps));   // the stage is in registers
+                }
+                if (nt == 0) {
+                    // the A slot is free when the MMAs of the k-block that used it last (AST k-blocks ago) have completed
+                    if (i >= C::AST && !lazy_wait(bar_done(as), ((i / C::AST) & 1) ^ 1)) { ok = false; break; }
+                    tc_fence_after();
+                    if (tid == MD_W_CONV * 32) MD_STAMP(3, i);
+                }
+                tc_st32(tmem_a + lane_base + (uint32_t)((as * C::NT + nt) * 32), a);
+            }
+            if (!ok) break;
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_full(as));
+            if (tid == MD_W_CONV * 32) MD_STAMP(4, i);
+        }
     } else {
-        // ------------------------------ workers ------------------------------
+        // ------------------------------ fold warps ------------------------------
         const int q4 = warp & 3;                              // TMEM lane quarter (= warp % 4)
         const int jj = warp >> 2;
         const int nt = C::NT == 2 ? (jj & 1) : 0;
-        const int rs = C::NT == 2 ? (jj >> 1) : jj;           // which split of the k-block (conversion) and of the rows (fold)
+        const int rs = C::NT == 2 ? (jj >> 1) : jj;           // which share of the batch rows
         const int cl = nt * 128 + q4 * 32 + lane;             // column inside the CTA tile
         const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
         const int r0 = rs * C::RW;
         constexpr uint32_t ZMASK = (1u << BITS) - 1u;
+        const int zsh = (cl % C::PACK) * BITS;
         const T* __restrict__ bias = reinterpret_cast<const T*>(p.bias);
         uint16_t* __restrict__ out = reinterpret_cast<uint16_t*>(p.out);
         const uint16_t* __restrict__ resid = reinterpret_cast<const uint16_t*>(p.residual);
@@ -321,8 +419,6 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
         float acc[C::RW];
 #pragma unroll
         for (int r = 0; r < C::RW; ++r) acc[r] = 0.f;
-        float s_prev = 0.f; int zp1_prev = 0;
-        bool ok = true;
 
         // the finished part of column tile `tile`: stored, or left as an fp32 partial slice that the last warp to arrive sums
         auto flush = [&](int tile) {
@@ -337,7 +433,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
                 for (int r = 0; r < C::RW; ++r) __stcg(part + (size_t)(r0 + r) * C::COLS + cl, acc[r]);
                 __threadfence();
                 __syncwarp();
-                const int cidx = tile * MD_WORKERS + warp;     // one 16-bit counter per (tile, worker warp), two per word
+                const int cidx = tile * MD_FOLD + warp;        // one 16-bit counter per (tile, fold warp), two per word
                 const int sh = (cidx & 1) * 16;
                 unsigned old = 0;
                 if (lane == 0) old = (atomicAdd(p.counters + (cidx >> 1), 1u << sh) >> sh) & 0xffffu;
@@ -358,12 +454,17 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
             if (write && okc) {
                 const float bv = bias ? H::to_float(reinterpret_cast<const uint16_t*>(bias)[col]) : 0.f;
                 if (fused_ar && !epoch_read) { epoch = ar_epoch(p.ar); epoch_read = true; }
+                if (fused_ar) {
+#pragma unroll
+                    for (int r = 0; r < C::RW; ++r)
+                        if (r0 + r < p.m) ar_push1(p.ar, epoch, (size_t)(r0 + r) * p.n + col, acc[r] + bv);
+                }
 #pragma unroll
                 for (int r = 0; r < C::RW; ++r) {
                     const int row = r0 + r;
                     if (row < p.m) {
                         float v = acc[r] + bv;
-                        if (fused_ar) v = ar_exchange1(p.ar, epoch, (size_t)row * p.n + col, v);
+                        if (fused_ar) v = ar_pull1(p.ar, epoch, (size_t)row * p.n + col, v);
                         if (resid) v += H::to_float(resid[(size_t)row * p.n + col]);
                         out[(size_t)row * p.n + col] = H::from_float(v);
                     }
@@ -373,85 +474,69 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
             for (int r = 0; r < C::RW; ++r) acc[r] = 0.f;
         };
 
-        int tile = x0 / p.kbt, kb = x0 - tile * p.kbt;        // of the unit being CONVERTED
-        int f_tile = tile, f_kb = kb;                          // of the unit being FOLDED (one behind)
-        if (p.pdl) griddep_wait();                              // before the first read of anything an earlier kernel wrote (out / partial / x tiles)
-        for (int i = 0; i <= nrun && ok; ++i) {
-            float s_cur = 0.f; int zp1_cur = 0;
-            if (i < nrun) {
-                const int ps = i % C::PST;
-                if (!wait(bar_pfull(ps), (i / C::PST) & 1)) { ok = false; break; }
-                const unsigned char* st = smem + C::OFF_P + ps * C::P_STAGE;
-                const uint32_t* pk = reinterpret_cast<const uint32_t*>(st) + (size_t)(rs * C::WPW) * C::COLS + cl;
-                uint32_t wq[C::WPW];
+        int tile = x0 / p.kbt, kb = x0 - tile * p.kbt;
+        if (p.pdl) griddep_wait();                              // before anything an earlier kernel wrote is touched (out / partial)
+        for (int j = 0; j < nrun; ++j) {
+            const int as = j % C::AST, db = j & 1;
+            if (tid == 0) MD_STAMP(8, j);
+            MD_SLOT(0);
+            // The MMAs of this k-block have completed.  Their issuing lanes waited for the copy engine's bytes of this stage
+            // (`full`) before they issued, so the stage's sums, scales and zero words are in shared memory long since.
+            if (!wait(bar_done(as), (j / C::AST) & 1)) break;
+            if (tid == 0) MD_STAMP(9, j);
+            tc_fence_after();
+            const uint32_t dbase = tmem_base + lane_base + (uint32_t)((db * C::NT + nt) * C::NB + r0);
+            const unsigned char* bst = smem + C::OFF_B + as * C::B_STAGE;
+            const float sf = H::to_float(reinterpret_cast<const uint16_t*>(bst + C::OFF_S)[cl]);
+            const int nzp1 = -(p.qz ? int((reinterpret_cast<const uint32_t*>(bst + C::OFF_Z)[cl / C::PACK] >> zsh) & ZMASK) + 1 : p.zp1_const);
+            bst += C::B_TILE;
 #pragma unroll
-                for (int r = 0; r < C::WPW; ++r) wq[r] = pk[r * C::COLS];
-                s_cur = H::to_float(reinterpret_cast<const uint16_t*>(st + C::W_BYTES)[cl]);
-                zp1_cur = p.has_zeros ? int((reinterpret_cast<const uint32_t*>(st + C::W_BYTES + C::S_BYTES)[cl / C::PACK] >> ((cl % C::PACK) * BITS)) & ZMASK) + 1
-                                      : p.zp1_const;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_pempty(ps));   // the stage is in registers
-                uint32_t a[C::AREGS];
-                if constexpr (BITS == 4) {
-#pragma unroll
-                    for (int r = 0; r < C::WPW; ++r) {
-                        a[2 * r] = wq[r] & 0x0f0f0f0fu;              // nibbles 0, 2, 4, 6 as bytes
-                        a[2 * r + 1] = (wq[r] >> 4) & 0x0f0f0f0fu;   // nibbles 1, 3, 5, 7
-                    }
-                } else {
-#pragma unroll
-                    for (int r = 0; r < C::WPW; ++r) a[r] = wq[r];
-                }
-                const int as = i % C::AST;
-                if (!wait(bar_aempty(as), ((i / C::AST) & 1) ^ 1)) { ok = false; break; }
-                tc_fence_after();
-                md_st<C::AREGS>(tmem_a + lane_base + (uint32_t)((as * C::NT + nt) * 32 + rs * C::AREGS), a);
-                tc_wait_st();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_afull(as));
-                if (++kb == p.kbt) { kb = 0; ++tile; }
-            }
-            if (i >= 1) {
-                const int j = i - 1, db = j & 1, bs = j % C::BST;
-                if (!wait(bar_dfull(db), (j >> 1) & 1)) { ok = false; break; }
-                if (!wait(bar_bfull(bs), (j / C::BST) & 1)) { ok = false; break; }     // completed long ago: makes the bulk copy's bytes visible here
-                tc_fence_after();
-                uint32_t dh[C::RW], dl[C::RW];
-                const uint32_t dbase = tmem_base + lane_base + (uint32_t)((db * C::NT + nt) * C::NB + r0);
-                tc_ld<C::RW>(dbase, dh);
-                tc_ld<C::RW>(dbase + BM, dl);
-                const unsigned char* bst = smem + C::OFF_B + bs * C::B_STAGE + C::B_TILE;
-                int sx[C::RW]; float pe[C::RW];
-#pragma unroll
-                for (int r = 0; r < C::RW; r += 4) {
-                    const int4 sv = *reinterpret_cast<const int4*>(bst + (r0 + r) * 4);
-                    const float4 pv = *reinterpret_cast<const float4*>(bst + BM * 4 + (r0 + r) * 4);
-                    sx[r] = sv.x; sx[r + 1] = sv.y; sx[r + 2] = sv.z; sx[r + 3] = sv.w;
-                    pe[r] = pv.x; pe[r + 1] = pv.y; pe[r + 2] = pv.z; pe[r + 3] = pv.w;
-                }
+            for (int c0 = 0; c0 < C::RW; c0 += C::RC) {
+                uint32_t dh[C::RC], dl[C::RC];
+                { MD_T0();
+                tc_ld<C::RC>(dbase + c0, dh);
+                tc_ld<C::RC>(dbase + BM + c0, dl);
                 tc_wait_ld();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) { mbar_arrive(bar_dempty(db)); mbar_arrive(bar_bempty(bs)); }
-#pragma unroll
-                for (int r = 0; r < C::RW; ++r) {
-                    const int v = int(dh[r]) * 256 + int(dl[r]) - zp1_prev * sx[r];   // sum_k (q - (z + 1)) x'
-                    acc[r] = fmaf(s_prev * pe[r], __int2float_rn(v), acc[r]);
+                MD_T1(2); }
+                if (c0 + C::RC == C::RW) {                       // the accumulator buffer is in registers: it is free for the k-block after next
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_full((j + 2) % C::AST));
+                    if (tid == 0) MD_STAMP(10, j);
                 }
-                const bool tile_ends = (f_kb == p.kbt - 1) || (j == nrun - 1);
-                if (tile_ends) flush(f_tile);
-                if (++f_kb == p.kbt) { f_kb = 0; ++f_tile; }
+#pragma unroll
+                for (int r = 0; r < C::RC; r += 4) {
+                    const int4 sv = *reinterpret_cast<const int4*>(bst + (r0 + c0 + r) * 4);                  // sum_k x' of four batch rows
+                    const float4 pv = *reinterpret_cast<const float4*>(bst + BM * 4 + (r0 + c0 + r) * 4);    // their 2^-e
+                    const int sx[4] = {sv.x, sv.y, sv.z, sv.w};
+                    const float pe[4] = {pv.x, pv.y, pv.z, pv.w};
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int v = (int(dh[r + u]) << 8) + int(dl[r + u]) + nzp1 * sx[u];                  // sum_k (q - (z + 1)) x'
+                        acc[c0 + r + u] = fmaf(sf * pe[u], __int2float_rn(v), acc[c0 + r + u]);
+                    }
+                }
             }
-            s_prev = s_cur; zp1_prev = zp1_cur;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_bempty(as));
+            if (tid == 0) MD_STAMP(11, j);
+            if (kb == p.kbt - 1 || j == nrun - 1) flush(tile);
+            if (++kb == p.kbt) { kb = 0; ++tile; }
         }
         if (fused_ar) {
             // every CTA of the grid reports when its exchanges are done; the last one publishes the epoch for the next call
-            asm volatile("bar.sync 1, %0;" ::"n"(MD_WORKERS * 32) : "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(MD_FOLD * 32) : "memory");
             if (tid == 0) ar_leave(p.ar, epoch_read ? epoch : ar_epoch(p.ar), gridDim.x);
         }
     }
 
+#ifdef MD_TL
+    if (blockIdx.x == 3 && lane == 0) {
+        long long* dst = reinterpret_cast<long long*>(p.counters + (30 << 18)) + 64 * 16 + warp * 8;
+        dst[0] = clock64() - t_begin;
+        for (int q = 0; q < 7; ++q) dst[1 + q] = tw[q];
+    }
+#endif
     tc_fence_before();
     __syncthreads();
     if (warp == MD_W_MMA) {
@@ -534,7 +619,7 @@ bool mid_supported(const QGemmArgs& a) {
     if (a.workspace == nullptr || a.workspace_bytes < kCounterBytes) return false;
     if (!get_tensor_map_encoder()) return false;
     const MdPlan pl = plan(a.m < 64 ? a.m : 64, a.n, a.k);
-    if ((long long)pl.tiles * MD_WORKERS >= 2LL * (kMaxTiles - 1)) return false;   // 16-bit counters, two per word, the last word is the error word
+    if ((long long)(pl.tiles + 1) * MD_FOLD > 2LL * (kMaxTiles - 1)) return false;   // 16-bit counters, two per word, the last word is the error word
     if ((long long)pl.tiles * pl.kbt > (1LL << 30)) return false;
     return pl.partial_bytes + pl.xl_bytes <= a.workspace_bytes - kCounterBytes;
 }
@@ -600,7 +685,7 @@ int launch_mid(cudaStream_t st, const QGemmArgs& a) {
         p.counters = static_cast<unsigned*>(a.workspace);
         p.err = p.counters + (kMaxTiles - 1);
         p.m = m; p.n = a.n; p.k = a.k;
-        p.has_zeros = a.qzeros ? 1 : 0;
+        p.scales = a.scales; p.qz = a.qzeros;
         p.tiles = pl.tiles; p.kbt = pl.kbt; p.kpg = (a.k / a.groups) / MD_KB;
         p.units = pl.tiles * pl.kbt; p.per = p.units / pl.grid; p.rem = p.units % pl.grid;
         p.zp1_const = 1 << (a.bits - 1);

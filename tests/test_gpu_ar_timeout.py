@@ -13,11 +13,11 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-@pytest.mark.parametrize("m,force_small", [(1, False), (2, False), (4, True)])
-def test_expired_peer_wait_sets_the_error_word_and_raises(lib_built, m, force_small):
+@pytest.mark.parametrize("m,force_small,k,n", [(1, False, 1024, 512), (2, False, 1024, 512), (4, True, 1024, 512),
+                                               (8, False, 4096, 8192)])     # the last one: the integer tensor-core kernel
+def test_expired_peer_wait_sets_the_error_word_and_raises(lib_built, m, force_small, k, n):
     from minit_b200 import _lib
     L = _lib.lib
-    k, n = 1024, 512
     c = O.make_gptq_case(k, n, m, bits=4, seed=40 + m)
     d = to_dev(c, DEV)
     dev = torch.device(DEV)
