@@ -41,6 +41,9 @@ namespace {
 #define MD_FOLD_WARPS 8
 #endif
 constexpr int MD_FOLD = MD_FOLD_WARPS;             // fold warps: 0 .. MD_FOLD - 1
+#ifndef MD_ROWS_PER_LD
+#define MD_ROWS_PER_LD 8
+#endif
 #ifndef MD_FAST_NS
 #define MD_FAST_NS 20
 #endif
@@ -59,32 +62,39 @@ template <int BITS, int BM> struct MdCfg {
     static constexpr int COLS = NT * 128;
     static constexpr int RS = MD_FOLD / (4 * NT);  // fold warps that share a (tile, lane quarter) split the batch rows: 1 | 2
     static constexpr int RW = BM / RS;             // batch rows a fold warp handles: 16 | 32
-    static constexpr int RC = RW < 16 ? RW : 16;   // rows per tcgen05.ld
+    static constexpr int RC = MD_ROWS_PER_LD;      // rows per tcgen05.ld and per stage of the fold arithmetic
     static constexpr int NB = 2 * BM;              // MMA N: h rows then l rows
     static constexpr int D_COLS = 2 * NT * NB;     // two accumulator buffers
     static constexpr int A_STAGE = NT * 32;        // TMEM columns of one k-block of the A operand
-    static constexpr int AST = BM == 64 ? 4 : (512 - D_COLS) / A_STAGE;   // slots of the A operand, and of the activation stage: 6 | 4 | 4
+    static constexpr int AST = BM == 64 ? 4 : (512 - D_COLS) / A_STAGE;   // slots of the A operand in tensor memory: 6 | 4 | 4
     static constexpr int W_BYTES = PROWS * COLS * 4;
     static constexpr int P_STAGE = W_BYTES;
-    static constexpr int PST = (128 * 1024) / P_STAGE;                 // 128 KB of packed weights in flight per SM
+    static constexpr int PST = ((BM == 64 ? 96 : 128) * 1024) / P_STAGE / 4 * 4;   // packed weights in flight per SM; a multiple of the four lanes that fill it
     static constexpr int B_TILE = NB * 128;
     static constexpr int B_COPY = B_TILE + BM * 8;                    // tile + sum(x') [BM] int32 + 2^-e [BM] fp32
     static constexpr int S_BYTES = COLS * 2;                          // scales of the stage's group, this CTA tile's columns
     static constexpr int Z_BYTES = COLS / PACK * 4;                   // zero words
     static constexpr int OFF_S = B_TILE + 512, OFF_Z = B_TILE + 1024;
     static constexpr int B_STAGE = B_TILE + 2048;
+    // An activation stage is busy from the request of its copies (three asynchronous copies issued by one lane: ~2500
+    // cycles) to the end of the fold of its k-block, about four k-block periods: the ring is deeper than the A ring
+    static constexpr int BST = BM == 64 ? 6 : 8;
     static constexpr int OFF_P = 0;
     static constexpr int OFF_B = OFF_P + PST * P_STAGE;
-    static constexpr int OFF_BAR = OFF_B + AST * B_STAGE;
-    static constexpr int NBARS = 2 * PST + 3 * AST;
+    static constexpr int OFF_BAR = OFF_B + BST * B_STAGE;
+    static constexpr int NBARS = 2 * PST + 3 * BST;
     static constexpr int TOTAL = OFF_BAR + NBARS * 8 + 64 + 1024;
     static_assert(BM * 8 <= 512 && S_BYTES <= 512 && Z_BYTES <= 1024, "activation stage layout");
+    // A wait by phase parity is only right for a thread that has seen every earlier phase of that barrier: each
+    // producer lane therefore always serves the same stages (four lanes over PST stages, one lane per activation stage)
+    // and the two converter groups see every other phase of barriers whose ring length is even.
+    static_assert(PST >= 4 && PST % 4 == 0 && BST % 2 == 0 && PST % 2 == 0 && BST <= 16, "ring lengths against the lanes and groups that wait on them");
     static_assert(D_COLS + AST * A_STAGE <= 512 && AST >= 3, "TMEM budget");
     static_assert(OFF_B % 1024 == 0, "B tiles need 1024-byte alignment");
     static_assert(TOTAL <= 227 * 1024, "shared memory budget");
 };
 
-#ifdef MD_TL
+#if defined(MD_TL) || defined(MD_TL_LIGHT)
 #define MD_STAMP(slot, unit) do { if (blockIdx.x == 3 && (unit) < 64) reinterpret_cast<long long*>(p.counters + (30 << 18))[(unit) * 16 + (slot)] = clock64(); } while (0)
 #else
 #define MD_STAMP(slot, unit) do { } while (0)
@@ -216,12 +226,12 @@ __global__ void __launch_bounds__(256) xprep_kernel(const T* __restrict__ x, uns
 // Barriers.  Every mbarrier operation costs its thread 200-350 cycles even when the phase is long complete, so the
 // protocol is built to give the busiest roles ONE wait per k-block:
 //   pfull[PST] / pempty[PST]   packed rows in the stage (copy engine)            / read by the converter group (4 warps)
-//   full[AST]                  everything the MMAs of a k-block need: the A operand in tensor memory (4 converter warps),
+//   full[BST]                  everything the MMAs of a k-block need: the A operand in tensor memory (4 converter warps),
 //                              the activation tile with its scales / zero words (copy engine, one arrival of a producer
 //                              lane) and a free accumulator buffer (the MD_FOLD fold warps, two k-blocks earlier)
-//   done[AST]                  the MMAs of a k-block have completed (one commit per MMA lane): frees the A slot for the
+//   done[BST]                  the MMAs of a k-block have completed (one commit per MMA lane): frees the A slot for the
 //                              converters and hands the accumulators to the fold warps
-//   bempty[AST]                the fold warps are done with the activation stage (sum(x'), 2^-e, scales, zero words)
+//   bempty[BST]                the fold warps are done with the activation stage (sum(x'), 2^-e, scales, zero words)
 template <int BITS, typename T, int BM>
 __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_s,
                                                                   const __grid_constant__ CUtensorMap tmap_z, const MdParams p) {
@@ -235,8 +245,8 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
     auto bar_pfull = [&](int s) { return bar0 + 8u * s; };
     auto bar_pempty = [&](int s) { return bar0 + 8u * (C::PST + s); };
     auto bar_full = [&](int s) { return bar0 + 8u * (2 * C::PST + s); };
-    auto bar_done = [&](int s) { return bar0 + 8u * (2 * C::PST + C::AST + s); };
-    auto bar_bempty = [&](int s) { return bar0 + 8u * (2 * C::PST + 2 * C::AST + s); };
+    auto bar_done = [&](int s) { return bar0 + 8u * (2 * C::PST + C::BST + s); };
+    auto bar_bempty = [&](int s) { return bar0 + 8u * (2 * C::PST + 2 * C::BST + s); };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::NBARS * 8);
     __shared__ int abort_flag;
 
@@ -248,7 +258,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
     if (tid == 0) {
         abort_flag = 0;
         for (int s = 0; s < C::PST; ++s) { mbar_init(bar_pfull(s), 1); mbar_init(bar_pempty(s), 4); }
-        for (int s = 0; s < C::AST; ++s) { mbar_init(bar_full(s), 4 + 1 + MD_FOLD); mbar_init(bar_done(s), C::NT); mbar_init(bar_bempty(s), MD_FOLD); }
+        for (int s = 0; s < C::BST; ++s) { mbar_init(bar_full(s), 4 + 1 + MD_FOLD); mbar_init(bar_done(s), C::NT); mbar_init(bar_bempty(s), MD_FOLD); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         // the first two k-blocks find both accumulator buffers free: stand in for the fold warps' arrivals
         for (int s = 0; s < 2; ++s)
@@ -294,10 +304,10 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
     };
 
     if (warp == MD_W_PROD) {
-        // ------------------------------ producers: eight lanes, each with its own stream of copies ------------------------------
+        // ------------------------------ producers: 4 + BST lanes, each with its own stream of copies ------------------------------
         // One thread completes only about four asynchronous copies per microsecond (each wait / expect / issue step is a
         // long-latency instruction and they depend on one another).  Lanes 0-3 fetch the packed rows of every fourth
-        // k-block, lanes 4-7 the activation tile, scales and zero words of every fourth one.
+        // k-block, one further lane per activation stage its tile, scales and zero words.
         if (lane < 4) {
             // The packed weights do not depend on the previous kernel in the stream: the first ring of stages is requested
             // at once; every later stage waits for the converters to have read its previous content.
@@ -309,18 +319,18 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
                 tma_load_2d(sbase + C::OFF_P + ps * C::P_STAGE, &tmap_q, t * C::COLS, b * C::PROWS, bar_pfull(ps));
                 MD_STAMP(0, i);
             }
-        } else if (lane < 8) {
+        } else if (lane < 4 + C::BST) {
             if (p.pdl) griddep_wait();                           // the activation tiles are written by the pre-pass
             const uint32_t btx = (uint32_t)(C::B_COPY + C::S_BYTES + (p.qz ? C::Z_BYTES : 0));
-            for (int i = lane - 4; i < nrun; i += 4) {
-                const int as = i % C::AST;
-                if (i >= C::AST && !lazy_wait(bar_bempty(as), ((i / C::AST) & 1) ^ 1)) break;
+            for (int i = lane - 4; i < nrun; i += C::BST) {           // lane 4 + s owns activation stage s
+                const int bs = i % C::BST;
+                if (i >= C::BST && !lazy_wait(bar_bempty(bs), ((i / C::BST) & 1) ^ 1)) break;
                 const int u = x0 + i, t = u / p.kbt, kb = u - t * p.kbt;
-                const uint32_t dst = sbase + C::OFF_B + as * C::B_STAGE;
-                mbar_expect_tx(bar_full(as), btx);
-                md_bulk_load(dst, p.xl + (size_t)kb * C::B_COPY, (uint32_t)C::B_COPY, bar_full(as));
-                tma_load_2d(dst + C::OFF_S, &tmap_s, t * C::COLS, kb / p.kpg, bar_full(as));
-                if (p.qz) tma_load_2d(dst + C::OFF_Z, &tmap_z, t * C::COLS / C::PACK, kb / p.kpg, bar_full(as));
+                const uint32_t dst = sbase + C::OFF_B + bs * C::B_STAGE;
+                mbar_expect_tx(bar_full(bs), btx);
+                md_bulk_load(dst, p.xl + (size_t)kb * C::B_COPY, (uint32_t)C::B_COPY, bar_full(bs));
+                tma_load_2d(dst + C::OFF_S, &tmap_s, t * C::COLS, kb / p.kpg, bar_full(bs));
+                if (p.qz) tma_load_2d(dst + C::OFF_Z, &tmap_z, t * C::COLS / C::PACK, kb / p.kpg, bar_full(bs));
                 MD_STAMP(1, i);
             }
         } else if (lane == 31 && p.pdl) {
@@ -333,17 +343,17 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
             // kind::i8: D s32 (2 << 4), A unsigned 8-bit (0 << 7), B signed 8-bit (1 << 10), K-major both, N = 2 BM, M = 128
             const uint32_t idesc = (2u << 4) | (1u << 10) | ((uint32_t)(C::NB >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
             for (int i = 0; i < nrun; ++i) {
-                const int as = i % C::AST, db = i & 1;
+                const int as = i % C::AST, bs = i % C::BST, db = i & 1;
                 MD_SLOT(0);
-                if (!wait(bar_full(as), (i / C::AST) & 1)) break;
+                if (!wait(bar_full(bs), (i / C::BST) & 1)) break;
                 tc_fence_after();
                 if (nt == 0) MD_STAMP(6, i);
-                const uint64_t bdesc = tc_desc_sw128(sbase + C::OFF_B + as * C::B_STAGE);
+                const uint64_t bdesc = tc_desc_sw128(sbase + C::OFF_B + bs * C::B_STAGE);
                 const uint32_t d = tmem_base + (uint32_t)((db * C::NT + nt) * C::NB), a = tmem_a + (uint32_t)((as * C::NT + nt) * 32);
                 { MD_T0();
 #pragma unroll
                 for (int k4 = 0; k4 < 4; ++k4) md_mma_i8(d, a + (uint32_t)(k4 * 8), bdesc + (uint64_t)(k4 * 2), idesc, k4 ? 1u : 0u);
-                tc_commit(bar_done(as));
+                tc_commit(bar_done(bs));
                 MD_T1(3); }
                 if (nt == 0) MD_STAMP(7, i);
             }
@@ -358,7 +368,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
         const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
         const int cq = q4 * 32 + lane;                          // column inside a 128-column tile
         for (int i = grp; i < nrun; i += MD_CGROUPS) {
-            const int ps = i % C::PST, as = i % C::AST;
+            const int ps = i % C::PST, as = i % C::AST, bs = i % C::BST;
             MD_SLOT(0);
             if (!lazy_wait(bar_pfull(ps), (i / C::PST) & 1)) break;
             MD_SLOT(1);
@@ -385,7 +395,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
                 }
                 if (nt == 0) {
                     // the A slot is free when the MMAs of the k-block that used it last (AST k-blocks ago) have completed
-                    if (i >= C::AST && !lazy_wait(bar_done(as), ((i / C::AST) & 1) ^ 1)) { ok = false; break; }
+                    if (i >= C::AST && !lazy_wait(bar_done((i - C::AST) % C::BST), ((i - C::AST) / C::BST) & 1)) { ok = false; break; }
                     tc_fence_after();
                     if (tid == MD_W_CONV * 32) MD_STAMP(3, i);
                 }
@@ -395,7 +405,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_full(as));
+            if (lane == 0) mbar_arrive(bar_full(bs));
             if (tid == MD_W_CONV * 32) MD_STAMP(4, i);
         }
     } else {
@@ -477,19 +487,26 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
         int tile = x0 / p.kbt, kb = x0 - tile * p.kbt;
         if (p.pdl) griddep_wait();                              // before anything an earlier kernel wrote is touched (out / partial)
         for (int j = 0; j < nrun; ++j) {
-            const int as = j % C::AST, db = j & 1;
+            const int bs = j % C::BST, db = j & 1;
             if (tid == 0) MD_STAMP(8, j);
             MD_SLOT(0);
             // The MMAs of this k-block have completed.  Their issuing lanes waited for the copy engine's bytes of this stage
             // (`full`) before they issued, so the stage's sums, scales and zero words are in shared memory long since.
-            if (!wait(bar_done(as), (j / C::AST) & 1)) break;
+            if (!wait(bar_done(bs), (j / C::BST) & 1)) break;
             if (tid == 0) MD_STAMP(9, j);
+#ifdef MD_TL
+            const long long t_top = clock64();
+#endif
             tc_fence_after();
             const uint32_t dbase = tmem_base + lane_base + (uint32_t)((db * C::NT + nt) * C::NB + r0);
-            const unsigned char* bst = smem + C::OFF_B + as * C::B_STAGE;
+            const unsigned char* bst = smem + C::OFF_B + bs * C::B_STAGE;
             const float sf = H::to_float(reinterpret_cast<const uint16_t*>(bst + C::OFF_S)[cl]);
             const int nzp1 = -(p.qz ? int((reinterpret_cast<const uint32_t*>(bst + C::OFF_Z)[cl / C::PACK] >> zsh) & ZMASK) + 1 : p.zp1_const);
             bst += C::B_TILE;
+#ifdef MD_TL
+            asm volatile("" : "+f"(const_cast<float&>(sf)));
+            tw[3] += clock64() - t_top;
+#endif
 #pragma unroll
             for (int c0 = 0; c0 < C::RW; c0 += C::RC) {
                 uint32_t dh[C::RC], dl[C::RC];
@@ -499,26 +516,51 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
                 tc_wait_ld();
                 MD_T1(2); }
                 if (c0 + C::RC == C::RW) {                       // the accumulator buffer is in registers: it is free for the k-block after next
+                    { MD_T0();
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_full((j + 2) % C::AST));
+                    if (lane == 0) mbar_arrive(bar_full((j + 2) % C::BST));
+                    MD_T1(5); }
                     if (tid == 0) MD_STAMP(10, j);
                 }
+#ifdef MD_TL
+                const long long t_m0 = clock64();
+#endif
+#ifndef MD_ABL_NOMATH
+                // stage by stage over the rows of the chunk, so that independent instructions sit next to one another
+                int sx[C::RC]; float pe[C::RC];
 #pragma unroll
                 for (int r = 0; r < C::RC; r += 4) {
                     const int4 sv = *reinterpret_cast<const int4*>(bst + (r0 + c0 + r) * 4);                  // sum_k x' of four batch rows
                     const float4 pv = *reinterpret_cast<const float4*>(bst + BM * 4 + (r0 + c0 + r) * 4);    // their 2^-e
-                    const int sx[4] = {sv.x, sv.y, sv.z, sv.w};
-                    const float pe[4] = {pv.x, pv.y, pv.z, pv.w};
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const int v = (int(dh[r + u]) << 8) + int(dl[r + u]) + nzp1 * sx[u];                  // sum_k (q - (z + 1)) x'
-                        acc[c0 + r + u] = fmaf(sf * pe[u], __int2float_rn(v), acc[c0 + r + u]);
-                    }
+                    sx[r] = sv.x; sx[r + 1] = sv.y; sx[r + 2] = sv.z; sx[r + 3] = sv.w;
+                    pe[r] = pv.x; pe[r + 1] = pv.y; pe[r + 2] = pv.z; pe[r + 3] = pv.w;
                 }
+                int v[C::RC];
+#pragma unroll
+                for (int r = 0; r < C::RC; ++r) v[r] = (int(dh[r]) << 8) + int(dl[r]);
+#pragma unroll
+                for (int r = 0; r < C::RC; ++r) v[r] += nzp1 * sx[r];                                         // sum_k (q - (z + 1)) x'
+                float f[C::RC];
+#pragma unroll
+                for (int r = 0; r < C::RC; ++r) f[r] = __int2float_rn(v[r]);
+#pragma unroll
+                for (int r = 0; r < C::RC; ++r) pe[r] *= sf;
+#pragma unroll
+                for (int r = 0; r < C::RC; ++r) acc[c0 + r] = fmaf(pe[r], f[r], acc[c0 + r]);
+#else
+                acc[c0] += __uint_as_float(dh[0] ^ dl[C::RC - 1]) * sf;
+#endif
+#ifdef MD_TL
+#pragma unroll
+                for (int r = 0; r < C::RC; ++r) asm volatile("" : "+f"(acc[c0 + r]));
+                tw[4] += clock64() - t_m0;
+#endif
             }
+            { MD_T0();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_bempty(as));
+            if (lane == 0) mbar_arrive(bar_bempty(bs));
+            MD_T1(6); }
             if (tid == 0) MD_STAMP(11, j);
             if (kb == p.kbt - 1 || j == nrun - 1) flush(tile);
             if (++kb == p.kbt) { kb = 0; ++tile; }
@@ -537,6 +579,12 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
         for (int q = 0; q < 7; ++q) dst[1 + q] = tw[q];
     }
 #endif
+    // A wait that expired has raised the abort flag and every role has left its loop.  Copies this CTA requested may
+    // still be in flight towards its shared memory and MMAs may still be running: give them time to land (they complete
+    // within microseconds) before the tensor memory is freed and the CTA exits.
+    if (*reinterpret_cast<volatile int*>(&abort_flag)) {
+        for (int i = 0; i < 100; ++i) __nanosleep(1000);
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == MD_W_MMA) {
