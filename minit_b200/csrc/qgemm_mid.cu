@@ -27,8 +27,9 @@
 // the packed words from the stage, masks, one tcgen05.st per tile); 8 fold warps = (tile, TMEM lane quarter)
 // or (TMEM lane quarter, half of the batch rows): a thread owns one output column and folds the k-block the tensor core finished
 // while it works on the next one (two accumulator buffers), scale and zero word read straight from global
-// memory one k-block ahead; 6 producer lanes (TMA of the packed rows of a k-block, 16 KB per stage, 8 stages;
-// one bulk copy of the B tile; one lane cannot issue the copies fast enough); one MMA lane per tile.  Stream-K over (column tile, k-block) units as in the other
+// memory one k-block ahead; two producer warps of one lane each (TMA of the packed rows of a k-block, 16 KB per
+// stage, 8 stages | one bulk copy of the B tile per k-block, scales and zero words in blocks of eight groups); one MMA
+// lane per tile.  Stream-K over (column tile, k-block) units as in the other
 // kernels; a tile shared by several CTAs is finished, slice by slice, by the last warp to arrive.
 // Every wait is bounded and reports through the workspace error word.
 #include "tma.cuh"
@@ -41,6 +42,9 @@ namespace {
 #define MD_FOLD_WARPS 8
 #endif
 constexpr int MD_FOLD = MD_FOLD_WARPS;             // fold warps: 0 .. MD_FOLD - 1
+#ifndef MD_DBUF16
+#define MD_DBUF16 4
+#endif
 #ifndef MD_ROWS_PER_LD
 #define MD_ROWS_PER_LD 8
 #endif
@@ -51,8 +55,12 @@ constexpr int MD_FOLD = MD_FOLD_WARPS;             // fold warps: 0 .. MD_FOLD -
 #define MD_SLOW_NS 400
 #endif
 constexpr int MD_CGROUPS = 2;                      // converter groups of four warps, alternating k-blocks
-constexpr int MD_W_CONV = MD_FOLD, MD_W_PROD = MD_FOLD + 4 * MD_CGROUPS, MD_W_MMA = MD_W_PROD + 1;   // then the producer warp and two MMA warps (column tile 0 and 1)
+constexpr int MD_W_CONV = MD_FOLD;                                  // the converter warps follow the fold warps
+constexpr int MD_W_PROD = MD_FOLD + 4 * MD_CGROUPS;                 // two producer warps, one lane each: packed rows | activation tiles, scales and zero words
+constexpr int MD_W_MMA = MD_W_PROD + 2;                             // two MMA warps (column tile 0 and 1)
 constexpr int MD_THREADS = (MD_W_MMA + 2) * 32;
+constexpr int MD_SZG = 8;                                           // scale groups per scale / zero block
+constexpr int MD_SZST = 3;                                          // blocks in the ring
 constexpr int MD_KB = 128;                         // values of k per unit
 
 template <int BITS, int BM> struct MdCfg {
@@ -64,32 +72,34 @@ template <int BITS, int BM> struct MdCfg {
     static constexpr int RW = BM / RS;             // batch rows a fold warp handles: 16 | 32
     static constexpr int RC = MD_ROWS_PER_LD;      // rows per tcgen05.ld and per stage of the fold arithmetic
     static constexpr int NB = 2 * BM;              // MMA N: h rows then l rows
-    static constexpr int D_COLS = 2 * NT * NB;     // two accumulator buffers
+    static constexpr int DBUF = BM == 16 ? MD_DBUF16 : 2;   // accumulator buffers: the MMAs of a k-block wait for the fold of DBUF k-blocks earlier
+    static constexpr int D_COLS = DBUF * NT * NB;
     static constexpr int A_STAGE = NT * 32;        // TMEM columns of one k-block of the A operand
     static constexpr int AST = BM == 64 ? 4 : (512 - D_COLS) / A_STAGE;   // slots of the A operand in tensor memory: 6 | 4 | 4
     static constexpr int W_BYTES = PROWS * COLS * 4;
     static constexpr int P_STAGE = W_BYTES;
-    static constexpr int PST = ((BM == 64 ? 96 : 128) * 1024) / P_STAGE / 4 * 4;   // packed weights in flight per SM; a multiple of the four lanes that fill it
+    static constexpr int PST = ((BM == 64 ? 96 : 128) * 1024) / P_STAGE / 2 * 2;   // packed weights in flight per SM
     static constexpr int B_TILE = NB * 128;
     static constexpr int B_COPY = B_TILE + BM * 8;                    // tile + sum(x') [BM] int32 + 2^-e [BM] fp32
-    static constexpr int S_BYTES = COLS * 2;                          // scales of the stage's group, this CTA tile's columns
-    static constexpr int Z_BYTES = COLS / PACK * 4;                   // zero words
-    static constexpr int OFF_S = B_TILE + 512, OFF_Z = B_TILE + 1024;
-    static constexpr int B_STAGE = B_TILE + 2048;
+    static constexpr int B_STAGE = B_TILE + 1024;                     // the sums and block scales behind the tile
+    static constexpr int S_BYTES = MD_SZG * COLS * 2;                 // scales of MD_SZG groups, this CTA tile's columns
+    static constexpr int Z_BYTES = MD_SZG * (COLS / PACK) * 4;        // zero words of the same groups
+    static constexpr int SZ_STAGE = S_BYTES + Z_BYTES;
     // An activation stage is busy from the request of its copies (three asynchronous copies issued by one lane: ~2500
     // cycles) to the end of the fold of its k-block, about four k-block periods: the ring is deeper than the A ring
     static constexpr int BST = BM == 64 ? 6 : 8;
     static constexpr int OFF_P = 0;
     static constexpr int OFF_B = OFF_P + PST * P_STAGE;
-    static constexpr int OFF_BAR = OFF_B + BST * B_STAGE;
-    static constexpr int NBARS = 2 * PST + 3 * BST;
+    static constexpr int OFF_SZ = OFF_B + BST * B_STAGE;
+    static constexpr int OFF_BAR = OFF_SZ + MD_SZST * SZ_STAGE;
+    static constexpr int NBARS = 2 * PST + 3 * BST + 2 * MD_SZST;
     static constexpr int TOTAL = OFF_BAR + NBARS * 8 + 64 + 1024;
-    static_assert(BM * 8 <= 512 && S_BYTES <= 512 && Z_BYTES <= 1024, "activation stage layout");
-    // A wait by phase parity is only right for a thread that has seen every earlier phase of that barrier: each
-    // producer lane therefore always serves the same stages (four lanes over PST stages, one lane per activation stage)
-    // and the two converter groups see every other phase of barriers whose ring length is even.
-    static_assert(PST >= 4 && PST % 4 == 0 && BST % 2 == 0 && PST % 2 == 0 && BST <= 16, "ring lengths against the lanes and groups that wait on them");
-    static_assert(D_COLS + AST * A_STAGE <= 512 && AST >= 3, "TMEM budget");
+    static_assert(BM * 8 <= 1024 && OFF_SZ % 128 == 0 && S_BYTES % 128 == 0, "activation stage and scale block layout");
+    // A wait by phase parity is only right for a thread that has seen every earlier phase of that barrier: every
+    // producer is ONE thread that walks its ring in order, and the two converter groups see every other phase of
+    // barriers whose ring length is even.
+    static_assert(PST >= 2 && BST % 2 == 0 && PST % 2 == 0, "ring lengths against the groups that wait on them");
+    static_assert(D_COLS + AST * A_STAGE <= 512 && AST >= 3 && DBUF < BST, "TMEM budget");
     static_assert(OFF_B % 1024 == 0, "B tiles need 1024-byte alignment");
     static_assert(TOTAL <= 227 * 1024, "shared memory budget");
 };
@@ -247,6 +257,8 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
     auto bar_full = [&](int s) { return bar0 + 8u * (2 * C::PST + s); };
     auto bar_done = [&](int s) { return bar0 + 8u * (2 * C::PST + C::BST + s); };
     auto bar_bempty = [&](int s) { return bar0 + 8u * (2 * C::PST + 2 * C::BST + s); };
+    auto bar_szfull = [&](int s) { return bar0 + 8u * (2 * C::PST + 3 * C::BST + s); };
+    auto bar_szempty = [&](int s) { return bar0 + 8u * (2 * C::PST + 3 * C::BST + MD_SZST + s); };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::NBARS * 8);
     __shared__ int abort_flag;
 
@@ -259,9 +271,10 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
         abort_flag = 0;
         for (int s = 0; s < C::PST; ++s) { mbar_init(bar_pfull(s), 1); mbar_init(bar_pempty(s), 4); }
         for (int s = 0; s < C::BST; ++s) { mbar_init(bar_full(s), 4 + 1 + MD_FOLD); mbar_init(bar_done(s), C::NT); mbar_init(bar_bempty(s), MD_FOLD); }
+        for (int s = 0; s < MD_SZST; ++s) { mbar_init(bar_szfull(s), 1); mbar_init(bar_szempty(s), MD_FOLD); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        // the first two k-blocks find both accumulator buffers free: stand in for the fold warps' arrivals
-        for (int s = 0; s < 2; ++s)
+        // the first DBUF k-blocks find their accumulator buffers free: stand in for the fold warps' arrivals
+        for (int s = 0; s < C::DBUF; ++s)
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(bar_full(s)), "r"((uint32_t)MD_FOLD) : "memory");
     }
     if (warp == MD_W_MMA) tc_alloc<512>(smem_u32(tmem_slot));
@@ -303,38 +316,50 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
         return u < big ? u / (p.per + 1) : p.rem + (u - big) / p.per;
     };
 
-    if (warp == MD_W_PROD) {
-        // ------------------------------ producers: 4 + BST lanes, each with its own stream of copies ------------------------------
-        // One thread completes only about four asynchronous copies per microsecond (each wait / expect / issue step is a
-        // long-latency instruction and they depend on one another).  Lanes 0-3 fetch the packed rows of every fourth
-        // k-block, one further lane per activation stage its tile, scales and zero words.
-        if (lane < 4) {
+    if (warp >= MD_W_PROD && warp < MD_W_MMA) {
+        // ------------------------------ producers: two warps, one lane each ------------------------------
+        // A thread completes only about four asynchronous copies per microsecond (each wait / expect / issue step is a
+        // long-latency instruction and they depend on one another), and several lanes of ONE warp in such loops fall
+        // into step with the slowest.  So: one thread for the packed rows (one copy per k-block) and one for the activation
+        // tiles (one copy per k-block) plus the scales and zero words (two copies per MD_SZG scale groups).
+        const int role = warp - MD_W_PROD;
+        if (lane == 0 && role == 0) {
             // The packed weights do not depend on the previous kernel in the stream: the first ring of stages is requested
             // at once; every later stage waits for the converters to have read its previous content.
-            for (int i = lane; i < nrun; i += 4) {
+            int t = x0 / p.kbt, b = x0 - t * p.kbt;
+            for (int i = 0; i < nrun; ++i) {
                 const int ps = i % C::PST;
                 if (i >= C::PST && !lazy_wait(bar_pempty(ps), ((i / C::PST) & 1) ^ 1)) break;
-                const int u = x0 + i, t = u / p.kbt, b = u - t * p.kbt;
                 mbar_expect_tx(bar_pfull(ps), (uint32_t)C::W_BYTES);
                 tma_load_2d(sbase + C::OFF_P + ps * C::P_STAGE, &tmap_q, t * C::COLS, b * C::PROWS, bar_pfull(ps));
                 MD_STAMP(0, i);
+                if (++b == p.kbt) { b = 0; ++t; }
             }
-        } else if (lane < 4 + C::BST) {
-            if (p.pdl) griddep_wait();                           // the activation tiles are written by the pre-pass
-            const uint32_t btx = (uint32_t)(C::B_COPY + C::S_BYTES + (p.qz ? C::Z_BYTES : 0));
-            for (int i = lane - 4; i < nrun; i += C::BST) {           // lane 4 + s owns activation stage s
+        } else if (lane == 0 && role == 1) {
+            if (p.pdl) { griddep_launch_dependents(); griddep_wait(); }   // the activation tiles are written by the pre-pass
+            // one scale / zero block = the scales and zero words of MD_SZG consecutive groups of a column tile; a new block
+            // starts with the run, with every column tile and every MD_SZG groups
+            const uint32_t stx = (uint32_t)(C::S_BYTES + (p.qz ? C::Z_BYTES : 0));
+            int t = x0 / p.kbt, kb = x0 - t * p.kbt, nblk = 0, cur = -1;
+            for (int i = 0; i < nrun; ++i) {
+                const int gb = (kb / p.kpg) / MD_SZG;
+                if (gb != cur) {
+                    cur = gb;
+                    const int ss = nblk % MD_SZST;
+                    if (nblk >= MD_SZST && !lazy_wait(bar_szempty(ss), ((nblk / MD_SZST) & 1) ^ 1)) break;
+                    const uint32_t dst = sbase + C::OFF_SZ + ss * C::SZ_STAGE;
+                    mbar_expect_tx(bar_szfull(ss), stx);
+                    tma_load_2d(dst, &tmap_s, t * C::COLS, gb * MD_SZG, bar_szfull(ss));
+                    if (p.qz) tma_load_2d(dst + C::S_BYTES, &tmap_z, t * C::COLS / C::PACK, gb * MD_SZG, bar_szfull(ss));
+                    ++nblk;
+                }
                 const int bs = i % C::BST;
                 if (i >= C::BST && !lazy_wait(bar_bempty(bs), ((i / C::BST) & 1) ^ 1)) break;
-                const int u = x0 + i, t = u / p.kbt, kb = u - t * p.kbt;
-                const uint32_t dst = sbase + C::OFF_B + bs * C::B_STAGE;
-                mbar_expect_tx(bar_full(bs), btx);
-                md_bulk_load(dst, p.xl + (size_t)kb * C::B_COPY, (uint32_t)C::B_COPY, bar_full(bs));
-                tma_load_2d(dst + C::OFF_S, &tmap_s, t * C::COLS, kb / p.kpg, bar_full(bs));
-                if (p.qz) tma_load_2d(dst + C::OFF_Z, &tmap_z, t * C::COLS / C::PACK, kb / p.kpg, bar_full(bs));
+                mbar_expect_tx(bar_full(bs), (uint32_t)C::B_COPY);
+                md_bulk_load(sbase + C::OFF_B + bs * C::B_STAGE, p.xl + (size_t)kb * C::B_COPY, (uint32_t)C::B_COPY, bar_full(bs));
                 MD_STAMP(1, i);
+                if (++kb == p.kbt) { kb = 0; ++t; cur = -1; }
             }
-        } else if (lane == 31 && p.pdl) {
-            griddep_launch_dependents();
         }
     } else if (warp >= MD_W_MMA) {
         // ------------------------------ MMA issuers: one lane per column tile ------------------------------
@@ -342,10 +367,11 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
         if (lane == 0 && nt < C::NT) {
             // kind::i8: D s32 (2 << 4), A unsigned 8-bit (0 << 7), B signed 8-bit (1 << 10), K-major both, N = 2 BM, M = 128
             const uint32_t idesc = (2u << 4) | (1u << 10) | ((uint32_t)(C::NB >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+            uint32_t early_ok = 0u;
             for (int i = 0; i < nrun; ++i) {
-                const int as = i % C::AST, bs = i % C::BST, db = i & 1;
+                const int as = i % C::AST, bs = i % C::BST, db = i % C::DBUF;
                 MD_SLOT(0);
-                if (!wait(bar_full(bs), (i / C::BST) & 1)) break;
+                if (!early_ok && !wait(bar_full(bs), (i / C::BST) & 1)) break;
                 tc_fence_after();
                 if (nt == 0) MD_STAMP(6, i);
                 const uint64_t bdesc = tc_desc_sw128(sbase + C::OFF_B + bs * C::B_STAGE);
@@ -355,6 +381,13 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
                 for (int k4 = 0; k4 < 4; ++k4) md_mma_i8(d, a + (uint32_t)(k4 * 8), bdesc + (uint64_t)(k4 * 2), idesc, k4 ? 1u : 0u);
                 tc_commit(bar_done(bs));
                 MD_T1(3); }
+                // ask about the next k-block now: the answer takes ~200 cycles either way and is read at the top of the next turn
+                early_ok = 0u;
+                if (i + 1 < nrun) {
+                    const int in = i + 1;
+                    asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}"
+                                 : "=r"(early_ok) : "r"(bar_full(in % C::BST)), "r"((uint32_t)((in / C::BST) & 1)) : "memory");
+                }
                 if (nt == 0) MD_STAMP(7, i);
             }
         }
@@ -486,27 +519,53 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
 
         int tile = x0 / p.kbt, kb = x0 - tile * p.kbt;
         if (p.pdl) griddep_wait();                              // before anything an earlier kernel wrote is touched (out / partial)
-        for (int j = 0; j < nrun; ++j) {
-            const int bs = j % C::BST, db = j & 1;
+        // one column tile's share of the run at a time: the store / partial-sum code sits between the tiles, outside the
+        // loop over k-blocks, which stays small enough for the instruction cache next to the other roles' loops
+        bool live = true;
+        uint32_t early_ok = 0u;
+        int sz_cur = -1, sz_n = 0;                                // scale / zero block in use (group block index) and blocks seen
+        const unsigned char* sz_stage = smem;
+        for (int j = 0; j < nrun && live;) {
+            const int seg_end = (nrun - j < p.kbt - kb) ? nrun : j + (p.kbt - kb);
+            int g0 = kb / p.kpg;                                   // once per column tile
+            int kin = kb - g0 * p.kpg, gb = g0 / MD_SZG, gi = g0 - gb * MD_SZG;
+        for (; j < seg_end; ++j) {
+            const int bs = j % C::BST, db = j % C::DBUF;
             if (tid == 0) MD_STAMP(8, j);
             MD_SLOT(0);
             // The MMAs of this k-block have completed.  Their issuing lanes waited for the copy engine's bytes of this stage
             // (`full`) before they issued, so the stage's sums, scales and zero words are in shared memory long since.
-            if (!wait(bar_done(bs), (j / C::BST) & 1)) break;
+            if (!early_ok && !wait(bar_done(bs), (j / C::BST) & 1)) { live = false; break; }
             if (tid == 0) MD_STAMP(9, j);
 #ifdef MD_TL
             const long long t_top = clock64();
 #endif
             tc_fence_after();
             const uint32_t dbase = tmem_base + lane_base + (uint32_t)((db * C::NT + nt) * C::NB + r0);
-            const unsigned char* bst = smem + C::OFF_B + bs * C::B_STAGE;
-            const float sf = H::to_float(reinterpret_cast<const uint16_t*>(bst + C::OFF_S)[cl]);
-            const int nzp1 = -(p.qz ? int((reinterpret_cast<const uint32_t*>(bst + C::OFF_Z)[cl / C::PACK] >> zsh) & ZMASK) + 1 : p.zp1_const);
-            bst += C::B_TILE;
+            // scale and zero word of this k-block's group, from the block of MD_SZG groups in shared memory
+            if (gb != sz_cur) {                                   // a new block (once per MD_SZG groups): hand the old one back, wait for the new one
+                if (sz_cur >= 0) { __syncwarp(); if (lane == 0) mbar_arrive(bar_szempty((sz_n - 1) % MD_SZST)); }
+                sz_cur = gb;
+                if (!wait(bar_szfull(sz_n % MD_SZST), (sz_n / MD_SZST) & 1)) { live = false; break; }
+                sz_stage = smem + C::OFF_SZ + (sz_n % MD_SZST) * C::SZ_STAGE;
+                ++sz_n;
+            }
+            const float sf = H::to_float(reinterpret_cast<const uint16_t*>(sz_stage)[gi * C::COLS + cl]);
+            const int nzp1 = -(p.qz ? int((reinterpret_cast<const uint32_t*>(sz_stage + C::S_BYTES)[gi * (C::COLS / C::PACK) + cl / C::PACK] >> zsh) & ZMASK) + 1
+                                   : p.zp1_const);
+            const unsigned char* bst = smem + C::OFF_B + bs * C::B_STAGE + C::B_TILE;
 #ifdef MD_TL
             asm volatile("" : "+f"(const_cast<float&>(sf)));
             tw[3] += clock64() - t_top;
 #endif
+            // An early poll for the NEXT k-block: the barrier unit answers after ~200 cycles whatever the answer, so the
+            // question is asked now and the answer read at the top of the next turn, behind this turn's arithmetic.
+            early_ok = 0u;
+            if (j + 1 < nrun) {
+                const int jn = j + 1;
+                asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}"
+                             : "=r"(early_ok) : "r"(bar_done(jn % C::BST)), "r"((uint32_t)((jn / C::BST) & 1)) : "memory");
+            }
 #pragma unroll
             for (int c0 = 0; c0 < C::RW; c0 += C::RC) {
                 uint32_t dh[C::RC], dl[C::RC];
@@ -515,11 +574,11 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
                 tc_ld<C::RC>(dbase + BM + c0, dl);
                 tc_wait_ld();
                 MD_T1(2); }
-                if (c0 + C::RC == C::RW) {                       // the accumulator buffer is in registers: it is free for the k-block after next
+                if (c0 + C::RC == C::RW) {                       // the accumulator buffer is in registers: it is free for the k-block DBUF later
                     { MD_T0();
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_full((j + 2) % C::BST));
+                    if (lane == 0) mbar_arrive(bar_full((j + C::DBUF) % C::BST));
                     MD_T1(5); }
                     if (tid == 0) MD_STAMP(10, j);
                 }
@@ -562,8 +621,13 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
             if (lane == 0) mbar_arrive(bar_bempty(bs));
             MD_T1(6); }
             if (tid == 0) MD_STAMP(11, j);
-            if (kb == p.kbt - 1 || j == nrun - 1) flush(tile);
-            if (++kb == p.kbt) { kb = 0; ++tile; }
+            ++kb;
+            if (++kin == p.kpg) { kin = 0; if (++gi == MD_SZG) { gi = 0; ++gb; } }   // next group / next block of groups, no division
+        }
+            if (!live) break;
+            flush(tile);
+            kb = 0; ++tile;
+            if (sz_cur >= 0) { __syncwarp(); if (lane == 0) mbar_arrive(bar_szempty((sz_n - 1) % MD_SZST)); sz_cur = -1; }   // the next tile starts a new block
         }
         if (fused_ar) {
             // every CTA of the grid reports when its exchanges are done; the last one publishes the epoch for the next call
@@ -697,7 +761,7 @@ int launch_mid(cudaStream_t st, const QGemmArgs& a) {
     {
         cuuint64_t dims[2] = {(cuuint64_t)a.n, (cuuint64_t)a.groups};
         cuuint64_t strides[1] = {(cuuint64_t)a.n * 2};
-        cuuint32_t box[2] = {(cuuint32_t)pl0.cols, 1};
+        cuuint32_t box[2] = {(cuuint32_t)pl0.cols, (cuuint32_t)MD_SZG};
         cuuint32_t es[2] = {1, 1};
         if (enc(&ms, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(a.scales), dims, strides, box, es,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -707,7 +771,7 @@ int launch_mid(cudaStream_t st, const QGemmArgs& a) {
     if (a.qzeros) {
         cuuint64_t dims[2] = {(cuuint64_t)(a.n / pack), (cuuint64_t)a.groups};
         cuuint64_t strides[1] = {(cuuint64_t)(a.n / pack) * 4};
-        cuuint32_t box[2] = {(cuuint32_t)(pl0.cols / pack), 1};
+        cuuint32_t box[2] = {(cuuint32_t)(pl0.cols / pack), (cuuint32_t)MD_SZG};
         cuuint32_t es[2] = {1, 1};
         if (enc(&mz, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(a.qzeros), dims, strides, box, es,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

@@ -59,8 +59,22 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
 
 // Eight consecutive activations of a row, optionally read through the act-order permutation
 // (x[perm[k0 .. k0+7]]): the weights' rows were sorted by group once, the activations follow here.
-template <typename T>
+template <typename T, bool COHERENT = false>
 __device__ __forceinline__ uint4 load_x8(const T* __restrict__ xrow, const int32_t* __restrict__ perm, size_t k0, int kmax) {
+    if constexpr (COHERENT) {
+        // activations written earlier in the SAME launch by other SMs: read through L2, never through the read-only path
+        if (!perm) return __ldcg(reinterpret_cast<const uint4*>(xrow + k0));
+        int idx[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) idx[i] = min(max(__ldg(perm + k0 + i), 0), kmax);
+        const unsigned short* xs = reinterpret_cast<const unsigned short*>(xrow);
+        uint4 r;
+        r.x = uint32_t(__ldcg(xs + idx[0])) | (uint32_t(__ldcg(xs + idx[1])) << 16);
+        r.y = uint32_t(__ldcg(xs + idx[2])) | (uint32_t(__ldcg(xs + idx[3])) << 16);
+        r.z = uint32_t(__ldcg(xs + idx[4])) | (uint32_t(__ldcg(xs + idx[5])) << 16);
+        r.w = uint32_t(__ldcg(xs + idx[6])) | (uint32_t(__ldcg(xs + idx[7])) << 16);
+        return r;
+    }
     if (!perm) return __ldg(reinterpret_cast<const uint4*>(xrow + k0));
     int4 i0 = __ldg(reinterpret_cast<const int4*>(perm + k0)), i1 = __ldg(reinterpret_cast<const int4*>(perm + k0 + 4));
     // a permutation entry outside [0, K) is clamped, like every other index this library reads from the caller

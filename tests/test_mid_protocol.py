@@ -26,7 +26,7 @@ class Bar:
         return (self.phase & 1) != parity
 
 
-def run(nrun, AST, BST, PST, NT, FOLD, seed, planes=4, blanes=None, cgroups=2):
+def run(nrun, AST, BST, PST, NT, FOLD, seed, planes=4, blanes=None, cgroups=2, DBUF=2):
     blanes = BST if blanes is None else blanes
     rnd = random.Random(seed)
     pfull = [Bar(f"pfull{s}", 1) for s in range(PST)]
@@ -34,7 +34,7 @@ def run(nrun, AST, BST, PST, NT, FOLD, seed, planes=4, blanes=None, cgroups=2):
     full = [Bar(f"full{s}", 4 + 1 + FOLD) for s in range(BST)]
     done = [Bar(f"done{s}", NT) for s in range(BST)]
     bempty = [Bar(f"bempty{s}", FOLD) for s in range(BST)]
-    for s in range(2):
+    for s in range(DBUF):
         full[s].arrive("init", FOLD)
     log = []
     # expected unit of every arrival, to check aliasing: full[s] phase p must only get arrivals of unit s + p*BST
@@ -97,8 +97,8 @@ def run(nrun, AST, BST, PST, NT, FOLD, seed, planes=4, blanes=None, cgroups=2):
             while not done[bs].done((j // BST) & 1):
                 yield
             yield
-            t = (j + 2) % BST
-            check(full, t, BST, j + 2, f"F{w}")
+            t = (j + DBUF) % BST
+            check(full, t, BST, j + DBUF, f"F{w}")
             full[t].arrive(f"F{w}:{j}")
             yield
             check(bempty, bs, BST, j, f"F{w}")
@@ -127,8 +127,8 @@ def run(nrun, AST, BST, PST, NT, FOLD, seed, planes=4, blanes=None, cgroups=2):
 
 
 CONFIGS = {
-    "int4 rows<=16": dict(AST=6, BST=8, PST=8, NT=2), "int4 rows<=32": dict(AST=4, BST=8, PST=8, NT=2),
-    "int4 rows<=64": dict(AST=4, BST=6, PST=12, NT=1), "int8 rows<=32": dict(AST=4, BST=8, PST=4, NT=2),
+    "int4 rows<=16": dict(AST=4, BST=8, PST=8, NT=2, DBUF=4), "int4 rows<=32": dict(AST=4, BST=8, PST=8, NT=2),
+    "int4 rows<=64": dict(AST=4, BST=6, PST=12, NT=1), "int8 rows<=16": dict(AST=4, BST=8, PST=4, NT=2, DBUF=4), "int8 rows<=32": dict(AST=4, BST=8, PST=4, NT=2),
     "int8 rows<=64": dict(AST=4, BST=6, PST=4, NT=1),
 }
 
