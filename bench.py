@@ -585,7 +585,7 @@ def run_ours(args):
             far = FusedAllReduce(m_max=max(16, args.m), n_max=HIDDEN)
 
     m = args.m
-    shapes = layer_shapes(world)
+    shapes = layer_shapes(args.shard_as if (world == 1 and args.shard_as > 1) else world)
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
     layers = []
     for _ in range(args.layers):
@@ -604,7 +604,27 @@ def run_ours(args):
     out_host = torch.empty((m, HIDDEN), dtype=torch.float16).pin_memory()
     flags = _lib.FLAG_PDL if args.pdl else 0
 
+    # decode (M <= 2): the linears of `--chain` consecutive layers go to ONE resident launch (mt_qgemm_chain); every
+    # entry waits for the one before it, as the stream order of separate launches would make it
+    chains = []
+    chain_layers = max(0, min(args.chain, 4)) if m <= 2 else 0
+    if chain_layers:
+        from minit_b200.chain import ChainEntry, LinearChain
+        for l0 in range(0, len(layers), chain_layers):
+            entries = []
+            for lin in layers[l0:l0 + chain_layers]:
+                for i, (qw, qz, sc) in enumerate(lin):
+                    entries.append(ChainEntry(xs[i], qw, qz, sc, outs[i], allreduce=(far is not None and shapes[i][3] == "row")))
+            chains.append(LinearChain(entries, bits=BITS, fused=far, flags=args.chain_flags))
+        if comm is not None and far is None:
+            chains = []                                   # NCCL all-reduce between the linears: separate launches
+    launches_per_step = len(chains) if chains else args.layers * len(shapes)
+
     def one_pass():
+        if chains:
+            for c in chains:
+                c()
+            return
         for lin in layers:
             for i, (qw, qz, sc) in enumerate(lin):
                 if comm is not None and shapes[i][3] == "row" and far is not None:
@@ -685,21 +705,24 @@ def run_ours(args):
     per_rank_wbytes = args.layers * sum(weight_bytes(k, n) for _, k, n, _ in shapes)
     per_rank_abytes = args.layers * sum(algorithmic_bytes(m, k, n) for _, k, n, _ in shapes)
     total_wbytes = per_rank_wbytes * world
-    launches_per_step = args.layers * len(shapes)
     hbm_peak, peak_kind = peaks()
+    linears_per_step = args.layers * len(shapes)
+    if chains and not all(c.single_launch for c in chains):
+        raise SystemExit("the library declined the chain launch; rerun with --chain 0")
     achieved = per_rank_abytes / (ms_step * 1e-3) / 1e9     # per GPU: bytes of its launches / time of its launches
     # DRAM bytes per launch of the decode GEMV: ncu measured 245.85 MB read + 3.77 MB written for
     # 244.2 MB of algorithmic bytes on gate/up, 122.12 + 3.41 MB for 122.1 MB on down
     # (profiles/qgemm_vstream_8192x57344_m1.md, profiles/qgemm_vec_split_28672x8192_m1.md); traffic
     # scales with the bytes.
     traffic = 1.025 * per_rank_abytes / launches_per_step
+    launch_desc = ("chain: %d linears (%d layers) per launch" % (chain_layers * len(shapes), chain_layers)) if chains else "one launch per linear"
     line = {
         "metric": "int4 dequant-GEMM weight GB/s at M=%d" % m, "value": total_wbytes / (ms_step * 1e-3) / 1e9, "unit": "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 (int4 weights, f32 accumulate)",
         "data": "synthetic",
         "config": {"workload": f"llama3-70b-gptq-int4-g128-decode-linears-tp{world}", "m": m, "layers": args.layers,
-                   "linears_per_layer": [[n_, k_, nn_] for n_, k_, nn_, _ in shapes], "launch": mode, "pdl": bool(args.pdl), "allreduce": (args.allreduce if world > 1 else "none"),
+                   "linears_per_layer": [[n_, k_, nn_] for n_, k_, nn_, _ in shapes], "launch": mode, "launches_per_step": launches_per_step, "kernel_launch": launch_desc, "pdl": bool(args.pdl), "allreduce": (args.allreduce if world > 1 else "none"),
                    "l2": "inputs larger than L2 (%.1f GB of weights per rank per step)" % (per_rank_wbytes / 1e9),
                    "tokens_per_s": m / (ms_step * 1e-3)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
@@ -709,7 +732,7 @@ def run_ours(args):
                 "h2d_bytes_per_step": sum(x.numel() * 2 for x in xs_host), "d2h_bytes_per_step": out_host.numel() * 2,
                 "note": "weights stay resident (loaded once, like model parameters); activations cross PCIe every step"},
         "e2e_eager": None if ms_e2e_eager is None else {"value": total_wbytes / (ms_e2e_eager * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e_eager,
-                                                          "launch": "eager: one Python call per linear, %d per step" % launches_per_step},
+                                                          "launch": "eager: %d Python calls per step (%s)" % (launches_per_step, launch_desc)},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
         "parity_check": parity,
@@ -856,6 +879,9 @@ def main():
     ap.add_argument("--batch", "--m", dest="m", type=int, default=1, help="decode batch M (use --batch under torchrun)")
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--pdl", type=int, default=1)
+    ap.add_argument("--chain", type=int, default=0, help="decode: layers per resident launch of mt_qgemm_chain (0: one launch per linear, which measures faster)")
+    ap.add_argument("--chain-flags", type=int, default=0, help="tuning bits passed to the chain launch")
+    ap.add_argument("--shard-as", type=int, default=1, help="one GPU only: time the per-rank shapes of an N-way split, no exchange")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
                     help="row-parallel exchange: fused into the GEMM epilogue over peer memory, or an NCCL all-reduce after it")

@@ -134,6 +134,40 @@ int mt_qgemm_allreduce(void* stream, const void* x, const uint32_t* qweight, con
                        int m, int n, int k, int nr_groups, int bits, int dtype,
                        void* workspace, size_t workspace_bytes, int flags,
                        void* const* peer_buffers, int rank, int world, size_t buffer_bytes);
+
+/*
+ * Several decode linears (M <= 2) of a layer in ONE launch, in list order.  Replaces a run of fused-kernel launches
+ * of the reference (examples/qwen1_5_int8.py:244-267 calls its launcher once per linear; a decoder layer issues
+ * q/k/v, o, gate/up, down back to back) and, for row-parallel entries, the all_reduce after each of them
+ * (minit/nccl/kernel.py:51-53).  An entry may read what an EARLIER entry of the same call wrote (x or residual
+ * = an earlier out): before a warp reads its activations it waits -- bounded; on expiry the workspace error word
+ * is set to 6 -- until every column block of the earlier entries is stored.  The weights do not wait: the grid is
+ * resident as a whole and the first rows of the next entry are requested before the previous entry's partial sums
+ * are combined, so the weight stream does not stop between linears.
+ *   Every entry must be a request the decode GEMV accepts: no g_idx, N % 128 == 0, group size % 32 == 0 (all
+ *   entries of a call with the same group size class: all % 64 == 0, or none).  m, bits, dtype, workspace and the
+ *   peers are shared.  epilogue: MT_EPILOGUE_NONE or MT_EPILOGUE_SWIGLU (out is [M, N/2]).  allreduce != 0: the
+ *   entry's finished sums are exchanged over peer_buffers as in mt_qgemm_allreduce (residual added after the sum).
+ *   count <= MT_CHAIN_MAX.  The launch is cooperative: it fails with MT_ERR_CUDA rather than wait for CTAs that
+ *   cannot be resident.  Returns MT_ERR_UNSUPPORTED when the list does not fit; the caller then issues the
+ *   linears one by one.
+ */
+#define MT_CHAIN_MAX 16
+typedef struct mt_chain_linear {
+    const void* x;             /* [M,K] T */
+    const uint32_t* qweight;   /* [K/pack, N] */
+    const uint32_t* qzeros;    /* [G, N/pack] or null */
+    const void* scales;        /* [G, N] T */
+    const void* bias;          /* [N] T or null */
+    const void* residual;      /* [M,N] T or null */
+    void* out;                 /* [M,N] T ([M,N/2] with MT_EPILOGUE_SWIGLU) */
+    int n, k, nr_groups;
+    int epilogue;
+    int allreduce;
+} mt_chain_linear;
+int mt_qgemm_chain(void* stream, const mt_chain_linear* linears, int count, int m, int bits, int dtype,
+                   void* workspace, size_t workspace_bytes, int flags,
+                   void* const* peer_buffers, int rank, int world, size_t buffer_bytes);
 size_t mt_allreduce_buffer_bytes(int m_max, int n_max, int world);
 
 /*

@@ -11,6 +11,7 @@ from .qlinear import (QLinear, QLinearWithBias, W8Linear, pack_w8, quantized_mat
                       w8_perchannel_matrix_multiply)
 from .feedforward import (QFeedForward, interleave_gate_up, quantized_gate_up_swiglu, quantized_matrix_multiply_residual,
                           swiglu_interleaved)
+from .chain import ChainEntry, LinearChain
 from .quantize import Dequantize, QuantizedTensor, dequantize
 from .operator.linalg import MatrixMultiply
 from .functional.linalg import matrix_multiply
@@ -21,6 +22,7 @@ __all__ = [
     "quantized_matrix_multiply_ordered", "sort_act_order", "pack_w8",
     "unpack", "Dequantize", "QuantizedTensor", "dequantize", "MatrixMultiply", "matrix_multiply",
     "dispatch", "register_dispatch",
+    "ChainEntry", "LinearChain",
     "QFeedForward", "interleave_gate_up", "quantized_gate_up_swiglu", "quantized_matrix_multiply_residual", "swiglu_interleaved",
 ]
 __version__ = "0.1.0"

@@ -24,6 +24,18 @@ lib = ctypes.CDLL(LIB_PATH)
 MT_F16, MT_BF16 = 0, 1
 FLAG_FORCE_SMALL, FLAG_FORCE_TC, FLAG_PDL, FLAG_FORCE_VEC, FLAG_FORCE_UMMA, FLAG_AR_SHORT_WAIT, FLAG_FORCE_MID = 1, 2, 4, 16, 32, 64, 128
 ERR_PEER_TIMEOUT = -12
+ERR_UNSUPPORTED = -8
+CHAIN_MAX = 16
+EPILOGUE_NONE, EPILOGUE_SWIGLU = 0, 1
+
+
+class ChainLinear(ctypes.Structure):
+    """``mt_chain_linear`` of include/minit_b200.h."""
+    _fields_ = [("x", ctypes.c_void_p), ("qweight", ctypes.c_void_p), ("qzeros", ctypes.c_void_p), ("scales", ctypes.c_void_p),
+                ("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("out", ctypes.c_void_p),
+                ("n", ctypes.c_int), ("k", ctypes.c_int), ("nr_groups", ctypes.c_int), ("epilogue", ctypes.c_int),
+                ("allreduce", ctypes.c_int)]
+
 COUNTER_BYTES = 16384
 STATIC_SCRATCH_BYTES = 8 << 20
 
@@ -38,6 +50,7 @@ SYMBOLS = {
     "mt_unpack": (_i, [_vp, _vp, _vp, _i, _i, _i, _i]),
     "mt_qgemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _i]),
     "mt_qgemm_allreduce": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _i, _vp, _i, _i, _sz]),
+    "mt_qgemm_chain": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _sz, _i, _vp, _i, _i, _sz]),
     "mt_allreduce_buffer_bytes": (_sz, [_i, _i, _i]),
     "mt_qgemm_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _i, _vp, _i, _i, _sz]),
     "mt_interleave_gate_up": (_i, [_vp] * 13 + [_i, _i, _i, _i]),

@@ -352,6 +352,48 @@ int mt_qgemm_residual(void* stream, const void* x, const uint32_t* qweight, cons
     return rc;
 }
 
+int mt_qgemm_chain(void* stream, const mt_chain_linear* linears, int count, int m, int bits, int dtype,
+                   void* workspace, size_t workspace_bytes, int flags,
+                   void* const* peer_buffers, int rank, int world, size_t buffer_bytes) {
+    if (count < 0) return MT_ERR_SHAPE;
+    if (count == 0 || m == 0) return MT_OK;
+    if (!linears) return MT_ERR_NULL;
+    if (count > MT_CHAIN_MAX || m < 0 || m > 2) return MT_ERR_UNSUPPORTED;
+    if (world < 1 || world > kArMaxWorld || rank < 0 || rank >= world) return MT_ERR_SHAPE;
+    if (!workspace) return MT_ERR_NULL;
+    if (!aligned16(workspace)) return MT_ERR_ALIGN;
+    QGemmArgs list[MT_CHAIN_MAX];
+    bool any_ar = false;
+    for (int e = 0; e < count; ++e) {
+        const mt_chain_linear& l = linears[e];
+        int rc = validate_gptq(l.qweight, l.qzeros, l.scales, l.n, l.k, l.nr_groups, bits, dtype);
+        if (rc != MT_OK) return rc;
+        if (l.n == 0 || l.k == 0) return MT_ERR_SHAPE;
+        if (l.epilogue != MT_EPILOGUE_NONE && l.epilogue != MT_EPILOGUE_SWIGLU) return MT_ERR_UNSUPPORTED;
+        if (l.epilogue == MT_EPILOGUE_SWIGLU && (l.n % 16 != 0 || l.allreduce || l.residual)) return MT_ERR_UNSUPPORTED;
+        if (!l.x || !l.out) return MT_ERR_NULL;
+        if (!aligned16(l.x) || !aligned16(l.out) || (l.bias && !aligned16(l.bias)) || (l.residual && !aligned16(l.residual))) return MT_ERR_ALIGN;
+        if ((l.k / l.nr_groups) % (4 * (32 / bits)) != 0) return MT_ERR_SHAPE;
+        QGemmArgs a = {};
+        a.x = l.x; a.qweight = l.qweight; a.qzeros = l.qzeros; a.scales = l.scales; a.bias = l.bias; a.out = l.out;
+        a.residual = l.residual; a.epilogue = l.epilogue;
+        a.m = m; a.n = l.n; a.k = l.k; a.groups = l.nr_groups; a.bits = bits; a.dtype = dtype;
+        a.workspace = workspace; a.workspace_bytes = workspace_bytes; a.flags = flags;
+        if (l.allreduce && world > 1) {
+            if (!peer_buffers) return MT_ERR_NULL;
+            if (buffer_bytes < kArDataOffset + 2 * (size_t)world * 256) return MT_ERR_WORKSPACE;
+            a.ar_peers = reinterpret_cast<unsigned char* const*>(peer_buffers);
+            a.ar_rank = rank; a.ar_world = world; a.ar_bytes = buffer_bytes;
+            any_ar = true;
+        }
+        list[e] = a;
+    }
+    (void)any_ar;
+    const int rc = check_device();
+    if (rc != MT_OK) return rc;
+    return launch_vec_chain(static_cast<cudaStream_t>(stream), list, count);
+}
+
 int mt_qgemm_swiglu(void* stream, const void* x, const uint32_t* qweight, const uint32_t* qzeros, const void* scales,
                     const void* bias, void* out, void* scratch, int m, int n, int k, int nr_groups, int bits, int dtype,
                     void* workspace, size_t workspace_bytes, int flags) {

@@ -188,6 +188,7 @@ int launch_small_w8(cudaStream_t st, const QGemmArgs& a);       // int8 [K,N] pe
 int launch_w8vec(cudaStream_t st, const QGemmArgs& a);          // int8 [K,N] per-channel, CUDA-core GEMV, M <= 2, N % 256 == 0
 bool w8vec_supported(const QGemmArgs& a);
 int launch_vec(cudaStream_t st, const QGemmArgs& a);            // CUDA-core decode GEMV, M <= 2, contiguous groups
+int launch_vec_chain(cudaStream_t st, const QGemmArgs* list, int count);   // several such linears in one resident launch
 bool vec_supported(const QGemmArgs& a);
 int vec_plan(const QGemmArgs& a);                               // > 0 split-K factor, 0 stream-K, < 0 MT_ERR_*
 int launch_interleave_gate_up(cudaStream_t st, const uint32_t* qw_g, const uint32_t* qw_u, const uint32_t* qz_g, const uint32_t* qz_u,

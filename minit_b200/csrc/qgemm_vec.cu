@@ -412,8 +412,33 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr)); return v;
 }
 
-template <int BITS, typename T, int MB, int CK, int NW, int D, int MINB>
-__global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const StreamParams p) {
+// The cursor of a warp's weight copies: which packed row comes next, and where its column block ends.
+struct RingIt {
+    const uint4* ptr;       // next packed row (this lane's 16 bytes of it)
+    const uint4* qbase;     // the lane's 16 bytes of row 0, column block 0
+    uint32_t rstride_b;     // bytes between packed rows
+    int rows;               // rows left in the current column block
+    int tile;               // current column block
+    int issued, total;      // rows requested so far / rows of the run
+    int tile_rows;          // packed rows of a whole column block
+};
+
+// A list of linears walked inside one launch (qgemm_vchain_kernel): what an entry needs to know about its neighbours.
+struct ChainCtx {
+    unsigned* done;             // column blocks finished so far in this launch, all entries together (entries finish in order)
+    volatile unsigned* seen;    // shared memory: the largest value of *done that this CTA's polling thread has read
+    unsigned* err;              // error word (6: the wait for the previous entry ran out)
+    unsigned need;              // column blocks that must be finished before this entry reads its activations
+    unsigned epoch;             // epoch of this entry's all-reduce
+    int spin_limit;
+    const StreamParams* next;   // the entry after this one (null: last)
+    bool late;                  // tuning: request the next entry's rows after the combine step, not before
+    bool prefilled;             // `it` is this entry's cursor and its first D rows are already on their way
+    RingIt it;
+};
+
+template <int BITS, typename T, int MB, int CK, int NW, int D, bool CHAIN>
+__device__ __forceinline__ void vstream_body(const StreamParams& p, unsigned char* smem, float* seg, int* seg_tile, ChainCtx& cx) {
     using H = F16x2<T>;
     constexpr int PACK = 32 / BITS;
     constexpr int RPK = 8 / PACK;            // packed rows per k-step (8 values of k)
@@ -427,18 +452,18 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
     constexpr uint32_t MASK_HI = 0x00f000f0u;
     static_assert(D % RG == 0 && BODY % D == 0, "ring depth");
 
-    extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // partial rows of column blocks that this warp shares with others: at most two per warp (the
-    // block its run starts in and the block it ends in), combined across the CTA before they leave it
-    __shared__ __align__(16) float seg[NW * 2 * MB * VEC_COLS];
-    __shared__ int seg_tile[NW * 2];
-    if (p.pdl) griddep_launch_dependents();
+    if (!CHAIN && p.pdl) griddep_launch_dependents();
     const int j = blockIdx.x * NW + warp;
     const bool idle = j >= p.warps;
 
-    const int u0 = idle ? 0 : j * p.per + (j < p.rem ? j : p.rem);
-    const int nun = idle ? 0 : p.per + (j < p.rem ? 1 : 0);   // chunks of this warp's run (0: no run, the warp only joins the CTA's combine step)
+    // the run of warp jj in entry q: the first `rem` warps get per + 1 units
+    auto run_of = [](const StreamParams& q, int jj, int& first, int& count) {
+        if (jj >= q.warps) { first = 0; count = 0; return; }
+        first = jj * q.per + (jj < q.rem ? jj : q.rem); count = q.per + (jj < q.rem ? 1 : 0);
+    };
+    int u0, nun;                      // chunks of this warp's run (0: no run, the warp only joins the CTA's combine step)
+    run_of(p, j, u0, nun);
     int tile = u0 / p.nchunks;
     const int c_first = u0 - tile * p.nchunks;
     const int total_rows = nun * CRW;
@@ -460,7 +485,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
         const size_t k = (size_t)cl * CK + (size_t)(ks % CKS) * 8;
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb)
-            xr[mb] = (ok && mb < p.m) ? load_x8(xg + (size_t)mb * p.k, p.xperm, k, p.k - 1) : make_uint4(0, 0, 0, 0);
+            xr[mb] = (ok && mb < p.m) ? load_x8<T, CHAIN>(xg + (size_t)mb * p.k, p.xperm, k, p.k - 1) : make_uint4(0, 0, 0, 0);
     };
     auto stage_x = [&](int b, const uint4 (&xr)[MB]) {
         const int buf = b & 1;
@@ -505,40 +530,54 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
     uint4 xr[MB], xr0[MB];
 
     // ---- weight copies: issue iterator runs D rows ahead of the consumer ----
-    const size_t rstride = size_t(p.n) / 4;
-    const uint4* qbase = reinterpret_cast<const uint4*>(p.qw) + lane;
-    const uint4* it_ptr = qbase + (size_t)tile * (VEC_COLS / 4) + (size_t)c_first * CRW * rstride;
-    int it_rows = (p.nchunks - c_first) * CRW;
-    int it_tile = tile;
-    int issued = 0;
-    auto issue = [&](int slot) {
-        const bool valid = issued < total_rows;
-        cp_async16(ring_s + uint32_t(slot) * SLOT_BYTES, valid ? it_ptr : qbase, valid);
-        ++issued;
-        it_ptr += rstride;
-        if (--it_rows == 0) { ++it_tile; it_ptr = qbase + (size_t)it_tile * (VEC_COLS / 4); it_rows = p.nchunks * CRW; }
+    auto ring_begin = [&](const StreamParams& q) -> RingIt {
+        int q_u0, q_nun;
+        run_of(q, j, q_u0, q_nun);
+        const int q_tile = q_u0 / q.nchunks, q_c = q_u0 - q_tile * q.nchunks;
+        RingIt r;
+        r.qbase = reinterpret_cast<const uint4*>(q.qw) + lane;
+        r.rstride_b = uint32_t(q.n) * 4u;
+        r.ptr = r.qbase + (size_t)q_tile * (VEC_COLS / 4) + (size_t)q_c * CRW * (size_t(q.n) / 4);
+        r.rows = (q.nchunks - q_c) * CRW;
+        r.tile = q_tile; r.issued = 0; r.total = q_nun * CRW; r.tile_rows = q.nchunks * CRW;
+        return r;
+    };
+    auto issue = [&](RingIt& r, int slot) {
+        const bool valid = r.issued < r.total;
+        cp_async16(ring_s + uint32_t(slot) * SLOT_BYTES, valid ? r.ptr : r.qbase, valid);
+        ++r.issued;
+        r.ptr = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(r.ptr) + r.rstride_b);
+        if (--r.rows == 0) { ++r.tile; r.ptr = r.qbase + (size_t)r.tile * (VEC_COLS / 4); r.rows = r.tile_rows; }
     };
     // RG consecutive rows at once: when they lie in one column block and are all valid (almost always) the
     // addresses are base + r * stride and the bookkeeping runs once per group instead of once per row
-    const uint32_t rstride_b = uint32_t(p.n) * 4u;        // bytes between packed rows
-    auto issue_group = [&](int slot0) {
-        if (it_rows > RG && issued + RG <= total_rows) {
-            const char* base = reinterpret_cast<const char*>(it_ptr);
+    auto issue_group = [&](RingIt& r, int slot0) {
+        if (r.rows > RG && r.issued + RG <= r.total) {
+            const char* base = reinterpret_cast<const char*>(r.ptr);
 #pragma unroll
-            for (int r = 0; r < RG; ++r)
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ring_s + uint32_t(slot0 + r) * SLOT_BYTES),
-                             "l"(base + (unsigned long long)(uint32_t(r) * rstride_b)) : "memory");
-            issued += RG; it_rows -= RG;
-            it_ptr = reinterpret_cast<const uint4*>(base + (unsigned long long)(uint32_t(RG) * rstride_b));
+            for (int q = 0; q < RG; ++q)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ring_s + uint32_t(slot0 + q) * SLOT_BYTES),
+                             "l"(base + (unsigned long long)(uint32_t(q) * r.rstride_b)) : "memory");
+            r.issued += RG; r.rows -= RG;
+            r.ptr = reinterpret_cast<const uint4*>(base + (unsigned long long)(uint32_t(RG) * r.rstride_b));
         } else {
 #pragma unroll
-            for (int r = 0; r < RG; ++r) issue(slot0 + r);
+            for (int q = 0; q < RG; ++q) issue(r, slot0 + q);
         }
     };
+    auto fill_ring = [&](RingIt& r) {
 #pragma unroll
-    for (int gq = 0; gq < NG; ++gq) {
-        issue_group(gq * RG);
-        cp_async_commit();
+        for (int gq = 0; gq < NG; ++gq) {
+            issue_group(r, gq * RG);
+            cp_async_commit();
+        }
+    };
+    RingIt it;
+    if (CHAIN && cx.prefilled) {
+        it = cx.it;                       // requested while the previous entry's sums were being combined
+    } else {
+        it = ring_begin(p);
+        fill_ring(it);
     }
 
     // ---- scales / zero points: current group converted, next two raw ----
@@ -561,7 +600,31 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
     uint2 s1 = load_s(); uint32_t z1 = load_z(); pf_advance();
     uint2 s2 = load_s(); uint32_t z2 = load_z();
 
-    if (p.pdl) griddep_wait();
+    if constexpr (CHAIN) {
+        // the activations may be the previous entry's output: wait, bounded, until all its column blocks are stored
+        // One thread of the CTA polls the counter in global memory and relays what it saw through shared memory:
+        // thousands of warps polling one word would queue at its L2 slice and hold up the weight stream behind them.
+        // (Warps without a run in this entry do not wait; the CTA's warp 0 has a run whenever any of its warps has.)
+        if (cx.need && !idle) {
+            if (lane == 0) {
+                int spins = 0;
+                for (;;) {
+                    if (*cx.seen >= cx.need) break;
+                    if (warp == 0) {
+                        unsigned v;
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(cx.done) : "memory");
+                        if (v >= cx.need) { __threadfence(); *cx.seen = v; break; }
+                    }
+                    if (++spins > cx.spin_limit) { if (cx.err) atomicExch(cx.err, 6u); break; }   // give up and flag it: the host reads the word
+                    __nanosleep(warp == 0 ? 100 : 40);
+                }
+                __threadfence();
+            }
+            __syncwarp();
+        }
+    } else {
+        if (p.pdl) griddep_wait();
+    }
     load_x(0, xr0);
     load_x(1, xr);
 
@@ -592,7 +655,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
     const T* bias = reinterpret_cast<const T*>(p.bias);
     uint16_t* out = reinterpret_cast<uint16_t*>(p.out);
     const bool fused_ar = ar_active(p.ar);
-    const unsigned epoch = fused_ar ? ar_epoch(p.ar) : 0u;      // after griddepcontrol.wait: the previous call has published its epoch
+    const unsigned epoch = !fused_ar ? 0u : CHAIN ? cx.epoch : ar_epoch(p.ar);   // after griddepcontrol.wait: the previous call has published its epoch
     auto write_out = [&](int t, const float4 (&r)[MB]) {
         const int colb = t * VEC_COLS + lane * 4;
         float b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
@@ -623,13 +686,19 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
                 }
                 if (fused_ar) v = ar_exchange(p.ar, epoch, (size_t)mb * p.n + colb, v);
                 if (p.residual) {
-                    const uint2 rv = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p.residual) + (size_t)mb * p.n + colb));
+                    const uint2* rp = reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p.residual) + (size_t)mb * p.n + colb);
+                    const uint2 rv = CHAIN ? __ldcg(rp) : __ldg(rp);
                     v.x += H::to_float(uint16_t(rv.x & 0xffff)); v.y += H::to_float(uint16_t(rv.x >> 16));
                     v.z += H::to_float(uint16_t(rv.y & 0xffff)); v.w += H::to_float(uint16_t(rv.y >> 16));
                 }
                 uint2 o; o.x = H::pack(v.x, v.y); o.y = H::pack(v.z, v.w);
                 *reinterpret_cast<uint2*>(out + (size_t)mb * p.n + colb) = o;
             }
+        if constexpr (CHAIN) {
+            // one more column block of this launch is in memory: release it to the entries that read it
+            __syncwarp();
+            if (lane == 0) { __threadfence(); atomicAdd(cx.done, 1u); }
+        }
     };
     // first and last warp with a run in column block t
     auto owner = [&](int u) -> int {
@@ -719,7 +788,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
             }
             if (rb % RG == RG - 1) {
                 // the four rows of this group are in registers: refill their slots
-                issue_group((rb - (RG - 1)) % D);
+                issue_group(it, (rb - (RG - 1)) % D);
                 cp_async_commit();
             }
             if (rr == RPK - 1 && (kj + 1) % CKS == 0) {
@@ -754,6 +823,11 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
         }
     }
     cp_async_wait<0>();
+    if constexpr (CHAIN) {
+        // the ring is free: request the first rows of the next entry now, so that its weights stream while this
+        // entry's partial sums are combined and while the next entry waits for them
+        if (cx.next && !cx.late) { cx.it = ring_begin(*cx.next); fill_ring(cx.it); cx.prefilled = true; }
+    }
 
     // ---- combine the shared partial rows: CTA first, then across CTAs ----
     if (lane == 0) {
@@ -785,26 +859,35 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
         const int cf = jf / NW, cl = jl / NW;               // first and last CTA with a share in the block
         bool write = true;
         if (cf != cl) {
+            // The LAST CTA with a share in the block finishes it.  The others store their partial row and count
+            // themselves in with a release-add that nobody waits for (every lane releases its own 16 bytes); the owner
+            // polls the count -- bounded -- and then adds the rows in CTA order, its own (still in registers) last.
+            // It only ever waits for CTAs with a smaller index, which were dispatched before it.
+            if (cta != cl) {
 #pragma unroll
-            for (int mb = 0; mb < MB; ++mb)
-                if (mb < p.m) __stcg(reinterpret_cast<float4*>(p.partial + ((size_t)(cta + t) * MB + mb) * VEC_COLS + lane * 4), r[mb]);
-            __threadfence();
-            __syncwarp();
-            unsigned old = 0;
-            if (lane == 0) old = atomicAdd(p.counters + t, 1u);
-            old = __shfl_sync(0xffffffffu, old, 0);
-            write = old == unsigned(cl - cf);
-            if (write) {
-                __threadfence();
+                for (int mb = 0; mb < MB; ++mb)
+                    if (mb < p.m) __stcg(reinterpret_cast<float4*>(p.partial + ((size_t)(cta + t) * MB + mb) * VEC_COLS + lane * 4), r[mb]);
+                asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.counters + t) : "memory");
+                write = false;
+            } else {
+                const unsigned target = 32u * unsigned(cl - cf);
+                for (int spins = 0;; ++spins) {
+                    unsigned v;
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.counters + t) : "memory");
+                    if (v >= target) break;
+                    if (spins > (1 << 21)) { if (p.ar.err) atomicExch(p.ar.err, 7u); break; }   // give up and flag it: the host reads the word
+                    if (spins > 8) __nanosleep(40);
+                }
+                float4 own[MB];
 #pragma unroll
-                for (int mb = 0; mb < MB; ++mb) r[mb] = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int cc = cf; cc <= cl; cc += 8) {      // eight independent loads in flight, summed in CTA order
+                for (int mb = 0; mb < MB; ++mb) { own[mb] = r[mb]; r[mb] = make_float4(0.f, 0.f, 0.f, 0.f); }
+                for (int cc = cf; cc < cl; cc += 8) {       // eight independent loads in flight, summed in CTA order
                     float4 v[8][MB];
 #pragma unroll
                     for (int qq = 0; qq < 8; ++qq)
 #pragma unroll
                         for (int mb = 0; mb < MB; ++mb)
-                            v[qq][mb] = (cc + qq <= cl && mb < p.m)
+                            v[qq][mb] = (cc + qq < cl && mb < p.m)
                                 ? __ldcg(reinterpret_cast<const float4*>(p.partial + ((size_t)(cc + qq + t) * MB + mb) * VEC_COLS + lane * 4))
                                 : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -812,14 +895,84 @@ __global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const Stre
 #pragma unroll
                         for (int mb = 0; mb < MB; ++mb) { r[mb].x += v[qq][mb].x; r[mb].y += v[qq][mb].y; r[mb].z += v[qq][mb].z; r[mb].w += v[qq][mb].w; }
                 }
+#pragma unroll
+                for (int mb = 0; mb < MB; ++mb) { r[mb].x += own[mb].x; r[mb].y += own[mb].y; r[mb].z += own[mb].z; r[mb].w += own[mb].w; }
+                __syncwarp();
                 if (lane == 0) p.counters[t] = 0;
             }
         }
         if (write) write_out(t, r);
     }
-    if (fused_ar) {
+    if constexpr (CHAIN) {
+        if (cx.next && cx.late) { cx.it = ring_begin(*cx.next); fill_ring(cx.it); cx.prefilled = true; }
+        __syncthreads();                 // the next entry rewrites the partial rows in shared memory
+    } else if (fused_ar) {
         __syncthreads();
         if (tid == 0) ar_leave(p.ar, epoch, gridDim.x);
+    }
+}
+
+template <int BITS, typename T, int MB, int CK, int NW, int D, int MINB>
+__global__ void __launch_bounds__(NW * 32, MINB) qgemm_vstream_kernel(const StreamParams p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    // partial rows of column blocks that a warp shares with others: at most two per warp (the
+    // block its run starts in and the block it ends in), combined across the CTA before they leave it
+    __shared__ __align__(16) float seg[NW * 2 * MB * VEC_COLS];
+    __shared__ int seg_tile[NW * 2];
+    ChainCtx cx;
+    vstream_body<BITS, T, MB, CK, NW, D, false>(p, smem, seg, seg_tile, cx);
+}
+
+// ----------------------------------------------------------------------------------------------
+// Several linears in ONE launch.  The grid is resident as a whole (cooperative launch, one CTA per
+// half SM) and every CTA walks the list: entry e+1 may read what entry e wrote (a decoder layer's
+// o-projection -> gate/up -> down), so a warp waits -- bounded -- until the launch-wide count of
+// stored column blocks reaches the end of entry e before it reads entry e+1's activations.  Its
+// weight ring is already filling by then: the copies of an entry's first rows are requested before
+// the previous entry's partial sums are combined, so the weight stream never stops at a boundary.
+// All-reduce entries use consecutive epochs; the last CTA to leave publishes the final one and
+// returns the two control words to zero for the next launch (or graph replay).
+// ----------------------------------------------------------------------------------------------
+constexpr int kChainMax = MT_CHAIN_MAX;
+struct ChainParams {
+    StreamParams e[kChainMax];
+    unsigned need[kChainMax];     // column blocks of all earlier entries
+    int ar_index[kChainMax];      // this entry's exchange is the i-th of the launch (-1: none)
+    int count, ar_count;
+    unsigned* done; unsigned* leave; unsigned* err;
+    int spin_limit;
+    int late;
+    ArParams ar;                  // shared by the entries that exchange
+};
+
+template <int BITS, typename T, int MB, int CK, int NW, int D, int MINB>
+__global__ void __launch_bounds__(NW * 32, MINB) qgemm_vchain_kernel(const __grid_constant__ ChainParams cp) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ __align__(16) float seg[NW * 2 * MB * VEC_COLS];
+    __shared__ int seg_tile[NW * 2];
+    __shared__ unsigned seen;
+    if (threadIdx.x == 0) seen = 0;
+    __syncthreads();
+    ChainCtx cx;
+    cx.seen = &seen;
+    cx.late = cp.late != 0;
+    cx.done = cp.done; cx.err = cp.err; cx.spin_limit = cp.spin_limit; cx.prefilled = false;
+    const unsigned epoch0 = cp.ar_count ? ar_epoch(cp.ar) : 0u;    // the previous launch has completed: the word is stable
+    for (int e = 0; e < cp.count; ++e) {
+        cx.need = cp.need[e];
+        cx.epoch = epoch0 + unsigned(cp.ar_index[e] < 0 ? 0 : cp.ar_index[e]);
+        cx.next = e + 1 < cp.count ? &cp.e[e + 1] : nullptr;
+        vstream_body<BITS, T, MB, CK, NW, D, true>(cp.e[e], smem, seg, seg_tile, cx);
+    }
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(cp.leave, 1u) == gridDim.x - 1) {
+            *cp.done = 0; *cp.leave = 0;
+            if (cp.ar_count) {
+                __threadfence();
+                *reinterpret_cast<volatile unsigned*>(cp.ar.peers[cp.ar.rank]) = epoch0 + unsigned(cp.ar_count - 1);
+            }
+        }
     }
 }
 
@@ -886,11 +1039,10 @@ int launch_stream_mb(cudaStream_t st, const StreamParams& p, int ck, int grid) {
     return ck == 64 ? launch_stream_one<BITS, T, 2, 64, NW, D, MINB>(st, p, grid) : launch_stream_one<BITS, T, 2, 32, NW, D, MINB>(st, p, grid);
 }
 
-template <int NW, int D, int MINB>
-int launch_stream_cfg(cudaStream_t st, const QGemmArgs& a, int ctas) {
+// Parameters of the stream-K schedule for one linear on `ctas` CTAs of NW warps.
+static int make_stream_params(const QGemmArgs& a, int ctas, int NW, StreamParams& p, int& ck) {
     const int gs = a.k / a.groups;
-    const int ck = gs % 64 == 0 ? 64 : 32;
-    StreamParams p;
+    ck = gs % 64 == 0 ? 64 : 32;
     p.x = a.x; p.qw = a.qweight; p.qz = a.qzeros; p.scales = a.scales; p.bias = a.bias; p.out = a.out;
     p.xperm = a.x_perm;
     p.counters = static_cast<unsigned*>(a.workspace);
@@ -913,9 +1065,55 @@ int launch_stream_cfg(cudaStream_t st, const QGemmArgs& a, int ctas) {
     if (a.rope) p.rope = *a.rope; else p.rope.cosv = nullptr;
     p.zp1_const = 1 << (a.bits - 1);
     p.pdl = (a.flags & MT_FLAG_PDL) ? 1 : 0;
+    return MT_OK;
+}
+
+template <int NW, int D, int MINB>
+int launch_stream_cfg(cudaStream_t st, const QGemmArgs& a, int ctas) {
+    StreamParams p;
+    int ck = 0;
+    const int rc = make_stream_params(a, ctas, NW, p, ck);
+    if (rc != MT_OK) return rc;
     const int grid = (p.warps + NW - 1) / NW;
     if (a.bits == 4) return a.dtype == MT_F16 ? launch_stream_mb<4, __half, NW, D, MINB>(st, p, ck, grid) : launch_stream_mb<4, __nv_bfloat16, NW, D, MINB>(st, p, ck, grid);
     return a.dtype == MT_F16 ? launch_stream_mb<8, __half, NW, D, MINB>(st, p, ck, grid) : launch_stream_mb<8, __nv_bfloat16, NW, D, MINB>(st, p, ck, grid);
+}
+
+constexpr int CH_NW = 8, CH_D = 16, CH_MINB = 2;
+
+template <int BITS, typename T, int MB, int CK>
+int launch_chain_one(cudaStream_t st, const ChainParams& cp) {
+    auto kern = qgemm_vchain_kernel<BITS, T, MB, CK, CH_NW, CH_D, CH_MINB>;
+    constexpr int CKS = CK / 8;
+    const size_t smem = (size_t)CH_D * CH_NW * 32 * 16 + (size_t)CH_NW * 2 * MB * 32 * 16 + (size_t)CH_NW * 2 * MB * (32 / CKS) * 8;
+    static int resident[64] = {};                          // per device ordinal: CTAs that fit the GPU at once (0: not asked yet)
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return MT_ERR_CUDA; }
+    if (!resident[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
+        int per_sm = 0, sms = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, CH_NW * 32, smem) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || per_sm < 1 || sms < 1) { cudaGetLastError(); return MT_ERR_CUDA; }
+        resident[dev] = per_sm * sms;
+    }
+    int grid = 0;
+    for (int e = 0; e < cp.count; ++e) grid = max(grid, (cp.e[e].warps + CH_NW - 1) / CH_NW);
+    // the CTAs wait for one another, so all of them must be resident: a cooperative launch fails instead of hanging
+    if (grid > resident[dev]) return MT_ERR_UNSUPPORTED;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(CH_NW * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, cp) != cudaSuccess) { cudaGetLastError(); return MT_ERR_CUDA; }
+    return MT_OK;
+}
+
+template <int BITS, typename T>
+int launch_chain_mb(cudaStream_t st, const ChainParams& cp, int m, int ck) {
+    if (m == 1) return ck == 64 ? launch_chain_one<BITS, T, 1, 64>(st, cp) : launch_chain_one<BITS, T, 1, 32>(st, cp);
+    return ck == 64 ? launch_chain_one<BITS, T, 2, 64>(st, cp) : launch_chain_one<BITS, T, 2, 32>(st, cp);
 }
 
 }  // namespace
@@ -1000,6 +1198,43 @@ int vec_plan(const QGemmArgs& a) {
     const double t_stream = 6.5 + total_kb * 1.024 * tiles / (6000.0 * slow);
     if (variant == 0 && t_stream < best) return 0;
     return splits;
+}
+
+// `count` linears (each one a request the stream-K GEMV accepts: M <= 2, no g_idx) in one launch, in list order, every
+// entry free to read what an earlier one wrote.  All entries share M, the bit width, the dtype, the workspace and --
+// where they exchange -- the peers.  Returns MT_ERR_UNSUPPORTED when the list does not fit the scheme (the caller
+// then launches the linears one by one).
+int launch_vec_chain(cudaStream_t st, const QGemmArgs* list, int count) {
+    if (count < 1 || count > kChainMax) return MT_ERR_UNSUPPORTED;
+    ChainParams cp;
+    cp.count = count; cp.ar_count = 0;
+    int ck0 = 0;
+    unsigned tiles_before = 0;
+    const QGemmArgs& a0 = list[0];
+    for (int e = 0; e < count; ++e) {
+        const QGemmArgs& a = list[e];
+        if (!vec_supported(a) || a.m != a0.m || a.bits != a0.bits || a.dtype != a0.dtype || a.workspace != a0.workspace ||
+            a.workspace_bytes != a0.workspace_bytes) return MT_ERR_UNSUPPORTED;
+        if (a.n / VEC_COLS >= kMaxTiles - 4) return MT_ERR_UNSUPPORTED;      // the last words of the counter area are the chain's
+        int ck = 0;
+        const int rc = make_stream_params(a, 296, CH_NW, cp.e[e], ck);
+        if (rc != MT_OK) return rc;
+        if (e == 0) ck0 = ck; else if (ck != ck0) return MT_ERR_UNSUPPORTED;
+        cp.need[e] = tiles_before;
+        tiles_before += unsigned(cp.e[e].tiles);
+        cp.ar_index[e] = -1;
+        if (cp.e[e].ar.world > 1) {
+            if (cp.ar_count && (cp.e[e].ar.peers != cp.ar.peers || cp.e[e].ar.slot_bytes != cp.ar.slot_bytes)) return MT_ERR_UNSUPPORTED;
+            cp.ar = cp.e[e].ar;
+            cp.ar_index[e] = cp.ar_count++;
+        }
+    }
+    unsigned* words = static_cast<unsigned*>(a0.workspace);
+    cp.done = words + (kMaxTiles - 3); cp.leave = words + (kMaxTiles - 2); cp.err = words + (kMaxTiles - 1);
+    cp.spin_limit = (a0.flags & MT_FLAG_AR_SHORT_WAIT) ? (1 << 10) : (1 << 21);
+    cp.late = ((a0.flags >> 24) & 0xf) == 3;
+    if (a0.bits == 4) return a0.dtype == MT_F16 ? launch_chain_mb<4, __half>(st, cp, a0.m, ck0) : launch_chain_mb<4, __nv_bfloat16>(st, cp, a0.m, ck0);
+    return a0.dtype == MT_F16 ? launch_chain_mb<8, __half>(st, cp, a0.m, ck0) : launch_chain_mb<8, __nv_bfloat16>(st, cp, a0.m, ck0);
 }
 
 int launch_vec(cudaStream_t st, const QGemmArgs& a) {
