@@ -104,12 +104,6 @@ template <int BITS, int BM> struct MdCfg {
     static_assert(TOTAL <= 227 * 1024, "shared memory budget");
 };
 
-#if defined(MD_TL) || defined(MD_TL_LIGHT)
-#define MD_STAMP(slot, unit) do { if (blockIdx.x == 3 && (unit) < 64) reinterpret_cast<long long*>(p.counters + (30 << 18))[(unit) * 16 + (slot)] = clock64(); } while (0)
-#else
-#define MD_STAMP(slot, unit) do { } while (0)
-#endif
-
 struct MdParams {
     const unsigned char* xl;      // pre-pass output: per k-block [B tile | sum(x') | 2^-e]
     const void* scales; const uint32_t* qz;   // [G, N] T; [G, N / pack] or null (symmetric midpoint)
@@ -283,32 +277,8 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_a = tmem_base + C::D_COLS;
-#ifdef MD_TL
-    long long tw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    int tslot = 0;
-    const long long t_begin = clock64();
-    auto wait = [&](uint32_t bar, uint32_t parity) {
-        const long long t0 = clock64();
-        const bool r = md_wait<MD_FAST_NS>(bar, parity, &abort_flag);
-        tw[tslot] += clock64() - t0;
-        return r;
-    };
-    auto lazy_wait = [&](uint32_t bar, uint32_t parity) {
-        const long long t0 = clock64();
-        const bool r = md_wait<MD_SLOW_NS>(bar, parity, &abort_flag);
-        tw[tslot] += clock64() - t0;
-        return r;
-    };
-#define MD_SLOT(n) tslot = n
-#define MD_T0() const long long t_x0 = clock64()
-#define MD_T1(n) tw[n] += clock64() - t_x0
-#else
     auto wait = [&](uint32_t bar, uint32_t parity) { return md_wait<MD_FAST_NS>(bar, parity, &abort_flag); };        // critical path
     auto lazy_wait = [&](uint32_t bar, uint32_t parity) { return md_wait<MD_SLOW_NS>(bar, parity, &abort_flag); };   // roles that run ahead
-#define MD_SLOT(n)
-#define MD_T0()
-#define MD_T1(n)
-#endif
 
     // first / last CTA with a unit of column tile t
     auto owner = [&](int u) -> int {
@@ -332,7 +302,6 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
                 if (i >= C::PST && !lazy_wait(bar_pempty(ps), ((i / C::PST) & 1) ^ 1)) break;
                 mbar_expect_tx(bar_pfull(ps), (uint32_t)C::W_BYTES);
                 tma_load_2d(sbase + C::OFF_P + ps * C::P_STAGE, &tmap_q, t * C::COLS, b * C::PROWS, bar_pfull(ps));
-                MD_STAMP(0, i);
                 if (++b == p.kbt) { b = 0; ++t; }
             }
         } else if (lane == 0 && role == 1) {
@@ -357,7 +326,6 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
                 if (i >= C::BST && !lazy_wait(bar_bempty(bs), ((i / C::BST) & 1) ^ 1)) break;
                 mbar_expect_tx(bar_full(bs), (uint32_t)C::B_COPY);
                 md_bulk_load(sbase + C::OFF_B + bs * C::B_STAGE, p.xl + (size_t)kb * C::B_COPY, (uint32_t)C::B_COPY, bar_full(bs));
-                MD_STAMP(1, i);
                 if (++kb == p.kbt) { kb = 0; ++t; cur = -1; }
             }
         }
@@ -370,17 +338,13 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
             uint32_t early_ok = 0u;
             for (int i = 0; i < nrun; ++i) {
                 const int as = i % C::AST, bs = i % C::BST, db = i % C::DBUF;
-                MD_SLOT(0);
                 if (!early_ok && !wait(bar_full(bs), (i / C::BST) & 1)) break;
                 tc_fence_after();
-                if (nt == 0) MD_STAMP(6, i);
                 const uint64_t bdesc = tc_desc_sw128(sbase + C::OFF_B + bs * C::B_STAGE);
                 const uint32_t d = tmem_base + (uint32_t)((db * C::NT + nt) * C::NB), a = tmem_a + (uint32_t)((as * C::NT + nt) * 32);
-                { MD_T0();
 #pragma unroll
                 for (int k4 = 0; k4 < 4; ++k4) md_mma_i8(d, a + (uint32_t)(k4 * 8), bdesc + (uint64_t)(k4 * 2), idesc, k4 ? 1u : 0u);
                 tc_commit(bar_done(bs));
-                MD_T1(3); }
                 // ask about the next k-block now: the answer takes ~200 cycles either way and is read at the top of the next turn
                 early_ok = 0u;
                 if (i + 1 < nrun) {
@@ -388,7 +352,6 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
                     asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}"
                                  : "=r"(early_ok) : "r"(bar_full(in % C::BST)), "r"((uint32_t)((in / C::BST) & 1)) : "memory");
                 }
-                if (nt == 0) MD_STAMP(7, i);
             }
         }
     } else if (warp >= MD_W_CONV) {
@@ -402,10 +365,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
         const int cq = q4 * 32 + lane;                          // column inside a 128-column tile
         for (int i = grp; i < nrun; i += MD_CGROUPS) {
             const int ps = i % C::PST, as = i % C::AST, bs = i % C::BST;
-            MD_SLOT(0);
             if (!lazy_wait(bar_pfull(ps), (i / C::PST) & 1)) break;
-            MD_SLOT(1);
-            if (tid == MD_W_CONV * 32) MD_STAMP(2, i);
             const uint32_t* pk = reinterpret_cast<const uint32_t*>(smem + C::OFF_P + ps * C::P_STAGE) + cq;
             bool ok = true;
 #pragma unroll
@@ -430,7 +390,6 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
                     // the A slot is free when the MMAs of the k-block that used it last (AST k-blocks ago) have completed
                     if (i >= C::AST && !lazy_wait(bar_done((i - C::AST) % C::BST), ((i - C::AST) / C::BST) & 1)) { ok = false; break; }
                     tc_fence_after();
-                    if (tid == MD_W_CONV * 32) MD_STAMP(3, i);
                 }
                 tc_st32(tmem_a + lane_base + (uint32_t)((as * C::NT + nt) * 32), a);
             }
@@ -439,7 +398,6 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_full(bs));
-            if (tid == MD_W_CONV * 32) MD_STAMP(4, i);
         }
     } else {
         // ------------------------------ fold warps ------------------------------
@@ -531,15 +489,9 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
             int kin = kb - g0 * p.kpg, gb = g0 / MD_SZG, gi = g0 - gb * MD_SZG;
         for (; j < seg_end; ++j) {
             const int bs = j % C::BST, db = j % C::DBUF;
-            if (tid == 0) MD_STAMP(8, j);
-            MD_SLOT(0);
             // The MMAs of this k-block have completed.  Their issuing lanes waited for the copy engine's bytes of this stage
             // (`full`) before they issued, so the stage's sums, scales and zero words are in shared memory long since.
             if (!early_ok && !wait(bar_done(bs), (j / C::BST) & 1)) { live = false; break; }
-            if (tid == 0) MD_STAMP(9, j);
-#ifdef MD_TL
-            const long long t_top = clock64();
-#endif
             tc_fence_after();
             const uint32_t dbase = tmem_base + lane_base + (uint32_t)((db * C::NT + nt) * C::NB + r0);
             // scale and zero word of this k-block's group, from the block of MD_SZG groups in shared memory
@@ -554,10 +506,6 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
             const int nzp1 = -(p.qz ? int((reinterpret_cast<const uint32_t*>(sz_stage + C::S_BYTES)[gi * (C::COLS / C::PACK) + cl / C::PACK] >> zsh) & ZMASK) + 1
                                    : p.zp1_const);
             const unsigned char* bst = smem + C::OFF_B + bs * C::B_STAGE + C::B_TILE;
-#ifdef MD_TL
-            asm volatile("" : "+f"(const_cast<float&>(sf)));
-            tw[3] += clock64() - t_top;
-#endif
             // An early poll for the NEXT k-block: the barrier unit answers after ~200 cycles whatever the answer, so the
             // question is asked now and the answer read at the top of the next turn, behind this turn's arithmetic.
             early_ok = 0u;
@@ -569,24 +517,16 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
 #pragma unroll
             for (int c0 = 0; c0 < C::RW; c0 += C::RC) {
                 uint32_t dh[C::RC], dl[C::RC];
-                { MD_T0();
                 tc_ld<C::RC>(dbase + c0, dh);
                 tc_ld<C::RC>(dbase + BM + c0, dl);
                 tc_wait_ld();
-                MD_T1(2); }
                 if (c0 + C::RC == C::RW) {                       // the accumulator buffer is in registers: it is free for the k-block DBUF later
-                    { MD_T0();
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_full((j + C::DBUF) % C::BST));
-                    MD_T1(5); }
-                    if (tid == 0) MD_STAMP(10, j);
                 }
-#ifdef MD_TL
-                const long long t_m0 = clock64();
-#endif
-#ifndef MD_ABL_NOMATH
                 // stage by stage over the rows of the chunk, so that independent instructions sit next to one another
+                // (issuing the next chunk's TMEM loads ahead of this arithmetic measured 3-8 % slower at every batch size)
                 int sx[C::RC]; float pe[C::RC];
 #pragma unroll
                 for (int r = 0; r < C::RC; r += 4) {
@@ -607,20 +547,9 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
                 for (int r = 0; r < C::RC; ++r) pe[r] *= sf;
 #pragma unroll
                 for (int r = 0; r < C::RC; ++r) acc[c0 + r] = fmaf(pe[r], f[r], acc[c0 + r]);
-#else
-                acc[c0] += __uint_as_float(dh[0] ^ dl[C::RC - 1]) * sf;
-#endif
-#ifdef MD_TL
-#pragma unroll
-                for (int r = 0; r < C::RC; ++r) asm volatile("" : "+f"(acc[c0 + r]));
-                tw[4] += clock64() - t_m0;
-#endif
             }
-            { MD_T0();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_bempty(bs));
-            MD_T1(6); }
-            if (tid == 0) MD_STAMP(11, j);
             ++kb;
             if (++kin == p.kpg) { kin = 0; if (++gi == MD_SZG) { gi = 0; ++gb; } }   // next group / next block of groups, no division
         }
@@ -636,13 +565,6 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
         }
     }
 
-#ifdef MD_TL
-    if (blockIdx.x == 3 && lane == 0) {
-        long long* dst = reinterpret_cast<long long*>(p.counters + (30 << 18)) + 64 * 16 + warp * 8;
-        dst[0] = clock64() - t_begin;
-        for (int q = 0; q < 7; ++q) dst[1 + q] = tw[q];
-    }
-#endif
     // A wait that expired has raised the abort flag and every role has left its loop.  Copies this CTA requested may
     // still be in flight towards its shared memory and MMAs may still be running: give them time to land (they complete
     // within microseconds) before the tensor memory is freed and the CTA exits.

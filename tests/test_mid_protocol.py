@@ -2,7 +2,8 @@
 generator, every mbarrier a pending count with a phase, the scheduler is random.  It fails on a deadlock, on an arrival
 that lands in another k-block's phase, and on over-arrival.  The ring lengths below are the kernel's (MdCfg); the last
 case is a configuration that must FAIL: eight producer lanes over six activation stages make a lane skip phases of a
-barrier, its parity wait then passes one phase early (this is the fault the model was written to find)."""
+barrier, its parity wait then passes one phase early (this is the fault the model was written to find; the kernel now
+has one issuing thread per ring, which cannot skip a phase)."""
 import random
 
 import pytest
@@ -26,9 +27,18 @@ class Bar:
         return (self.phase & 1) != parity
 
 
-def run(nrun, AST, BST, PST, NT, FOLD, seed, planes=4, blanes=None, cgroups=2, DBUF=2):
-    blanes = BST if blanes is None else blanes
+def run(nrun, AST, BST, PST, NT, FOLD, seed, planes=1, blanes=1, cgroups=2, DBUF=2, SZST=3):
+    """planes / blanes: threads that issue the packed-weight copies / the activation-stage copies, each taking every
+    planes-th (blanes-th) k-block.  The kernel uses one of each, walking its ring in order; the thread of the activation
+    stages also loads the blocks of scales and zero words (ring of SZST, a new block every few k-blocks and at every
+    column tile, so a block can be a single k-block long)."""
     rnd = random.Random(seed)
+    block = []                                   # scale / zero block of every k-block: random lengths 1 .. 10
+    while len(block) < nrun:
+        block += [(block[-1] + 1) if block else 0] * rnd.randint(1, 10)
+    block = block[:nrun]
+    szfull = [Bar(f"szfull{s}", 1) for s in range(SZST)]
+    szempty = [Bar(f"szempty{s}", FOLD) for s in range(SZST)]
     pfull = [Bar(f"pfull{s}", 1) for s in range(PST)]
     pempty = [Bar(f"pempty{s}", 4) for s in range(PST)]
     full = [Bar(f"full{s}", 4 + 1 + FOLD) for s in range(BST)]
@@ -57,6 +67,13 @@ def run(nrun, AST, BST, PST, NT, FOLD, seed, planes=4, blanes=None, cgroups=2, D
     def b_lane(l):
         for i in range(l, nrun, blanes):
             bs = i % BST
+            if blanes == 1 and (i == 0 or block[i] != block[i - 1]):
+                n = block[i]
+                if n >= SZST:
+                    while not szempty[n % SZST].done(((n // SZST) & 1) ^ 1):
+                        yield
+                szfull[n % SZST].arrive(f"B{l}:block{n}")
+                yield
             if i >= BST:
                 while not bempty[bs].done(((i // BST) & 1) ^ 1):
                     yield
@@ -92,11 +109,19 @@ def run(nrun, AST, BST, PST, NT, FOLD, seed, planes=4, blanes=None, cgroups=2, D
             yield
 
     def fold(w):
+        cur = -1
         for j in range(nrun):
             bs = j % BST
             while not done[bs].done((j // BST) & 1):
                 yield
             yield
+            if blanes == 1 and block[j] != cur:
+                if cur >= 0:
+                    szempty[cur % SZST].arrive(f"F{w}:block{cur}")
+                cur = block[j]
+                while not szfull[cur % SZST].done((cur // SZST) & 1):
+                    yield
+                yield
             t = (j + DBUF) % BST
             check(full, t, BST, j + DBUF, f"F{w}")
             full[t].arrive(f"F{w}:{j}")
@@ -111,14 +136,14 @@ def run(nrun, AST, BST, PST, NT, FOLD, seed, planes=4, blanes=None, cgroups=2, D
     idle = 0
     while alive:
         k = rnd.choice(alive)
-        before = (tuple(b.phase for b in pfull + pempty + full + done + bempty), tuple(b.pending for b in pfull + pempty + full + done + bempty))
+        before = (tuple(b.phase for b in pfull + pempty + full + done + bempty + szfull + szempty), tuple(b.pending for b in pfull + pempty + full + done + bempty + szfull + szempty))
         try:
             next(procs[k])
         except StopIteration:
             alive.remove(k)
             idle = 0
             continue
-        after = (tuple(b.phase for b in pfull + pempty + full + done + bempty), tuple(b.pending for b in pfull + pempty + full + done + bempty))
+        after = (tuple(b.phase for b in pfull + pempty + full + done + bempty + szfull + szempty), tuple(b.pending for b in pfull + pempty + full + done + bempty + szfull + szempty))
         idle = idle + 1 if before == after else 0
         if idle > 20000:
             raise RuntimeError(f"deadlock: alive {alive}")
@@ -143,4 +168,4 @@ def test_protocol_has_no_deadlock_and_no_phase_aliasing(name):
 def test_model_catches_a_lane_that_skips_phases():
     with pytest.raises(RuntimeError, match="arrives for unit"):
         for seed in range(8):
-            run(24, AST=4, BST=6, PST=12, NT=1, FOLD=8, seed=seed, blanes=8)
+            run(24, AST=4, BST=6, PST=12, NT=1, FOLD=8, seed=seed, planes=4, blanes=8)
