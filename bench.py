@@ -688,6 +688,40 @@ def run_ours(args):
     if mode == "cuda_graph" and not args.no_extra:
         ms_e2e_eager, _ = timed(one_pass_e2e, 5, 2)
 
+    # where the step's time goes at N > 1: the same per-rank linears with no exchange at all, and the exchange on a
+    # GEMV so small ([1,128] x [128,8192]) that the difference to the same GEMV alone is the mailbox hand-over itself
+    # (peer stores + bounded poll + the skew between the ranks)
+    ar_split = None
+    if world > 1 and far is not None and not args.no_extra:
+        def local_pass():
+            for lin in layers:
+                for i, (qw, qz, sc) in enumerate(lin):
+                    M.quantized_matrix_multiply(xs[i], qw, qz, sc, None, bits=BITS, out=outs[i], flags=flags)
+        r_local, _ = make_runner(local_pass)
+        ms_local, _ = timed(r_local, max(3, args.steps // 2), 3)
+        tiny = []
+        for _ in range(2):
+            tiny.append((torch.randint(-2**31, 2**31 - 1, (128 // 8, HIDDEN), device=dev, dtype=torch.int64, generator=gen).to(torch.int32),
+                         torch.randint(-2**31, 2**31 - 1, (1, HIDDEN // 8), device=dev, dtype=torch.int64, generator=gen).to(torch.int32),
+                         (0.002 + 0.018 * torch.rand((1, HIDDEN), device=dev, generator=gen)).half()))
+        xt = torch.randn((m, 128), device=dev).half()
+        ot = torch.empty((m, HIDDEN), dtype=torch.float16, device=dev)
+
+        def tiny_fused():
+            for i in range(40):
+                far.matmul(xt, *tiny[i & 1], None, bits=BITS, out=ot, flags=flags)
+
+        def tiny_local():
+            for i in range(40):
+                M.quantized_matrix_multiply(xt, *tiny[i & 1], None, bits=BITS, out=ot, flags=flags)
+        r_f, _ = make_runner(tiny_fused)
+        r_l, _ = make_runner(tiny_local)
+        ms_f, _ = timed(r_f, 10, 3)
+        ms_l, _ = timed(r_l, 10, 3)
+        ar_split = {"ms_per_step_no_exchange": ms_local, "exchanges_per_step": 2 * args.layers,
+                    "gemv_128x8192_us": ms_l * 1e3 / 40, "gemv_128x8192_allreduce_us": ms_f * 1e3 / 40,
+                    "exchange_us": (ms_f - ms_l) * 1e3 / 40}
+
     # correctness evidence beside the timing, at every N: no bounded wait expired during the timed steps, and the
     # row-parallel linears (with their all-reduce) reproduce the oracle on unsharded weights
     words_timed = error_words()
@@ -737,6 +771,8 @@ def run_ours(args):
         "clocks": clocks,
         "parity_check": parity,
     }
+    if ar_split is not None:
+        line["allreduce_split"] = ar_split
     if rank == 0 and world == 1 and m == 1 and not args.no_prefill:
         line["prefill_m4096"] = prefill_m4096(dev)
     if rank == 0 and world == 1 and m == 1 and not args.no_extra:

@@ -240,6 +240,17 @@ int mt_unpack(void* stream, const uint32_t* packed, uint8_t* out, int rows, int 
     return launch_unpack(static_cast<cudaStream_t>(stream), packed, out, rows, cols, bits, axis);
 }
 
+// Where the integer tensor-core kernel beats the register-ring kernel, from timings of both on the linears of a
+// 70B decoder layer split 1, 2, 4 and 8 ways (K or N from 1024 to 57344): the more rows, the smaller the weights at
+// which its set-up is paid back; with few k-blocks (K < 3072) the ring kernel always wins.
+static bool mid_preferred(int m, int n, int k) {
+    if (m < 3 || m > 32 || k < 3072) return false;
+    const long long weights = (long long)k * n;
+    if (m <= 8) return weights >= 100LL * 1000 * 1000;
+    if (m <= 16) return weights >= 40LL * 1000 * 1000;
+    return weights >= 8LL * 1000 * 1000;
+}
+
 int mt_qgemm(void* stream, const void* x, const uint32_t* qweight, const int32_t* g_idx,
              const uint32_t* qzeros, const void* scales, const void* bias, void* out,
              int m, int n, int k, int nr_groups, int bits, int dtype,
@@ -264,14 +275,14 @@ int mt_qgemm(void* stream, const void* x, const uint32_t* qweight, const int32_t
     if (flags & MT_FLAG_FORCE_VEC) return vec_supported(a) ? launch_vec(st, a) : MT_ERR_UNSUPPORTED;
     if (flags & MT_FLAG_FORCE_UMMA) return umma_supported(a) ? launch_umma(st, a) : MT_ERR_UNSUPPORTED;
     if (flags & MT_FLAG_FORCE_MID) return mid_supported(a) ? launch_mid(st, a) : MT_ERR_UNSUPPORTED;
-    // Mid-size batches.  Up to 32 rows on weights of at least 32 M elements the integer tensor-core kernel (packed
-    // nibbles as unsigned bytes, two-limb activations, scale and zero point folded per 128 values of k) holds
-    // 0.35-0.5 of HBM peak; it pays ~10 us of set-up (a pre-pass launch, tensor maps, tensor-memory allocation), so
-    // small weights stay on the register-ring kernel.  From 33 to 64 rows its fold costs more than dequantizing, and
-    // the tcgen05 kernel whose sixteen warps rebuild fp16 weights takes over; between 64 and 128 rows two passes of
-    // that one beat the prefill kernels when K is deep (their grid has no split along K).
+    // Mid-size batches.  Up to 32 rows the integer tensor-core kernel (packed nibbles as unsigned bytes, two-limb
+    // activations, scale and zero point folded per 128 values of k) holds 0.38-0.56 of HBM peak on large weights; it
+    // pays ~10 us of set-up (a pre-pass launch, tensor maps, tensor-memory allocation), so smaller weights stay on the
+    // register-ring kernel (mid_preferred).  From 33 to 64 rows its fold costs more than dequantizing, and the tcgen05
+    // kernel whose sixteen warps rebuild fp16 weights takes over; between 64 and 128 rows two passes of that one beat
+    // the prefill kernels when K is deep (their grid has no split along K).
     const long long weights = (long long)k * n;
-    if (m > 2 && m <= 32 && weights >= (32LL << 20) && mid_supported(a)) return launch_mid(st, a);
+    if (mid_preferred(m, n, k) && mid_supported(a)) return launch_mid(st, a);
     if (umma_supported(a)) {
         if (m > 32 && m <= 64) return launch_umma(st, a);
         if (m > 8 && m <= 32 && weights >= (128LL << 20)) return launch_umma(st, a);
@@ -313,7 +324,7 @@ static int qgemm_allreduce_impl(void* stream, const void* x, const uint32_t* qwe
         a.residual = residual;                                   // the GEMV adds it to the reduced sum before its one rounding
         return launch_vec(st, a);
     }
-    if (!(flags & MT_FLAG_FORCE_SMALL) && m > 2 && m <= 32 && (long long)k * n >= (32LL << 20) && mid_supported(a)) {
+    if (!(flags & MT_FLAG_FORCE_SMALL) && (mid_preferred(m, n, k) || ((flags & MT_FLAG_FORCE_MID) && m > 2)) && mid_supported(a)) {
         a.residual = residual;                                   // the integer kernel exchanges and adds it in its epilogue too
         return launch_mid(st, a);
     }

@@ -28,7 +28,7 @@ def test_expired_peer_wait_sets_the_error_word_and_raises(lib_built, m, force_sm
     stream = _lib.current_stream(dev)
     ws = _lib.workspace(dev, stream, L.mt_workspace_bytes(m, n, k, 4))
     _lib.raise_on_error_words()                                   # clean before the experiment
-    flags = _lib.FLAG_AR_SHORT_WAIT | (_lib.FLAG_FORCE_SMALL if force_small else 0)
+    flags = _lib.FLAG_AR_SHORT_WAIT | (_lib.FLAG_FORCE_SMALL if force_small else 0) | (_lib.FLAG_FORCE_MID if m == 8 else 0)
     rc = L.mt_qgemm_allreduce(stream, d["x"].data_ptr(), d["qweight"].data_ptr(), None, d["qzeros"].data_ptr(),
                               d["scales"].data_ptr(), None, out.data_ptr(), m, n, k, k // 128, 4, 0, ws.data_ptr(), ws.numel(),
                               flags, table.data_ptr(), 0, 2, nbytes)

@@ -87,6 +87,7 @@ def _worker(rank, size, port, results):
         # batches of 8 and 32 rows on a weight large enough for the integer tensor-core kernel: the same exchange in its epilogue
         # (one value per thread), residual added after the reduction, identical on all ranks, replayable from a graph
         far32 = FusedAllReduce(m_max=32, n_max=8192)
+        MID = 128                                            # MT_FLAG_FORCE_MID: the integer kernel whatever the size rule says
         for m5, seed5 in [(8, 51), (32, 52), (5, 53)]:
             c5 = O.make_gptq_case(8192, 8192, m5, bits=4, seed=seed5, bias=True)
             rowf5 = RowParallelQLinear(comm, g(c5, "qweight"), g(c5, "qzeros"), g(c5, "scales"), None, 4, bias=g(c5, "bias"), fused=far32)
@@ -97,26 +98,26 @@ def _worker(rank, size, port, results):
                                      c5["scales"][:, sl].contiguous(), 4)
             ref5 = O.qlinear(c5["x"], w5, c5["bias"][sl])
             for it in range(3):
-                y5 = rowf5(x5)
+                y5 = rowf5(x5, flags=MID)
                 ok, err, bound = O.tolerance_ok(y5[:, sl], ref5, 1e-2)
                 assert ok, f"rank {rank} fused integer kernel M={m5} call {it}: err {err} > {bound}"
             g5 = [torch.empty_like(y5) for _ in range(size)]
             dist.all_gather(g5, y5)
             assert all(torch.equal(g5[0], t) for t in g5), "fused integer-kernel all-reduce results differ between ranks"
             res5 = torch.randn((m5, 8192), generator=torch.Generator().manual_seed(seed5)).half()
-            y5r = rowf5(x5, residual=res5.to(dev))
+            y5r = rowf5(x5, flags=MID, residual=res5.to(dev))
             ok, err, bound = O.tolerance_ok(y5r[:, sl], O.add_residual(res5[:, sl], ref5), 1e-2)
             assert ok, f"rank {rank} fused integer kernel + residual M={m5}: err {err} > {bound}"
         y5g = torch.empty_like(y5)
         side5 = torch.cuda.Stream()
         side5.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side5):
-            rowf5(x5, out=y5g)
+            rowf5(x5, out=y5g, flags=MID)
             torch.cuda.synchronize()
             graph5 = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph5, stream=side5):
-                rowf5(x5, out=y5g)
-                rowf5(x5, out=y5g)
+                rowf5(x5, out=y5g, flags=MID)
+                rowf5(x5, out=y5g, flags=MID)
             for _ in range(3):
                 graph5.replay()
             torch.cuda.synchronize()
