@@ -200,3 +200,66 @@ def test_oracle_unpack_matches_the_reference_unpack(name):
     assert np.array_equal(O.unpack_rows(x, 8), g[f"{name}.axis0"])
     assert np.array_equal(O.unpack_cols(x, 8), g[f"{name}.axis1"])
     assert g[f"{name}.axis0"].shape == (x.shape[0] * 4, x.shape[1]) and g[f"{name}.axis1"].shape == (x.shape[0], x.shape[1] * 4)
+
+
+# ---------------------------------------------------------------------------------------------
+# The oracle against the reference's OWN CUDA kernels: tests/golden/ref_cuda_golden.npz holds what those kernels
+# (built unchanged from the reference's source strings by oracle/build_ref_cuda.py) produced on a B200
+# (tests/golden/make_cuda_golden.py).
+# ---------------------------------------------------------------------------------------------
+REF_CUDA = os.path.join(os.path.dirname(__file__), "golden", "ref_cuda_golden.npz")
+
+
+def _h(a):
+    return torch.from_numpy(a).view(torch.float16)
+
+
+def _ulps_fp16(a: torch.Tensor, b: torch.Tensor) -> int:
+    """Largest distance in representable fp16 values (same sign assumed where it matters)."""
+    ia, ib = a.contiguous().view(torch.int16).int(), b.contiguous().view(torch.int16).int()
+    return int((ia - ib).abs().max())
+
+
+@pytest.mark.parametrize("i", range(4))
+def test_oracle_matches_the_reference_fused_kernel(i):
+    """examples/qwen1_5_int8.py:156-216 run on the GPU: 8-bit, contiguous and act-order groups, 1 to 16 rows.  That kernel
+    adds one fp16-rounded partial sum per 32 values of k into the output with atomicAdd (any order), so it agrees with
+    the dequantize-then-matmul contract only to the north-star bound, not bit for bit."""
+    f = np.load(REF_CUDA)
+    x, sc = _h(f[f"qmm{i}_x"]), _h(f[f"qmm{i}_scales"])
+    qw, qz, g = (torch.from_numpy(f[f"qmm{i}_{k}"]) for k in ("qweight", "qzeros", "g_idx"))
+    ref_kernel = _h(f[f"qmm{i}_out"])
+    ours = O.qlinear(x, O.dequantize_packed(qw, g, qz, sc, 8))
+    ok, err, bound = O.tolerance_ok(ref_kernel, ours, 1e-2)
+    assert ok, f"case {i}: |reference kernel - oracle| = {err} > {bound}"
+
+
+@pytest.mark.parametrize("i", range(3))
+def test_oracle_rms_norm_matches_the_reference_kernel(i):
+    """minit/cuda/kernel/cuda/rms_norm.py:56-97 normalises the middle axis of [a, b, c]; the oracle the last one."""
+    f = np.load(REF_CUDA)
+    x, w, out = _h(f[f"rms{i}_x"]), _h(f[f"rms{i}_w"]), _h(f[f"rms{i}_out"])
+    ours = O.rms_norm(x.permute(0, 2, 1).contiguous(), w).permute(0, 2, 1).contiguous()
+    assert _ulps_fp16(ours, out) <= 1                            # the order of the fp32 sum of squares differs
+    assert (ours.view(torch.int16) != out.view(torch.int16)).float().mean() < 0.01
+
+
+@pytest.mark.parametrize("i", range(2))
+def test_oracle_rope_matches_the_reference_kernel(i):
+    """minit/cuda/kernel/cuda/rope.py:57-85 (float instantiation): adjacent pairs rotated by the angle of (position,
+    pair index); the difference is the compiler's fused multiply-add."""
+    f = np.load(REF_CUDA)
+    x, cos, sin, out = (torch.from_numpy(f[f"rope{i}_{k}"]) for k in ("x", "cos", "sin", "out"))
+    ours = torch.stack([O.rope(x[b], cos, sin, 0) for b in range(x.shape[0])])
+    assert (ours - out).abs().max().item() <= 1e-6
+
+
+@pytest.mark.parametrize("i", range(3))
+def test_softmax_of_the_attention_oracle_matches_the_reference_kernel(i):
+    """minit/cuda/kernel/cuda/softmax.py:55-114 over the middle axis, fp32 inside, one rounding to fp16: what
+    O.attention computes with torch.softmax on the fp32 copy.  Case 0 has a row with masked (-inf) positions."""
+    f = np.load(REF_CUDA)
+    x, out = _h(f[f"smx{i}_x"]), _h(f[f"smx{i}_out"])
+    ours = torch.softmax(x.float(), dim=1).half()
+    assert _ulps_fp16(ours, out) <= 1
+    assert (ours.view(torch.int16) != out.view(torch.int16)).float().mean() < 0.01
