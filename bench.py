@@ -877,7 +877,7 @@ def run_single_shape(args):
         sets.append((qw, qz, sc))
     x = torch.randn((m, k), device=dev, dtype=torch.float32).to(dtype)
     out = torch.empty((m, n), device=dev, dtype=dtype)
-    flags = {"auto": 0, "ring": 1, "tc": 2, "vec": 16, "umma": 32, "mid": 128}[args.kernel] | (4 if args.pdl and args.kernel in ("auto", "ring", "vec") else 0)
+    flags = {"auto": 0, "ring": 1, "tc": 2, "vec": 16, "umma": 32, "mid": 128, "tcx": 256}[args.kernel] | (4 if args.pdl and args.kernel in ("auto", "ring", "vec") else 0)
 
     def one():
         for qw, qz, sc in sets:
@@ -929,7 +929,7 @@ def main():
     ap.add_argument("--decode-layer", action="store_true", help="time whole decoder layers (norms, rope, attention, fused linears) for one token")
     ap.add_argument("--attention", action="store_true", help="time decode attention alone over --context cached positions")
     ap.add_argument("--context", type=int, default=4096, help="--decode-layer: cached positions")
-    ap.add_argument("--kernel", default="auto", choices=["auto", "ring", "tc", "vec", "umma", "mid"])
+    ap.add_argument("--kernel", default="auto", choices=["auto", "ring", "tc", "vec", "umma", "mid", "tcx"])
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--bf16", action="store_true")
     args = ap.parse_args()

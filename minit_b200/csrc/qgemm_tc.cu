@@ -436,6 +436,215 @@ qgemm_tcw_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     if (tid == 0 && abort_flag && p.err) atomicExch(p.err, 1u);
 }
 
+// =============================================================================================
+// Prefill variant with the dequantized weights in TENSOR MEMORY: 256 (columns) x 192 (batch rows) per CTA.
+// The 256 x 256 tile above moves, per k-block of 1024 tensor-pipe cycles, 96 KB of MMA operand reads, 32 KB of
+// dequantized-A writes and 40 KB of TMA writes through shared memory: 168 B/clk against the SM's 128, so the
+// tensor pipe waits for shared memory half of the time.  Here the converter warps write W straight into tensor
+// memory (one tcgen05.st per thread and k-block, as the mid-batch kernel does) and the MMA takes A from there:
+// shared memory carries the x tile (read twice, once per 128-column half), the packed words and nothing else
+// (117 B/clk at the full tensor rate), and a stage shrinks from 72 KB to 32 KB, so six stages cover the latency of
+// the TMA loads.  Tensor memory: 2 x 192 accumulator columns + 2 slots x 2 halves x 32 columns of A = 512.
+//   warp 0 TMA, warp 1 MMA issue, warps 2-17 converters in two groups that take alternate k-blocks (a group's
+//   chain -- wait for the stage, convert, wait for its A slot, tcgen05.st -- is longer than the 768 cycles the MMAs
+//   of a k-block take; thread <-> column, TMEM lane quarter = warp % 4), warps 18-21 epilogue (not overlapped with
+//   the next tile: the accumulators are single-buffered).
+// =============================================================================================
+constexpr int TCX_STAGES = 6;
+constexpr int TCX_THREADS = 22 * 32;     // TMA, MMA, 2 x 8 converter warps, 4 epilogue warps
+constexpr int TCX_BM = 192;
+
+struct TcxSmem {
+    static constexpr int QROWS = TC_BK / 8;
+    static constexpr int B_BYTES = TCX_BM * 128;
+    static constexpr int Q_BYTES = QROWS * 256 * 4;
+    static constexpr int OFF_B = 0;
+    static constexpr int OFF_Q = OFF_B + TCX_STAGES * B_BYTES;
+    static constexpr int OFF_BAR = OFF_Q + TCX_STAGES * Q_BYTES;
+    static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+    static_assert(B_BYTES % 1024 == 0, "x tiles need 1024-byte alignment");
+};
+
+template <typename T>
+__global__ void __launch_bounds__(TCX_THREADS, 1)
+qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_q, const TcParams p) {
+    using S = TcxSmem;
+    using H = F16x2<T>;
+    constexpr int PACK = 8, QROWS = S::QROWS, BM = TCX_BM;
+    constexpr uint32_t A_COL0 = 2 * BM;                      // first tensor-memory column of the A slots
+
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar0 = sbase + S::OFF_BAR;
+    auto bar_full = [&](int s) { return bar0 + 8u * s; };
+    auto bar_empty = [&](int s) { return bar0 + 8u * (TCX_STAGES + s); };
+    auto bar_aready = [&](int a) { return bar0 + 8u * (2 * TCX_STAGES + a); };
+    auto bar_afree = [&](int a) { return bar0 + 8u * (2 * TCX_STAGES + 2 + a); };
+    const uint32_t bar_tfull = bar0 + 8u * (2 * TCX_STAGES + 4), bar_tempty = bar0 + 8u * (2 * TCX_STAGES + 5);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + S::OFF_BAR + 8 * (2 * TCX_STAGES + 6));
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kblocks = (p.k + TC_BK - 1) / TC_BK;
+    const int total_tiles = p.n_tiles * p.m_tiles;      // n_tiles counts 256-column tiles, m_tiles 192-row tiles
+
+    if (tid == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < TCX_STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(bar_aready(a), 8); mbar_init(bar_afree(a), 1); }
+        mbar_init(bar_tfull, 1); mbar_init(bar_tempty, 128);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_a = tmem_base + A_COL0;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0; bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int n0 = (tile / p.m_tiles) * 256, m0 = (tile % p.m_tiles) * BM;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % TCX_STAGES; const uint32_t ph = (it / TCX_STAGES) & 1;
+                    if (!mbar_wait(bar_empty(s), ph ^ 1, &abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(bar_full(s), S::Q_BYTES + S::B_BYTES);
+                    tma_load_2d(sbase + S::OFF_Q + s * S::Q_BYTES, &tmap_q, n0, kb * QROWS, bar_full(s));
+                    tma_load_2d(sbase + S::OFF_B + s * S::B_BYTES, &tmap_x, kb * TC_BK, m0, bar_full(s));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t fmt = H::kIsBf16 ? 1u : 0u;
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BM >> 3) << 17) | ((uint32_t)(TC_BN >> 4) << 24);
+            int it = 0, lt = 0; bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
+                if (!mbar_wait(bar_tempty, (lt & 1) ^ 1, &abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % TCX_STAGES; const uint32_t ph = (it / TCX_STAGES) & 1;
+                    const int as = it & 1; const uint32_t aph = (it >> 1) & 1;
+                    if (!mbar_wait(bar_full(s), ph, &abort_flag) || !mbar_wait(bar_aready(as), aph, &abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t bdesc = tc_desc_sw128(sbase + S::OFF_B + s * S::B_BYTES);
+#pragma unroll
+                    for (int k4 = 0; k4 < TC_BK / 16; ++k4)
+#pragma unroll
+                        for (int nt = 0; nt < 2; ++nt)
+                            tc_mma_ts(tmem_base + (uint32_t)(nt * BM), tmem_a + (uint32_t)((as * 2 + nt) * 32 + k4 * 8), bdesc + (uint64_t)(k4 * 2), idesc,
+                                      (kb | k4) != 0 ? 1u : 0u);
+                    tc_commit(bar_empty(s));       // the x tile and the packed words of this stage are free
+                    tc_commit(bar_afree(as));      // and so is this slot of A in tensor memory
+                }
+                if (ok) tc_commit(bar_tfull);
+            }
+        }
+    } else if (warp < 18) {
+        // converters: group = which k-blocks (even | odd) and which A slot; TMEM lane quarter = warp % 4 (the
+        // hardware's rule); 128-column half = second bit of the warp's index inside its group
+        const int grp = (warp - 2) >> 3;
+        const int q4 = warp & 3, nt = ((warp - 2) >> 2) & 1;
+        const int i = nt * 128 + q4 * 32 + lane;          // column inside the 256-column tile
+        const T* __restrict__ sg = reinterpret_cast<const T*>(p.scales);
+        int it = 0; bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int n = (tile / p.m_tiles) * 256 + i;
+            const bool n_ok = n < p.n;
+            int g_cur = -1;
+            GroupConst<4, T> gc;
+            uint32_t sraw0 = 0, zraw0 = 0, sraw1 = 0, zraw1 = 0;
+            auto fetch = [&](int g, uint32_t& sr, uint32_t& zr) {
+                sr = 0; zr = 0;
+                if (n_ok && g < p.groups) {
+                    sr = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(sg) + (size_t)g * p.n + n);
+                    if (p.qz) zr = __ldg(p.qz + (size_t)g * (p.n / PACK) + n / PACK);
+                }
+            };
+            fetch(0, sraw0, zraw0);
+            int g_next = 0;                                 // group whose raw words are in sraw0 / zraw0
+            for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                if ((it & 1) != grp) continue;              // the other group's k-block
+                const int s = it % TCX_STAGES; const uint32_t ph = (it / TCX_STAGES) & 1;
+                const int as = grp; const uint32_t aph = (it >> 1) & 1;
+                const int g = min((kb * TC_BK) / p.gs, p.groups - 1);
+                if (g != g_cur) {
+                    if (g != g_next) fetch(g, sraw0, zraw0);                 // the prefetch guessed another group (a tile boundary)
+                    g_cur = g;
+                    make_group_const<4, T>(gc, make_uint2(sraw0, 0u), zraw0 >> ((n % PACK) * 4), p.qz != nullptr, p.zp1_const);
+                    g_next = g + 1;
+                    fetch(g_next, sraw0, zraw0);                             // the next group's words, in flight until that group starts
+                }
+                if (!mbar_wait(bar_full(s), ph, &abort_flag)) { ok = false; break; }
+                const uint32_t* q = reinterpret_cast<const uint32_t*>(smem + S::OFF_Q + s * S::Q_BYTES) + i;
+                uint32_t a[32];
+#pragma unroll
+                for (int r = 0; r < QROWS; ++r) {
+                    uint32_t f[4];
+                    dequant_word<4, T>(q[r * 256], gc, 0, f);   // (k0,k4) (k1,k5) (k2,k6) (k3,k7)
+                    a[4 * r + 0] = prmt(f[0], f[1], 0x5410u); a[4 * r + 1] = prmt(f[2], f[3], 0x5410u);   // k in order: two per column
+                    a[4 * r + 2] = prmt(f[0], f[1], 0x7632u); a[4 * r + 3] = prmt(f[2], f[3], 0x7632u);
+                }
+                if (!mbar_wait(bar_afree(as), aph ^ 1, &abort_flag)) { ok = false; break; }   // the MMAs two k-blocks back have read this slot
+                tc_fence_after();
+                tc_st32(tmem_a + ((uint32_t)(q4 * 32) << 16) + (uint32_t)((as * 2 + nt) * 32), a);
+                tc_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_aready(as));
+            }
+        }
+    } else {
+        // epilogue: warp & 3 = TMEM lane quarter; each thread owns one column of each 128-column half
+        const int q4 = warp & 3;
+        const int nl = q4 * 32 + lane;
+        const T* __restrict__ bias = reinterpret_cast<const T*>(p.bias);
+        T* __restrict__ out = reinterpret_cast<T*>(p.out);
+        int lt = 0; bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
+            const int n0 = (tile / p.m_tiles) * 256, m0 = (tile % p.m_tiles) * BM;
+            if (!mbar_wait(bar_tfull, lt & 1, &abort_flag)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll 1
+            for (int nt = 0; nt < 2; ++nt) {
+                const int n = n0 + nt * 128 + nl;
+                const float bv = (bias && n < p.n) ? H::to_float(reinterpret_cast<const uint16_t*>(bias)[n]) : 0.f;
+#pragma unroll 1
+                for (int c0 = 0; c0 < TCX_BM; c0 += 32) {
+                    uint32_t r[32];
+                    tc_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(nt * BM + c0), r);
+                    tc_wait_ld();
+                    if (n < p.n) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int mrow = m0 + c0 + j;
+                            if (mrow < p.m)
+                                reinterpret_cast<uint16_t*>(out)[(size_t)mrow * p.n + n] = H::from_float(__uint_as_float(r[j]) + bv);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar_tempty);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+    if (tid == 0 && abort_flag && p.err) atomicExch(p.err, 1u);
+}
+
 // ---- host side -------------------------------------------------------------------------
 EncodeTiledFn get_tensor_map_encoder() {
     static EncodeTiledFn fn = nullptr;
@@ -521,6 +730,36 @@ int launch_tc(cudaStream_t st, const QGemmArgs& a) {
     p.m = a.m; p.n = a.n; p.k = a.k; p.groups = a.groups; p.gs = a.k / a.groups;
     p.n_tiles = (a.n + TC_BN - 1) / TC_BN; p.m_tiles = (a.m + bm - 1) / bm;
     p.zp1_const = 1 << (a.bits - 1);
+    if (wide && (a.flags & MT_FLAG_TC_TMEM_A)) {
+        // dequantized weights through tensor memory, 256 x 192 tiles (the x box has 192 rows)
+        CUtensorMap mx192;
+        {
+            cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)a.m};
+            cuuint64_t strides[1] = {(cuuint64_t)a.k * 2};
+            cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)TCX_BM};
+            cuuint32_t es[2] = {1, 1};
+            const CUtensorMapDataType dt = a.dtype == MT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+            if (enc(&mx192, dt, 2, const_cast<void*>(a.x), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+                return MT_ERR_CUDA;
+        }
+        p.n_tiles = (a.n + 255) / 256; p.m_tiles = (a.m + TCX_BM - 1) / TCX_BM;
+        int dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const int tiles = p.n_tiles * p.m_tiles;
+        const int grid = tiles < sms ? tiles : sms;
+        if (a.dtype == MT_F16) {
+            auto kern = qgemm_tcx_kernel<__half>;
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcxSmem::TOTAL) != cudaSuccess) { cudaGetLastError(); return MT_ERR_TOO_LARGE; }
+            kern<<<grid, TCX_THREADS, TcxSmem::TOTAL, st>>>(mx192, mq, p);
+        } else {
+            auto kern = qgemm_tcx_kernel<__nv_bfloat16>;
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcxSmem::TOTAL) != cudaSuccess) { cudaGetLastError(); return MT_ERR_TOO_LARGE; }
+            kern<<<grid, TCX_THREADS, TcxSmem::TOTAL, st>>>(mx192, mq, p);
+        }
+        return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_CUDA;
+    }
     if (wide) {
         p.n_tiles = (a.n + 255) / 256;
         int dev = 0, sms = 148;

@@ -110,3 +110,20 @@ def test_unsupported_is_refused(M):
     c = O.make_gptq_case(1024, 256, 4, bits=4, group_size=64, seed=1)       # groups of 64: not a multiple of the k-block
     with pytest.raises(RuntimeError):
         run(M, c, 4)
+
+
+@pytest.mark.parametrize("k,n,ms", [(3072, 2688, (16, 17, 32, 33)),        # 8.3 M weights: the integer kernel from 17 rows on
+                                    (4096, 10240, (8, 9, 16, 17)),          # 42 M: from 9 rows on
+                                    (2048, 8192, (5, 32)),                  # K < 3072: never
+                                    (8192, 14336, (3, 8, 32))])             # 117 M: from 3 rows on
+def test_default_dispatch_on_both_sides_of_the_size_rule(M, k, n, ms):
+    """mt_qgemm with no flags picks the integer tensor-core kernel or the register-ring kernel by rows and weight size
+    (mid_preferred in csrc/api.cu); either way the result is inside the bound.  Checked on a 512-column slice for the
+    large weights so that the oracle stays quick."""
+    for m in ms:
+        c = O.make_gptq_case(k, n, m, bits=4, seed=k // 64 + n // 64 + m)
+        out = run(M, c, 4, flags=0)
+        sl = slice(n // 2 - 256, n // 2 + 256)
+        w = O.dequantize_packed(c["qweight"][:, sl].contiguous(), None, c["qzeros"][:, sl.start // 8:sl.stop // 8].contiguous(),
+                                c["scales"][:, sl].contiguous(), 4)
+        assert_close(out[:, sl].cpu(), O.qlinear(c["x"], w), f"default dispatch {k}x{n} M={m}")
