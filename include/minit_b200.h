@@ -44,8 +44,9 @@ extern "C" {
 #define MT_FLAG_FORCE_TC     2   /* always use the tcgen05 kernel */
 #define MT_FLAG_FORCE_UMMA  32   /* always use the mid-batch tcgen05 kernel (all warps dequantize; contiguous groups, group size % 64 == 0) */
 #define MT_FLAG_FORCE_MID  128   /* always use the integer tensor-core kernel (contiguous groups of a multiple of 128, N % 32 == 0) */
-#define MT_FLAG_TC_TMEM_A  256   /* prefill (M > 128, int4): the 256 x 192 tile with the dequantized weights in tensor memory instead of
-                                    the 256 x 256 tile with the weights in shared memory (the default) */
+#define MT_FLAG_TC_TMEM_A  256   /* prefill (M > 128, int4): always the 256 x 192 tile with the dequantized weights in tensor memory */
+#define MT_FLAG_TC_SMEM_A  512   /* prefill (M > 128, int4): always the 256 x 256 tile with them in shared memory (default: whichever
+                                    fills its last wave of tiles better) */
 #define MT_FLAG_FORCE_VEC   16   /* always use the CUDA-core decode GEMV (M <= 2, contiguous groups, N % 128 == 0) */
 #define MT_FLAG_SPLITS(s)   (((s) & 0xff) << 16)   /* tuning: force the split-K factor of the decode GEMV */
 #define MT_FLAG_PDL          4   /* launch with programmatic stream serialization: the kernel starts

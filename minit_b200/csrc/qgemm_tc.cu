@@ -37,6 +37,7 @@ struct TcParams {
     int m, n, k, groups, gs;
     int n_tiles, m_tiles;
     int zp1_const;
+    int band;               // row tiles per band of the tile order (qgemm_tcx_kernel)
 };
 
 constexpr int TC_BN = 128;     // output columns per tile (MMA M)
@@ -447,11 +448,11 @@ qgemm_tcw_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 // the TMA loads.  Tensor memory: 2 x 192 accumulator columns + 2 slots x 2 halves x 32 columns of A = 512.
 //   warp 0 TMA, warp 1 MMA issue, warps 2-17 converters in two groups that take alternate k-blocks (a group's
 //   chain -- wait for the stage, convert, wait for its A slot, tcgen05.st -- is longer than the 768 cycles the MMAs
-//   of a k-block take; thread <-> column, TMEM lane quarter = warp % 4), warps 18-21 epilogue (not overlapped with
-//   the next tile: the accumulators are single-buffered).
+//   of a k-block take; thread <-> column, TMEM lane quarter = warp % 4), warps 18-25 epilogue (not overlapped with
+//   the next tile: the accumulators are single-buffered; eight warps keep it short).
 // =============================================================================================
 constexpr int TCX_STAGES = 6;
-constexpr int TCX_THREADS = 22 * 32;     // TMA, MMA, 2 x 8 converter warps, 4 epilogue warps
+constexpr int TCX_THREADS = 27 * 32;     // TMA, MMA (first half), 2 x 8 converter warps, 8 epilogue warps, MMA (second half)
 constexpr int TCX_BM = 192;
 
 struct TcxSmem {
@@ -465,6 +466,18 @@ struct TcxSmem {
     static_assert(B_BYTES % 1024 == 0, "x tiles need 1024-byte alignment");
 };
 
+// Tile order of the persistent grid: row tiles in bands, inside a band column tile major.  The ~148 tiles in flight
+// then share one band of x tiles (1.5 MB each) and a few weight tiles instead of every x tile of the batch, which at
+// 8192 rows (67 MB of x) no longer fits the L2 next to the output stream.
+constexpr int TCX_BAND_MAX = 24;
+__device__ __forceinline__ void tcx_tile_origin(int tile, const TcParams& p, int& n0, int& m0) {
+    const int per_band = p.band * p.n_tiles;
+    const int band = tile / per_band, r = tile - band * per_band;
+    const int rows = min(p.band, p.m_tiles - band * p.band);          // row tiles of this band (the last one may be short)
+    const int nt = r / rows, mt = band * p.band + (r - nt * rows);
+    n0 = nt * 256; m0 = mt * TCX_BM;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(TCX_THREADS, 1)
 qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_q, const TcParams p) {
@@ -477,12 +490,15 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar0 = sbase + S::OFF_BAR;
+    // One barrier per stage for everything the MMAs of a k-block need: `full` counts the x tile's bytes AND the eight
+    // converter warps that wrote this k-block's weights into tensor memory, so the issuing thread waits once per
+    // k-block; its one commit (`empty`) frees the stage for the producer and tells the converters two k-blocks later
+    // that their A slot has been read.  `qfull`: the packed words of the stage have landed (the converters' input).
     auto bar_full = [&](int s) { return bar0 + 8u * s; };
     auto bar_empty = [&](int s) { return bar0 + 8u * (TCX_STAGES + s); };
-    auto bar_aready = [&](int a) { return bar0 + 8u * (2 * TCX_STAGES + a); };
-    auto bar_afree = [&](int a) { return bar0 + 8u * (2 * TCX_STAGES + 2 + a); };
-    const uint32_t bar_tfull = bar0 + 8u * (2 * TCX_STAGES + 4), bar_tempty = bar0 + 8u * (2 * TCX_STAGES + 5);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + S::OFF_BAR + 8 * (2 * TCX_STAGES + 6));
+    auto bar_qfull = [&](int s) { return bar0 + 8u * (2 * TCX_STAGES + s); };
+    const uint32_t bar_tfull = bar0 + 8u * (3 * TCX_STAGES), bar_tempty = bar0 + 8u * (3 * TCX_STAGES + 1);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + S::OFF_BAR + 8 * (3 * TCX_STAGES + 2));
     __shared__ int abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -491,9 +507,8 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 
     if (tid == 0) {
         abort_flag = 0;
-        for (int s = 0; s < TCX_STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(bar_aready(a), 8); mbar_init(bar_afree(a), 1); }
-        mbar_init(bar_tfull, 1); mbar_init(bar_tempty, 128);
+        for (int s = 0; s < TCX_STAGES; ++s) { mbar_init(bar_full(s), 1 + 8); mbar_init(bar_empty(s), 2); mbar_init(bar_qfull(s), 1); }
+        mbar_init(bar_tfull, 2); mbar_init(bar_tempty, 256);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -510,43 +525,50 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         if (lane == 0) {
             int it = 0; bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int n0 = (tile / p.m_tiles) * 256, m0 = (tile % p.m_tiles) * BM;
+                int n0, m0; tcx_tile_origin(tile, p, n0, m0);
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % TCX_STAGES; const uint32_t ph = (it / TCX_STAGES) & 1;
                     if (!mbar_wait(bar_empty(s), ph ^ 1, &abort_flag)) { ok = false; break; }
-                    mbar_expect_tx(bar_full(s), S::Q_BYTES + S::B_BYTES);
-                    tma_load_2d(sbase + S::OFF_Q + s * S::Q_BYTES, &tmap_q, n0, kb * QROWS, bar_full(s));
+                    mbar_expect_tx(bar_qfull(s), S::Q_BYTES);
+                    tma_load_2d(sbase + S::OFF_Q + s * S::Q_BYTES, &tmap_q, n0, kb * QROWS, bar_qfull(s));
+                    mbar_expect_tx(bar_full(s), S::B_BYTES);
                     tma_load_2d(sbase + S::OFF_B + s * S::B_BYTES, &tmap_x, kb * TC_BK, m0, bar_full(s));
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 26) {
+        // two issuing threads, one per 128-column half (separate warps, so that they really run side by side): each
+        // waits for the stage, issues its four MMAs of the k-block and commits; a stage is free after both commits
+        const int nt = warp == 1 ? 0 : 1;
         if (lane == 0) {
             const uint32_t fmt = H::kIsBf16 ? 1u : 0u;
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BM >> 3) << 17) | ((uint32_t)(TC_BN >> 4) << 24);
             int it = 0, lt = 0; bool ok = true;
+            uint32_t early = 0u;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
                 if (!mbar_wait(bar_tempty, (lt & 1) ^ 1, &abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % TCX_STAGES; const uint32_t ph = (it / TCX_STAGES) & 1;
-                    const int as = it & 1; const uint32_t aph = (it >> 1) & 1;
-                    if (!mbar_wait(bar_full(s), ph, &abort_flag) || !mbar_wait(bar_aready(as), aph, &abort_flag)) { ok = false; break; }
+                    const int as = it & 1;
+                    if (!early && !mbar_wait(bar_full(s), ph, &abort_flag)) { ok = false; break; }
                     tc_fence_after();
+                    // ask about the next k-block now; the answer is read at the top of the next turn, behind this turn's MMAs
+                    {
+                        const int nit = it + 1;
+                        early = mbar_test(bar_full(nit % TCX_STAGES), (uint32_t)((nit / TCX_STAGES) & 1));
+                    }
                     const uint64_t bdesc = tc_desc_sw128(sbase + S::OFF_B + s * S::B_BYTES);
 #pragma unroll
                     for (int k4 = 0; k4 < TC_BK / 16; ++k4)
-#pragma unroll
-                        for (int nt = 0; nt < 2; ++nt)
-                            tc_mma_ts(tmem_base + (uint32_t)(nt * BM), tmem_a + (uint32_t)((as * 2 + nt) * 32 + k4 * 8), bdesc + (uint64_t)(k4 * 2), idesc,
-                                      (kb | k4) != 0 ? 1u : 0u);
-                    tc_commit(bar_empty(s));       // the x tile and the packed words of this stage are free
-                    tc_commit(bar_afree(as));      // and so is this slot of A in tensor memory
+                        tc_mma_ts(tmem_base + (uint32_t)(nt * BM), tmem_a + (uint32_t)((as * 2 + nt) * 32 + k4 * 8), bdesc + (uint64_t)(k4 * 2), idesc,
+                                  (kb | k4) != 0 ? 1u : 0u);
+                    tc_commit(bar_empty(s));       // the stage is free, and so is this slot of A in tensor memory
                 }
                 if (ok) tc_commit(bar_tfull);
             }
         }
-    } else if (warp < 18) {
+    } else if (warp >= 2 && warp < 18) {
         // converters: group = which k-blocks (even | odd) and which A slot; TMEM lane quarter = warp % 4 (the
         // hardware's rule); 128-column half = second bit of the warp's index inside its group
         const int grp = (warp - 2) >> 3;
@@ -554,8 +576,10 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         const int i = nt * 128 + q4 * 32 + lane;          // column inside the 256-column tile
         const T* __restrict__ sg = reinterpret_cast<const T*>(p.scales);
         int it = 0; bool ok = true;
+        uint32_t q_early = 0u;                              // answer of the early look at this turn's `qfull`
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const int n = (tile / p.m_tiles) * 256 + i;
+            int n0c, m0c; tcx_tile_origin(tile, p, n0c, m0c);
+            const int n = n0c + i;
             const bool n_ok = n < p.n;
             int g_cur = -1;
             GroupConst<4, T> gc;
@@ -572,7 +596,7 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             for (int kb = 0; kb < kblocks; ++kb, ++it) {
                 if ((it & 1) != grp) continue;              // the other group's k-block
                 const int s = it % TCX_STAGES; const uint32_t ph = (it / TCX_STAGES) & 1;
-                const int as = grp; const uint32_t aph = (it >> 1) & 1;
+                const int as = grp;
                 const int g = min((kb * TC_BK) / p.gs, p.groups - 1);
                 if (g != g_cur) {
                     if (g != g_next) fetch(g, sraw0, zraw0);                 // the prefetch guessed another group (a tile boundary)
@@ -581,7 +605,12 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     g_next = g + 1;
                     fetch(g_next, sraw0, zraw0);                             // the next group's words, in flight until that group starts
                 }
-                if (!mbar_wait(bar_full(s), ph, &abort_flag)) { ok = false; break; }
+                if (!q_early && !mbar_wait(bar_qfull(s), ph, &abort_flag)) { ok = false; break; }
+                // two early looks, answered behind the conversion arithmetic: is this group's A slot free (the MMAs of its
+                // previous turn have committed), and have the packed words of its next turn landed
+                uint32_t a_free = 1u;
+                if (it >= 2) a_free = mbar_test(bar_empty((it - 2) % TCX_STAGES), (uint32_t)(((it - 2) / TCX_STAGES) & 1));
+                q_early = mbar_test(bar_qfull((it + 2) % TCX_STAGES), (uint32_t)(((it + 2) / TCX_STAGES) & 1));
                 const uint32_t* q = reinterpret_cast<const uint32_t*>(smem + S::OFF_Q + s * S::Q_BYTES) + i;
                 uint32_t a[32];
 #pragma unroll
@@ -591,28 +620,31 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     a[4 * r + 0] = prmt(f[0], f[1], 0x5410u); a[4 * r + 1] = prmt(f[2], f[3], 0x5410u);   // k in order: two per column
                     a[4 * r + 2] = prmt(f[0], f[1], 0x7632u); a[4 * r + 3] = prmt(f[2], f[3], 0x7632u);
                 }
-                if (!mbar_wait(bar_afree(as), aph ^ 1, &abort_flag)) { ok = false; break; }   // the MMAs two k-blocks back have read this slot
+                if (!a_free) {                                   // the MMAs two k-blocks back (this group's previous turn) have read this slot
+                    const int pit = it - 2;
+                    if (!mbar_wait(bar_empty(pit % TCX_STAGES), (pit / TCX_STAGES) & 1, &abort_flag)) { ok = false; break; }
+                }
                 tc_fence_after();
                 tc_st32(tmem_a + ((uint32_t)(q4 * 32) << 16) + (uint32_t)((as * 2 + nt) * 32), a);
                 tc_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_aready(as));
+                if (lane == 0) mbar_arrive(bar_full(s));
             }
         }
-    } else {
-        // epilogue: warp & 3 = TMEM lane quarter; each thread owns one column of each 128-column half
+    } else if (warp >= 18 && warp < 26) {
+        // epilogue, eight warps: warp & 3 = TMEM lane quarter, the other bit = 128-column half; a thread owns one column
         const int q4 = warp & 3;
+        const int nt = (warp - 18) >> 2;
         const int nl = q4 * 32 + lane;
         const T* __restrict__ bias = reinterpret_cast<const T*>(p.bias);
         T* __restrict__ out = reinterpret_cast<T*>(p.out);
         int lt = 0; bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
-            const int n0 = (tile / p.m_tiles) * 256, m0 = (tile % p.m_tiles) * BM;
+            int n0, m0; tcx_tile_origin(tile, p, n0, m0);
             if (!mbar_wait(bar_tfull, lt & 1, &abort_flag)) { ok = false; break; }
             tc_fence_after();
-#pragma unroll 1
-            for (int nt = 0; nt < 2; ++nt) {
+            {
                 const int n = n0 + nt * 128 + nl;
                 const float bv = (bias && n < p.n) ? H::to_float(reinterpret_cast<const uint16_t*>(bias)[n]) : 0.f;
 #pragma unroll 1
@@ -730,7 +762,20 @@ int launch_tc(cudaStream_t st, const QGemmArgs& a) {
     p.m = a.m; p.n = a.n; p.k = a.k; p.groups = a.groups; p.gs = a.k / a.groups;
     p.n_tiles = (a.n + TC_BN - 1) / TC_BN; p.m_tiles = (a.m + bm - 1) / bm;
     p.zp1_const = 1 << (a.bits - 1);
-    if (wide && (a.flags & MT_FLAG_TC_TMEM_A)) {
+    // Two int4 prefill tiles: 256 x 192 with the dequantized weights in tensor memory (about 8 % faster per unit of work)
+    // and 256 x 256 with them in shared memory.  Both run one tile per CTA at a time on a persistent grid, so the one
+    // whose tile count fills the last wave better wins: compare waves x rows per tile.
+    bool tmem_a = (a.flags & MT_FLAG_TC_TMEM_A) != 0;
+    if (wide && !tmem_a && !(a.flags & MT_FLAG_TC_SMEM_A)) {
+        int dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const long long nt256 = (a.n + 255) / 256;
+        const long long waves_x = (nt256 * ((a.m + TCX_BM - 1) / TCX_BM) + sms - 1) / sms;
+        const long long waves_w = (nt256 * ((a.m + TCW_BM - 1) / TCW_BM) + sms - 1) / sms;
+        tmem_a = waves_x * TCX_BM * 92 <= waves_w * TCW_BM * 100;
+    }
+    if (wide && tmem_a) {
         // dequantized weights through tensor memory, 256 x 192 tiles (the x box has 192 rows)
         CUtensorMap mx192;
         {
@@ -744,6 +789,11 @@ int launch_tc(cudaStream_t st, const QGemmArgs& a) {
                 return MT_ERR_CUDA;
         }
         p.n_tiles = (a.n + 255) / 256; p.m_tiles = (a.m + TCX_BM - 1) / TCX_BM;
+        // bands of at most 24 row tiles, all of the same height (measured on 4096 x 28672: all 22 row tiles in one band at
+        // 4096 rows 1124 TFLOP/s against 1081 with bands of 8; at 8192 rows one band of 43 gives 994, bands of 16 1065)
+        const int nbands = (p.m_tiles + TCX_BAND_MAX - 1) / TCX_BAND_MAX;
+        p.band = (p.m_tiles + nbands - 1) / nbands;
+        if ((a.flags >> 24) & 0xf) p.band = ((a.flags >> 24) & 0xf) * 4;      // tuning: bits 24-27 of the flags = band / 4
         int dev = 0, sms = 148;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

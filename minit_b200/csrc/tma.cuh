@@ -24,6 +24,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// One non-blocking look at a barrier.  The answer takes a few hundred cycles to come back whatever it is, so a thread that
+// knows which barrier it will need next can ask early and read the answer behind other work.
+__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
 // Bounded wait: spins, then backs off with nanosleep; gives up after roughly a second.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     for (int i = 0; i < 4096; ++i) if (mbar_try_wait(bar, parity)) return true;

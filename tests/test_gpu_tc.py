@@ -88,3 +88,27 @@ def test_tc_prefill_config_shapes(M, k, n, dtype, m):
     assert tuple(out.shape) == (m, n)
     for r0 in (0, m // 2 - 64, m - 128):
         assert_close(out[r0:r0 + 128], O.qlinear(d["x"][r0:r0 + 128], c["w"]), f"prefill {k}x{n} M={m} {dtype} rows {r0}")
+
+
+TMEM_A = 2 | 256          # MT_FLAG_FORCE_TC | MT_FLAG_TC_TMEM_A: the 256 x 192 tile with the dequantized weights in tensor memory
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m", [129, 192, 193, 256, 400, 1000])
+def test_tensor_memory_operand_variant_matches_oracle(M, dtype, m):
+    """Row counts on both sides of the 192-row tile; K = 1024 gives 16 k-blocks, so both converter groups and both
+    slots of A in tensor memory are reused."""
+    c = O.make_gptq_case(1024, 512, m, bits=4, dtype=dtype, seed=m + 1)
+    assert_close(run(M, c, 4, flags=TMEM_A), oracle_out(c, False), f"tensor-memory A {dtype} M={m}")
+
+
+@pytest.mark.parametrize("k,n", [(64, 256), (192, 264), (4096, 6144), (2048, 1000), (448, 512)])
+def test_tensor_memory_operand_variant_shapes_edges_bias(M, k, n):
+    """One k-block, an odd number of k-blocks (the groups swap slots from tile to tile), ragged N, bias."""
+    c = O.make_gptq_case(k, n, 260, bits=4, group_size=64, seed=k + n + 1, bias=True)
+    assert_close(run(M, c, 4, bias=c["bias"], flags=TMEM_A), oracle_out(c, False, c["bias"]), f"tensor-memory A {k}x{n}")
+
+
+def test_tensor_memory_operand_variant_many_tiles_per_cta(M):
+    c = O.make_gptq_case(512, 256 * 24, 2048, bits=4, seed=10)
+    assert_close(run(M, c, 4, flags=TMEM_A), oracle_out(c, False), "tensor-memory A, 264 tiles")
