@@ -877,7 +877,7 @@ def run_single_shape(args):
         sets.append((qw, qz, sc))
     x = torch.randn((m, k), device=dev, dtype=torch.float32).to(dtype)
     out = torch.empty((m, n), device=dev, dtype=dtype)
-    flags = {"auto": 0, "ring": 1, "tc": 2, "vec": 16, "umma": 32, "mid": 128, "tcx": 256, "tcw": 512}[args.kernel] | ((args.tune & 0xf) << 24) | (4 if args.pdl and args.kernel in ("auto", "ring", "vec") else 0)
+    flags = {"auto": 0, "ring": 1, "tc": 2, "vec": 16, "umma": 32, "mid": 128, "tcx": 258, "tcw": 514}[args.kernel] | ((args.tune & 0xf) << 24) | (4 if args.pdl and args.kernel in ("auto", "ring", "vec") else 0)
 
     def one():
         for qw, qz, sc in sets:

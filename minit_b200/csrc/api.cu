@@ -286,7 +286,7 @@ int mt_qgemm(void* stream, const void* x, const uint32_t* qweight, const int32_t
     if (umma_supported(a)) {
         if (m > 32 && m <= 64) return launch_umma(st, a);
         if (m > 8 && m <= 32 && weights >= (128LL << 20)) return launch_umma(st, a);
-        if (m > 64 && m <= 128 && k >= 8192) return launch_umma(st, a);
+        if (m > 64 && m <= 128 && k >= 8192 && !(tc_tmem_a_preferred(m, n, bits) && tc_supported(a))) return launch_umma(st, a);
     }
     if (m > 64 && tc_supported(a)) return launch_tc(st, a);
     // Decode at M <= 2: the CUDA-core GEMV (packed integers multiplied as fp16 subnormals) streams

@@ -252,10 +252,11 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
 // per MAC than the 128 x 256 tile above, which was running at the L2 bandwidth limit.  All 512
 // TMEM columns hold the two accumulators, so the epilogue of a tile is not overlapped with the
 // next tile's main loop (about 5 % of a tile at K = 4096).
-//   warp 0 TMA, warp 1 MMA issue, warps 2-9 dequant (thread i <-> column i of 256), warps 10-13 epilogue.
+//   warp 0 TMA, warps 1 and 14 MMA issue (one per 128-column half), warps 2-9 dequant (thread i <-> column i of 256),
+//   warps 10-13 epilogue.
 // =============================================================================================
 constexpr int TCW_STAGES = 3;
-constexpr int TCW_THREADS = 14 * 32;
+constexpr int TCW_THREADS = 15 * 32;     // TMA, MMA (first half), 8 dequant warps, 4 epilogue warps, MMA (second half)
 constexpr int TCW_BM = 256;
 
 struct TcwSmem {
@@ -294,8 +295,8 @@ qgemm_tcw_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 
     if (tid == 0) {
         abort_flag = 0;
-        for (int s = 0; s < TCW_STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_aready(s), 256); mbar_init(bar_empty(s), 1); }
-        mbar_init(bar_tfull, 1); mbar_init(bar_tempty, 128);
+        for (int s = 0; s < TCW_STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_aready(s), 256); mbar_init(bar_empty(s), 2); }
+        mbar_init(bar_tfull, 2); mbar_init(bar_tempty, 128);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -321,7 +322,9 @@ qgemm_tcw_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 14) {
+        // two issuing threads in separate warps, one per 128-column half: a stage is free after both have committed
+        const int nt = warp == 1 ? 0 : 1;
         if (lane == 0) {
             const uint32_t fmt = H::kIsBf16 ? 1u : 0u;
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BM >> 3) << 17) | ((uint32_t)(TC_BN >> 4) << 24);
@@ -334,19 +337,16 @@ qgemm_tcw_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     if (!mbar_wait(bar_full(s), ph, &abort_flag) || !mbar_wait(bar_aready(s), ph, &abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     const uint64_t bdesc = tc_desc_sw128(sbase + S::OFF_B + s * S::B_BYTES);
+                    const uint64_t adesc = tc_desc_sw128(sbase + S::OFF_A + s * S::A_BYTES + nt * (TC_BN * 128));
 #pragma unroll
                     for (int k4 = 0; k4 < TC_BK / 16; ++k4)
-#pragma unroll
-                        for (int nt = 0; nt < 2; ++nt) {
-                            const uint64_t adesc = tc_desc_sw128(sbase + S::OFF_A + s * S::A_BYTES + nt * (TC_BN * 128));
-                            tc_mma_ss(tmem_base + (uint32_t)(nt * BM), adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, (kb | k4) != 0 ? 1u : 0u);
-                        }
+                        tc_mma_ss(tmem_base + (uint32_t)(nt * BM), adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, (kb | k4) != 0 ? 1u : 0u);
                     tc_commit(bar_empty(s));
                 }
                 if (ok) tc_commit(bar_tfull);
             }
         }
-    } else if (warp < 10) {
+    } else if (warp >= 2 && warp < 10) {
         // dequant: thread i <-> column i of the 256-column tile
         const int i = tid - 64;
         const int nt = i >> 7, il = i & 127;
@@ -392,7 +392,7 @@ qgemm_tcw_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 mbar_arrive(bar_aready(s));
             }
         }
-    } else {
+    } else if (warp >= 10 && warp < 14) {
         // epilogue: warp & 3 = TMEM lane quarter; each thread owns one column of each 128-column tile
         const int q4 = warp & 3;
         const int nl = q4 * 32 + lane;
@@ -694,6 +694,12 @@ EncodeTiledFn get_tensor_map_encoder() {
     return fn;
 }
 
+// 65 to 128 rows: the 256 x 192 tile with the weights in tensor memory is the kernel of choice when its one row of tiles
+// gives at least ~100 CTAs work.
+bool tc_tmem_a_preferred(int m, int n, int bits) {
+    return bits == 4 && m > 64 && m <= 128 && (n + 255) / 256 >= 100;
+}
+
 bool tc_supported(const QGemmArgs& a) {
     if (a.g_idx != nullptr) return false;
     const int gs = a.k / a.groups;
@@ -745,17 +751,7 @@ int launch_tc(cudaStream_t st, const QGemmArgs& a) {
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return MT_ERR_CUDA;
     }
-    const bool wide = a.bits == 4 && a.m > 128 && a.n >= 256;
-    if (wide) {   // the packed-weight box covers 256 columns
-        cuuint64_t dims[2] = {(cuuint64_t)a.n, (cuuint64_t)(a.k / pack)};
-        cuuint64_t strides[1] = {(cuuint64_t)a.n * 4};
-        cuuint32_t box[2] = {256u, (cuuint32_t)(TC_BK / pack)};
-        cuuint32_t es[2] = {1, 1};
-        if (enc(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(a.qweight), dims, strides, box, es,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            return MT_ERR_CUDA;
-    }
+    const bool wide = a.bits == 4 && a.m > 64 && a.n >= 256;       // the 256-column tiles (int4)
     TcParams p;
     p.qz = a.qzeros; p.scales = a.scales; p.bias = a.bias; p.out = a.out;
     p.err = (a.workspace && a.workspace_bytes >= kCounterBytes) ? static_cast<unsigned*>(a.workspace) + (kMaxTiles - 1) : nullptr;
@@ -765,8 +761,11 @@ int launch_tc(cudaStream_t st, const QGemmArgs& a) {
     // Two int4 prefill tiles: 256 x 192 with the dequantized weights in tensor memory (about 8 % faster per unit of work)
     // and 256 x 256 with them in shared memory.  Both run one tile per CTA at a time on a persistent grid, so the one
     // whose tile count fills the last wave better wins: compare waves x rows per tile.
-    bool tmem_a = (a.flags & MT_FLAG_TC_TMEM_A) != 0;
-    if (wide && !tmem_a && !(a.flags & MT_FLAG_TC_SMEM_A)) {
+    // From 65 to 128 rows only the first has a tile that fits (the 256 x 256 one would be half empty), and it pays when
+    // its single row of tiles nearly fills the GPU (tc_tmem_a_preferred): 8192 x 57344 at 128 rows 196 us against 336 us
+    // for the mid-batch kernel, but 28672 x 8192 (32 tiles) 309 us against 218 us.
+    bool tmem_a = (a.flags & MT_FLAG_TC_TMEM_A) != 0 || (wide && a.m <= 128 && tc_tmem_a_preferred(a.m, a.n, a.bits));
+    if (wide && a.m > 128 && !tmem_a && !(a.flags & MT_FLAG_TC_SMEM_A)) {
         int dev = 0, sms = 148;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -774,6 +773,16 @@ int launch_tc(cudaStream_t st, const QGemmArgs& a) {
         const long long waves_x = (nt256 * ((a.m + TCX_BM - 1) / TCX_BM) + sms - 1) / sms;
         const long long waves_w = (nt256 * ((a.m + TCW_BM - 1) / TCW_BM) + sms - 1) / sms;
         tmem_a = waves_x * TCX_BM * 92 <= waves_w * TCW_BM * 100;
+    }
+    if (wide && (tmem_a || a.m > 128)) {   // the packed-weight box covers 256 columns
+        cuuint64_t dims[2] = {(cuuint64_t)a.n, (cuuint64_t)(a.k / pack)};
+        cuuint64_t strides[1] = {(cuuint64_t)a.n * 4};
+        cuuint32_t box[2] = {256u, (cuuint32_t)(TC_BK / pack)};
+        cuuint32_t es[2] = {1, 1};
+        if (enc(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(a.qweight), dims, strides, box, es,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return MT_ERR_CUDA;
     }
     if (wide && tmem_a) {
         // dequantized weights through tensor memory, 256 x 192 tiles (the x box has 192 rows)
@@ -810,7 +819,7 @@ int launch_tc(cudaStream_t st, const QGemmArgs& a) {
         }
         return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_CUDA;
     }
-    if (wide) {
+    if (wide && a.m > 128) {
         p.n_tiles = (a.n + 255) / 256;
         int dev = 0, sms = 148;
         cudaGetDevice(&dev);
