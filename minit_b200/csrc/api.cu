@@ -190,6 +190,10 @@ size_t mt_workspace_bytes(int m, int n, int k, int bits) {
         const size_t mid = mid_workspace_bytes(m, n, k);
         if (mid > bytes) bytes = mid;
     }
+    if (m > 128 && bits == 4) {                                  // prefill: the last wave of tiles cut along K
+        const size_t tail = tcx_workspace_bytes(m, n, k);
+        if (tail > bytes) bytes = tail;
+    }
     return kCounterBytes + bytes;
 }
 

@@ -211,6 +211,7 @@ bool mid_supported(const QGemmArgs& a);
 size_t mid_workspace_bytes(int m, int n, int k);
 int launch_tc(cudaStream_t st, const QGemmArgs& a);             // tcgen05 path (any M), GPTQ layout without g_idx
 bool tc_supported(const QGemmArgs& a);
+size_t tcx_workspace_bytes(int m, int n, int k);     // fp32 partial tiles of the prefill kernel's split last wave
 bool tc_tmem_a_preferred(int m, int n, int bits);   // 65..128 rows: the tensor-memory-A prefill tile beats the mid-batch kernel
 
 }  // namespace mt

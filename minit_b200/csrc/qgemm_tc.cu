@@ -38,6 +38,10 @@ struct TcParams {
     int n_tiles, m_tiles;
     int zp1_const;
     int band;               // row tiles per band of the tile order (qgemm_tcx_kernel)
+    // qgemm_tcx_kernel: the tiles of the last, partly filled wave are cut along K into `split` parts each (items), so that
+    // the wave's CTAs all have work; parts leave fp32 partial tiles, the last part to arrive adds them in part order
+    int full_tiles, split, total_items;
+    float* partial; unsigned* counters;
 };
 
 constexpr int TC_BN = 128;     // output columns per tile (MMA M)
@@ -478,6 +482,15 @@ __device__ __forceinline__ void tcx_tile_origin(int tile, const TcParams& p, int
     n0 = nt * 256; m0 = mt * TCX_BM;
 }
 
+// Work item -> tile, k-block range, and (for a part of a split tile) its part number and the split tile's index.
+__device__ __forceinline__ void tcx_item(int item, const TcParams& p, int kblocks, int& tile, int& kb0, int& kb1, int& part, int& sidx) {
+    if (item < p.full_tiles) { tile = item; kb0 = 0; kb1 = kblocks; part = -1; sidx = 0; return; }
+    const int j = item - p.full_tiles;
+    sidx = j / p.split; part = j - sidx * p.split; tile = p.full_tiles + sidx;
+    const int per = (kblocks + p.split - 1) / p.split;
+    kb0 = part * per; kb1 = min(kblocks, kb0 + per);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(TCX_THREADS, 1)
 qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_q, const TcParams p) {
@@ -503,7 +516,7 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kblocks = (p.k + TC_BK - 1) / TC_BK;
-    const int total_tiles = p.n_tiles * p.m_tiles;      // n_tiles counts 256-column tiles, m_tiles 192-row tiles
+    const int total_items = p.total_items;              // tiles of 256 columns x 192 rows; the last wave's are cut along K
 
     if (tid == 0) {
         abort_flag = 0;
@@ -524,9 +537,10 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     if (warp == 0) {
         if (lane == 0) {
             int it = 0; bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+                int tile, kb0, kb1, part, sidx; tcx_item(item, p, kblocks, tile, kb0, kb1, part, sidx);
                 int n0, m0; tcx_tile_origin(tile, p, n0, m0);
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % TCX_STAGES; const uint32_t ph = (it / TCX_STAGES) & 1;
                     if (!mbar_wait(bar_empty(s), ph ^ 1, &abort_flag)) { ok = false; break; }
                     mbar_expect_tx(bar_qfull(s), S::Q_BYTES);
@@ -545,10 +559,11 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BM >> 3) << 17) | ((uint32_t)(TC_BN >> 4) << 24);
             int it = 0, lt = 0; bool ok = true;
             uint32_t early = 0u;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
+            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++lt) {
+                int tile, kb0, kb1, part, sidx; tcx_item(item, p, kblocks, tile, kb0, kb1, part, sidx);
                 if (!mbar_wait(bar_tempty, (lt & 1) ^ 1, &abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % TCX_STAGES; const uint32_t ph = (it / TCX_STAGES) & 1;
                     const int as = it & 1;
                     if (!early && !mbar_wait(bar_full(s), ph, &abort_flag)) { ok = false; break; }
@@ -562,7 +577,7 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 #pragma unroll
                     for (int k4 = 0; k4 < TC_BK / 16; ++k4)
                         tc_mma_ts(tmem_base + (uint32_t)(nt * BM), tmem_a + (uint32_t)((as * 2 + nt) * 32 + k4 * 8), bdesc + (uint64_t)(k4 * 2), idesc,
-                                  (kb | k4) != 0 ? 1u : 0u);
+                                  (kb != kb0 || k4 != 0) ? 1u : 0u);
                     tc_commit(bar_empty(s));       // the stage is free, and so is this slot of A in tensor memory
                 }
                 if (ok) tc_commit(bar_tfull);
@@ -577,7 +592,8 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         const T* __restrict__ sg = reinterpret_cast<const T*>(p.scales);
         int it = 0; bool ok = true;
         uint32_t q_early = 0u;                              // answer of the early look at this turn's `qfull`
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+            int tile, kb0, kb1, part, sidx; tcx_item(item, p, kblocks, tile, kb0, kb1, part, sidx);
             int n0c, m0c; tcx_tile_origin(tile, p, n0c, m0c);
             const int n = n0c + i;
             const bool n_ok = n < p.n;
@@ -591,9 +607,9 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     if (p.qz) zr = __ldg(p.qz + (size_t)g * (p.n / PACK) + n / PACK);
                 }
             };
-            fetch(0, sraw0, zraw0);
-            int g_next = 0;                                 // group whose raw words are in sraw0 / zraw0
-            for (int kb = 0; kb < kblocks; ++kb, ++it) {
+            int g_next = min((kb0 * TC_BK) / p.gs, p.groups - 1);   // group whose raw words are in sraw0 / zraw0
+            fetch(g_next, sraw0, zraw0);
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 if ((it & 1) != grp) continue;              // the other group's k-block
                 const int s = it % TCX_STAGES; const uint32_t ph = (it / TCX_STAGES) & 1;
                 const int as = grp;
@@ -640,11 +656,58 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         const T* __restrict__ bias = reinterpret_cast<const T*>(p.bias);
         T* __restrict__ out = reinterpret_cast<T*>(p.out);
         int lt = 0; bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
+        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++lt) {
+            int tile, kb0, kb1, part, sidx; tcx_item(item, p, kblocks, tile, kb0, kb1, part, sidx);
             int n0, m0; tcx_tile_origin(tile, p, n0, m0);
             if (!mbar_wait(bar_tfull, lt & 1, &abort_flag)) { ok = false; break; }
             tc_fence_after();
-            {
+            if (part >= 0) {
+                // A part of a tile that was cut along K: leave the fp32 sums of this part in the workspace; the warp that
+                // finds all other parts there adds them in part order (its own from tensor memory) and stores the tile.
+                const size_t slice = (size_t)TCX_BM * 128;                     // one 128-column half of one part
+                float* mine = p.partial + ((size_t)(sidx * p.split + part) * 2 + nt) * slice;
+#pragma unroll 1
+                for (int c0 = 0; c0 < TCX_BM; c0 += 32) {
+                    uint32_t r[32];
+                    tc_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(nt * BM + c0), r);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) __stcg(mine + (size_t)(c0 + j) * 128 + nl, __uint_as_float(r[j]));
+                }
+                __threadfence();
+                __syncwarp();
+                unsigned old = 0;
+                unsigned* ctr = p.counters + sidx * 8 + (warp - 18);
+                if (lane == 0) old = atomicAdd(ctr, 1u);
+                old = __shfl_sync(0xffffffffu, old, 0);
+                if (old == unsigned(p.split - 1)) {
+                    __threadfence();
+                    const int n = n0 + nt * 128 + nl;
+                    const float bv = (bias && n < p.n) ? H::to_float(reinterpret_cast<const uint16_t*>(bias)[n]) : 0.f;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < TCX_BM; c0 += 16) {                   // 16 rows at a time: the sums and the own values fit the registers
+                        uint32_t r[16];
+                        tc_ld<16>(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(nt * BM + c0), r);
+                        tc_wait_ld();
+                        float acc[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+                        for (int q = 0; q < p.split; ++q) {                     // part order, whoever arrives last
+                            const float* src = p.partial + ((size_t)(sidx * p.split + q) * 2 + nt) * slice + (size_t)c0 * 128 + nl;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) acc[j] += (q == part) ? __uint_as_float(r[j]) : __ldcg(src + (size_t)j * 128);
+                        }
+                        if (n < p.n) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const int mrow = m0 + c0 + j;
+                                if (mrow < p.m) reinterpret_cast<uint16_t*>(out)[(size_t)mrow * p.n + n] = H::from_float(acc[j] + bv);
+                            }
+                        }
+                    }
+                    if (lane == 0) *ctr = 0;
+                }
+            } else {
                 const int n = n0 + nt * 128 + nl;
                 const float bv = (bias && n < p.n) ? H::to_float(reinterpret_cast<const uint16_t*>(bias)[n]) : 0.f;
 #pragma unroll 1
@@ -698,6 +761,26 @@ EncodeTiledFn get_tensor_map_encoder() {
 // gives at least ~100 CTAs work.
 bool tc_tmem_a_preferred(int m, int n, int bits) {
     return bits == 4 && m > 64 && m <= 128 && (n + 255) / 256 >= 100;
+}
+
+// Parts per tile of the last, partly filled wave of 256 x 192 tiles (1: leave it alone).  A wave that is at most half
+// full is cut so that its parts fill the GPU once: the wave then takes 1 / split of a tile's time.
+int tcx_tail_split(int m, int n, int k, int sms) {
+    const int tiles = ((n + 255) / 256) * ((m + TCX_BM - 1) / TCX_BM);
+    const int rest = tiles % sms;
+    if (tiles < sms || rest == 0) return 1;                  // less than one wave in all: one tile per CTA is all there is
+    int split = sms / rest;
+    if (split > 4) split = 4;
+    const int kblocks = (k + TC_BK - 1) / TC_BK;
+    while (split > 1 && kblocks < 16 * split) --split;       // a part keeps at least 16 k-blocks
+    return split < 1 ? 1 : split;
+}
+size_t tcx_workspace_bytes(int m, int n, int k) {
+    int sms = 148;
+    const int split = tcx_tail_split(m, n, k, sms);
+    if (split <= 1) return 0;
+    const int tiles = ((n + 255) / 256) * ((m + TCX_BM - 1) / TCX_BM);
+    return (size_t)(tiles % sms) * split * 2 * TCX_BM * 128 * 4;
 }
 
 bool tc_supported(const QGemmArgs& a) {
@@ -770,9 +853,12 @@ int launch_tc(cudaStream_t st, const QGemmArgs& a) {
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         const long long nt256 = (a.n + 255) / 256;
-        const long long waves_x = (nt256 * ((a.m + TCX_BM - 1) / TCX_BM) + sms - 1) / sms;
+        const long long tiles_x = nt256 * ((a.m + TCX_BM - 1) / TCX_BM);
         const long long waves_w = (nt256 * ((a.m + TCW_BM - 1) / TCW_BM) + sms - 1) / sms;
-        tmem_a = waves_x * TCX_BM * 92 <= waves_w * TCW_BM * 100;
+        // time of the 256 x 192 tiles in units of one row of a tile: full waves, plus the last wave cut along K
+        const int split = tcx_tail_split(a.m, a.n, a.k, sms);
+        const long long cost_x = (tiles_x / sms) * TCX_BM * split + ((tiles_x % sms) ? TCX_BM : 0);     // x split
+        tmem_a = cost_x * 92 <= waves_w * TCW_BM * 100 * split;
     }
     if (wide && (tmem_a || a.m > 128)) {   // the packed-weight box covers 256 columns
         cuuint64_t dims[2] = {(cuuint64_t)a.n, (cuuint64_t)(a.k / pack)};
@@ -798,6 +884,22 @@ int launch_tc(cudaStream_t st, const QGemmArgs& a) {
                 return MT_ERR_CUDA;
         }
         p.n_tiles = (a.n + 255) / 256; p.m_tiles = (a.m + TCX_BM - 1) / TCX_BM;
+        {
+            int dev0 = 0, sms0 = 148;
+            cudaGetDevice(&dev0);
+            cudaDeviceGetAttribute(&sms0, cudaDevAttrMultiProcessorCount, dev0);
+            const int tiles0 = p.n_tiles * p.m_tiles;
+            p.full_tiles = tiles0; p.split = 1; p.partial = nullptr; p.counters = nullptr;
+            const int split = tcx_tail_split(a.m, a.n, a.k, sms0);
+            const int rest = tiles0 % sms0;
+            const size_t need = (size_t)rest * split * 2 * TCX_BM * 128 * 4;
+            if (split > 1 && a.workspace && a.workspace_bytes >= kCounterBytes + need && rest * 8 <= kMaxTiles - 8) {
+                p.full_tiles = tiles0 - rest; p.split = split;
+                p.counters = static_cast<unsigned*>(a.workspace);
+                p.partial = reinterpret_cast<float*>(static_cast<char*>(a.workspace) + kCounterBytes);
+            }
+            p.total_items = p.full_tiles + (tiles0 - p.full_tiles) * p.split;
+        }
         // bands of at most 24 row tiles, all of the same height (measured on 4096 x 28672: all 22 row tiles in one band at
         // 4096 rows 1124 TFLOP/s against 1081 with bands of 8; at 8192 rows one band of 43 gives 994, bands of 16 1065)
         const int nbands = (p.m_tiles + TCX_BAND_MAX - 1) / TCX_BAND_MAX;
@@ -806,7 +908,7 @@ int launch_tc(cudaStream_t st, const QGemmArgs& a) {
         int dev = 0, sms = 148;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        const int tiles = p.n_tiles * p.m_tiles;
+        const int tiles = p.total_items;
         const int grid = tiles < sms ? tiles : sms;
         if (a.dtype == MT_F16) {
             auto kern = qgemm_tcx_kernel<__half>;

@@ -112,3 +112,21 @@ def test_tensor_memory_operand_variant_shapes_edges_bias(M, k, n):
 def test_tensor_memory_operand_variant_many_tiles_per_cta(M):
     c = O.make_gptq_case(512, 256 * 24, 2048, bits=4, seed=10)
     assert_close(run(M, c, 4, flags=TMEM_A), oracle_out(c, False), "tensor-memory A, 264 tiles")
+
+
+@pytest.mark.parametrize("k,n,m,dtype,bias", [(2048, 4096, 1920, torch.float16, False),     # 160 tiles: the last 12 are cut in 2 along K
+                                              (4096, 4096, 1900, torch.bfloat16, True),     # cut in 4, ragged last row tile, bias
+                                              (1024, 4352, 1728, torch.float16, False)])    # 153 tiles, 16 k-blocks: too short to cut
+def test_last_wave_of_tiles_cut_along_k(M, k, n, m, dtype, bias):
+    """More tiles than SMs with a small remainder: the remaining tiles are split along K, their fp32 partial tiles are
+    added in part order by whichever part arrives last, and the workspace counters return to zero."""
+    from minit_b200 import _lib
+    c = O.make_gptq_case(k, n, m, bits=4, dtype=dtype, seed=k + n + m, bias=bias)
+    b = c["bias"] if bias else None
+    out1 = run(M, c, 4, bias=b, flags=TMEM_A)
+    out2 = run(M, c, 4, bias=b, flags=TMEM_A)
+    assert torch.equal(out1, out2), "the split tiles must not depend on which part arrives last"
+    assert_close(out1, oracle_out(c, False, b), f"split last wave {k}x{n} M={m}")
+    torch.cuda.synchronize()
+    for ws in _lib._workspaces.values():
+        assert int(ws[:_lib.COUNTER_BYTES].view(torch.int32).abs().sum().item()) == 0
