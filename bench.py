@@ -877,7 +877,7 @@ def run_single_shape(args):
         sets.append((qw, qz, sc))
     x = torch.randn((m, k), device=dev, dtype=torch.float32).to(dtype)
     out = torch.empty((m, n), device=dev, dtype=dtype)
-    flags = {"auto": 0, "ring": 1, "tc": 2, "vec": 16, "umma": 32, "mid": 128, "tcx": 258, "tcw": 514}[args.kernel] | ((args.tune & 0xf) << 24) | (4 if args.pdl and args.kernel in ("auto", "ring", "vec") else 0)
+    flags = {"auto": 0, "ring": 1, "tc": 2, "vec": 16, "umma": 32, "mid": 128, "tcx": 258, "tcw": 514}[args.kernel] | ((args.tune & 0x1f) << 24) | (4 if args.pdl and args.kernel in ("auto", "ring", "vec") else 0)
 
     def one():
         for qw, qz, sc in sets:
@@ -916,7 +916,7 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--chain", type=int, default=0, help="decode: layers per resident launch of mt_qgemm_chain (0: one launch per linear, which measures faster)")
-    ap.add_argument("--tune", type=int, default=0, help="--single-shape: tuning bits 24-27 of the flags")
+    ap.add_argument("--tune", type=int, default=0, help="--single-shape: tuning bits 24-28 of the flags")
     ap.add_argument("--chain-flags", type=int, default=0, help="tuning bits passed to the chain launch")
     ap.add_argument("--shard-as", type=int, default=1, help="one GPU only: time the per-rank shapes of an N-way split, no exchange")
     ap.add_argument("--no-graph", action="store_true")

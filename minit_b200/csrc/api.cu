@@ -190,6 +190,10 @@ size_t mt_workspace_bytes(int m, int n, int k, int bits) {
         const size_t mid = mid_workspace_bytes(m, n, k);
         if (mid > bytes) bytes = mid;
     }
+    if (m > 32 && m <= 64 && bits == 4) {                        // 64-row tiles of the tensor-memory-A kernel, every tile cut along K
+        const size_t parts = tcx64_workspace_bytes(n, k);
+        if (parts > bytes) bytes = parts;
+    }
     if (m > 128 && bits == 4) {                                  // prefill: the last wave of tiles cut along K
         const size_t tail = tcx_workspace_bytes(m, n, k);
         if (tail > bytes) bytes = tail;

@@ -38,6 +38,7 @@ struct TcParams {
     int n_tiles, m_tiles;
     int zp1_const;
     int band;               // row tiles per band of the tile order (qgemm_tcx_kernel)
+    int bm;                 // batch rows per tile (qgemm_tcx_kernel)
     // qgemm_tcx_kernel: the tiles of the last, partly filled wave are cut along K into `split` parts each (items), so that
     // the wave's CTAs all have work; parts leave fp32 partial tiles, the last part to arrive adds them in part order
     int full_tiles, split, total_items;
@@ -455,18 +456,19 @@ qgemm_tcw_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 //   of a k-block take; thread <-> column, TMEM lane quarter = warp % 4), warps 18-25 epilogue (not overlapped with
 //   the next tile: the accumulators are single-buffered; eight warps keep it short).
 // =============================================================================================
-constexpr int TCX_STAGES = 6;
-constexpr int TCX_THREADS = 27 * 32;     // TMA, MMA (first half), 2 x 8 converter warps, 8 epilogue warps, MMA (second half)
+constexpr int TCX_THREADS = 28 * 32;     // TMA (x), MMA (first half), 2 x 8 converter warps, 8 epilogue warps, MMA (second half), TMA (packed words)
 constexpr int TCX_BM = 192;
 
-struct TcxSmem {
+template <int BM> struct TcxSmem {
+    static constexpr int STAGES = BM > 64 ? 6 : 12;      // 192 KB in flight either way
     static constexpr int QROWS = TC_BK / 8;
-    static constexpr int B_BYTES = TCX_BM * 128;
+    static constexpr int B_BYTES = BM * 128;
     static constexpr int Q_BYTES = QROWS * 256 * 4;
     static constexpr int OFF_B = 0;
-    static constexpr int OFF_Q = OFF_B + TCX_STAGES * B_BYTES;
-    static constexpr int OFF_BAR = OFF_Q + TCX_STAGES * Q_BYTES;
-    static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+    static constexpr int OFF_Q = OFF_B + STAGES * B_BYTES;
+    static constexpr int OFF_SZ = OFF_Q + STAGES * Q_BYTES;          // per converter thread: 2 x (scale word, zero word)
+    static constexpr int OFF_BAR = OFF_SZ + 512 * 16;
+    static constexpr int TOTAL = OFF_BAR + 512 + 1024;
     static_assert(B_BYTES % 1024 == 0, "x tiles need 1024-byte alignment");
 };
 
@@ -479,7 +481,7 @@ __device__ __forceinline__ void tcx_tile_origin(int tile, const TcParams& p, int
     const int band = tile / per_band, r = tile - band * per_band;
     const int rows = min(p.band, p.m_tiles - band * p.band);          // row tiles of this band (the last one may be short)
     const int nt = r / rows, mt = band * p.band + (r - nt * rows);
-    n0 = nt * 256; m0 = mt * TCX_BM;
+    n0 = nt * 256; m0 = mt * p.bm;
 }
 
 // Work item -> tile, k-block range, and (for a part of a split tile) its part number and the split tile's index.
@@ -491,12 +493,19 @@ __device__ __forceinline__ void tcx_item(int item, const TcParams& p, int kblock
     kb0 = part * per; kb1 = min(kblocks, kb0 + per);
 }
 
-template <typename T>
+template <typename T, int BM>
 __global__ void __launch_bounds__(TCX_THREADS, 1)
 qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_q, const TcParams p) {
-    using S = TcxSmem;
+    using S = TcxSmem<BM>;
     using H = F16x2<T>;
-    constexpr int PACK = 8, QROWS = S::QROWS, BM = TCX_BM;
+    constexpr int PACK = 8, QROWS = S::QROWS;
+    static_assert(BM % 32 == 0 && BM <= 192, "batch rows per tile: 2 * BM accumulator columns + at least 128 columns of A");
+    // Slots of A in tensor memory (64 columns each: two halves x 32).  A slot is rewritten only after the MMAs that read it
+    // have committed, the converters have seen that, stored and said so, and the issuing thread has seen THAT: about 2000
+    // cycles, during which the tensor pipe lives on the other slots.  Two slots (192-row tiles) hold 1536 cycles of MMA
+    // work, three (160 rows) 1920, four (128 rows and fewer) more than enough.
+    constexpr int NSLOT = (512 - 2 * BM) / 64 > 4 ? 4 : (512 - 2 * BM) / 64;
+    static_assert(NSLOT >= 2 && NSLOT < S::STAGES, "A slots");
     constexpr uint32_t A_COL0 = 2 * BM;                      // first tensor-memory column of the A slots
 
     extern __shared__ unsigned char smem_raw[];
@@ -508,19 +517,20 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     // k-block; its one commit (`empty`) frees the stage for the producer and tells the converters two k-blocks later
     // that their A slot has been read.  `qfull`: the packed words of the stage have landed (the converters' input).
     auto bar_full = [&](int s) { return bar0 + 8u * s; };
-    auto bar_empty = [&](int s) { return bar0 + 8u * (TCX_STAGES + s); };
-    auto bar_qfull = [&](int s) { return bar0 + 8u * (2 * TCX_STAGES + s); };
-    const uint32_t bar_tfull = bar0 + 8u * (3 * TCX_STAGES), bar_tempty = bar0 + 8u * (3 * TCX_STAGES + 1);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + S::OFF_BAR + 8 * (3 * TCX_STAGES + 2));
+    auto bar_empty = [&](int s) { return bar0 + 8u * (S::STAGES + s); };
+    auto bar_qfull = [&](int s) { return bar0 + 8u * (2 * S::STAGES + s); };
+    const uint32_t bar_tfull = bar0 + 8u * (3 * S::STAGES), bar_tempty = bar0 + 8u * (3 * S::STAGES + 1);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + S::OFF_BAR + 8 * (3 * S::STAGES + 2));
     __shared__ int abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kblocks = (p.k + TC_BK - 1) / TC_BK;
+    const int kpg = p.gs / TC_BK;                        // k-blocks per scale group (the group size is a multiple of 64)
     const int total_items = p.total_items;              // tiles of 256 columns x 192 rows; the last wave's are cut along K
 
     if (tid == 0) {
         abort_flag = 0;
-        for (int s = 0; s < TCX_STAGES; ++s) { mbar_init(bar_full(s), 1 + 8); mbar_init(bar_empty(s), 2); mbar_init(bar_qfull(s), 1); }
+        for (int s = 0; s < S::STAGES; ++s) { mbar_init(bar_full(s), 1 + 8); mbar_init(bar_empty(s), 2); mbar_init(bar_qfull(s), 1); }
         mbar_init(bar_tfull, 2); mbar_init(bar_tempty, 256);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -534,19 +544,25 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_a = tmem_base + A_COL0;
 
-    if (warp == 0) {
+    if (warp == 0 || warp == 27) {
+        // two producer threads in separate warps, one for the x tiles and one for the packed words: a thread issues about
+        // four TMA copies per microsecond, and a k-block of the MMAs lasts 0.2-0.4 us
+        const bool words = warp == 27;
         if (lane == 0) {
             int it = 0; bool ok = true;
             for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
                 int tile, kb0, kb1, part, sidx; tcx_item(item, p, kblocks, tile, kb0, kb1, part, sidx);
                 int n0, m0; tcx_tile_origin(tile, p, n0, m0);
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = it % TCX_STAGES; const uint32_t ph = (it / TCX_STAGES) & 1;
-                    if (!mbar_wait(bar_empty(s), ph ^ 1, &abort_flag)) { ok = false; break; }
-                    mbar_expect_tx(bar_qfull(s), S::Q_BYTES);
-                    tma_load_2d(sbase + S::OFF_Q + s * S::Q_BYTES, &tmap_q, n0, kb * QROWS, bar_qfull(s));
-                    mbar_expect_tx(bar_full(s), S::B_BYTES);
-                    tma_load_2d(sbase + S::OFF_B + s * S::B_BYTES, &tmap_x, kb * TC_BK, m0, bar_full(s));
+                    const int s = it % S::STAGES; const uint32_t ph = (it / S::STAGES) & 1;
+                    if (!mbar_wait_sleep<200>(bar_empty(s), ph ^ 1, &abort_flag)) { ok = false; break; }
+                    if (words) {
+                        mbar_expect_tx(bar_qfull(s), S::Q_BYTES);
+                        tma_load_2d(sbase + S::OFF_Q + s * S::Q_BYTES, &tmap_q, n0, kb * QROWS, bar_qfull(s));
+                    } else {
+                        mbar_expect_tx(bar_full(s), S::B_BYTES);
+                        tma_load_2d(sbase + S::OFF_B + s * S::B_BYTES, &tmap_x, kb * TC_BK, m0, bar_full(s));
+                    }
                 }
             }
         }
@@ -561,17 +577,17 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             uint32_t early = 0u;
             for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++lt) {
                 int tile, kb0, kb1, part, sidx; tcx_item(item, p, kblocks, tile, kb0, kb1, part, sidx);
-                if (!mbar_wait(bar_tempty, (lt & 1) ^ 1, &abort_flag)) { ok = false; break; }
+                if (!mbar_wait_sleep<100>(bar_tempty, (lt & 1) ^ 1, &abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = it % TCX_STAGES; const uint32_t ph = (it / TCX_STAGES) & 1;
-                    const int as = it & 1;
-                    if (!early && !mbar_wait(bar_full(s), ph, &abort_flag)) { ok = false; break; }
+                    const int s = it % S::STAGES; const uint32_t ph = (it / S::STAGES) & 1;
+                    const int as = it % NSLOT;
+                    if (!early && !mbar_wait_sleep<20>(bar_full(s), ph, &abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     // ask about the next k-block now; the answer is read at the top of the next turn, behind this turn's MMAs
                     {
                         const int nit = it + 1;
-                        early = mbar_test(bar_full(nit % TCX_STAGES), (uint32_t)((nit / TCX_STAGES) & 1));
+                        early = mbar_test(bar_full(nit % S::STAGES), (uint32_t)((nit / S::STAGES) & 1));
                     }
                     const uint64_t bdesc = tc_desc_sw128(sbase + S::OFF_B + s * S::B_BYTES);
 #pragma unroll
@@ -592,6 +608,8 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         const T* __restrict__ sg = reinterpret_cast<const T*>(p.scales);
         int it = 0; bool ok = true;
         uint32_t q_early = 0u;                              // answer of the early look at this turn's `qfull`
+        volatile uint32_t* szbuf = reinterpret_cast<volatile uint32_t*>(smem + S::OFF_SZ) + (tid - 64) * 4;
+        const uint32_t szbuf_s = sbase + S::OFF_SZ + (uint32_t)(tid - 64) * 16u;
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
             int tile, kb0, kb1, part, sidx; tcx_item(item, p, kblocks, tile, kb0, kb1, part, sidx);
             int n0c, m0c; tcx_tile_origin(tile, p, n0c, m0c);
@@ -599,34 +617,55 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             const bool n_ok = n < p.n;
             int g_cur = -1;
             GroupConst<4, T> gc;
-            uint32_t sraw0 = 0, zraw0 = 0, sraw1 = 0, zraw1 = 0;
-            auto fetch = [&](int g, uint32_t& sr, uint32_t& zr) {
+            // Scale and zero word of the NEXT group travel through two private words of shared memory (cp.async): a load
+            // into a register that the loop carries to the next turn makes the compiler's register moves at the loop edge
+            // wait for it, and the turn then pays the whole global-load latency (measured: 1000 of 2600 cycles).
+            auto prefetch = [&](int g, int buf) {
+                if (n_ok && g < p.groups) {
+                    const uint32_t dst = szbuf_s + (uint32_t)buf * 8u;
+                    const uint16_t* sp = reinterpret_cast<const uint16_t*>(sg) + (((size_t)g * p.n + n) & ~(size_t)1);
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(sp) : "memory");
+                    if (p.qz) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u), "l"(p.qz + (size_t)g * (p.n / PACK) + n / PACK) : "memory");
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            };
+            auto take = [&](int g, int buf, uint32_t& sr, uint32_t& zr) {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
                 sr = 0; zr = 0;
                 if (n_ok && g < p.groups) {
-                    sr = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(sg) + (size_t)g * p.n + n);
-                    if (p.qz) zr = __ldg(p.qz + (size_t)g * (p.n / PACK) + n / PACK);
+                    sr = (szbuf[buf * 2] >> ((n & 1) * 16)) & 0xffffu;
+                    if (p.qz) zr = szbuf[buf * 2 + 1];
                 }
             };
-            int g_next = min((kb0 * TC_BK) / p.gs, p.groups - 1);   // group whose raw words are in sraw0 / zraw0
-            fetch(g_next, sraw0, zraw0);
-            for (int kb = kb0; kb < kb1; ++kb, ++it) {
+            // this group's first k-block of the item, its scale group and its place inside the group: tracked by addition from
+            // here on (a division per turn is a chain of forty dependent instructions in a warp that has no others to issue)
+            const int kb_first = kb0 + (((it & 1) != grp) ? 1 : 0);
+            int g = min(kb_first / kpg, p.groups - 1), kin = kb_first - (kb_first / kpg) * kpg;
+            int g_next = g;                                         // group whose words are on their way into buffer `cur`
+            int cur = 0;
+            asm volatile("cp.async.wait_group 0;" ::: "memory");   // the last prefetch of the previous item must not land after this one
+            prefetch(g_next, cur);
+            int s = it % S::STAGES; uint32_t ph = (it / S::STAGES) & 1;          // stage and phase of k-block `it`, kept by addition too
+            for (int kb = kb0; kb < kb1; ++kb, ++it, s = (s + 1 == S::STAGES ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
                 if ((it & 1) != grp) continue;              // the other group's k-block
-                const int s = it % TCX_STAGES; const uint32_t ph = (it / TCX_STAGES) & 1;
-                const int as = grp;
-                const int g = min((kb * TC_BK) / p.gs, p.groups - 1);
+                const int as = it % NSLOT;
                 if (g != g_cur) {
-                    if (g != g_next) fetch(g, sraw0, zraw0);                 // the prefetch guessed another group (a tile boundary)
+                    if (g != g_next) prefetch(g, cur);                       // the prefetch guessed another group
+                    uint32_t sraw, zraw;
+                    take(g, cur, sraw, zraw);
                     g_cur = g;
-                    make_group_const<4, T>(gc, make_uint2(sraw0, 0u), zraw0 >> ((n % PACK) * 4), p.qz != nullptr, p.zp1_const);
-                    g_next = g + 1;
-                    fetch(g_next, sraw0, zraw0);                             // the next group's words, in flight until that group starts
+                    make_group_const<4, T>(gc, make_uint2(sraw, 0u), zraw >> ((n % PACK) * 4), p.qz != nullptr, p.zp1_const);
+                    g_next = g + 1; cur ^= 1;
+                    prefetch(g_next, cur);                                   // the next group's words, on their way until that group starts
                 }
-                if (!q_early && !mbar_wait(bar_qfull(s), ph, &abort_flag)) { ok = false; break; }
+                if (!q_early && !mbar_wait_sleep<40>(bar_qfull(s), ph, &abort_flag)) { ok = false; break; }
                 // two early looks, answered behind the conversion arithmetic: is this group's A slot free (the MMAs of its
                 // previous turn have committed), and have the packed words of its next turn landed
+                const int s_prev = s >= NSLOT ? s - NSLOT : s - NSLOT + S::STAGES; const uint32_t ph_prev = s >= NSLOT ? ph : ph ^ 1u;   // k-block it - NSLOT: the last user of this slot
+                const int s_next = s + 2 < S::STAGES ? s + 2 : s + 2 - S::STAGES; const uint32_t ph_next = s + 2 < S::STAGES ? ph : ph ^ 1u;   // k-block it + 2
                 uint32_t a_free = 1u;
-                if (it >= 2) a_free = mbar_test(bar_empty((it - 2) % TCX_STAGES), (uint32_t)(((it - 2) / TCX_STAGES) & 1));
-                q_early = mbar_test(bar_qfull((it + 2) % TCX_STAGES), (uint32_t)(((it + 2) / TCX_STAGES) & 1));
+                if (it >= NSLOT) a_free = mbar_test(bar_empty(s_prev), ph_prev);
+                q_early = mbar_test(bar_qfull(s_next), ph_next);
                 const uint32_t* q = reinterpret_cast<const uint32_t*>(smem + S::OFF_Q + s * S::Q_BYTES) + i;
                 uint32_t a[32];
 #pragma unroll
@@ -636,9 +675,8 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     a[4 * r + 0] = prmt(f[0], f[1], 0x5410u); a[4 * r + 1] = prmt(f[2], f[3], 0x5410u);   // k in order: two per column
                     a[4 * r + 2] = prmt(f[0], f[1], 0x7632u); a[4 * r + 3] = prmt(f[2], f[3], 0x7632u);
                 }
-                if (!a_free) {                                   // the MMAs two k-blocks back (this group's previous turn) have read this slot
-                    const int pit = it - 2;
-                    if (!mbar_wait(bar_empty(pit % TCX_STAGES), (pit / TCX_STAGES) & 1, &abort_flag)) { ok = false; break; }
+                if (!a_free) {                                   // the MMAs NSLOT k-blocks back have read this slot
+                    if (!mbar_wait_sleep<40>(bar_empty(s_prev), ph_prev, &abort_flag)) { ok = false; break; }
                 }
                 tc_fence_after();
                 tc_st32(tmem_a + ((uint32_t)(q4 * 32) << 16) + (uint32_t)((as * 2 + nt) * 32), a);
@@ -646,6 +684,8 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_full(s));
+                kin += 2;                                        // this group's next k-block is two further
+                while (kin >= kpg) { kin -= kpg; if (g < p.groups - 1) ++g; }
             }
         }
     } else if (warp >= 18 && warp < 26) {
@@ -659,15 +699,15 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++lt) {
             int tile, kb0, kb1, part, sidx; tcx_item(item, p, kblocks, tile, kb0, kb1, part, sidx);
             int n0, m0; tcx_tile_origin(tile, p, n0, m0);
-            if (!mbar_wait(bar_tfull, lt & 1, &abort_flag)) { ok = false; break; }
+            if (!mbar_wait_sleep<500>(bar_tfull, lt & 1, &abort_flag)) { ok = false; break; }
             tc_fence_after();
             if (part >= 0) {
                 // A part of a tile that was cut along K: leave the fp32 sums of this part in the workspace; the warp that
                 // finds all other parts there adds them in part order (its own from tensor memory) and stores the tile.
-                const size_t slice = (size_t)TCX_BM * 128;                     // one 128-column half of one part
+                const size_t slice = (size_t)BM * 128;                     // one 128-column half of one part
                 float* mine = p.partial + ((size_t)(sidx * p.split + part) * 2 + nt) * slice;
 #pragma unroll 1
-                for (int c0 = 0; c0 < TCX_BM; c0 += 32) {
+                for (int c0 = 0; c0 < BM; c0 += 32) {
                     uint32_t r[32];
                     tc_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(nt * BM + c0), r);
                     tc_wait_ld();
@@ -685,7 +725,7 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     const int n = n0 + nt * 128 + nl;
                     const float bv = (bias && n < p.n) ? H::to_float(reinterpret_cast<const uint16_t*>(bias)[n]) : 0.f;
 #pragma unroll 1
-                    for (int c0 = 0; c0 < TCX_BM; c0 += 16) {                   // 16 rows at a time: the sums and the own values fit the registers
+                    for (int c0 = 0; c0 < BM; c0 += 16) {                   // 16 rows at a time: the sums and the own values fit the registers
                         uint32_t r[16];
                         tc_ld<16>(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(nt * BM + c0), r);
                         tc_wait_ld();
@@ -711,7 +751,7 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 const int n = n0 + nt * 128 + nl;
                 const float bv = (bias && n < p.n) ? H::to_float(reinterpret_cast<const uint16_t*>(bias)[n]) : 0.f;
 #pragma unroll 1
-                for (int c0 = 0; c0 < TCX_BM; c0 += 32) {
+                for (int c0 = 0; c0 < BM; c0 += 32) {
                     uint32_t r[32];
                     tc_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(nt * BM + c0), r);
                     tc_wait_ld();
@@ -765,8 +805,8 @@ bool tc_tmem_a_preferred(int m, int n, int bits) {
 
 // Parts per tile of the last, partly filled wave of 256 x 192 tiles (1: leave it alone).  A wave that is at most half
 // full is cut so that its parts fill the GPU once: the wave then takes 1 / split of a tile's time.
-int tcx_tail_split(int m, int n, int k, int sms) {
-    const int tiles = ((n + 255) / 256) * ((m + TCX_BM - 1) / TCX_BM);
+int tcx_tail_split(int m, int n, int k, int sms, int bm) {
+    const int tiles = ((n + 255) / 256) * ((m + bm - 1) / bm);
     const int rest = tiles % sms;
     if (tiles < sms || rest == 0) return 1;                  // less than one wave in all: one tile per CTA is all there is
     int split = sms / rest;
@@ -776,11 +816,16 @@ int tcx_tail_split(int m, int n, int k, int sms) {
     return split < 1 ? 1 : split;
 }
 size_t tcx_workspace_bytes(int m, int n, int k) {
-    int sms = 148;
-    const int split = tcx_tail_split(m, n, k, sms);
-    if (split <= 1) return 0;
-    const int tiles = ((n + 255) / 256) * ((m + TCX_BM - 1) / TCX_BM);
-    return (size_t)(tiles % sms) * split * 2 * TCX_BM * 128 * 4;
+    const int sms = 148;
+    size_t need = 0;
+    for (int bm : {192, 160}) {
+        const int split = tcx_tail_split(m, n, k, sms, bm);
+        if (split <= 1) continue;
+        const int tiles = ((n + 255) / 256) * ((m + bm - 1) / bm);
+        const size_t b = (size_t)(tiles % sms) * split * 2 * bm * 128 * 4;
+        if (b > need) need = b;
+    }
+    return need;
 }
 
 bool tc_supported(const QGemmArgs& a) {
@@ -808,9 +853,120 @@ static int launch_tc_inst(cudaStream_t st, const QGemmArgs& a, const CUtensorMap
     return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_CUDA;
 }
 
+// Launch of qgemm_tcx_kernel with tiles of 256 columns x bm rows.  split_all == 0: one item per tile, the tiles of a last
+// wave that is at most half full cut along K (tcx_tail_split); split_all > 0: EVERY tile cut into that many parts (the
+// schedule for few, deep tiles).  `mq` is the packed-weight map with the 256-column box; `p` holds the common fields.
+static int launch_tcx(cudaStream_t st, const QGemmArgs& a, EncodeTiledFn enc, const CUtensorMap& mq, TcParams p, int bm, int split_all) {
+    CUtensorMap mxb;
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)a.m};
+        cuuint64_t strides[1] = {(cuuint64_t)a.k * 2};
+        cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)bm};
+        cuuint32_t es[2] = {1, 1};
+        const CUtensorMapDataType dt = a.dtype == MT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+        if (enc(&mxb, dt, 2, const_cast<void*>(a.x), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return MT_ERR_CUDA;
+    }
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    p.bm = bm;
+    p.n_tiles = (a.n + 255) / 256; p.m_tiles = (a.m + bm - 1) / bm;
+    // bands of at most 24 row tiles, all of the same height (measured on 4096 x 28672: all 22 row tiles in one band at
+    // 4096 rows 1124 TFLOP/s against 1081 with bands of 8; at 8192 rows one band of 43 gives 994, bands of 16 1065)
+    const int nbands = (p.m_tiles + TCX_BAND_MAX - 1) / TCX_BAND_MAX;
+    p.band = (p.m_tiles + nbands - 1) / nbands;
+    if ((a.flags >> 24) & 0xf) p.band = ((a.flags >> 24) & 0xf) * 4;      // tuning: bits 24-27 of the flags = band / 4
+    const int tiles = p.n_tiles * p.m_tiles;
+    p.full_tiles = tiles; p.split = 1; p.partial = nullptr; p.counters = nullptr;
+    const bool ws_ok = a.workspace && a.workspace_bytes >= kCounterBytes;
+    if (split_all == 1) {
+        // one part per tile: nothing to add
+    } else if (split_all > 1) {
+        const size_t need = (size_t)tiles * split_all * 2 * bm * 128 * 4;
+        if (!ws_ok || a.workspace_bytes < kCounterBytes + need || tiles * 8 > kMaxTiles - 8) return MT_ERR_WORKSPACE;
+        p.full_tiles = 0; p.split = split_all;
+    } else {
+        const int split = bm > 64 ? tcx_tail_split(a.m, a.n, a.k, sms, bm) : 1;
+        const int rest = tiles % sms;
+        const size_t need = (size_t)rest * split * 2 * bm * 128 * 4;
+        if (split > 1 && ws_ok && a.workspace_bytes >= kCounterBytes + need && rest * 8 <= kMaxTiles - 8) {
+            p.full_tiles = tiles - rest; p.split = split;
+        }
+    }
+    if (p.split > 1) {
+        p.counters = static_cast<unsigned*>(a.workspace);
+        p.partial = reinterpret_cast<float*>(static_cast<char*>(a.workspace) + kCounterBytes);
+    }
+    p.total_items = p.full_tiles + (tiles - p.full_tiles) * p.split;
+    const int grid = p.total_items < sms ? p.total_items : sms;
+#define MT_TCX(T_, BM_) do { \
+        auto kern = qgemm_tcx_kernel<T_, BM_>; \
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcxSmem<BM_>::TOTAL) != cudaSuccess) { cudaGetLastError(); return MT_ERR_TOO_LARGE; } \
+        kern<<<grid, TCX_THREADS, TcxSmem<BM_>::TOTAL, st>>>(mxb, mq, p); } while (0)
+    if (bm == 192)      { if (a.dtype == MT_F16) MT_TCX(__half, 192); else MT_TCX(__nv_bfloat16, 192); }
+    else if (bm == 160) { if (a.dtype == MT_F16) MT_TCX(__half, 160); else MT_TCX(__nv_bfloat16, 160); }
+    else if (bm == 64)  { if (a.dtype == MT_F16) MT_TCX(__half, 64); else MT_TCX(__nv_bfloat16, 64); }
+    else return MT_ERR_UNSUPPORTED;
+#undef MT_TCX
+    return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_CUDA;
+}
+
+// 64-row tiles of the tensor-memory-A kernel for mid-size batches: every tile is cut into `split` parts along K so that
+// the parts fill the GPU's waves (few, deep tiles otherwise: 224 tiles of 128 k-blocks on 8192 x 57344).
+static int tcx64_split(int n, int k, int sms) {
+    const int tiles = (n + 255) / 256;
+    const int kblocks = (k + TC_BK - 1) / TC_BK;
+    int best = 1; double best_cost = 1e30;
+    for (int s : {1, 2, 3, 4, 6, 8}) {
+        if (s > 1 && kblocks < 16 * s) break;
+        const double waves = double((tiles * s + sms - 1) / sms);
+        const double cost = waves / s + 0.03 * s;            // a part pays for its partial tile
+        if (cost < best_cost) { best_cost = cost; best = s; }
+    }
+    return best;
+}
+bool tcx64_supported(const QGemmArgs& a) {
+    if (!tc_supported(a) || a.bits != 4 || a.m < 1 || a.m > 64 || a.n < 256) return false;
+    if (((a.n + 255) / 256) * 8 > kMaxTiles - 8) return false;
+    return a.workspace != nullptr && a.workspace_bytes >= kCounterBytes + tcx64_workspace_bytes(a.n, a.k);
+}
+size_t tcx64_workspace_bytes(int n, int k) {
+    const int s = tcx64_split(n, k, 148);
+    return s > 1 ? (size_t)((n + 255) / 256) * s * 2 * 64 * 128 * 4 : 0;
+}
+int launch_tcx64(cudaStream_t st, const QGemmArgs& a) {
+    EncodeTiledFn enc = get_tensor_map_encoder();
+    if (!enc || !tcx64_supported(a)) return MT_ERR_UNSUPPORTED;
+    CUtensorMap mq;
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)a.n, (cuuint64_t)(a.k / 8)};
+        cuuint64_t strides[1] = {(cuuint64_t)a.n * 4};
+        cuuint32_t box[2] = {256u, (cuuint32_t)(TC_BK / 8)};
+        cuuint32_t es[2] = {1, 1};
+        if (enc(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(a.qweight), dims, strides, box, es,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return MT_ERR_CUDA;
+    }
+    TcParams p;
+    p.qz = a.qzeros; p.scales = a.scales; p.bias = a.bias; p.out = a.out;
+    p.err = static_cast<unsigned*>(a.workspace) + (kMaxTiles - 1);
+    p.m = a.m; p.n = a.n; p.k = a.k; p.groups = a.groups; p.gs = a.k / a.groups;
+    p.zp1_const = 1 << (a.bits - 1);
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int split = tcx64_split(a.n, a.k, sms);
+    if (((a.flags >> 16) & 0xff) != 0) split = (a.flags >> 16) & 0xff;      // tuning: MT_FLAG_SPLITS forces the parts per tile
+    return launch_tcx(st, a, enc, mq, p, 64, split);
+}
+
 int launch_tc(cudaStream_t st, const QGemmArgs& a) {
     EncodeTiledFn enc = get_tensor_map_encoder();
     if (!enc) return MT_ERR_UNSUPPORTED;
+    if ((a.flags & MT_FLAG_TC_TMEM_A) && a.m <= 64) return launch_tcx64(st, a);
     const int pack = 32 / a.bits;
     const int bm = a.m > 128 ? 256 : (a.m > 64 ? 128 : 64);
     CUtensorMap mx, mq;
@@ -847,17 +1003,18 @@ int launch_tc(cudaStream_t st, const QGemmArgs& a) {
     // From 65 to 128 rows only the first has a tile that fits (the 256 x 256 one would be half empty), and it pays when
     // its single row of tiles nearly fills the GPU (tc_tmem_a_preferred): 8192 x 57344 at 128 rows 196 us against 336 us
     // for the mid-batch kernel, but 28672 x 8192 (32 tiles) 309 us against 218 us.
+    const int xbm = ((a.flags >> 28) & 1) ? 192 : 160;             // row tile of the tensor-memory-A kernel (bit 28 of the flags: tuning)
     bool tmem_a = (a.flags & MT_FLAG_TC_TMEM_A) != 0 || (wide && a.m <= 128 && tc_tmem_a_preferred(a.m, a.n, a.bits));
     if (wide && a.m > 128 && !tmem_a && !(a.flags & MT_FLAG_TC_SMEM_A)) {
         int dev = 0, sms = 148;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         const long long nt256 = (a.n + 255) / 256;
-        const long long tiles_x = nt256 * ((a.m + TCX_BM - 1) / TCX_BM);
+        const long long tiles_x = nt256 * ((a.m + xbm - 1) / xbm);
         const long long waves_w = (nt256 * ((a.m + TCW_BM - 1) / TCW_BM) + sms - 1) / sms;
         // time of the 256 x 192 tiles in units of one row of a tile: full waves, plus the last wave cut along K
-        const int split = tcx_tail_split(a.m, a.n, a.k, sms);
-        const long long cost_x = (tiles_x / sms) * TCX_BM * split + ((tiles_x % sms) ? TCX_BM : 0);     // x split
+        const int split = tcx_tail_split(a.m, a.n, a.k, sms, xbm);
+        const long long cost_x = (tiles_x / sms) * xbm * split + ((tiles_x % sms) ? xbm : 0);     // x split
         tmem_a = cost_x * 92 <= waves_w * TCW_BM * 100 * split;
     }
     if (wide && (tmem_a || a.m > 128)) {   // the packed-weight box covers 256 columns
@@ -870,57 +1027,7 @@ int launch_tc(cudaStream_t st, const QGemmArgs& a) {
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return MT_ERR_CUDA;
     }
-    if (wide && tmem_a) {
-        // dequantized weights through tensor memory, 256 x 192 tiles (the x box has 192 rows)
-        CUtensorMap mx192;
-        {
-            cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)a.m};
-            cuuint64_t strides[1] = {(cuuint64_t)a.k * 2};
-            cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)TCX_BM};
-            cuuint32_t es[2] = {1, 1};
-            const CUtensorMapDataType dt = a.dtype == MT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-            if (enc(&mx192, dt, 2, const_cast<void*>(a.x), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-                return MT_ERR_CUDA;
-        }
-        p.n_tiles = (a.n + 255) / 256; p.m_tiles = (a.m + TCX_BM - 1) / TCX_BM;
-        {
-            int dev0 = 0, sms0 = 148;
-            cudaGetDevice(&dev0);
-            cudaDeviceGetAttribute(&sms0, cudaDevAttrMultiProcessorCount, dev0);
-            const int tiles0 = p.n_tiles * p.m_tiles;
-            p.full_tiles = tiles0; p.split = 1; p.partial = nullptr; p.counters = nullptr;
-            const int split = tcx_tail_split(a.m, a.n, a.k, sms0);
-            const int rest = tiles0 % sms0;
-            const size_t need = (size_t)rest * split * 2 * TCX_BM * 128 * 4;
-            if (split > 1 && a.workspace && a.workspace_bytes >= kCounterBytes + need && rest * 8 <= kMaxTiles - 8) {
-                p.full_tiles = tiles0 - rest; p.split = split;
-                p.counters = static_cast<unsigned*>(a.workspace);
-                p.partial = reinterpret_cast<float*>(static_cast<char*>(a.workspace) + kCounterBytes);
-            }
-            p.total_items = p.full_tiles + (tiles0 - p.full_tiles) * p.split;
-        }
-        // bands of at most 24 row tiles, all of the same height (measured on 4096 x 28672: all 22 row tiles in one band at
-        // 4096 rows 1124 TFLOP/s against 1081 with bands of 8; at 8192 rows one band of 43 gives 994, bands of 16 1065)
-        const int nbands = (p.m_tiles + TCX_BAND_MAX - 1) / TCX_BAND_MAX;
-        p.band = (p.m_tiles + nbands - 1) / nbands;
-        if ((a.flags >> 24) & 0xf) p.band = ((a.flags >> 24) & 0xf) * 4;      // tuning: bits 24-27 of the flags = band / 4
-        int dev = 0, sms = 148;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        const int tiles = p.total_items;
-        const int grid = tiles < sms ? tiles : sms;
-        if (a.dtype == MT_F16) {
-            auto kern = qgemm_tcx_kernel<__half>;
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcxSmem::TOTAL) != cudaSuccess) { cudaGetLastError(); return MT_ERR_TOO_LARGE; }
-            kern<<<grid, TCX_THREADS, TcxSmem::TOTAL, st>>>(mx192, mq, p);
-        } else {
-            auto kern = qgemm_tcx_kernel<__nv_bfloat16>;
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcxSmem::TOTAL) != cudaSuccess) { cudaGetLastError(); return MT_ERR_TOO_LARGE; }
-            kern<<<grid, TCX_THREADS, TcxSmem::TOTAL, st>>>(mx192, mq, p);
-        }
-        return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_CUDA;
-    }
+    if (wide && tmem_a) return launch_tcx(st, a, enc, mq, p, xbm, /*split_all=*/0);
     if (wide && a.m > 128) {
         p.n_tiles = (a.n + 255) / 256;
         int dev = 0, sms = 148;

@@ -43,6 +43,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     *abort_flag = 1;
     return false;
 }
+// Bounded wait that SLEEPS between looks.  A warp that spins on try_wait takes issue slots from the warps of its
+// scheduler and keeps the barrier unit busy; roles that wait long by design (an epilogue waiting for a whole tile, a
+// producer that runs stages ahead) look every NS nanoseconds instead, and roles on the critical path every few tens.
+template <int NS>
+__device__ __forceinline__ bool mbar_wait_sleep(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    constexpr int LIMIT = NS >= 256 ? (1 << 22) : (1 << 25);          // about a second either way
+    for (int i = 0; i < LIMIT; ++i) {
+        if (mbar_test(bar, parity)) return true;
+        if ((i & 63) == 63 && *abort_flag) return false;
+        __nanosleep(NS);
+    }
+    *abort_flag = 1;
+    return false;
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");

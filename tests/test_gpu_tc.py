@@ -130,3 +130,19 @@ def test_last_wave_of_tiles_cut_along_k(M, k, n, m, dtype, bias):
     torch.cuda.synchronize()
     for ws in _lib._workspaces.values():
         assert int(ws[:_lib.COUNTER_BYTES].view(torch.int32).abs().sum().item()) == 0
+
+
+@pytest.mark.parametrize("k,n", [(2048, 512), (8192, 1024), (1024, 4352), (512, 264)])
+@pytest.mark.parametrize("m,dtype", [(3, torch.float16), (33, torch.float16), (64, torch.bfloat16)])
+def test_tensor_memory_operand_variant_with_64_row_tiles(M, k, n, m, dtype):
+    """Up to 64 rows the same kernel runs with 64-row tiles, every tile cut along K into parts that are added in part
+    order (deep K: up to 8 parts; K = 512: no cut); results repeat bit for bit and the counters return to zero."""
+    from minit_b200 import _lib
+    c = O.make_gptq_case(k, n, m, bits=4, dtype=dtype, seed=k + n + m + 5, bias=True)
+    out1 = run(M, c, 4, bias=c["bias"], flags=TMEM_A)
+    out2 = run(M, c, 4, bias=c["bias"], flags=TMEM_A)
+    assert torch.equal(out1, out2)
+    assert_close(out1, oracle_out(c, False, c["bias"]), f"64-row tiles {k}x{n} M={m}")
+    torch.cuda.synchronize()
+    for ws in _lib._workspaces.values():
+        assert int(ws[:_lib.COUNTER_BYTES].view(torch.int32).abs().sum().item()) == 0
