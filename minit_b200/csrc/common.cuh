@@ -212,9 +212,9 @@ size_t mid_workspace_bytes(int m, int n, int k);
 int launch_tc(cudaStream_t st, const QGemmArgs& a);             // tcgen05 path (any M), GPTQ layout without g_idx
 bool tc_supported(const QGemmArgs& a);
 size_t tcx_workspace_bytes(int m, int n, int k);     // fp32 partial tiles of the prefill kernel's split last wave
-bool tcx64_supported(const QGemmArgs& a);             // 64-row tiles of the tensor-memory-A prefill kernel, cut along K
-size_t tcx64_workspace_bytes(int n, int k);
-int launch_tcx64(cudaStream_t st, const QGemmArgs& a);
+bool tcx_rows_supported(const QGemmArgs& a);          // up to 192 rows: one row of tiles of the tensor-memory-A prefill kernel, cut along K
+size_t tcx_rows_workspace_bytes(int m, int n, int k);
+int launch_tcx_rows(cudaStream_t st, const QGemmArgs& a);
 bool tc_tmem_a_preferred(int m, int n, int bits);   // 65..128 rows: the tensor-memory-A prefill tile beats the mid-batch kernel
 
 }  // namespace mt

@@ -913,32 +913,37 @@ static int launch_tcx(cudaStream_t st, const QGemmArgs& a, EncodeTiledFn enc, co
     return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_CUDA;
 }
 
-// 64-row tiles of the tensor-memory-A kernel for mid-size batches: every tile is cut into `split` parts along K so that
-// the parts fill the GPU's waves (few, deep tiles otherwise: 224 tiles of 128 k-blocks on 8192 x 57344).
-static int tcx64_split(int n, int k, int sms) {
+// Batches that fit ONE row of tiles of the tensor-memory-A kernel (up to 192 rows; tiles of 64, 160 or 192 rows): every
+// tile is cut into `split` parts along K so that the parts fill the GPU's waves (few, deep tiles otherwise: 224 tiles of
+// 128 k-blocks on 8192 x 57344, 32 tiles of 448 on 28672 x 8192).
+static int tcx_rows_bm(int m) { return m <= 64 ? 64 : (m <= 160 ? 160 : 192); }
+static int tcx_rows_split(int m, int n, int k, int sms) {
     const int tiles = (n + 255) / 256;
     const int kblocks = (k + TC_BK - 1) / TC_BK;
+    // time in k-blocks: waves x (k-blocks of a part + the part's fp32 partial tile, written and read back: 2 x bm x 128 x 4
+    // bytes per 128-column half, about bm / 16 k-blocks' worth at an SM's share of the memory bandwidth)
+    const double partial = tcx_rows_bm(m) / 16.0;
     int best = 1; double best_cost = 1e30;
     for (int s : {1, 2, 3, 4, 6, 8}) {
         if (s > 1 && kblocks < 16 * s) break;
         const double waves = double((tiles * s + sms - 1) / sms);
-        const double cost = waves / s + 0.03 * s;            // a part pays for its partial tile
+        const double cost = waves * (double(kblocks) / s + (s > 1 ? partial : 0.0));
         if (cost < best_cost) { best_cost = cost; best = s; }
     }
     return best;
 }
-bool tcx64_supported(const QGemmArgs& a) {
-    if (!tc_supported(a) || a.bits != 4 || a.m < 1 || a.m > 64 || a.n < 256) return false;
+size_t tcx_rows_workspace_bytes(int m, int n, int k) {
+    const int s = tcx_rows_split(m, n, k, 148);
+    return s > 1 ? (size_t)((n + 255) / 256) * s * 2 * tcx_rows_bm(m) * 128 * 4 : 0;
+}
+bool tcx_rows_supported(const QGemmArgs& a) {
+    if (!tc_supported(a) || a.bits != 4 || a.m < 1 || a.m > 192 || a.n < 256) return false;
     if (((a.n + 255) / 256) * 8 > kMaxTiles - 8) return false;
-    return a.workspace != nullptr && a.workspace_bytes >= kCounterBytes + tcx64_workspace_bytes(a.n, a.k);
+    return a.workspace != nullptr && a.workspace_bytes >= kCounterBytes + tcx_rows_workspace_bytes(a.m, a.n, a.k);
 }
-size_t tcx64_workspace_bytes(int n, int k) {
-    const int s = tcx64_split(n, k, 148);
-    return s > 1 ? (size_t)((n + 255) / 256) * s * 2 * 64 * 128 * 4 : 0;
-}
-int launch_tcx64(cudaStream_t st, const QGemmArgs& a) {
+int launch_tcx_rows(cudaStream_t st, const QGemmArgs& a) {
     EncodeTiledFn enc = get_tensor_map_encoder();
-    if (!enc || !tcx64_supported(a)) return MT_ERR_UNSUPPORTED;
+    if (!enc || !tcx_rows_supported(a)) return MT_ERR_UNSUPPORTED;
     CUtensorMap mq;
     {
         cuuint64_t dims[2] = {(cuuint64_t)a.n, (cuuint64_t)(a.k / 8)};
@@ -958,15 +963,18 @@ int launch_tcx64(cudaStream_t st, const QGemmArgs& a) {
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int split = tcx64_split(a.n, a.k, sms);
+    int split = tcx_rows_split(a.m, a.n, a.k, sms);
     if (((a.flags >> 16) & 0xff) != 0) split = (a.flags >> 16) & 0xff;      // tuning: MT_FLAG_SPLITS forces the parts per tile
-    return launch_tcx(st, a, enc, mq, p, 64, split);
+    return launch_tcx(st, a, enc, mq, p, tcx_rows_bm(a.m), split);
 }
 
 int launch_tc(cudaStream_t st, const QGemmArgs& a) {
     EncodeTiledFn enc = get_tensor_map_encoder();
     if (!enc) return MT_ERR_UNSUPPORTED;
-    if ((a.flags & MT_FLAG_TC_TMEM_A) && a.m <= 64) return launch_tcx64(st, a);
+    // one row of tiles of the tensor-memory-A kernel, cut along K: up to 64 rows by flag only (mt_qgemm sends 33..64 rows here
+    // itself), from 65 to 192 rows whenever the request fits
+    if (a.m <= 64 && (a.flags & MT_FLAG_TC_TMEM_A)) return launch_tcx_rows(st, a);
+    if (a.m > 64 && a.m <= 192 && !(a.flags & MT_FLAG_TC_SMEM_A) && tcx_rows_supported(a)) return launch_tcx_rows(st, a);
     const int pack = 32 / a.bits;
     const int bm = a.m > 128 ? 256 : (a.m > 64 ? 128 : 64);
     CUtensorMap mx, mq;
@@ -1003,7 +1011,9 @@ int launch_tc(cudaStream_t st, const QGemmArgs& a) {
     // From 65 to 128 rows only the first has a tile that fits (the 256 x 256 one would be half empty), and it pays when
     // its single row of tiles nearly fills the GPU (tc_tmem_a_preferred): 8192 x 57344 at 128 rows 196 us against 336 us
     // for the mid-batch kernel, but 28672 x 8192 (32 tiles) 309 us against 218 us.
-    const int xbm = ((a.flags >> 28) & 1) ? 192 : 160;             // row tile of the tensor-memory-A kernel (bit 28 of the flags: tuning)
+    // row tile of the tensor-memory-A kernel: 192 rows (two A slots) measured 1099 / 1113 / 1099 TFLOP/s on the three 4096-row
+    // shapes, 160 rows (three slots) 1044 / 1106 / 993 on the same GPU; bit 28 of the flags selects the latter (tuning)
+    const int xbm = ((a.flags >> 28) & 1) ? 160 : 192;
     bool tmem_a = (a.flags & MT_FLAG_TC_TMEM_A) != 0 || (wide && a.m <= 128 && tc_tmem_a_preferred(a.m, a.n, a.bits));
     if (wide && a.m > 128 && !tmem_a && !(a.flags & MT_FLAG_TC_SMEM_A)) {
         int dev = 0, sms = 148;

@@ -146,3 +146,13 @@ def test_tensor_memory_operand_variant_with_64_row_tiles(M, k, n, m, dtype):
     torch.cuda.synchronize()
     for ws in _lib._workspaces.values():
         assert int(ws[:_lib.COUNTER_BYTES].view(torch.int32).abs().sum().item()) == 0
+
+
+@pytest.mark.parametrize("k,n", [(2048, 1024), (8192, 512), (1024, 4352)])
+@pytest.mark.parametrize("m", [33, 64, 65, 100, 160, 161, 192])
+def test_default_dispatch_33_to_192_rows(M, k, n, m):
+    """mt_qgemm with no flags: 33 to 192 rows on int4 weights with contiguous groups go to one row of tiles (64, 160 or 192
+    rows) of the tensor-memory-A kernel, every tile cut along K where that fills the GPU better."""
+    c = O.make_gptq_case(k, n, m, bits=4, seed=k + n + m + 9, bias=True)
+    out = run(M, c, 4, bias=c["bias"], flags=0)
+    assert_close(out, oracle_out(c, False, c["bias"]), f"default dispatch {k}x{n} M={m}")
