@@ -229,7 +229,7 @@ int mt_swiglu(void* stream, const void* gate_up, void* out, int m, int n, int dt
  *   rotated by (cos, sin)[position, i] in fp32 (minit/cuda/kernel/cuda/rope.py:58-73; tables fp32
  *   [table_rows, d/2]); q goes to q_out[m, hq, d], k and v to k_cache / v_cache[capacity, hkv, d] at row
  *   offset + token.  This replaces rope + F.tie of examples/llama3_70b.py:97-102: the cache is preallocated
- *   and holds every kv head once (the reference stores it nr_groups times, :85-94).  d == 128.
+ *   and holds every kv head once (the reference stores it nr_groups times, :85-94).  Any even d.
  *   offset_dev (device int32, may be NULL) overrides `offset` so that a captured graph can be replayed as
  *   the sequence grows; rows beyond capacity are not written.
  *
@@ -254,6 +254,17 @@ int mt_qgemm_rope_append(void* stream, const void* x, const uint32_t* qweight, c
                          int m, int hq, int hkv, int d, int k, int nr_groups, int bits, int dtype,
                          int offset, const int32_t* offset_dev, int capacity, int table_rows,
                          void* workspace, size_t workspace_bytes, int flags);
+/*
+ * mt_attention: the same attention for prefill-sized and multi-sequence batches and for any head size that is a multiple
+ *   of 32 up to 256 (examples/llama3_70b.py:103-115: all (query, key) scores, the causal mask shifted by the cached
+ *   positions, softmax over the keys, weighted sum of the values; minit/cuda/kernel/cuda/softmax.py:55-114).
+ *   q[batch, m, hq, d] (rotated), k_cache / v_cache[batch, capacity, hkv, d] holding positions 0 .. offset_b + m - 1 of every
+ *   sequence, out[batch, m, hq * d]; query i of sequence b sits at position offset_b + i and sees keys 0 .. offset_b + i.
+ *   offsets_dev (device int32 [batch], may be NULL) gives every sequence its own offset_b, else `offset` holds for all.
+ *   fp32 throughout, one rounding.  mt_rope_append (any even d) fills the cache of one sequence at a time.
+ */
+int mt_attention(void* stream, const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* offsets_dev,
+                 int batch, int m, int hq, int hkv, int d, int offset, int capacity, float scale, int dtype);
 size_t mt_attention_workspace_bytes(int m, int hkv, int max_len);
 int mt_attention_decode(void* stream, const void* q, const void* k_cache, const void* v_cache, void* out, int m, int hq, int hkv, int d,
                         int offset, const int32_t* offset_dev, int max_len, float scale, void* workspace, size_t workspace_bytes, int dtype);

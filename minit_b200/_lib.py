@@ -60,6 +60,7 @@ SYMBOLS = {
     "mt_rms_norm": (_i, [_vp, _vp, _vp, _vp, _i, _i, ctypes.c_float, _i]),
     "mt_rope_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _i, _i]),
     "mt_qgemm_rope_append": (_i, [_vp] * 12 + [_i] * 8 + [_i, _vp, _i, _i, _vp, _sz, _i]),
+    "mt_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, ctypes.c_float, _i]),
     "mt_attention_workspace_bytes": (_sz, [_i, _i, _i]),
     "mt_attention_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, ctypes.c_float, _vp, _sz, _i]),
     "mt_decode_plan": (_i, [_i, _i, _i, _i, _i, _sz, _i]),

@@ -489,14 +489,28 @@ int mt_rope_append(void* stream, const void* qkv, const float* cos_table, const 
                    int m, int hq, int hkv, int d, int offset, const int32_t* offset_dev, int capacity, int table_rows, int dtype) {
     if (dtype != MT_F16 && dtype != MT_BF16) return MT_ERR_DTYPE;
     if (m < 0 || hq < 1 || hkv < 1 || offset < 0 || capacity < 1 || table_rows < 1) return MT_ERR_SHAPE;
-    if (d != 128) return MT_ERR_UNSUPPORTED;
+    if (d < 2 || d % 2 != 0 || d > 1024) return MT_ERR_UNSUPPORTED;
     if (!offset_dev && (offset + m > capacity || offset + m > table_rows)) return MT_ERR_SHAPE;
     if (m == 0) return MT_OK;
     if (!qkv || !cos_table || !sin_table || !q_out || !k_cache || !v_cache) return MT_ERR_NULL;
     int rc = check_device();
     if (rc != MT_OK) return rc;
-    return launch_rope_append(static_cast<cudaStream_t>(stream), qkv, cos_table, sin_table, q_out, k_cache, v_cache, m, hq, hkv, offset,
+    return launch_rope_append(static_cast<cudaStream_t>(stream), qkv, cos_table, sin_table, q_out, k_cache, v_cache, m, hq, hkv, d, offset,
                               offset_dev, capacity, table_rows, dtype);
+}
+
+int mt_attention(void* stream, const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* offsets_dev,
+                 int batch, int m, int hq, int hkv, int d, int offset, int capacity, float scale, int dtype) {
+    if (dtype != MT_F16 && dtype != MT_BF16) return MT_ERR_DTYPE;
+    if (batch < 0 || m < 0 || hq < 1 || hkv < 1 || offset < 0 || capacity < 1) return MT_ERR_SHAPE;
+    if (!offsets_dev && offset + m > capacity) return MT_ERR_SHAPE;
+    if (batch == 0 || m == 0) return MT_OK;
+    if (!q || !k_cache || !v_cache || !out) return MT_ERR_NULL;
+    if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out)) return MT_ERR_ALIGN;
+    int rc = check_device();
+    if (rc != MT_OK) return rc;
+    return launch_attention_rows(static_cast<cudaStream_t>(stream), q, k_cache, v_cache, out, offsets_dev, batch, m, hq, hkv, d, offset,
+                                 capacity, scale, dtype);
 }
 
 int mt_qgemm_rope_append(void* stream, const void* x, const uint32_t* qweight, const uint32_t* qzeros, const void* scales, const void* bias,
@@ -505,7 +519,7 @@ int mt_qgemm_rope_append(void* stream, const void* x, const uint32_t* qweight, c
                          int offset, const int32_t* offset_dev, int capacity, int table_rows,
                          void* workspace, size_t workspace_bytes, int flags) {
     if (hq < 1 || hkv < 1 || offset < 0 || capacity < 1 || table_rows < 1) return MT_ERR_SHAPE;
-    if (d != 128) return MT_ERR_UNSUPPORTED;
+    if (d < 2 || d % 2 != 0 || d > 1024) return MT_ERR_UNSUPPORTED;
     const int n = (hq + 2 * hkv) * d;
     int rc = validate_gptq(qweight, qzeros, scales, n, k, nr_groups, bits, dtype);
     if (rc != MT_OK) return rc;
@@ -523,7 +537,7 @@ int mt_qgemm_rope_append(void* stream, const void* x, const uint32_t* qweight, c
     a.m = m; a.n = n; a.k = k; a.groups = nr_groups; a.bits = bits; a.dtype = dtype;
     a.workspace = workspace; a.workspace_bytes = workspace_bytes; a.flags = flags;
     const bool forced_other = (flags & (MT_FLAG_FORCE_SMALL | MT_FLAG_FORCE_TC | MT_FLAG_FORCE_UMMA)) != 0;
-    if (m <= 2 && !forced_other && vec_supported(a)) {
+    if (m <= 2 && d == 128 && !forced_other && vec_supported(a)) {       // the GEMV's rotary epilogue is written for 128-wide heads
         RopeArgs r;
         r.cosv = cos_table; r.sinv = sin_table; r.q_out = q_out; r.k_cache = k_cache; r.v_cache = v_cache; r.offset_dev = offset_dev;
         r.hq = hq; r.hkv = hkv; r.offset = offset; r.capacity = capacity; r.table_rows = table_rows;
@@ -533,7 +547,7 @@ int mt_qgemm_rope_append(void* stream, const void* x, const uint32_t* qweight, c
     if (!scratch) return MT_ERR_NULL;
     if (!aligned16(scratch)) return MT_ERR_ALIGN;
     rc = mt_qgemm(stream, x, qweight, nullptr, qzeros, scales, bias, scratch, m, n, k, nr_groups, bits, dtype, workspace, workspace_bytes, flags);
-    if (rc == MT_OK) rc = launch_rope_append(st, scratch, cos_table, sin_table, q_out, k_cache, v_cache, m, hq, hkv, offset, offset_dev, capacity, table_rows, dtype);
+    if (rc == MT_OK) rc = launch_rope_append(st, scratch, cos_table, sin_table, q_out, k_cache, v_cache, m, hq, hkv, d, offset, offset_dev, capacity, table_rows, dtype);
     return rc;
 }
 

@@ -198,7 +198,9 @@ int launch_swiglu_interleaved(cudaStream_t st, const void* in, void* out, int m,
 int launch_add_residual(cudaStream_t st, void* io, const void* res, int m, int n, int dtype);        // io += res
 int launch_rms_norm(cudaStream_t st, const void* x, const void* w, void* out, int rows, int h, float eps, int dtype);
 int launch_rope_append(cudaStream_t st, const void* qkv, const float* cosv, const float* sinv, void* q_out, void* k_cache, void* v_cache,
-                       int m, int hq, int hkv, int offset, const int* offset_dev, int capacity, int table_rows, int dtype);
+                       int m, int hq, int hkv, int d, int offset, const int* offset_dev, int capacity, int table_rows, int dtype);
+int launch_attention_rows(cudaStream_t st, const void* q, const void* k_cache, const void* v_cache, void* out, const int* offsets,
+                          int batch, int m, int hq, int hkv, int d, int offset, int capacity, float scale, int dtype);
 size_t attention_workspace_bytes(int m, int hkv, int max_len);
 int launch_attention_decode(cudaStream_t st, const void* q, const void* k_cache, const void* v_cache, void* out,
                             int m, int hq, int hkv, int d, int offset, const int* offset_dev, int max_len, float scale,

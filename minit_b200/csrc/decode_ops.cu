@@ -107,9 +107,8 @@ __global__ void __launch_bounds__(1024) rms_norm_kernel(const uint4* __restrict_
 template <typename T>
 __global__ void rope_append_kernel(const uint32_t* __restrict__ qkv, const float* __restrict__ cosv, const float* __restrict__ sinv,
                                    uint32_t* __restrict__ q_out, uint32_t* __restrict__ k_cache, uint32_t* __restrict__ v_cache,
-                                   int m, int hq, int hkv, int offset, const int* __restrict__ offset_dev, int capacity, int table_rows) {
+                                   int m, int hq, int hkv, int offset, const int* __restrict__ offset_dev, int capacity, int table_rows, int HALF) {
     using H = F16x2<T>;
-    constexpr int HALF = ATT_D / 2;
     const int heads = hq + 2 * hkv;
     const long long total = (long long)m * heads * HALF;
     griddep_launch_dependents();
@@ -440,17 +439,17 @@ int launch_rms_norm(cudaStream_t st, const void* x, const void* w, void* out, in
 }
 
 int launch_rope_append(cudaStream_t st, const void* qkv, const float* cosv, const float* sinv, void* q_out, void* k_cache, void* v_cache,
-                       int m, int hq, int hkv, int offset, const int* offset_dev, int capacity, int table_rows, int dtype) {
-    const long long total = (long long)m * (hq + 2 * hkv) * (ATT_D / 2);
+                       int m, int hq, int hkv, int d, int offset, const int* offset_dev, int capacity, int table_rows, int dtype) {
+    const long long total = (long long)m * (hq + 2 * hkv) * (d / 2);
     long long blocks = (total + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
     if (dtype == MT_F16)
         return launch_plain(rope_append_kernel<__half>, dim3((unsigned)blocks), dim3(256), st, static_cast<const uint32_t*>(qkv), cosv, sinv,
                           static_cast<uint32_t*>(q_out), static_cast<uint32_t*>(k_cache), static_cast<uint32_t*>(v_cache), m, hq, hkv, offset,
-                          offset_dev, capacity, table_rows);
+                          offset_dev, capacity, table_rows, d / 2);
     return launch_plain(rope_append_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), st, static_cast<const uint32_t*>(qkv), cosv, sinv,
                       static_cast<uint32_t*>(q_out), static_cast<uint32_t*>(k_cache), static_cast<uint32_t*>(v_cache), m, hq, hkv, offset,
-                      offset_dev, capacity, table_rows);
+                      offset_dev, capacity, table_rows, d / 2);
 }
 
 size_t attention_workspace_bytes(int m, int hkv, int max_len) {
@@ -499,6 +498,136 @@ int launch_attention_decode(cudaStream_t st, const void* q, const void* k_cache,
     const dim3 grid(p.splits, hkv, m);
     if (dtype == MT_F16) return warps == 8 ? launch_attention_inst<__half, 8>(st, p, grid) : launch_attention_inst<__half, 4>(st, p, grid);
     return warps == 8 ? launch_attention_inst<__nv_bfloat16, 8>(st, p, grid) : launch_attention_inst<__nv_bfloat16, 4>(st, p, grid);
+}
+
+// ----------------------------------------------------------------------------------------------
+// Attention for prefill-sized and multi-sequence batches, any head size that is a multiple of 32 up to 256:
+//   out[b, i, n, :] = softmax_t(q[b, i, n, :] . k[b, t, n / group, :] * scale, t <= offset_b + i) @ v[b, :, n / group, :]
+// (examples/llama3_70b.py:103-115: scores for every (query, key) pair, -inf above the diagonal shifted by the cached
+// positions, softmax over the keys, weighted sum of the values).  One warp per (sequence, head, four query positions): a
+// lane scores one key of a block of 32 against the four scaled query rows in shared memory (whole dot products), each
+// row's block maximum and sum update its running softmax, then every lane adds its d / 32 output values of the 32
+// weighted value rows to the four rows; a key or value row is read once for the four.  fp32
+// throughout, one rounding at the end (the reference rounds scores, scaled scores, probabilities and output separately).
+// ----------------------------------------------------------------------------------------------
+struct AttRowsParams {
+    const void* q; const void* k_cache; const void* v_cache; void* out;
+    const int* offsets;         // [batch] cached positions before the first new token of each sequence, or null: `offset` for all
+    int batch, m, hq, hkv, d, offset, capacity;
+    float scale;
+};
+
+constexpr int ATR_WARPS = 4;
+constexpr int ATR_ROWS = 4;     // consecutive query positions per warp: every key and value row is read once for the four
+constexpr int ATR_MAXE = 8;     // d / 32 <= 8
+
+template <typename T>
+__global__ void __launch_bounds__(ATR_WARPS * 32) attention_rows_kernel(const AttRowsParams p) {
+    using H = F16x2<T>;
+    __shared__ float qs[ATR_WARPS][ATR_ROWS][256];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int i0 = (blockIdx.x * ATR_WARPS + warp) * ATR_ROWS;      // first query position of this warp
+    const int n = blockIdx.y, b = blockIdx.z;
+    if (i0 >= p.m) return;                                // whole warps leave together: no block-wide barrier below
+    const int d = p.d, E = d >> 5;
+    const int kvh = n / (p.hq / p.hkv);
+    const int off = p.offsets ? p.offsets[b] : p.offset;
+    const int rows = min(ATR_ROWS, p.m - i0);
+    int nk[ATR_ROWS];                                     // the causal mask: row r sees keys 0 .. off + i0 + r
+#pragma unroll
+    for (int r = 0; r < ATR_ROWS; ++r) nk[r] = r < rows ? min(off + i0 + r + 1, p.capacity) : 0;
+    const int nkeys = nk[rows - 1];
+#pragma unroll
+    for (int r = 0; r < ATR_ROWS; ++r) {
+        const uint16_t* q = reinterpret_cast<const uint16_t*>(p.q) + (((size_t)b * p.m + min(i0 + r, p.m - 1)) * p.hq + n) * d;
+        for (int e = lane; e < d; e += 32) qs[warp][r][e] = H::to_float(q[e]) * p.scale;
+    }
+    __syncwarp();
+    const size_t row = (size_t)p.hkv * d;                 // elements between cache positions
+    const uint16_t* kb = reinterpret_cast<const uint16_t*>(p.k_cache) + ((size_t)b * p.capacity * p.hkv + kvh) * d;
+    const uint16_t* vb = reinterpret_cast<const uint16_t*>(p.v_cache) + ((size_t)b * p.capacity * p.hkv + kvh) * d;
+    float acc[ATR_ROWS][ATR_MAXE];
+    float mx[ATR_ROWS], l[ATR_ROWS];
+#pragma unroll
+    for (int r = 0; r < ATR_ROWS; ++r) {
+        mx[r] = -INFINITY; l[r] = 0.f;
+#pragma unroll
+        for (int e = 0; e < ATR_MAXE; ++e) acc[r][e] = 0.f;
+    }
+    for (int t0 = 0; t0 < nkeys; t0 += 32) {
+        const int t = t0 + lane;
+        float dot[ATR_ROWS];
+#pragma unroll
+        for (int r = 0; r < ATR_ROWS; ++r) dot[r] = 0.f;
+        if (t < nkeys) {
+            const uint4* kr = reinterpret_cast<const uint4*>(kb + (size_t)t * row);
+            for (int c = 0; c < d / 8; ++c) {
+                const uint4 kv = __ldg(kr + c);
+                const uint32_t w[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float k0 = H::to_float(uint16_t(w[j] & 0xffff)), k1 = H::to_float(uint16_t(w[j] >> 16));
+#pragma unroll
+                    for (int r = 0; r < ATR_ROWS; ++r) dot[r] = fmaf(qs[warp][r][c * 8 + 2 * j + 1], k1, fmaf(qs[warp][r][c * 8 + 2 * j], k0, dot[r]));
+                }
+            }
+        }
+        float pr[ATR_ROWS];
+#pragma unroll
+        for (int r = 0; r < ATR_ROWS; ++r) {
+            const float sc = t < nk[r] ? dot[r] : -INFINITY;
+            float bm = sc;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+            const float mnew = fmaxf(mx[r], bm);
+            // a row whose keys all lie before this block (or a padding row) keeps -inf here: no change, no NaN
+            const float corr = mnew == -INFINITY ? 1.f : __expf(mx[r] - mnew);
+            pr[r] = t < nk[r] ? __expf(sc - mnew) : 0.f;
+            float ps = pr[r];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+            l[r] = l[r] * corr + ps;
+#pragma unroll
+            for (int e = 0; e < ATR_MAXE; ++e) acc[r][e] *= corr;
+            mx[r] = mnew;
+        }
+        const int cnt = min(32, nkeys - t0);
+        for (int j = 0; j < cnt; ++j) {
+            const uint16_t* vr = vb + (size_t)(t0 + j) * row + lane * E;
+            float vv[ATR_MAXE];
+#pragma unroll
+            for (int e = 0; e < ATR_MAXE; ++e) vv[e] = e < E ? H::to_float(vr[e]) : 0.f;
+#pragma unroll
+            for (int r = 0; r < ATR_ROWS; ++r) {
+                const float pj = __shfl_sync(0xffffffffu, pr[r], j);
+#pragma unroll
+                for (int e = 0; e < ATR_MAXE; ++e) acc[r][e] = fmaf(pj, vv[e], acc[r][e]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < ATR_ROWS; ++r) {
+        if (r < rows) {
+            uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + (((size_t)b * p.m + i0 + r) * p.hq + n) * d + lane * E;
+            const float inv = 1.f / l[r];
+#pragma unroll
+            for (int e = 0; e < ATR_MAXE; ++e)
+                if (e < E) o[e] = H::from_float(acc[r][e] * inv);
+        }
+    }
+}
+
+int launch_attention_rows(cudaStream_t st, const void* q, const void* k_cache, const void* v_cache, void* out, const int* offsets,
+                          int batch, int m, int hq, int hkv, int d, int offset, int capacity, float scale, int dtype) {
+    if (d % 32 != 0 || d < 32 || d > 256 || hkv < 1 || hq % hkv != 0) return MT_ERR_UNSUPPORTED;
+    if (batch > 65535 || hq > 65535) return MT_ERR_TOO_LARGE;
+    AttRowsParams p;
+    p.q = q; p.k_cache = k_cache; p.v_cache = v_cache; p.out = out; p.offsets = offsets;
+    p.batch = batch; p.m = m; p.hq = hq; p.hkv = hkv; p.d = d; p.offset = offset; p.capacity = capacity; p.scale = scale;
+    const dim3 grid((m + ATR_WARPS * ATR_ROWS - 1) / (ATR_WARPS * ATR_ROWS), hq, batch);
+    if (dtype == MT_F16) attention_rows_kernel<__half><<<grid, ATR_WARPS * 32, 0, st>>>(p);
+    else attention_rows_kernel<__nv_bfloat16><<<grid, ATR_WARPS * 32, 0, st>>>(p);
+    return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_CUDA;
 }
 
 }  // namespace mt

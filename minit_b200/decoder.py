@@ -84,7 +84,7 @@ def qkv_rope_append(x: torch.Tensor, qweight: torch.Tensor, zeros: Optional[torc
     if qweight.shape != (k0 // pack, n0) or scales.shape[1] != n0 or scales.dtype != x.dtype or cos.dtype != torch.float32:
         raise ValueError("shape or dtype mismatch between x, qweight, scales and the tables")
     q = torch.empty((m, nr_querys, d), dtype=x.dtype, device=dev)
-    scratch = torch.empty((m, n0), dtype=x.dtype, device=dev) if (m > 2 or (k0 // scales.shape[0]) % 32) else None
+    scratch = torch.empty((m, n0), dtype=x.dtype, device=dev) if (m > 2 or d != 128 or (k0 // scales.shape[0]) % 32) else None
     stream = _lib.current_stream(dev)
     ws = _lib.workspace(dev, stream, _lib.lib.mt_workspace_bytes(m, n0, k0, bits))
     with torch.cuda.device(dev):
@@ -120,6 +120,33 @@ def attention_decode(q: torch.Tensor, cache: KVCache, offset: int, offset_dev: O
                                           cache.kv_heads, d, offset, _lib.ptr(offset_dev), max_len, 1.0 / math.sqrt(d),
                                           ws.data_ptr(), ws.numel(), _lib.dtype_code(q.dtype))
     _lib.check(rc, "mt_attention_decode")
+    return out
+
+
+def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, offset: int = 0,
+              offsets: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """softmax(q k^T / sqrt(d) + causal mask) v for batches of sequences and prefill-sized inputs
+    (examples/llama3_70b.py:103-115): q [B, M, hq, d] (rotated), k_cache / v_cache [B, capacity, hkv, d] with the M new
+    tokens of every sequence already appended at rows offset_b .. offset_b + M - 1; returns [B, M, hq * d].  ``offsets``
+    (int32 [B] on the device) gives every sequence its own number of cached positions, else ``offset`` holds for all.
+    Any head size that is a multiple of 32 up to 256."""
+    dev = _lib.require_cuda(q, k_cache, v_cache, offsets)
+    if q.dim() != 4 or k_cache.dim() != 4 or k_cache.shape != v_cache.shape:
+        raise ValueError("q must be [B, M, hq, d] and the caches [B, capacity, hkv, d]")
+    b, m, hq, d = q.shape
+    b2, capacity, hkv, d2 = k_cache.shape
+    if b2 != b or d2 != d or hq % hkv != 0 or q.dtype != k_cache.dtype or q.dtype != v_cache.dtype:
+        raise ValueError("q and the caches disagree on batch, head size, head grouping or dtype")
+    if not (q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise ValueError("q and the caches must be contiguous")
+    if offsets is not None and (offsets.dtype != torch.int32 or tuple(offsets.shape) != (b,)):
+        raise ValueError("offsets must be int32 [B]")
+    if out is None:
+        out = torch.empty((b, m, hq * d), dtype=q.dtype, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib.mt_attention(_lib.current_stream(dev), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                                   _lib.ptr(offsets), b, m, hq, hkv, d, offset, capacity, 1.0 / math.sqrt(d), _lib.dtype_code(q.dtype))
+    _lib.check(rc, "mt_attention")
     return out
 
 
@@ -173,8 +200,12 @@ class QAttention(Module):
             self._qkv = fuse_columns((self.q_proj, self.k_proj, self.v_proj))
         qw, qz, sc, bi = self._qkv
         q = qkv_rope_append(x, qw, qz, sc, cos, sin, cache, self.nr_querys, offset, bits=self.bits, bias=bi)
-        a = attention_decode(q, cache, offset)
-        cache.length = max(cache.length, offset + x.shape[0])
+        m = x.shape[0]
+        if self.head_size == 128 and self.nr_querys // self.nr_kv <= 8 and m <= 16:
+            a = attention_decode(q, cache, offset)                 # split over the cached positions: the decode kernel
+        else:                                                      # prefill-sized inputs and other head sizes: one warp per query row
+            a = attention(q.unsqueeze(0), cache.k.unsqueeze(0), cache.v.unsqueeze(0), offset).view(m, -1)
+        cache.length = max(cache.length, offset + m)
         o = self.o_proj
         if residual is None:
             return o._matmul(a, None)

@@ -43,9 +43,9 @@ def test_rms_norm(D, dtype, rows, h):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("m,hq,hkv,offset", [(1, 64, 8, 0), (1, 64, 8, 777), (5, 32, 8, 19), (3, 8, 8, 1000), (2, 4, 1, 7)])
-def test_rope_append(D, dtype, m, hq, hkv, offset):
-    d = 128
+@pytest.mark.parametrize("m,hq,hkv,offset,d", [(1, 64, 8, 0, 128), (1, 64, 8, 777, 128), (5, 32, 8, 19, 128), (3, 8, 8, 1000, 128), (2, 4, 1, 7, 128),
+                                               (4, 8, 2, 11, 64), (2, 6, 3, 300, 96), (40, 4, 4, 0, 256)])
+def test_rope_append(D, dtype, m, hq, hkv, offset, d):
     gen = torch.Generator().manual_seed(m + hq + offset)
     qkv = torch.randn((m, (hq + 2 * hkv) * d), generator=gen).to(dtype)
     cos, sin = O.rope_tables(d, 1024, 5e5, dtype)
@@ -159,7 +159,51 @@ def load_layer(D, layer, cases, norms):
     layer.update_buffer("post_attention_layernorm.weight", norms[1].to(DEV))
 
 
-@pytest.mark.parametrize("m,offset", [(1, 0), (1, 200), (3, 64)])
+@pytest.mark.parametrize("b,m,hq,hkv,d,offset", [(1, 64, 8, 2, 128, 0), (2, 33, 8, 8, 64, 5), (3, 7, 12, 4, 96, 100), (1, 300, 4, 1, 256, 0),
+                                                 (2, 1, 24, 2, 128, 57), (1, 130, 8, 8, 32, 3), (2, 40, 16, 2, 160, 31)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_attention_for_prefill_sized_and_multi_sequence_batches(D, dtype, b, m, hq, hkv, d, offset):
+    """examples/llama3_70b.py:103-115 for several sequences, many new tokens, head sizes other than 128 and more than eight
+    query heads per kv head: against an fp64 evaluation (tight) and the stepwise oracle (the north-star bound)."""
+    gen = torch.Generator().manual_seed(b + m + hq + d + offset)
+    total = offset + m
+    cap = total + 5
+    q = torch.randn((b, m, hq, d), generator=gen).to(dtype)
+    k = torch.full((b, cap, hkv, d), float("nan"), dtype=dtype)                      # rows past the sequence are never read
+    v = torch.full((b, cap, hkv, d), float("nan"), dtype=dtype)
+    k[:, :total] = torch.randn((b, total, hkv, d), generator=gen).to(dtype)
+    v[:, :total] = torch.randn((b, total, hkv, d), generator=gen).to(dtype)
+    out = D.attention(q.to(DEV), k.to(DEV), v.to(DEV), offset).cpu()
+    assert out.shape == (b, m, hq * d) and not torch.isnan(out).any()
+    for s_ in range(b):
+        exact = attention_fp32(q[s_], k[s_, :total], v[s_, :total], offset)
+        err = (out[s_].double() - exact).abs()
+        assert (err <= 2e-3 * exact.abs().max() + ulp_of(exact.float(), dtype).double()).all(), f"seq {s_}: max err {err.max().item():.4g}"
+        step = O.attention(q[s_], k[s_, :total], v[s_, :total], offset)
+        if dtype == torch.float16:
+            assert_close(out[s_], step, f"attention vs stepwise oracle b={b} m={m} d={d}")
+        else:
+            dev_step = (step.double() - exact).abs().max().item()
+            assert err.max().item() <= dev_step + 1e-6
+
+
+def test_attention_with_one_offset_per_sequence(D):
+    """A ragged batch: every sequence has its own number of cached positions (device array)."""
+    dtype, b, m, hq, hkv, d = torch.float16, 3, 5, 8, 2, 64
+    offs = [0, 17, 40]
+    gen = torch.Generator().manual_seed(77)
+    cap = max(offs) + m + 3
+    q = torch.randn((b, m, hq, d), generator=gen).to(dtype)
+    k = torch.randn((b, cap, hkv, d), generator=gen).to(dtype)
+    v = torch.randn((b, cap, hkv, d), generator=gen).to(dtype)
+    out = D.attention(q.to(DEV), k.to(DEV), v.to(DEV), offsets=torch.tensor(offs, dtype=torch.int32, device=DEV)).cpu()
+    for s_, off in enumerate(offs):
+        exact = attention_fp32(q[s_], k[s_, :off + m], v[s_, :off + m], off)
+        err = (out[s_].double() - exact).abs()
+        assert (err <= 2e-3 * exact.abs().max() + ulp_of(exact.float(), dtype).double()).all()
+
+
+@pytest.mark.parametrize("m,offset", [(1, 0), (1, 200), (3, 64), (40, 0), (24, 10)])
 def test_decoder_layer_matches_the_reference_composition(D, m, offset):
     """TransformerBlock.forward of the reference (examples/llama3_70b.py:158-162) restated with the oracle, against
     QDecoderLayer: RMSNorm -> q/k/v -> rope -> cache -> attention -> o_proj + x -> RMSNorm -> feed-forward + h."""
@@ -206,10 +250,14 @@ def test_status_codes(D):
     p = z.data_ptr()
     assert lib.mt_rms_norm(None, p, p, p, 1, 12, 1e-5, 0) == -3                     # H % 8
     assert lib.mt_rms_norm(None, p, p, p, 1, 16, 0.0, 0) == -3                      # eps
-    assert lib.mt_rope_append(None, p, p, p, p, p, p, 1, 8, 2, 64, 0, None, 16, 16, 0) == -8      # head size
+    assert lib.mt_rope_append(None, p, p, p, p, p, p, 1, 8, 2, 63, 0, None, 16, 16, 0) == -8      # odd head size
+    assert lib.mt_attention(None, p, p, p, p, None, 1, 1, 8, 2, 80, 0, 8, 0.1, 0) == -8           # head size not a multiple of 32
+    assert lib.mt_attention(None, p, p, p, p, None, 1, 4, 8, 3, 64, 0, 8, 0.1, 0) == -8           # 8 query heads over 3 kv heads
+    assert lib.mt_attention(None, p, p, p, p, None, 1, 4, 8, 2, 64, 6, 8, 0.1, 0) == -3           # beyond the capacity
     assert lib.mt_rope_append(None, p, p, p, p, p, p, 4, 8, 2, 128, 14, None, 16, 64, 0) == -3    # beyond the capacity
     assert lib.mt_attention_decode(None, p, p, p, p, 1, 24, 2, 128, 0, None, 8, 0.1, p, 1 << 18, 0) == -8   # 12 query heads per kv head
     assert lib.mt_attention_decode(None, p, p, p, p, 1, 8, 2, 128, 0, None, 8, 0.1, p, 16, 0) == -6         # workspace too small
     assert lib.mt_attention_workspace_bytes(1, 8, 4096) > 0
-    assert lib.mt_qgemm_rope_append(None, p, p, p, p, None, p, p, p, p, p, None, 1, 8, 2, 64, 256, 2, 4, 0, 0, None, 16, 16, p, 1 << 18, 0) == -8
+    assert lib.mt_qgemm_rope_append(None, p, p, p, p, None, p, p, p, p, p, None, 1, 8, 2, 63, 256, 2, 4, 0, 0, None, 16, 16, p, 1 << 18, 0) == -8
+    assert lib.mt_qgemm_rope_append(None, p, p, p, p, None, p, p, p, p, p, None, 1, 8, 2, 64, 256, 2, 4, 0, 0, None, 16, 16, p, 1 << 18, 0) == -1   # other head sizes go through scratch
     assert lib.mt_qgemm_rope_append(None, p, p, p, p, None, p, p, p, p, p, None, 4, 8, 2, 128, 256, 2, 4, 0, 0, None, 16, 16, p, 1 << 18, 0) == -1   # scratch at M > 2
