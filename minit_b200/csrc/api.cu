@@ -293,7 +293,10 @@ int mt_qgemm(void* stream, const void* x, const uint32_t* qweight, const int32_t
     if (mid_preferred(m, n, k) && mid_supported(a)) return launch_mid(st, a);
     // 33 to 192 rows on int4 weights with contiguous groups: one row of tiles of the tensor-memory-A prefill kernel, every tile
     // cut along K (28672 x 8192 at 64 rows: 76 us against 109 us for the mid-batch kernel; 8192 x 57344: 172 against 170).
-    if (m > 32 && m <= 192 && tcx_rows_supported(a)) return launch_tcx_rows(st, a);
+    // Up to 64 rows it wins where the weight has fewer 256-column tiles than the GPU has SMs (the cut along K then fills the
+    // GPU: 28672 x 8192 76-83 us against 109, 4096 x 28672 40 against 60); with more tiles the mid-batch kernel's stream-K
+    // partition is as good or better (8192 x 57344: 169 us against 172-212).
+    if (m > 32 && m <= 192 && tcx_rows_supported(a) && (m > 64 || (n + 255) / 256 < 148 || !umma_supported(a))) return launch_tcx_rows(st, a);
     if (umma_supported(a)) {
         if (m > 32 && m <= 64) return launch_umma(st, a);
         if (m > 8 && m <= 32 && weights >= (128LL << 20)) return launch_umma(st, a);

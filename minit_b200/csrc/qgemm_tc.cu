@@ -467,7 +467,8 @@ template <int BM> struct TcxSmem {
     static constexpr int OFF_B = 0;
     static constexpr int OFF_Q = OFF_B + STAGES * B_BYTES;
     static constexpr int OFF_SZ = OFF_Q + STAGES * Q_BYTES;          // per converter thread: 2 x (scale word, zero word)
-    static constexpr int OFF_BAR = OFF_SZ + 512 * 16;
+    static constexpr int OFF_ET = OFF_SZ + 512 * 16;                  // epilogue: two tiles of 32 rows x 128 columns of T
+    static constexpr int OFF_BAR = OFF_ET + 2 * 32 * 128 * 2;
     static constexpr int TOTAL = OFF_BAR + 512 + 1024;
     static_assert(B_BYTES % 1024 == 0, "x tiles need 1024-byte alignment");
 };
@@ -699,9 +700,14 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++lt) {
             int tile, kb0, kb1, part, sidx; tcx_item(item, p, kblocks, tile, kb0, kb1, part, sidx);
             int n0, m0; tcx_tile_origin(tile, p, n0, m0);
-            if (!mbar_wait_sleep<500>(bar_tfull, lt & 1, &abort_flag)) { ok = false; break; }
+            // A warp whose wait gives up must still pass the named barriers below as often as the other three warps of its
+            // half (which may have seen the tile complete just before the abort): it goes through the loop without touching
+            // tensor memory or the output, then leaves.
+            const bool got = mbar_wait_sleep<500>(bar_tfull, lt & 1, &abort_flag);
+            if (!got) ok = false;
             tc_fence_after();
             if (part >= 0) {
+                if (!got) break;
                 // A part of a tile that was cut along K: leave the fp32 sums of this part in the workspace; the warp that
                 // finds all other parts there adds them in part order (its own from tensor memory) and stores the tile.
                 const size_t slice = (size_t)BM * 128;                     // one 128-column half of one part
@@ -748,23 +754,43 @@ qgemm_tcx_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     if (lane == 0) *ctr = 0;
                 }
             } else {
+                // A thread holds one output COLUMN (its TMEM lane) and 32 rows of it; the output is row major.  Stored as it is,
+                // a warp writes 64 contiguous bytes per instruction (measured: 15 000 cycles per tile, during which the MMAs
+                // wait).  So the four warps of a 128-column half turn 32 rows x 128 columns through shared memory and store whole
+                // 256-byte row segments, 16 bytes per lane.
                 const int n = n0 + nt * 128 + nl;
                 const float bv = (bias && n < p.n) ? H::to_float(reinterpret_cast<const uint16_t*>(bias)[n]) : 0.f;
+                uint16_t* et = reinterpret_cast<uint16_t*>(smem + S::OFF_ET) + nt * (32 * 128);      // [32 rows][128 columns]
+                const int ncol = n0 + nt * 128 + 8 * (lane & 15);                                       // first of this lane's 8 columns
 #pragma unroll 1
                 for (int c0 = 0; c0 < BM; c0 += 32) {
-                    uint32_t r[32];
-                    tc_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(nt * BM + c0), r);
-                    tc_wait_ld();
-                    if (n < p.n) {
+                    if (got) {
+                        uint32_t r[32];
+                        tc_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(nt * BM + c0), r);
+                        tc_wait_ld();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const int mrow = m0 + c0 + j;
-                            if (mrow < p.m)
-                                reinterpret_cast<uint16_t*>(out)[(size_t)mrow * p.n + n] = H::from_float(__uint_as_float(r[j]) + bv);
+                        for (int j = 0; j < 32; ++j) et[j * 128 + nl] = H::from_float(__uint_as_float(r[j]) + bv);
+                    }
+                    if (nt == 0) asm volatile("bar.sync 2, 128;" ::: "memory"); else asm volatile("bar.sync 3, 128;" ::: "memory");
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int rr = q4 * 8 + 2 * q + (lane >> 4);                                     // row of the 32: two rows per instruction
+                        const int mrow = m0 + c0 + rr;
+                        const uint4 v = *reinterpret_cast<const uint4*>(et + rr * 128 + 8 * (lane & 15));
+                        if (got && mrow < p.m) {
+                            uint16_t* dst = reinterpret_cast<uint16_t*>(out) + (size_t)mrow * p.n + ncol;
+                            if (ncol + 8 <= p.n) {
+                                *reinterpret_cast<uint4*>(dst) = v;
+                            } else {
+                                const uint16_t* h = reinterpret_cast<const uint16_t*>(&v);
+                                for (int e = 0; e < 8; ++e) if (ncol + e < p.n) dst[e] = h[e];
+                            }
                         }
                     }
+                    if (nt == 0) asm volatile("bar.sync 2, 128;" ::: "memory"); else asm volatile("bar.sync 3, 128;" ::: "memory");   // the tile is rewritten by the next 32 rows
                 }
             }
+            if (!got) break;
             tc_fence_before();
             mbar_arrive(bar_tempty);
         }
