@@ -113,7 +113,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                 const int n0 = (tile / p.m_tiles) * TC_BN, m0 = (tile % p.m_tiles) * BM;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % TC_STAGES; const uint32_t ph = (it / TC_STAGES) & 1;
-                    if (!mbar_wait(bar_empty(s), ph ^ 1, &abort_flag)) { ok = false; break; }
+                    if (!mbar_wait_sleep<200>(bar_empty(s), ph ^ 1, &abort_flag)) { ok = false; break; }
                     mbar_expect_tx(bar_full(s), S::Q_BYTES + S::B_BYTES);
                     tma_load_2d(sbase + S::OFF_Q + s * S::Q_BYTES, &tmap_q, n0, kb * QROWS, bar_full(s));
                     tma_load_2d(sbase + S::OFF_B + s * S::B_BYTES, &tmap_x, kb * TC_BK, m0, bar_full(s));
@@ -130,12 +130,12 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
                 const int acc = lt & 1; const uint32_t aph = (lt >> 1) & 1;
-                if (!mbar_wait(bar_tempty(acc), aph ^ 1, &abort_flag)) { ok = false; break; }
+                if (!mbar_wait_sleep<100>(bar_tempty(acc), aph ^ 1, &abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BM);
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % TC_STAGES; const uint32_t ph = (it / TC_STAGES) & 1;
-                    if (!mbar_wait(bar_full(s), ph, &abort_flag) || !mbar_wait(bar_aready(s), ph, &abort_flag)) { ok = false; break; }
+                    if (!mbar_wait_sleep<20>(bar_full(s), ph, &abort_flag) || !mbar_wait_sleep<20>(bar_aready(s), ph, &abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     const uint64_t adesc = tc_desc_sw128(sbase + S::OFF_A + s * S::A_BYTES);
                     const uint64_t bdesc = tc_desc_sw128(sbase + S::OFF_B + s * S::B_BYTES);
@@ -180,7 +180,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                     sraw0 = sraw1; zraw0 = zraw1;
                     fetch(g + 2, sraw1, zraw1);
                 }
-                if (!mbar_wait(bar_full(s), ph, &abort_flag)) { ok = false; break; }
+                if (!mbar_wait_sleep<40>(bar_full(s), ph, &abort_flag)) { ok = false; break; }
                 const uint32_t* q = reinterpret_cast<const uint32_t*>(smem + S::OFF_Q + s * S::Q_BYTES) + i;
                 unsigned char* arow = smem + S::OFF_A + s * S::A_BYTES + (i >> 3) * 1024 + (i & 7) * 128;
                 if constexpr (BITS == 4) {
@@ -219,7 +219,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
             const int acc = lt & 1; const uint32_t aph = (lt >> 1) & 1;
             const int n = n0 + nl;
             const float bv = (bias && n < p.n) ? H::to_float(reinterpret_cast<const uint16_t*>(bias)[n]) : 0.f;
-            if (!mbar_wait(bar_tfull(acc), aph, &abort_flag)) { ok = false; break; }
+            if (!mbar_wait_sleep<500>(bar_tfull(acc), aph, &abort_flag)) { ok = false; break; }
             tc_fence_after();
 #pragma unroll 1
             for (int c0 = 0; c0 < BM; c0 += 32) {
@@ -320,7 +320,7 @@ qgemm_tcw_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 const int n0 = (tile / p.m_tiles) * 256, m0 = (tile % p.m_tiles) * BM;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % TCW_STAGES; const uint32_t ph = (it / TCW_STAGES) & 1;
-                    if (!mbar_wait(bar_empty(s), ph ^ 1, &abort_flag)) { ok = false; break; }
+                    if (!mbar_wait_sleep<200>(bar_empty(s), ph ^ 1, &abort_flag)) { ok = false; break; }
                     mbar_expect_tx(bar_full(s), S::Q_BYTES + S::B_BYTES);
                     tma_load_2d(sbase + S::OFF_Q + s * S::Q_BYTES, &tmap_q, n0, kb * QROWS, bar_full(s));
                     tma_load_2d(sbase + S::OFF_B + s * S::B_BYTES, &tmap_x, kb * TC_BK, m0, bar_full(s));
@@ -335,11 +335,11 @@ qgemm_tcw_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BM >> 3) << 17) | ((uint32_t)(TC_BN >> 4) << 24);
             int it = 0, lt = 0; bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
-                if (!mbar_wait(bar_tempty, (lt & 1) ^ 1, &abort_flag)) { ok = false; break; }
+                if (!mbar_wait_sleep<100>(bar_tempty, (lt & 1) ^ 1, &abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % TCW_STAGES; const uint32_t ph = (it / TCW_STAGES) & 1;
-                    if (!mbar_wait(bar_full(s), ph, &abort_flag) || !mbar_wait(bar_aready(s), ph, &abort_flag)) { ok = false; break; }
+                    if (!mbar_wait_sleep<20>(bar_full(s), ph, &abort_flag) || !mbar_wait_sleep<20>(bar_aready(s), ph, &abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     const uint64_t bdesc = tc_desc_sw128(sbase + S::OFF_B + s * S::B_BYTES);
                     const uint64_t adesc = tc_desc_sw128(sbase + S::OFF_A + s * S::A_BYTES + nt * (TC_BN * 128));
@@ -381,7 +381,7 @@ qgemm_tcw_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     sraw0 = sraw1; zraw0 = zraw1;
                     fetch(g + 2, sraw1, zraw1);
                 }
-                if (!mbar_wait(bar_full(s), ph, &abort_flag)) { ok = false; break; }
+                if (!mbar_wait_sleep<40>(bar_full(s), ph, &abort_flag)) { ok = false; break; }
                 const uint32_t* q = reinterpret_cast<const uint32_t*>(smem + S::OFF_Q + s * S::Q_BYTES) + i;
                 unsigned char* arow = smem + S::OFF_A + s * S::A_BYTES + nt * (TC_BN * 128) + (il >> 3) * 1024 + (il & 7) * 128;
 #pragma unroll
@@ -406,7 +406,7 @@ qgemm_tcw_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         int lt = 0; bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
             const int n0 = (tile / p.m_tiles) * 256, m0 = (tile % p.m_tiles) * BM;
-            if (!mbar_wait(bar_tfull, lt & 1, &abort_flag)) { ok = false; break; }
+            if (!mbar_wait_sleep<500>(bar_tfull, lt & 1, &abort_flag)) { ok = false; break; }
             tc_fence_after();
 #pragma unroll 1
             for (int nt = 0; nt < 2; ++nt) {
