@@ -521,12 +521,16 @@ def parity_check(world, rank, dev, far, comm, ms=(1, 8)):
                                     sc[:, cols].contiguous(), BITS)
         sqw, sqz, ssc, _ = shard_gptq_row(qw, qz, sc, BITS, rank, world)
         sqw, sqz, ssc = sqw.to(dev), sqz.to(dev), ssc.to(dev)
-        for m in ms:
+        # (rows, flags): the dispatch's own choice at 1 and 8 rows, and at 8 rows the integer tensor-core kernel by flag (its
+        # own exchange code in its epilogue)
+        from minit_b200 import _lib
+        cases = [(m, 0) for m in ms] + ([(8, _lib.FLAG_FORCE_MID)] if world > 1 and far is not None else [])
+        for m, case_flags in cases:
             x = torch.randn((m, k), generator=gen).half()
             ref = O.qlinear(x, w_ref)
             xs = x[:, k // world * rank:k // world * (rank + 1)].contiguous().to(dev)
             if world > 1 and far is not None:
-                out = far.matmul(xs, sqw, sqz, ssc, None, bits=BITS)
+                out = far.matmul(xs, sqw, sqz, ssc, None, bits=BITS, flags=case_flags)
             else:
                 out = M.quantized_matrix_multiply(xs, sqw, sqz, ssc, None, bits=BITS)
                 if world > 1:
@@ -542,7 +546,8 @@ def parity_check(world, rank, dev, far, comm, ms=(1, 8)):
                 flag = torch.tensor([0 if (ok and same) else 1], device=dev)
                 dist.all_reduce(flag, op=dist.ReduceOp.MAX)
                 ok = ok and int(flag.item()) == 0
-            res["cases"].append({"linear": name, "k": k, "n": n, "m": m, "max_err": err, "bound": bound, "ranks_identical": same})
+            res["cases"].append({"linear": name, "k": k, "n": n, "m": m, "max_err": err, "bound": bound, "ranks_identical": same,
+                                 "kernel": "integer tensor-core (by flag)" if case_flags else "dispatch"})
             res["ok"] = res["ok"] and ok and same
         del sqw, sqz, ssc
     return res
@@ -603,6 +608,7 @@ def run_ours(args):
     outs = [torch.empty((m, n), dtype=torch.float16, device=dev) for _, _, n, _ in shapes]
     out_host = torch.empty((m, HIDDEN), dtype=torch.float16).pin_memory()
     flags = _lib.FLAG_PDL if args.pdl else 0
+    flags |= {"auto": 0, "one": _lib.FLAG_AR_ONE_SHOT, "two": _lib.FLAG_AR_TWO_SHOT}[args.ar_mode]
 
     # decode (M <= 2): the linears of `--chain` consecutive layers go to ONE resident launch (mt_qgemm_chain); every
     # entry waits for the one before it, as the stream order of separate launches would make it
@@ -917,6 +923,8 @@ def main():
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--chain", type=int, default=0, help="decode: layers per resident launch of mt_qgemm_chain (0: one launch per linear, which measures faster)")
     ap.add_argument("--tune", type=int, default=0, help="--single-shape: tuning bits 24-28 of the flags")
+    ap.add_argument("--ar-mode", default="auto", choices=["auto", "one", "two"],
+                    help="fused all-reduce of 3..32 rows: one-shot, two-shot (partials to the column's owner, the sum back) or the library's default (one-shot)")
     ap.add_argument("--chain-flags", type=int, default=0, help="tuning bits passed to the chain launch")
     ap.add_argument("--shard-as", type=int, default=1, help="one GPU only: time the per-rank shapes of an N-way split, no exchange")
     ap.add_argument("--no-graph", action="store_true")

@@ -47,6 +47,11 @@ extern "C" {
 #define MT_FLAG_TC_TMEM_A  256   /* prefill (M > 128, int4): always the 256 x 192 tile with the dequantized weights in tensor memory */
 #define MT_FLAG_TC_SMEM_A  512   /* prefill (M > 128, int4): always the 256 x 256 tile with them in shared memory (default: whichever
                                     fills its last wave of tiles better) */
+#define MT_FLAG_AR_TWO_SHOT 1024 /* fused all-reduce of 3..32 rows on the integer tensor-core kernel: the two-shot exchange (a column's
+                                    partials go to its owner rank, the sum comes back: 2 (w-1)/w of the result's bytes per rank instead of
+                                    (w-1) x, two NVLink crossings instead of one).  Same bits as the one-shot form.  Off by default: on four
+                                    ranks at 32 rows it measured slower.  Every rank must pass the same flag. */
+#define MT_FLAG_AR_ONE_SHOT 2048 /* fused all-reduce: the one-shot exchange even if MT_FLAG_AR_TWO_SHOT is set (the default form) */
 #define MT_FLAG_FORCE_VEC   16   /* always use the CUDA-core decode GEMV (M <= 2, contiguous groups, N % 128 == 0) */
 #define MT_FLAG_SPLITS(s)   (((s) & 0xff) << 16)   /* tuning: force the split-K factor of the decode GEMV */
 #define MT_FLAG_PDL          4   /* launch with programmatic stream serialization: the kernel starts

@@ -23,7 +23,7 @@ lib = ctypes.CDLL(LIB_PATH)
 
 MT_F16, MT_BF16 = 0, 1
 FLAG_FORCE_SMALL, FLAG_FORCE_TC, FLAG_PDL, FLAG_FORCE_VEC, FLAG_FORCE_UMMA, FLAG_AR_SHORT_WAIT, FLAG_FORCE_MID = 1, 2, 4, 16, 32, 64, 128
-FLAG_TC_TMEM_A, FLAG_TC_SMEM_A = 256, 512
+FLAG_TC_TMEM_A, FLAG_TC_SMEM_A, FLAG_AR_TWO_SHOT, FLAG_AR_ONE_SHOT = 256, 512, 1024, 2048
 ERR_PEER_TIMEOUT = -12
 ERR_UNSUPPORTED = -8
 CHAIN_MAX = 16

@@ -34,6 +34,8 @@ struct ArParams {
     int rank, world;
     size_t slot_bytes;             // bytes of one (parity, sender) mailbox
     int spin_limit;                // polls per peer before the wait gives up (2^22: 0.1 s to a few seconds)
+    int two_shot;                  // != 0: a column's partials go to its OWNER rank only, which adds them and sends the sum back
+    int cols_per_owner;            // owner of column c = min(c / cols_per_owner, world - 1)
 };
 
 __device__ __forceinline__ bool ar_active(const ArParams& a) { return a.world > 1; }
@@ -103,6 +105,37 @@ __device__ __forceinline__ float ar_pull1(const ArParams& a, unsigned epoch, siz
         sum += __uint_as_float(c.x);
     }
     return sum;
+}
+
+// Two-shot form for batches of several rows.  The one-shot exchange above sends every value to every peer: (world - 1) x
+// the bytes of the result, 14.7 MB per rank at 32 rows x 8192 columns on 8 ranks.  Here the ranks split the columns: a
+// rank sends its partial of a column to the column's owner only; the owner adds all ranks' partials in rank order (its own
+// in its place) and sends the sum to everyone, so every rank holds the same bits.  2 x (world - 1) / world of the result's
+// bytes per rank and two NVLink crossings per value instead of one.  The cells are the same mailboxes: partials land in
+// the OWNER's buffer in the sender's mailbox (where ar_pull1 looks), the sum in every peer's buffer in the owner's
+// mailbox; a rank writes only its own mailbox in anybody's buffer, and the columns it owns and the columns it does not
+// are different cells, so the two phases never meet.
+__device__ __forceinline__ int ar_owner(const ArParams& a, int col) {
+    const int o = col / a.cols_per_owner;
+    return o < a.world ? o : a.world - 1;
+}
+__device__ __forceinline__ void ar_push_to(const ArParams& a, unsigned epoch, int dst_rank, size_t cell, float v) {
+    const int slot = int(epoch & 1u);
+    unsigned char* dst = a.peers[dst_rank] + kArDataOffset + ((size_t)slot * a.world + a.rank) * a.slot_bytes + cell * 8;
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(epoch) : "memory");
+}
+__device__ __forceinline__ float ar_read_from(const ArParams& a, unsigned epoch, int src_rank, size_t cell) {
+    const int slot = int(epoch & 1u);
+    const unsigned char* src = a.peers[a.rank] + kArDataOffset + ((size_t)slot * a.world + src_rank) * a.slot_bytes + cell * 8;
+    uint2 c;
+    int spins = 0;
+    for (;;) {
+        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(c.x), "=r"(c.y) : "l"(src) : "memory");
+        if (c.y == epoch) break;
+        if (++spins > a.spin_limit) { if (a.err) atomicExch(a.err, 4u); break; }   // the owner never answered: give up, flag the error
+        if (spins > 32) __nanosleep(32);
+    }
+    return __uint_as_float(c.x);
 }
 
 // Called by ONE thread of every CTA of the grid, after the CTA's last exchange: the last CTA to

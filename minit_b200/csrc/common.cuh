@@ -171,6 +171,12 @@ inline ArParams make_ar_params(const QGemmArgs& a) {
     r.err = a.workspace ? static_cast<unsigned*>(a.workspace) + (kMaxTiles - 1) : nullptr;
     r.slot_bytes = (a.ar_peers && a.ar_world > 0) ? ((a.ar_bytes - kArDataOffset) / (2 * (size_t)a.ar_world)) & ~(size_t)255 : 0;
     r.spin_limit = (a.flags & MT_FLAG_AR_SHORT_WAIT) ? (1 << 12) : (1 << 22);
+    // two-shot exchange (only the kernels that exchange one value at a time implement it: the integer mid-batch kernel): by
+    // flag only.  Measured on four ranks at 32 rows it loses to the one-shot form (19.1 against 18.3 ms per step): the
+    // exchange is bound by its latency there, not by its bytes, and two-shot has two NVLink crossings in a row.
+    r.two_shot = ((a.flags & MT_FLAG_AR_TWO_SHOT) && !(a.flags & MT_FLAG_AR_ONE_SHOT) && r.world > 1 && a.m >= 3) ? 1 : 0;
+    r.cols_per_owner = r.world > 0 ? (a.n + r.world - 1) / r.world : a.n;
+    if (r.cols_per_owner < 1) r.cols_per_owner = 1;
     return r;
 }
 

@@ -455,7 +455,23 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
             if (write && okc) {
                 const float bv = bias ? H::to_float(reinterpret_cast<const uint16_t*>(bias)[col]) : 0.f;
                 if (fused_ar && !epoch_read) { epoch = ar_epoch(p.ar); epoch_read = true; }
-                if (fused_ar) {
+                float bvf = bv;
+                const bool two_shot = fused_ar && p.ar.two_shot;
+                const int owner = two_shot ? ar_owner(p.ar, col) : 0;
+                if (two_shot && owner == p.ar.rank) {
+                    // this rank adds the column: wait for every rank's partial, add in rank order, send the sums to everyone
+#pragma unroll
+                    for (int r = 0; r < C::RW; ++r)
+                        if (r0 + r < p.m) acc[r] = ar_pull1(p.ar, epoch, (size_t)(r0 + r) * p.n + col, acc[r] + bv);
+#pragma unroll
+                    for (int r = 0; r < C::RW; ++r)
+                        if (r0 + r < p.m) ar_push1(p.ar, epoch, (size_t)(r0 + r) * p.n + col, acc[r]);
+                    bvf = 0.f;                                   // the sums hold every rank's bias already
+                } else if (two_shot) {
+#pragma unroll
+                    for (int r = 0; r < C::RW; ++r)
+                        if (r0 + r < p.m) ar_push_to(p.ar, epoch, owner, (size_t)(r0 + r) * p.n + col, acc[r] + bv);
+                } else if (fused_ar) {
 #pragma unroll
                     for (int r = 0; r < C::RW; ++r)
                         if (r0 + r < p.m) ar_push1(p.ar, epoch, (size_t)(r0 + r) * p.n + col, acc[r] + bv);
@@ -464,8 +480,9 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
                 for (int r = 0; r < C::RW; ++r) {
                     const int row = r0 + r;
                     if (row < p.m) {
-                        float v = acc[r] + bv;
-                        if (fused_ar) v = ar_pull1(p.ar, epoch, (size_t)row * p.n + col, v);
+                        float v = acc[r] + bvf;
+                        if (two_shot) { if (owner != p.ar.rank) v = ar_read_from(p.ar, epoch, owner, (size_t)row * p.n + col); }
+                        else if (fused_ar) v = ar_pull1(p.ar, epoch, (size_t)row * p.n + col, v);
                         if (resid) v += H::to_float(resid[(size_t)row * p.n + col]);
                         out[(size_t)row * p.n + col] = H::from_float(v);
                     }

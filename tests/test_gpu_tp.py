@@ -104,6 +104,16 @@ def _worker(rank, size, port, results):
             g5 = [torch.empty_like(y5) for _ in range(size)]
             dist.all_gather(g5, y5)
             assert all(torch.equal(g5[0], t) for t in g5), "fused integer-kernel all-reduce results differ between ranks"
+            # the two-shot exchange (partials to the column's owner rank, the sum back; by flag): the
+            # owner adds in the same rank order, so the result has the same bits; one-shot and two-shot calls alternate
+            TWO = 1024                                       # MT_FLAG_AR_TWO_SHOT
+            for it in range(3):
+                y5t = rowf5(x5, flags=MID | TWO)
+                assert torch.equal(y5t, y5), f"rank {rank} two-shot exchange differs from the one-shot one (M={m5}, call {it})"
+                assert torch.equal(rowf5(x5, flags=MID), y5)
+            g5t = [torch.empty_like(y5t) for _ in range(size)]
+            dist.all_gather(g5t, y5t)
+            assert all(torch.equal(g5t[0], t) for t in g5t), "two-shot all-reduce results differ between ranks"
             res5 = torch.randn((m5, 8192), generator=torch.Generator().manual_seed(seed5)).half()
             y5r = rowf5(x5, flags=MID, residual=res5.to(dev))
             ok, err, bound = O.tolerance_ok(y5r[:, sl], O.add_residual(res5[:, sl], ref5), 1e-2)
