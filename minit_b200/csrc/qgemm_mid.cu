@@ -138,6 +138,21 @@ __device__ __forceinline__ bool md_wait(uint32_t bar, uint32_t parity, volatile 
     return false;
 }
 
+// The peers' values of one column for the RW rows a fold thread holds, added to v[] (this rank's partials) in rank order.
+// Kept out of line, working on an array in local memory: inlined, its address registers and loaded cells pushed the
+// kernel's accumulators out of registers.
+template <int RW>
+__device__ __noinline__ void md_pull_all(ArParams ar, unsigned epoch, size_t cell0, size_t stride, int nrows, float* v) {
+    for (int r = 0; r < RW && r < nrows; r += 8) {
+        float v8[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v8[j] = v[r + j];
+        ar_pull_rows<8>(ar, epoch, cell0 + (size_t)r * stride, stride, min(8, nrows - r), v8);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[r + j] = v8[j];
+    }
+}
+
 __device__ __forceinline__ void md_mma_i8(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
                  "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n}"
@@ -456,13 +471,16 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
                 const float bv = bias ? H::to_float(reinterpret_cast<const uint16_t*>(bias)[col]) : 0.f;
                 if (fused_ar && !epoch_read) { epoch = ar_epoch(p.ar); epoch_read = true; }
                 float bvf = bv;
+                float xch[C::RW];                                // handed to md_pull_all by address: lives in local memory, acc stays in registers
                 const bool two_shot = fused_ar && p.ar.two_shot;
                 const int owner = two_shot ? ar_owner(p.ar, col) : 0;
                 if (two_shot && owner == p.ar.rank) {
                     // this rank adds the column: wait for every rank's partial, add in rank order, send the sums to everyone
 #pragma unroll
-                    for (int r = 0; r < C::RW; ++r)
-                        if (r0 + r < p.m) acc[r] = ar_pull1(p.ar, epoch, (size_t)(r0 + r) * p.n + col, acc[r] + bv);
+                    for (int r = 0; r < C::RW; ++r) xch[r] = acc[r] + bv;
+                    md_pull_all<C::RW>(p.ar, epoch, (size_t)r0 * p.n + col, (size_t)p.n, p.m - r0, xch);
+#pragma unroll
+                    for (int r = 0; r < C::RW; ++r) acc[r] = xch[r];
 #pragma unroll
                     for (int r = 0; r < C::RW; ++r)
                         if (r0 + r < p.m) ar_push1(p.ar, epoch, (size_t)(r0 + r) * p.n + col, acc[r]);
@@ -476,13 +494,21 @@ __global__ void __launch_bounds__(MD_THREADS, 1) qgemm_mid_kernel(const __grid_c
                     for (int r = 0; r < C::RW; ++r)
                         if (r0 + r < p.m) ar_push1(p.ar, epoch, (size_t)(r0 + r) * p.n + col, acc[r] + bv);
                 }
+                if (fused_ar && !two_shot) {
+                    // collect the peers' values eight rows at a time (one trip to memory per peer and group, not per value)
+#pragma unroll
+                    for (int r = 0; r < C::RW; ++r) xch[r] = acc[r] + bv;
+                    md_pull_all<C::RW>(p.ar, epoch, (size_t)r0 * p.n + col, (size_t)p.n, p.m - r0, xch);
+#pragma unroll
+                    for (int r = 0; r < C::RW; ++r) acc[r] = xch[r];
+                    bvf = 0.f;                                   // the sums hold every rank's bias already
+                }
 #pragma unroll
                 for (int r = 0; r < C::RW; ++r) {
                     const int row = r0 + r;
                     if (row < p.m) {
                         float v = acc[r] + bvf;
-                        if (two_shot) { if (owner != p.ar.rank) v = ar_read_from(p.ar, epoch, owner, (size_t)row * p.n + col); }
-                        else if (fused_ar) v = ar_pull1(p.ar, epoch, (size_t)row * p.n + col, v);
+                        if (two_shot && owner != p.ar.rank) v = ar_read_from(p.ar, epoch, owner, (size_t)row * p.n + col);
                         if (resid) v += H::to_float(resid[(size_t)row * p.n + col]);
                         out[(size_t)row * p.n + col] = H::from_float(v);
                     }
