@@ -15,13 +15,19 @@ from .. import _lib
 from .functional import dequantize
 
 
+def _torch(x):
+    view = getattr(x, "as_torch", None)
+    return view() if callable(view) else x
+
+
 class QuantizedTensor:
     def __init__(self, data: torch.Tensor, group: torch.Tensor, zero: torch.Tensor, scale: torch.Tensor,
                  packed: Optional[Tuple[torch.Tensor, torch.Tensor, int]] = None) -> None:
-        self._data = data
-        self._group = group
-        self._zero = zero
-        self._scale = scale
+        # operands may arrive in the compat layer's device-tensor wrapper (``minit_b200.compat.tensor.CUDATensor``)
+        self._data = _torch(data)
+        self._group = _torch(group)
+        self._zero = _torch(zero)
+        self._scale = _torch(scale)
         self.packed = packed
 
     @property
