@@ -6,17 +6,18 @@ real ``minit`` is importable, unless forced), so that
 * ``from minit.quantize.tensor import QuantizedTensor``, ``from minit.operator.linalg import MatrixMultiply``,
   ``from minit.module.checkpoint import load_from_safetensors_index`` and the distributed / collective / nccl
   modules resolve to this package's implementations of the quantized-linear path, and
-* the single-process example scripts of the reference (examples/mistral_7b.py, examples/qwen1_5_int8.py with their
+* example scripts of the reference (examples/mistral_7b.py, examples/qwen1_5_int8.py, examples/qwen1_5.py and the
   helper examples/agent.py) import unchanged: the tensor types (``minit.core.tensor``, ``minit.cuda.tensor``), the
   functional layer (``minit.functional`` and its submodules), ``minit.module`` / ``minit.module.list``, the
   run-time compiler helpers (``minit.compiler.cxx``, ``minit.compiler.template``, ``minit.cuda.compiler``,
-  ``minit.cuda.kernel.utils``, ``minit.core.cache``) and a stand-in for ``nvtx`` when that package is absent.
+  ``minit.cuda.kernel.utils``, ``minit.core.cache``), the interface classes of ``minit.chat`` and a stand-in for
+  ``nvtx`` when that package is absent.
   These sit on torch storage and are plumbing around the hot path, which a model reaches through
   ``F.matrix_multiply(x, QuantizedTensor)`` or this package's ``QLinear``.
 
 Not provided: the graph tracer and lazy tensors (``minit.trace``, ``minit.lazy``, ``minit.graph``, traced control
-flow), the chat server (``minit.chat``) and the remote controller (``minit.remote``) -- the multi-process example
-scripts need those and do not import."""
+flow) and the remote controller (``minit.remote``) -- examples/llama3.py and examples/llama3_70b.py need those and do
+not import."""
 from __future__ import annotations
 
 import importlib
@@ -60,13 +61,25 @@ _ALIASES = {
     "minit.distributed": "minit_b200.distributed",
     "minit.distributed.group": "minit_b200.distributed.group",
     "minit.distributed.communicator": "minit_b200.distributed.communicator",
+    "minit.distributed.operator": "minit_b200.distributed.operator",
     "minit.nccl": "minit_b200.nccl",
+    "minit.nccl.tensor": "minit_b200.nccl.tensor",
+    "minit.nccl.dispatch": "minit_b200.nccl.dispatch",
+    "minit.nccl.library": "minit_b200.nccl.library",
     "minit.collective": "minit_b200.collective",
+    "minit.collective.tensor": "minit_b200.collective.tensor",
+    "minit.collective.dispatch": "minit_b200.collective.dispatch",
+    "minit.collective.spec": "minit_b200.collective.spec",
+    "minit.chat.server": "minit_b200.compat.chat",
+    "minit.chat.sample": "minit_b200.compat.chat",
+    "minit.chat.template": "minit_b200.compat.chat",
+    "minit.chat.tokenizer": "minit_b200.compat.chat",
+    "minit.chat.agent": "minit_b200.compat.chat",
 }
 
 # packages that exist only as containers, and modules the reference imports for their side effect (registering
 # dispatch rules): the rules of this package are registered when its own modules load
-_CONTAINERS = ("minit.core", "minit.cuda", "minit.cuda.kernel", "minit.compiler")
+_CONTAINERS = ("minit.core", "minit.cuda", "minit.cuda.kernel", "minit.compiler", "minit.chat")
 _SIDE_EFFECT_ONLY = ("minit.cuda.dispatch", "minit.quantize.dispatch")
 
 

@@ -280,6 +280,51 @@ def test_modules_and_checkpoint_loader(minit, tmp_path):
         model.update_buffer("layers.0.weight", torch.zeros(4, 4, dtype=torch.float16))
 
 
+def test_chat_interfaces_drive_a_session(minit):
+    from minit.chat.agent import Agent
+    from minit.chat.sample import Top1Sampler
+    from minit.chat.server import CacheKeyValueSession, Server
+    from minit.chat.template import Template
+    from minit.chat.tokenizer import Tokenizer
+
+    class Echo(Server[CacheKeyValueSession]):
+        """scores that make the sampler return the last input id + 1, and 0 (the end marker) after 3"""
+
+        def create_session(self):
+            return CacheKeyValueSession([])
+
+        def decode(self, session, input_ids):
+            session.offset += len(input_ids)
+            scores = np.zeros(8, dtype=np.float32)
+            scores[(input_ids[-1] + 1) if input_ids[-1] < 3 else 0] = 1.0
+            return _t(scores)
+
+    class Digits(Tokenizer):
+        def tokenize(self, text):
+            return [int(c) for c in text]
+
+        def detokenize(self, ids):
+            return "".join(str(i) for i in ids)
+
+    class Plain(Template):
+        def generate_header(self):
+            return ""
+
+        def generate_prompt(self, prompt):
+            return prompt
+
+        def generate(self, user):
+            return user, "0"
+
+        def eos(self):
+            return "0"
+
+    server = Echo()
+    agent = Agent(server, Digits(), Plain(), Top1Sampler())
+    session = agent.create_session(None)
+    assert session.interact("1") == "23"                               # 1 -> 2 -> 3 -> end marker
+
+
 @pytest.mark.skipif(shutil.which("nvcc") is None, reason="needs nvcc")
 def test_runtime_compiled_unit_and_imported_symbol(minit, tmp_path, monkeypatch):
     import ctypes
@@ -316,8 +361,9 @@ def test_example_scripts_import_unchanged(minit):
     root = _reference_root()
     mistral = _import_example(root, "mistral_7b")
     qwen = _import_example(root, "qwen1_5_int8")
+    qwen_tp = _import_example(root, "qwen1_5")                           # the tensor-parallel script: chat + collective + nccl modules
     from minit.module import Module
-    assert issubclass(mistral.LlaMa2, Module) and issubclass(qwen.QLinearWithBias, Module)
+    assert issubclass(mistral.LlaMa2, Module) and issubclass(qwen.QLinearWithBias, Module) and issubclass(qwen_tp.Attention, Module)
     # the int8 example's own ``unpack`` (reinterpret, expand, add_axis, transpose, remove_axis, fold) agrees with the oracle
     c = O.make_gptq_case(64, 32, 1, bits=8, group_size=32, seed=4)
     assert np.array_equal(qwen.unpack(_t(c["qweight"].numpy()), 0).numpy(), O.unpack_rows(c["qweight"].numpy(), 8))
@@ -385,3 +431,27 @@ def test_example_model_runs_and_matches_plain_torch(minit):
 
     assert (out.as_torch() - plain(ids)).abs().max() < 1e-4
     assert (out2.as_torch() - plain(torch.cat([ids, nxt], 1))[:, -1:]).abs().max() < 1e-4
+
+
+@pytest.mark.skipif(_reference_root() is None, reason="reference tree not present")
+def test_tensor_parallel_example_model_runs_single_process(minit):
+    """examples/qwen1_5.py's QWenLM (biased qkv linears, one KV group) at toy sizes: a cached decode step gives the scores
+    of recomputing the whole sequence."""
+    import minit.functional as F
+    from minit.cuda.tensor import CUDATensor
+    from minit_b200.compat.tensor import to_immediate_shape, torch_dtype
+    ex = _import_example(_reference_root(), "qwen1_5")
+    ex.default_dtype = "float32"
+    model = ex.QWenLM(50, 2, 32, 4, 1, 8, 64)
+    g = torch.Generator().manual_seed(1)
+    for name, buf in list(model.named_buffers()):
+        shape = to_immediate_shape(buf.shape)
+        w = torch.randn(shape, generator=g) * 0.2 if len(shape) == 2 else 1 + 0.1 * torch.randn(shape, generator=g)
+        model.update_buffer(name, w.to(torch_dtype(buf.dtype)))
+    ids = torch.tensor([[3, 7, 11, 2, 9, 4]], dtype=torch.int32)
+    full = model.forward(CUDATensor.from_numpy(ids), F.constant(0, "int32"), model.create_kv_caches())
+    caches = model.create_kv_caches()
+    model.forward(CUDATensor.from_numpy(ids[:, :5].contiguous()), F.constant(0, "int32"), caches)
+    step = model.forward(CUDATensor.from_numpy(ids[:, 5:].contiguous()), F.constant(5, "int32"), caches)
+    assert full._shape == (1, 6, 50) and step._shape == (1, 1, 50) and np.isfinite(full.numpy()).all()
+    assert np.allclose(step.numpy()[0, 0], full.numpy()[0, 5], atol=1e-4)
