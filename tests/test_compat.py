@@ -455,3 +455,15 @@ def test_tensor_parallel_example_model_runs_single_process(minit):
     step = model.forward(CUDATensor.from_numpy(ids[:, 5:].contiguous()), F.constant(5, "int32"), caches)
     assert full._shape == (1, 6, 50) and step._shape == (1, 1, 50) and np.isfinite(full.numpy()).all()
     assert np.allclose(step.numpy()[0, 0], full.numpy()[0, 5], atol=1e-4)
+
+
+@pytest.mark.skipif(_reference_root() is None or shutil.which("nvcc") is None, reason="needs the reference tree and nvcc")
+def test_int8_example_builds_its_own_kernel_through_the_compiler_helpers(minit, tmp_path, monkeypatch):
+    """examples/qwen1_5_int8.py:53-241 fills its CUDA source template, compiles it (``nvcc.compile(CXXUnit(...))``) and binds the
+    entry point (``import_symbol``): all three helpers come from this package here; the build targets sm_100a."""
+    import ctypes
+    monkeypatch.setenv("MINIT_B200_CACHE", str(tmp_path))
+    qwen = _import_example(_reference_root(), "qwen1_5_int8")
+    entrance = qwen.generate_quantized_matrix_multiply("qmm_compat_test", "float16", "float16")
+    assert entrance.argtypes == [ctypes.c_void_p] * 7 + [ctypes.c_int] * 4 and entrance.restype is None
+    assert qwen.generate_quantized_matrix_multiply("qmm_compat_test", "float16", "float16") is entrance     # ``cached``
