@@ -467,3 +467,58 @@ def test_int8_example_builds_its_own_kernel_through_the_compiler_helpers(minit, 
     entrance = qwen.generate_quantized_matrix_multiply("qmm_compat_test", "float16", "float16")
     assert entrance.argtypes == [ctypes.c_void_p] * 7 + [ctypes.c_int] * 4 and entrance.restype is None
     assert qwen.generate_quantized_matrix_multiply("qmm_compat_test", "float16", "float16") is entrance     # ``cached``
+
+
+def test_register_dispatch_by_annotations(minit):
+    """the reference's registration form (minit/core/dispatch.py:52-58): operator and operand classes from the annotations"""
+    from dataclasses import dataclass
+    from typing import Literal, Union
+    from minit.core.dispatch import dispatch, register_dispatch
+    from minit.core.operator import Operator
+    from minit.core.tensor import Tensor
+    from minit.cuda.tensor import CUDATensor
+    from minit_b200.compat.tensor import ScalarTensor
+
+    @dataclass
+    class Scale(Operator):
+        factor: float
+
+    @dataclass
+    class Negate(Operator):
+        ...
+
+    @register_dispatch()
+    def scale_device(op: Scale, x: CUDATensor):
+        return (x * op.factor,)
+
+    @register_dispatch()
+    def scale_host(op: Scale, x: ScalarTensor):
+        return (ScalarTensor(x.value() * op.factor, (), x.dtype),)
+
+    @register_dispatch(priority=1, predicate=lambda *types: len(types) == 2)       # the predicate sees the operand TYPES
+    def scale_pair(op: Scale, *xs: Union[CUDATensor, ScalarTensor]):
+        assert all(isinstance(t, type) for t in (type(x) for x in xs))
+        return tuple(dispatch(op, x)[0] for x in xs)
+
+    @register_dispatch()
+    def any_unary(op: Union[Negate], x: Tensor):
+        return (0 - x,)
+
+    x = _t(np.float32([1, 2]))
+    (y,) = dispatch(Scale(3.0), x)
+    assert y.numpy().tolist() == [3, 6]
+    (h,) = dispatch(Scale(2.0), ScalarTensor(4.0, (), "float32"))
+    assert h.item() == 8.0
+    a, b = dispatch(Scale(2.0), x, ScalarTensor(1.0, (), "float32"))                   # two operands: the higher-priority rule
+    assert a.numpy().tolist() == [2, 4] and b.item() == 2.0
+    assert dispatch(Negate(), x)[0].numpy().tolist() == [-1, -2]
+    with pytest.raises(TypeError):
+        dispatch(Scale(1.0), "text")
+    with pytest.raises(TypeError):                                                      # parametrised patterns are refused
+        @register_dispatch()
+        def bad(op: Scale, x: Literal["cuda"]):
+            return (x,)
+    with pytest.raises(TypeError):
+        @register_dispatch()
+        def unannotated(op: Scale, x):
+            return (x,)
