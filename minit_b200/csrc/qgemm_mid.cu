@@ -38,22 +38,11 @@
 namespace mt {
 namespace {
 
-#ifndef MD_FOLD_WARPS
-#define MD_FOLD_WARPS 8
-#endif
-constexpr int MD_FOLD = MD_FOLD_WARPS;             // fold warps: 0 .. MD_FOLD - 1
-#ifndef MD_DBUF16
-#define MD_DBUF16 4
-#endif
-#ifndef MD_ROWS_PER_LD
-#define MD_ROWS_PER_LD 8
-#endif
-#ifndef MD_FAST_NS
-#define MD_FAST_NS 20
-#endif
-#ifndef MD_SLOW_NS
-#define MD_SLOW_NS 400
-#endif
+constexpr int MD_FOLD = 8;                         // fold warps: 0 .. MD_FOLD - 1
+constexpr int MD_DBUF16 = 4;                       // accumulator buffers of the 16-row tile
+constexpr int MD_ROWS_PER_LD = 8;                  // batch rows per tcgen05.ld in the fold
+constexpr int MD_FAST_NS = 20;                     // sleep between polls of a barrier on the critical path
+constexpr int MD_SLOW_NS = 400;                    // ... of a barrier that a role running ahead waits on
 constexpr int MD_CGROUPS = 2;                      // converter groups of four warps, alternating k-blocks
 constexpr int MD_W_CONV = MD_FOLD;                                  // the converter warps follow the fold warps
 constexpr int MD_W_PROD = MD_FOLD + 4 * MD_CGROUPS;                 // two producer warps, one lane each: packed rows | activation tiles, scales and zero words
