@@ -67,7 +67,7 @@ _ALIASES = {
     "minit.nccl.dispatch": "minit_b200.nccl.dispatch",
     "minit.nccl.library": "minit_b200.nccl.library",
     "minit.collective": "minit_b200.collective",
-    "minit.collective.tensor": "minit_b200.collective.tensor",
+    "minit.collective.tensor": "minit_b200.compat.collective",
     "minit.collective.dispatch": "minit_b200.collective.dispatch",
     "minit.collective.spec": "minit_b200.collective.spec",
     "minit.chat.server": "minit_b200.compat.chat",
