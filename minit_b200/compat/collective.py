@@ -9,7 +9,8 @@ Two rules carry the reference's behaviour (minit/collective/dispatch.py:13-44):
   operator runs locally and its results are broadcast-placed (``collective_aware`` wraps the functional layer);
 * ``matrix_multiply(x, w)`` with a weight split along its rows (output features) keeps the product split along the
   last axis, and with a weight split along its columns (input features) multiplies the matching slice of x and leaves
-  a partial sum -- the column- and row-parallel linears.
+  a partial sum -- the column- and row-parallel linears.  A ``ShardedQuantized`` weight (a rank's shard of a GPTQ
+  tensor, ``minit_b200.collective``) follows the same two rules with the fused kernels as the local product.
 
 The local tensor may be a torch tensor (what a checkpoint loader's epilogue receives) or one of this layer's tensors;
 collectives always run on torch tensors through ``DistributedCommunicator``."""
@@ -186,9 +187,19 @@ def collective_aware(function):
 def matrix_multiply(x, y, local_product):
     """The placement rules of a linear layer; ``local_product(x, w)`` multiplies this layer's tensors."""
     communicator = _communicator_of((x, y))
+    if communicator is None:
+        raise TypeError("a sharded weight needs a CollectiveTensor input (its communicator places the result)")
     if not isinstance(x, CollectiveTensor):
         x = CollectiveTensor.from_broadcast(communicator, x)
     lead = x._shape[:-1]
+    from ..collective.quantized import ShardedQuantized
+    if isinstance(y, ShardedQuantized):                                        # a rank's shard of a GPTQ weight: the fused kernels
+        def fused(xt: torch.Tensor) -> CUDATensor:
+            z = y.local_matmul(xt.reshape(-1, xt.shape[-1]))
+            return CUDATensor.from_torch(z.reshape(*xt.shape[:-1], z.shape[-1]))
+        if y.mode == "column":
+            return CollectiveTensor.from_split(communicator, fused(_torch(x.local())), len(lead))
+        return CollectiveTensor.from_partial(communicator, fused(_torch(x.to_split(len(lead))._local)))
     spec = y._spec if isinstance(y, CollectiveTensor) else None
     if isinstance(spec, CollectiveSpecSplit) and spec.axis == 0:               # column-parallel: the outputs stay split
         z = local_product(x.local(), _compat(y._local))

@@ -16,7 +16,8 @@ __all__ = ["matrix_multiply", "batch_matrix_multiply", "triangle_upper", "triang
 def matrix_multiply(x, y):
     from ...quantize.tensor import QuantizedTensor
     from ..collective import CollectiveTensor, matrix_multiply as placed
-    if isinstance(x, CollectiveTensor) or isinstance(y, CollectiveTensor):
+    from ...collective.quantized import ShardedQuantized
+    if isinstance(x, CollectiveTensor) or isinstance(y, (CollectiveTensor, ShardedQuantized)):
         return placed(x, y, matrix_multiply)
     if isinstance(x, torch.Tensor):                             # torch operands: the package's own torch-level function
         from ...functional.linalg import matrix_multiply as on_torch

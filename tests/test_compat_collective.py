@@ -81,6 +81,29 @@ def _worker(rank, size, port, reference, results):
         assert np.allclose(y.numpy(), (x @ w1.t() @ w2.t()).numpy(), atol=1e-5)
         assert np.allclose(F.matrix_multiply(cx, CollectiveTensor.from_broadcast(comm, w1)).numpy(), (x @ w1.t()).numpy(), atol=1e-5)
 
+        # 2b. the same pair with sharded GPTQ weights (CPU ranks have no kernel: the local product is the oracle's)
+        from oracle import qlinear_oracle as O
+        import minit_b200.collective.quantized as Q
+        from minit_b200.collective import shard_gptq_column, shard_gptq_row
+
+        def cpu_qmm(x, qweight, zeros, scales, groups, *, bits=8, bias=None, out=None, flags=0):
+            return O.qlinear(x, O.dequantize_packed(qweight, groups, zeros, scales, bits), bias)
+        Q.quantized_matrix_multiply = cpu_qmm
+        c1 = O.make_gptq_case(256, 512, 6, bits=4, seed=3)
+        c2 = O.make_gptq_case(512, 128, 6, bits=4, seed=4)
+        q1 = Q.ShardedQuantized("column", *shard_gptq_column(c1["qweight"], c1["qzeros"], c1["scales"], 4, rank, size)[:3], None, 4)
+        q2 = Q.ShardedQuantized("row", *shard_gptq_row(c2["qweight"], c2["qzeros"], c2["scales"], 4, rank, size)[:3], None, 4)
+        xq = CollectiveTensor.from_broadcast(comm, CUDATensor.from_torch(c1["x"].reshape(2, 3, 256)))
+        hq = F.matrix_multiply(xq, q1)
+        assert isinstance(hq.spec, CollectiveSpecSplit) and hq.spec.axis == 2 and hq._local._shape == (2, 3, 512 // size)
+        yq = F.matrix_multiply(hq * 0.05, q2)                        # the scaling gathers; the row-parallel rule slices again
+        assert isinstance(yq.spec, CollectiveSpecPartial) and yq._shape == (2, 3, 128)
+        w1q = O.dequantize_packed(c1["qweight"], None, c1["qzeros"], c1["scales"], 4)
+        w2q = O.dequantize_packed(c2["qweight"], None, c2["qzeros"], c2["scales"], 4)
+        refq = O.qlinear((O.qlinear(c1["x"], w1q).float() * 0.05).half(), w2q).reshape(2, 3, 128)
+        ok, err, bound = O.tolerance_ok(yq.local().as_torch(), refq, 2e-2)
+        assert ok, f"sharded quantized pair: {err} > {bound}"
+
         # 3. the reference's own tensor-parallel example model, sharded as its collective server shards it
         if reference is not None:
             examples = os.path.join(reference, "examples")
