@@ -6,8 +6,8 @@ real ``minit`` is importable, unless forced), so that
 * ``from minit.quantize.tensor import QuantizedTensor``, ``from minit.operator.linalg import MatrixMultiply``,
   ``from minit.module.checkpoint import load_from_safetensors_index`` and the distributed / collective / nccl
   modules resolve to this package's implementations of the quantized-linear path, and
-* example scripts of the reference (examples/mistral_7b.py, examples/qwen1_5_int8.py, examples/qwen1_5.py and the
-  helper examples/agent.py) import unchanged: the tensor types (``minit.core.tensor``, ``minit.cuda.tensor``), the
+* example scripts of the reference (examples/mistral_7b.py, examples/qwen1_5_int8.py, examples/qwen1_5.py,
+  examples/llama3.py and the helper examples/agent.py) import unchanged: the tensor types (``minit.core.tensor``, ``minit.cuda.tensor``), the
   functional layer (``minit.functional`` and its submodules), ``minit.module`` / ``minit.module.list``, the
   run-time compiler helpers (``minit.compiler.cxx``, ``minit.compiler.template``, ``minit.cuda.compiler``,
   ``minit.cuda.kernel.utils``, ``minit.core.cache``), the interface classes of ``minit.chat`` and a stand-in for
@@ -15,9 +15,11 @@ real ``minit`` is importable, unless forced), so that
   These sit on torch storage and are plumbing around the hot path, which a model reaches through
   ``F.matrix_multiply(x, QuantizedTensor)`` or this package's ``QLinear``.
 
-Not provided: the graph tracer and lazy tensors (``minit.trace``, ``minit.lazy``, ``minit.graph``, traced control
-flow) and the remote controller (``minit.remote``) -- examples/llama3.py and examples/llama3_70b.py need those and do
-not import."""
+The graph tracer is NOT rebuilt: ``minit.trace.function.trace_function`` / ``minit.trace.executor.TraceGraphExecutor``
+/ ``minit.graph.dump_graphviz`` are eager stand-ins (``compat/trace.py``: the function is kept and called).  Not
+provided at all: lazy tensors and traced control flow (``minit.lazy``, for_loop / while_loop / if_block) and the
+remote controller (``minit.remote``, ``minit.nccl.library.launch_server``) -- examples/llama3_70b.py needs those and
+does not import."""
 from __future__ import annotations
 
 import importlib
@@ -70,6 +72,9 @@ _ALIASES = {
     "minit.collective.tensor": "minit_b200.compat.collective",
     "minit.collective.dispatch": "minit_b200.collective.dispatch",
     "minit.collective.spec": "minit_b200.collective.spec",
+    "minit.trace.function": "minit_b200.compat.trace",
+    "minit.trace.executor": "minit_b200.compat.trace",
+    "minit.graph": "minit_b200.compat.trace",
     "minit.chat.server": "minit_b200.compat.chat",
     "minit.chat.sample": "minit_b200.compat.chat",
     "minit.chat.template": "minit_b200.compat.chat",
@@ -79,8 +84,8 @@ _ALIASES = {
 
 # packages that exist only as containers, and modules the reference imports for their side effect (registering
 # dispatch rules): the rules of this package are registered when its own modules load
-_CONTAINERS = ("minit.core", "minit.cuda", "minit.cuda.kernel", "minit.compiler", "minit.chat")
-_SIDE_EFFECT_ONLY = ("minit.cuda.dispatch", "minit.quantize.dispatch")
+_CONTAINERS = ("minit.core", "minit.cuda", "minit.cuda.kernel", "minit.compiler", "minit.chat", "minit.trace")
+_SIDE_EFFECT_ONLY = ("minit.cuda.dispatch", "minit.quantize.dispatch", "minit.trace.dispatch")
 
 
 class _Annotate:

@@ -522,3 +522,58 @@ def test_register_dispatch_by_annotations(minit):
         @register_dispatch()
         def unannotated(op: Scale, x):
             return (x,)
+
+
+def test_eager_stand_ins_for_the_tracer(minit, tmp_path):
+    import minit.functional as F
+    import minit.trace.dispatch                                         # noqa: F401  (imported by the scripts for its side effect)
+    from minit.graph import dump_graphviz
+    from minit.trace.executor import TraceGraphExecutor
+    from minit.trace.function import trace_function
+
+    def forward(x, offset, *rest):
+        return (x * 2 + offset, *rest)
+
+    x = _t(np.float32([1, 2, 3]))
+    graph = trace_function(forward, (x, F.constant(1, "float32"), x))
+    out, passed = TraceGraphExecutor(graph).execute(x, F.constant(1, "float32"), x)
+    assert out.numpy().tolist() == [3, 5, 7] and passed is x
+    dump_graphviz(graph).save(str(tmp_path / "graph.dot"))
+    text = open(tmp_path / "graph.dot").read()
+    assert text.startswith("digraph") and "forward (eager)" in text and "float32[3]" in text
+    assert TraceGraphExecutor(trace_function(lambda: None, ())).execute() == ()
+
+
+@pytest.mark.skipif(_reference_root() is None, reason="reference tree not present")
+def test_traced_example_imports_and_its_model_runs_through_the_executor(minit):
+    """examples/llama3.py (it wraps the forward pass in trace_function / TraceGraphExecutor, examples/llama3.py:360-367)"""
+    import minit.functional as F
+    from minit.cuda.tensor import CUDATensor
+    from minit.trace.executor import TraceGraphExecutor
+    from minit.trace.function import trace_function
+    from minit_b200.compat.tensor import to_immediate_shape, torch_dtype
+    ex = _import_example(_reference_root(), "llama3")
+    ex.default_dtype = "float32"
+    model = ex.Llama3LM(50, 2, 32, 4, 2, 8, 64)
+    g = torch.Generator().manual_seed(2)
+    for name, buf in list(model.named_buffers()):
+        shape = to_immediate_shape(buf.shape)
+        w = torch.randn(shape, generator=g) * 0.2 if len(shape) == 2 else 1 + 0.1 * torch.randn(shape, generator=g)
+        model.update_buffer(name, w.to(torch_dtype(buf.dtype)))
+
+    def model_forward(input, offset, *flat):
+        caches = [(flat[2 * i], flat[2 * i + 1]) for i in range(len(flat) // 2)]
+        probs = model.forward(input, offset, caches)
+        return (probs, *[t for pair in caches for t in pair])
+
+    def flat(caches):
+        return [t for pair in caches for t in pair]
+
+    ids = torch.tensor([[3, 7, 11, 2, 9, 4]], dtype=torch.int32)
+    full_in = CUDATensor.from_numpy(ids)
+    executor = TraceGraphExecutor(trace_function(model_forward, (full_in, F.constant(0, "int32"), *flat(model.create_kv_caches()))))
+    full, *_ = executor.execute(full_in, F.constant(0, "int32"), *flat(model.create_kv_caches()))
+    _, *kv = executor.execute(CUDATensor.from_numpy(ids[:, :5].contiguous()), F.constant(0, "int32"), *flat(model.create_kv_caches()))
+    step, *_ = executor.execute(CUDATensor.from_numpy(ids[:, 5:].contiguous()), F.constant(5, "int32"), *kv)
+    assert full._shape == (1, 6, 50) and step._shape == (1, 1, 50)
+    assert np.allclose(step.numpy()[0, 0], full.numpy()[0, 5], atol=1e-4)
