@@ -10,9 +10,14 @@ outputs of the reference's own ``dispatch_dequantize`` executed on CPU; those
 outputs are committed as fixtures (``tests/golden/*.npz``, produced by
 ``tests/golden/make_golden.py``).
 
-The decoder-layer steps added later (``rms_norm``, ``rope``, ``attention``, ``sigmoid`` / ``silu``) restate CUDA
-kernels of the reference that cannot run without a GPU and have no tests or vectors there either: their
-parity is *unpinned*; they are checked by construction properties (``tests/test_oracle.py``).
+The steps that restate CUDA kernel strings of the reference (``unpack_*`` + ``qlinear`` as the fused kernel of
+``examples/qwen1_5_int8.py:156-216``, ``rms_norm``, ``rope``, the softmax inside ``attention``) are pinned against
+outputs of those strings, compiled unchanged for sm_100a (``oracle/build_ref_cuda.py``) and run on a B200:
+``tests/golden/ref_cuda_golden.npz``, made by ``tests/golden/make_cuda_golden.py``, checked in ``tests/test_oracle.py``.
+``unpack_rows`` / ``unpack_cols`` are also pinned against the reference's own Python ``unpack`` run on CPU (same
+fixture script as the dequantizer).  Still *unpinned*: ``sigmoid`` / ``silu`` / ``swiglu`` / ``add_residual`` (an
+expression of the reference's generic elementwise generator, not a kernel string of its own); they are checked by
+construction properties (``tests/test_oracle.py``).
 
 What each function follows in the reference (paths relative to the reference
 project root):
